@@ -1,0 +1,345 @@
+#!/usr/bin/env python3
+"""Benchmark of the deformable-kernel layer: forward + backward images/s and achieved HBM
+bandwidth on the MobileNetV2-style depthwise layer sweep (batch 128 per GPU, fp16 storage,
+fp32 arithmetic; five layer shapes x stride 1 and 2, scope 4x4, kernel 3, pad 1).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" is one forward + backward of all ten layers on one batch.  Rank 0 prints ONE
+JSON line.  `value` is device-timed with inputs resident in HBM; `e2e` is the same step
+through the public autograd API with every input copied from pinned host memory and every
+result copied back inside the timed region.  The batch is sharded by replication of the
+per-GPU batch (weak scaling, no collective: nothing on this path is exchanged between
+samples except the bank gradient, which op-level runs do not all-reduce).
+
+--impl reference times the CPU oracle (oracle/dk_oracle.c, OpenMP over all host cores): the
+reference project has no CPU implementation of this path, so its restatement stands in.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "deformable-kernels_b200"), os.path.join(ROOT, "tests")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+LAYERS = [(c, hw, s) for (c, hw) in [(96, 112), (144, 56), (192, 28), (384, 14), (960, 7)] for s in (1, 2)]
+SCOPE, K, PAD = 4, 3, 1
+METRIC = "DK layer fwd+bwd images/sec (MobileNetV2 depthwise sweep, batch 128 fp16)"
+HBM_NOMINAL_GBS = 8000.0
+
+
+def out_hw(hw, s):
+    return (hw + 2 * PAD - K) // s + 1
+
+
+def layer_bytes(n, c, hw, s, e=2):
+    """Algorithmic bytes of one layer, every tensor touched once per pass."""
+    ho = out_hw(hw, s)
+    x, y, rot, w = n * c * hw * hw, n * c * ho * ho, n * 2 * K * K * ho * ho, c * SCOPE * SCOPE
+    fwd = e * (x + rot + y + w)
+    bwd = e * (y + x + rot + x + rot + 2 * w)
+    return fwd, bwd
+
+
+def kernel_bytes(name, n, c, hw, s, e=2):
+    ho = out_hw(hw, s)
+    x, y, rot, w = n * c * hw * hw, n * c * ho * ho, n * 2 * K * K * ho * ho, c * SCOPE * SCOPE
+    return e * {"forward": x + rot + y + w, "backward_data": y + rot + w + x, "backward_rotation": y + x + rot + w + rot,
+                "backward_filter": y + x + rot + w}[name]
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [v.strip() for v in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])), mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sweep(n_img, threads=None):
+    """Forward + backward of the ten layers on n_img images with the CPU oracle (fp32 math on
+    fp16-rounded inputs).  Returns seconds."""
+    import dk_cases
+    from oracle import dk_oracle as O
+    if threads:
+        O.set_threads(threads)
+    total = 0.0
+    for (c, hw, s) in LAYERS:
+        case = dk_cases.cfg3(c, hw, s, n=n_img, seed=7)
+        x, r, w, dy = (case[k].half().float() for k in ("input", "rotation", "weight", "grad_output"))
+        t0 = time.perf_counter()
+        O.sample_depthwise_forward(x, r, w, **case["args"])
+        O.sample_depthwise_backward(dy, x, r, w, **case["args"])
+        total += time.perf_counter() - t0
+    return total
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    from oracle import dk_oracle as O
+    cores = O.max_threads()
+    n_img = 4
+    for _ in range(args.warmup):
+        cpu_sweep(n_img)
+    t = [cpu_sweep(n_img) for _ in range(args.steps)]
+    sec = sum(t) / len(t)
+    val = n_img / sec
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "images/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg3 layer sweep (10 DeformKernel2d layers), %d images per step on host cores" % n_img},
+        "cpu_baseline": {"value": val, "unit": "images/s", "cores": cores, "kind": "port",
+                         "sample": "%d images through all ten layers per step, OpenMP C restatement of the "
+                                   "reference kernels (the reference has no CPU path)" % n_img},
+        "e2e": {"value": val, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=128, help="images per GPU")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+    from deformable_kernels.ops.deform_kernel.functions import sample_depthwise
+    from deformable_kernels.ops.deform_kernel import filter_sample_depthwise_cuda as fs
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    n = args.batch
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    layers = []
+    for (c, hw, s) in LAYERS:
+        ho = out_hw(hw, s)
+        t = dict(c=c, hw=hw, s=s, ho=ho)
+        t["w"] = (torch.randn(c, 1, SCOPE, SCOPE, device=dev, generator=gen) * (2.0 / 16) ** 0.5).half()
+        t["x"] = torch.randn(n, c, hw, hw, device=dev, generator=gen).half()
+        t["rot"] = torch.randn(n, 2 * K * K, ho, ho, device=dev, generator=gen).half()
+        t["dy"] = torch.randn(n, c, ho, ho, device=dev, generator=gen).half()
+        layers.append(t)
+
+    def fwd_bwd(t, x, rot, dy):
+        x.requires_grad_(True), rot.requires_grad_(True), t["w"].requires_grad_(True)
+        y = sample_depthwise(x, rot, t["w"], (K, K), (t["s"], t["s"]), (PAD, PAD), (1, 1), 1)
+        gx, gr, gw = torch.autograd.grad(y, [x, rot, t["w"]], dy)
+        return y, gx, gr, gw
+
+    def step():
+        for t in layers:
+            fwd_bwd(t, t["x"], t["rot"], t["dy"])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    tms = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms_step = float(tms.item()) / args.steps
+    value = world * n / (ms_step * 1e-3)
+
+    # per-layer forward / backward split and per-kernel times (device events on the launch stream)
+    def time_call(fn, iters=5):
+        fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters
+
+    per_layer, kern_tot = [], {}
+    big = None
+    for t in layers:
+        tail = (K, K, t["s"], t["s"], PAD, PAD, 1, 1, SCOPE, SCOPE, 1)
+        x, rot, dy, w = t["x"].detach(), t["rot"].detach(), t["dy"], t["w"].detach()
+        y, gx, gr, gw = torch.empty_like(dy), torch.empty_like(x), torch.empty_like(rot), torch.empty_like(w)
+        kt = {
+            "forward": time_call(lambda: fs.sample_depthwise_forward_cuda(x, rot, w, y, *tail)),
+            "backward_data": time_call(lambda: fs.sample_depthwise_backward_data_cuda(dy, x, rot, w, gx, *tail)),
+            "backward_rotation": time_call(lambda: fs.sample_depthwise_backward_rotation_cuda(dy, x, rot, w, gr, *tail)),
+            "backward_filter": time_call(lambda: fs.sample_depthwise_backward_filter_cuda(dy, x, rot, w, gw, *tail)),
+        }
+        fb, bb = layer_bytes(n, t["c"], t["hw"], t["s"])
+        tf, tb = kt["forward"], sum(v for k, v in kt.items() if k != "forward")
+        per_layer.append({"C": t["c"], "HW": t["hw"], "stride": t["s"], "fwd_ms": round(tf, 4), "bwd_ms": round(tb, 4),
+                          "GBps": round((fb + bb) / ((tf + tb) * 1e-3) / 1e9, 1)})
+        for k, v in kt.items():
+            kern_tot[k] = kern_tot.get(k, 0.0) + v
+        if big is None:
+            big = (t, kt)
+    peak, peak_kind = measured_peak()
+    dom = max(kern_tot, key=kern_tot.get)
+    bt, bkt = big
+    kb = kernel_bytes(dom, n, bt["c"], bt["hw"], bt["s"])
+    achieved = kb / (bkt[dom] * 1e-3) / 1e9
+    tot_bytes = sum(sum(layer_bytes(n, c, hw, s)) for (c, hw, s) in LAYERS)
+    sweep_gbs = tot_bytes / (ms_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "local DK " + dom + " (C=96, 112x112, stride 1, batch %d)" % n,
+                "achieved": round(achieved, 1), "peak": peak, "peak_source": peak_kind, "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "frac_of_nominal_8TBs": round(achieved / HBM_NOMINAL_GBS, 4),
+                "traffic": None, "kernel_ms": round(bkt[dom], 4),
+                "sweep_fwd_bwd_GBps": round(sweep_gbs, 1), "sweep_frac": round(sweep_gbs / peak, 4)}
+
+    # end to end: pinned host inputs -> device, forward + backward, all results -> pinned host
+    host = []
+    for t in layers:
+        h = {k: torch.empty(t[k].shape, dtype=t[k].dtype, pin_memory=True).copy_(t[k]) for k in ("x", "rot", "dy")}
+        ho = t["ho"]
+        h["y"] = torch.empty(n, t["c"], ho, ho, dtype=torch.float16, pin_memory=True)
+        h["gx"] = torch.empty(t["x"].shape, dtype=torch.float16, pin_memory=True)
+        h["gr"] = torch.empty(t["rot"].shape, dtype=torch.float16, pin_memory=True)
+        h["gw"] = torch.empty(t["w"].shape, dtype=torch.float16, pin_memory=True)
+        host.append(h)
+    h2d = sum(h[k].numel() * 2 for h in host for k in ("x", "rot", "dy"))
+    d2h = sum(h[k].numel() * 2 for h in host for k in ("y", "gx", "gr", "gw"))
+
+    def e2e_step():
+        for t, h in zip(layers, host):
+            x = h["x"].to(dev, non_blocking=True)
+            rot = h["rot"].to(dev, non_blocking=True)
+            dy = h["dy"].to(dev, non_blocking=True)
+            y, gx, gr, gw = fwd_bwd(t, x, rot, dy)
+            h["y"].copy_(y.detach(), non_blocking=True)
+            h["gx"].copy_(gx, non_blocking=True)
+            h["gr"].copy_(gr, non_blocking=True)
+            h["gw"].copy_(gw, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
+    tms = torch.tensor([e2e_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    e2e_val = world * n / (float(tms.item()) / args.e2e_steps * 1e-3)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import dk_oracle as O
+        n_img = 16
+        cpu_sweep(1)
+        sec = cpu_sweep(n_img)
+        cpu = {"value": n_img / sec, "unit": "images/s", "cores": O.max_threads(), "kind": "port",
+               "sample": "%d images through all ten layers once (%.1f s), OpenMP C restatement of the reference "
+                         "kernels; the reference has no CPU path" % (n_img, sec)}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "cfg3 layer sweep: DeformKernel2d (C,HW) in (96,112),(144,56),(192,28),(384,14),(960,7)"
+                                   " x stride 1,2; scope 4x4, kernel 3, pad 1; offsets ~N(0,1); batch %d per GPU" % n,
+                       "storage": "f16 tensors, f32 arithmetic and accumulation",
+                       "l2": "the sweep touches %.1f GB per step, far above the 126 MB L2, so every layer's tensors "
+                             "are evicted between steps" % (tot_bytes / 1e9)},
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_val, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps * len(LAYERS) * 5, "clocks": clocks, "per_layer": per_layer,
+            "kernel_ms_sum_over_layers": {k: round(v, 4) for k, v in kern_tot.items()},
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,340 @@
+// extern "C" surface of the library (see include/dk_b200.h): argument checks, dtype
+// dispatch, workspace carving.  No allocation, no synchronisation, no printing.
+#include <mutex>
+
+#include "dk_common.cuh"
+
+namespace dk {
+
+static thread_local int g_last_cuda_error = 0;
+void set_last_cuda_error(cudaError_t e) { g_last_cuda_error = (int)e; }
+
+int check_launch() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return DK_ERR_CUDA;
+  }
+  return DK_OK;
+}
+
+namespace {
+struct DevAttr {
+  bool known = false;
+  int smem_optin = 48 * 1024;
+  int sms = 148;
+};
+std::mutex g_attr_mutex;
+DevAttr g_attr[64];
+
+const DevAttr& attrs() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  std::lock_guard<std::mutex> lock(g_attr_mutex);
+  DevAttr& a = g_attr[dev];
+  if (!a.known) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) == cudaSuccess && v > 0) a.smem_optin = v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) a.sms = v;
+    a.known = true;
+  }
+  return a;
+}
+}  // namespace
+
+int device_smem_optin() { return attrs().smem_optin; }
+int device_sm_count() { return attrs().sms; }
+
+bool make_geom(const dk_geom* in, Geom* g) {
+  if (!in) return false;
+  if (in->batch <= 0 || in->channels <= 0 || in->in_h <= 0 || in->in_w <= 0) return false;
+  if (in->kernel_h <= 0 || in->kernel_w <= 0 || in->stride_h <= 0 || in->stride_w <= 0) return false;
+  if (in->pad_h < 0 || in->pad_w < 0 || in->dil_h <= 0 || in->dil_w <= 0) return false;
+  if (in->scope_h <= 0 || in->scope_w <= 0 || in->rotation_groups <= 0) return false;
+  if (in->channels % in->rotation_groups != 0) return false;
+  g->N = in->batch; g->C = in->channels; g->H = in->in_h; g->W = in->in_w;
+  g->kH = in->kernel_h; g->kW = in->kernel_w; g->sH = in->stride_h; g->sW = in->stride_w;
+  g->pH = in->pad_h; g->pW = in->pad_w; g->dH = in->dil_h; g->dW = in->dil_w;
+  g->scH = in->scope_h; g->scW = in->scope_w; g->G = in->rotation_groups;
+  const long long eh = (long long)g->H + 2LL * g->pH - ((long long)g->dH * (g->kH - 1) + 1);
+  const long long ew = (long long)g->W + 2LL * g->pW - ((long long)g->dW * (g->kW - 1) + 1);
+  if (eh < 0 || ew < 0) return false;  // "convolution input is too small"
+  g->Ho = (int)(eh / g->sH) + 1;
+  g->Wo = (int)(ew / g->sW) + 1;
+  const long long taps = (long long)g->kH * g->kW, P = (long long)g->Ho * g->Wo, HW = (long long)g->H * g->W;
+  const long long cells = (long long)g->scH * g->scW;
+  if (taps > 4096 || P > 0x3fffffffLL || HW > 0x3fffffffLL || cells > 65536) return false;
+  // per-sample offset planes are indexed with 32-bit arithmetic inside a sample
+  if (taps * 2 * P * g->G > 0x7fffffffLL) return false;
+  g->taps = (int)taps; g->P = (int)P; g->HW = (int)HW; g->cells = (int)cells;
+  g->Cg = g->C / g->G;
+  return true;
+}
+
+static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+static inline size_t acc_bytes(int dtype) { return dtype == DK_F64 ? 8 : 4; }
+static inline bool dtype_ok(int dtype) { return dtype == DK_F32 || dtype == DK_F16 || dtype == DK_F64; }
+
+}  // namespace dk
+
+using namespace dk;
+
+#define DK_DISPATCH(dtype, EXPR)                         \
+  switch (dtype) {                                       \
+    case DK_F32: { using T = float; return (EXPR); }     \
+    case DK_F16: { using T = __half; return (EXPR); }    \
+    case DK_F64: { using T = double; return (EXPR); }    \
+    default: return DK_ERR_BAD_ARGUMENT;                 \
+  }
+#define P_(T, p) reinterpret_cast<const T*>(p)
+#define M_(T, p) reinterpret_cast<T*>(p)
+
+extern "C" {
+
+const char* dk_status_string(int status) {
+  switch (status) {
+    case DK_OK: return "ok";
+    case DK_ERR_BAD_ARGUMENT: return "bad argument";
+    case DK_ERR_UNSUPPORTED: return "unsupported shape or size";
+    case DK_ERR_WORKSPACE: return "workspace missing or too small";
+    case DK_ERR_CUDA: return "CUDA error";
+    default: return "unknown status";
+  }
+}
+
+int dk_last_cuda_error(void) { return g_last_cuda_error; }
+const char* dk_version(void) { return "dk_b200 0.1 (sm_100a)"; }
+
+int dk_output_size(const dk_geom* g, int* out_h, int* out_w) {
+  Geom gg;
+  if (!make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+  if (out_h) *out_h = gg.Ho;
+  if (out_w) *out_w = gg.Wo;
+  return DK_OK;
+}
+
+/* ---------------------------------------------------------------- local DK */
+
+int dk_sample_depthwise_forward(const void* input, const void* rotation, const void* filter, void* output,
+                                const dk_geom* g, int dtype, void* stream) {
+  Geom gg;
+  if (!input || !rotation || !filter || !output || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+  DK_DISPATCH(dtype, local_forward<T>(P_(T, input), P_(T, rotation), P_(T, filter), M_(T, output), gg, (cudaStream_t)stream))
+}
+
+int dk_sample_depthwise_backward_data(const void* grad_output, const void* rotation, const void* filter,
+                                      void* grad_input, const dk_geom* g, int dtype, void* stream) {
+  Geom gg;
+  if (!grad_output || !rotation || !filter || !grad_input || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+  DK_DISPATCH(dtype, local_backward_data<T>(P_(T, grad_output), P_(T, rotation), P_(T, filter), M_(T, grad_input), gg,
+                                            (cudaStream_t)stream))
+}
+
+size_t dk_sample_depthwise_backward_filter_workspace_bytes(const dk_geom* g, int dtype) {
+  Geom gg;
+  if (!make_geom(g, &gg) || !dtype_ok(dtype)) return 0;
+  return align256(filter_plan(gg, acc_bytes(dtype)).ws_bytes);
+}
+
+int dk_sample_depthwise_backward_filter(const void* grad_output, const void* input, const void* rotation,
+                                        void* grad_filter, const dk_geom* g, int dtype, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+  Geom gg;
+  if (!grad_output || !input || !rotation || !grad_filter || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+  DK_DISPATCH(dtype, local_backward_filter<T>(P_(T, grad_output), P_(T, input), P_(T, rotation), M_(T, grad_filter), gg,
+                                              workspace, workspace_bytes, (cudaStream_t)stream))
+}
+
+int dk_sample_depthwise_backward_rotation(const void* grad_output, const void* input, const void* rotation,
+                                          const void* filter, void* grad_rotation, const dk_geom* g, int dtype,
+                                          void* stream) {
+  Geom gg;
+  if (!grad_output || !input || !rotation || !filter || !grad_rotation || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+  DK_DISPATCH(dtype, local_backward_rotation<T>(P_(T, grad_output), P_(T, input), P_(T, rotation), P_(T, filter),
+                                                M_(T, grad_rotation), gg, (cudaStream_t)stream))
+}
+
+int dk_sample_depthwise_backward(const void* grad_output, const void* input, const void* rotation, const void* filter,
+                                 void* grad_input, void* grad_rotation, void* grad_filter, const dk_geom* g, int dtype,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  if (!dtype_ok(dtype)) return DK_ERR_BAD_ARGUMENT;
+  int rc = DK_OK;
+  if (grad_input) {
+    rc = dk_sample_depthwise_backward_data(grad_output, rotation, filter, grad_input, g, dtype, stream);
+    if (rc) return rc;
+  }
+  if (grad_rotation) {
+    rc = dk_sample_depthwise_backward_rotation(grad_output, input, rotation, filter, grad_rotation, g, dtype, stream);
+    if (rc) return rc;
+  }
+  if (grad_filter) {
+    rc = dk_sample_depthwise_backward_filter(grad_output, input, rotation, grad_filter, g, dtype, workspace,
+                                             workspace_bytes, stream);
+  }
+  return rc;
+}
+
+/* ---------------------------------------------------------------- DK + DCN */
+
+int dk_deform_sample_depthwise_forward(const void* input, const void* offset, const void* rotation, const void* filter,
+                                       void* output, const dk_geom* g, int dtype, void* stream) {
+  Geom gg;
+  if (!input || !offset || !rotation || !filter || !output || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+  DK_DISPATCH(dtype, deform_forward<T>(P_(T, input), P_(T, offset), P_(T, rotation), P_(T, filter), M_(T, output), gg,
+                                       (cudaStream_t)stream))
+}
+
+size_t dk_deform_sample_depthwise_backward_data_workspace_bytes(const dk_geom* g, int dtype) {
+  Geom gg;
+  if (!make_geom(g, &gg) || !dtype_ok(dtype)) return 0;
+  if (dtype != DK_F16) return 0;
+  return align256((size_t)gg.N * gg.C * gg.HW * sizeof(float));
+}
+
+int dk_deform_sample_depthwise_backward_data(const void* grad_output, const void* offset, const void* rotation,
+                                             const void* filter, void* grad_input, const dk_geom* g, int dtype,
+                                             void* workspace, size_t workspace_bytes, void* stream) {
+  Geom gg;
+  if (!grad_output || !offset || !rotation || !filter || !grad_input || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+  DK_DISPATCH(dtype, deform_backward_data<T>(P_(T, grad_output), P_(T, offset), P_(T, rotation), P_(T, filter),
+                                             M_(T, grad_input), gg, workspace, workspace_bytes, (cudaStream_t)stream))
+}
+
+size_t dk_deform_sample_depthwise_backward_filter_workspace_bytes(const dk_geom* g, int dtype) {
+  return dk_sample_depthwise_backward_filter_workspace_bytes(g, dtype);
+}
+
+int dk_deform_sample_depthwise_backward_filter(const void* grad_output, const void* input, const void* offset,
+                                               const void* rotation, void* grad_filter, const dk_geom* g, int dtype,
+                                               void* workspace, size_t workspace_bytes, void* stream) {
+  Geom gg;
+  if (!grad_output || !input || !offset || !rotation || !grad_filter || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+  DK_DISPATCH(dtype, deform_backward_filter<T>(P_(T, grad_output), P_(T, input), P_(T, offset), P_(T, rotation),
+                                               M_(T, grad_filter), gg, workspace, workspace_bytes, (cudaStream_t)stream))
+}
+
+int dk_deform_sample_depthwise_backward_offset(const void* grad_output, const void* input, const void* offset,
+                                               const void* rotation, const void* filter, void* grad_offset,
+                                               const dk_geom* g, int dtype, void* stream) {
+  Geom gg;
+  if (!grad_output || !input || !offset || !rotation || !filter || !grad_offset || !make_geom(g, &gg))
+    return DK_ERR_BAD_ARGUMENT;
+  DK_DISPATCH(dtype, deform_backward_coords<T>(P_(T, grad_output), P_(T, input), P_(T, offset), P_(T, rotation),
+                                               P_(T, filter), M_(T, grad_offset), (T*)nullptr, gg, (cudaStream_t)stream))
+}
+
+int dk_deform_sample_depthwise_backward_rotation(const void* grad_output, const void* input, const void* offset,
+                                                 const void* rotation, const void* filter, void* grad_rotation,
+                                                 const dk_geom* g, int dtype, void* stream) {
+  Geom gg;
+  if (!grad_output || !input || !offset || !rotation || !filter || !grad_rotation || !make_geom(g, &gg))
+    return DK_ERR_BAD_ARGUMENT;
+  DK_DISPATCH(dtype, deform_backward_coords<T>(P_(T, grad_output), P_(T, input), P_(T, offset), P_(T, rotation),
+                                               P_(T, filter), (T*)nullptr, M_(T, grad_rotation), gg, (cudaStream_t)stream))
+}
+
+size_t dk_deform_sample_depthwise_backward_workspace_bytes(const dk_geom* g, int dtype) {
+  return dk_deform_sample_depthwise_backward_data_workspace_bytes(g, dtype) +
+         dk_deform_sample_depthwise_backward_filter_workspace_bytes(g, dtype);
+}
+
+static int deform_coords_dispatch(const void* grad_output, const void* input, const void* offset, const void* rotation,
+                                  const void* filter, void* grad_offset, void* grad_rotation, const Geom& gg, int dtype,
+                                  void* stream) {
+  DK_DISPATCH(dtype, deform_backward_coords<T>(P_(T, grad_output), P_(T, input), P_(T, offset), P_(T, rotation),
+                                               P_(T, filter), M_(T, grad_offset), M_(T, grad_rotation), gg,
+                                               (cudaStream_t)stream))
+}
+
+int dk_deform_sample_depthwise_backward(const void* grad_output, const void* input, const void* offset,
+                                        const void* rotation, const void* filter, void* grad_input, void* grad_offset,
+                                        void* grad_rotation, void* grad_filter, const dk_geom* g, int dtype,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+  Geom gg;
+  if (!grad_output || !input || !offset || !rotation || !filter || !make_geom(g, &gg) || !dtype_ok(dtype))
+    return DK_ERR_BAD_ARGUMENT;
+  const size_t data_ws = dk_deform_sample_depthwise_backward_data_workspace_bytes(g, dtype);
+  const size_t filt_ws = dk_deform_sample_depthwise_backward_filter_workspace_bytes(g, dtype);
+  int rc = DK_OK;
+  if (grad_input) {
+    if (data_ws && (!workspace || workspace_bytes < data_ws)) return DK_ERR_WORKSPACE;
+    rc = dk_deform_sample_depthwise_backward_data(grad_output, offset, rotation, filter, grad_input, g, dtype, workspace,
+                                                  data_ws, stream);
+    if (rc) return rc;
+  }
+  if (grad_offset || grad_rotation) {
+    rc = deform_coords_dispatch(grad_output, input, offset, rotation, filter, grad_offset, grad_rotation, gg, dtype, stream);
+    if (rc) return rc;
+  }
+  if (grad_filter) {
+    if (!workspace || workspace_bytes < data_ws + filt_ws) return DK_ERR_WORKSPACE;
+    rc = dk_deform_sample_depthwise_backward_filter(grad_output, input, offset, rotation, grad_filter, g, dtype,
+                                                    (char*)workspace + data_ws, filt_ws, stream);
+  }
+  return rc;
+}
+
+/* ---------------------------------------------------------------- N-d linear sample */
+
+static int nd_args(int batch, int channels, int dims, const int* shape, NdShape* sh, int* prod) {
+  if (batch <= 0 || channels <= 0 || dims <= 0 || !shape) return DK_ERR_BAD_ARGUMENT;
+  if (dims > kMaxNdDims) return DK_ERR_UNSUPPORTED;
+  long long p = 1;
+  for (int d = 0; d < kMaxNdDims; ++d) sh->s[d] = 1;
+  for (int d = 0; d < dims; ++d) {
+    if (shape[d] <= 0) return DK_ERR_BAD_ARGUMENT;
+    sh->s[d] = shape[d];
+    p *= shape[d];
+    if (p > 0x3fffffffLL) return DK_ERR_UNSUPPORTED;
+  }
+  *prod = (int)p;
+  return DK_OK;
+}
+
+int dk_nd_linear_sample_forward(const void* data, const void* coord, void* output, int batch, int channels, int dims,
+                                const int* shape, int dtype, void* stream) {
+  NdShape sh;
+  int prod;
+  if (!data || !coord || !output) return DK_ERR_BAD_ARGUMENT;
+  int rc = nd_args(batch, channels, dims, shape, &sh, &prod);
+  if (rc) return rc;
+  DK_DISPATCH(dtype, nd_forward<T>(P_(T, data), P_(T, coord), M_(T, output), batch, channels, dims, prod, sh,
+                                   (cudaStream_t)stream))
+}
+
+int dk_nd_linear_sample_backward_data(const void* grad_output, const void* coord, void* grad_data, int batch,
+                                      int channels, int dims, const int* shape, int dtype, void* stream) {
+  NdShape sh;
+  int prod;
+  if (!grad_output || !coord || !grad_data) return DK_ERR_BAD_ARGUMENT;
+  int rc = nd_args(batch, channels, dims, shape, &sh, &prod);
+  if (rc) return rc;
+  DK_DISPATCH(dtype, nd_backward_data<T>(P_(T, grad_output), P_(T, coord), M_(T, grad_data), batch, channels, dims, prod,
+                                         sh, (cudaStream_t)stream))
+}
+
+int dk_nd_linear_sample_backward_coord(const void* grad_output, const void* data, const void* coord,
+                                       void* grad_coord_per_channel, int batch, int channels, int dims, const int* shape,
+                                       int dtype, void* stream) {
+  NdShape sh;
+  int prod;
+  if (!grad_output || !data || !coord || !grad_coord_per_channel) return DK_ERR_BAD_ARGUMENT;
+  int rc = nd_args(batch, channels, dims, shape, &sh, &prod);
+  if (rc) return rc;
+  DK_DISPATCH(dtype, nd_backward_coord<T>(P_(T, grad_output), P_(T, data), P_(T, coord), M_(T, grad_coord_per_channel),
+                                          batch, channels, dims, prod, sh, false, (cudaStream_t)stream))
+}
+
+int dk_nd_linear_sample_backward_coord_sum(const void* grad_output, const void* data, const void* coord, void* grad_coord,
+                                           int batch, int channels, int dims, const int* shape, int dtype, void* stream) {
+  NdShape sh;
+  int prod;
+  if (!grad_output || !data || !coord || !grad_coord) return DK_ERR_BAD_ARGUMENT;
+  int rc = nd_args(batch, channels, dims, shape, &sh, &prod);
+  if (rc) return rc;
+  DK_DISPATCH(dtype, nd_backward_coord<T>(P_(T, grad_output), P_(T, data), P_(T, coord), M_(T, grad_coord), batch,
+                                          channels, dims, prod, sh, true, (cudaStream_t)stream))
+}
+
+}  // extern "C"

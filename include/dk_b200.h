@@ -1,0 +1,177 @@
+/* dk_b200.h -- C ABI of the B200 (sm_100a) deformable-kernel operator library.
+ *
+ * This is the drop-in boundary: one entry point per function the reference binds
+ * through pybind11 (9 in csrc/filter_sample_depthwise_cuda.cpp:540-569, 3 in
+ * csrc/nd_linear_sample_cuda.cpp:67-74; paths relative to
+ * deformable_kernels/ops/deform_kernel/ of the reference project), plus fused
+ * variants that the autograd functions of this package prefer.
+ *
+ * Conventions, same for every entry point
+ *   - all tensor pointers are DEVICE pointers to dense NCHW (row-major) arrays; all
+ *     tensors of one call share one element type, given by `dtype`;
+ *   - the caller owns and allocates every buffer, outputs and workspaces included;
+ *     nothing is allocated, freed or kept by the library between calls;
+ *   - outputs are fully written: no output needs to be zeroed by the caller (the
+ *     reference needs zeroed grad buffers, functions/filter_sample_depthwise.py:64-80);
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the
+ *     legacy default stream) of the CURRENT device and the call returns without
+ *     synchronising;
+ *   - the return value is a dk_status; nothing is printed and the process is never
+ *     terminated (the reference prints launch errors and returns 1 regardless,
+ *     csrc/filter_sample_depthwise_cuda_kernel.cu:427-430);
+ *   - half inputs are read as fp16, all arithmetic and accumulation is fp32, results
+ *     are rounded once on store; DK_F64 computes in fp64.
+ *   - entry points are thread-safe; the only global state is a per-device attribute
+ *     cache behind a mutex.
+ */
+#ifndef DK_B200_H
+#define DK_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum dk_status {
+  DK_OK = 0,
+  DK_ERR_BAD_ARGUMENT = 1,    /* null pointer, non-positive size, channels % groups != 0, ... */
+  DK_ERR_UNSUPPORTED = 2,     /* valid request outside what the kernels cover (e.g. > 8 sample dims) */
+  DK_ERR_WORKSPACE = 3,       /* workspace missing or smaller than the matching *_workspace_bytes() */
+  DK_ERR_CUDA = 4             /* a CUDA runtime call or launch failed; see dk_last_cuda_error() */
+} dk_status;
+
+typedef enum dk_dtype { DK_F32 = 0, DK_F16 = 1, DK_F64 = 2 } dk_dtype;
+
+/* Geometry of one depthwise call.  Same fields as the reference's
+ * SampleDepthwiseArgs (csrc/filter_sample_depthwise_cuda.h:1-28) minus the output
+ * extent, which is derived as in csrc/filter_sample_depthwise_cuda.cpp:42-43:
+ *   out = (in + 2*pad - (dil*(kernel-1)+1)) / stride + 1   (integer division).
+ * Tensor shapes: input [batch, channels, in_h, in_w]; filter (the weight bank)
+ * [channels, 1, scope_h, scope_w]; rotation (kernel-space offsets)
+ * [batch, rotation_groups*kernel_h*kernel_w*2, out_h, out_w] with channel index
+ * ((g*kernel_h*kernel_w + tap)*2 + dir), dir 0 = h, 1 = w, and channel c using group
+ * c % rotation_groups; offset (image-space offsets)
+ * [batch, kernel_h*kernel_w*2, out_h, out_w]; output [batch, channels, out_h, out_w]. */
+typedef struct dk_geom {
+  int batch, channels, in_h, in_w;
+  int kernel_h, kernel_w;
+  int stride_h, stride_w;
+  int pad_h, pad_w;
+  int dil_h, dil_w;
+  int scope_h, scope_w;
+  int rotation_groups;
+} dk_geom;
+
+const char *dk_status_string(int status);
+/* cudaError_t of the most recent DK_ERR_CUDA on the calling thread (0 if none). */
+int dk_last_cuda_error(void);
+const char *dk_version(void);
+/* Output extent for a geometry; returns DK_ERR_BAD_ARGUMENT if it is not positive. */
+int dk_output_size(const dk_geom *g, int *out_h, int *out_w);
+
+/* ---------------------------------------------------------------- local DK
+ * y[n,c,oh,ow] = sum over taps of x[n,c,oh*s-p+fh*d, ow*s-p+fw*d] * B(W[c]; u, v),
+ * u = fh + rot_h + (scope_h-kernel_h)/2, v alike; B = zero-extended bilinear read. */
+
+/* replaces sample_depthwise_forward_cuda, csrc/filter_sample_depthwise_cuda.cpp:8-62 */
+int dk_sample_depthwise_forward(const void *input, const void *rotation, const void *filter, void *output,
+                                const dk_geom *g, int dtype, void *stream);
+
+/* replaces sample_depthwise_backward_data_cuda, csrc/filter_sample_depthwise_cuda.cpp:64-119
+ * (the reference also takes `input`, for its shape only) */
+int dk_sample_depthwise_backward_data(const void *grad_output, const void *rotation, const void *filter,
+                                      void *grad_input, const dk_geom *g, int dtype, void *stream);
+
+/* replaces sample_depthwise_backward_filter_cuda, csrc/filter_sample_depthwise_cuda.cpp:121-176.
+ * Needs a workspace of dk_sample_depthwise_backward_filter_workspace_bytes() bytes:
+ * per-block fp32 partial sums, reduced in a fixed order (no atomics, deterministic). */
+size_t dk_sample_depthwise_backward_filter_workspace_bytes(const dk_geom *g, int dtype);
+int dk_sample_depthwise_backward_filter(const void *grad_output, const void *input, const void *rotation,
+                                        void *grad_filter, const dk_geom *g, int dtype, void *workspace,
+                                        size_t workspace_bytes, void *stream);
+
+/* replaces sample_depthwise_backward_rotation_cuda, csrc/filter_sample_depthwise_cuda.cpp:178-235 */
+int dk_sample_depthwise_backward_rotation(const void *grad_output, const void *input, const void *rotation,
+                                          const void *filter, void *grad_rotation, const dk_geom *g, int dtype,
+                                          void *stream);
+
+/* All gradients of the local operator in one call (what
+ * SampleDepthwiseFunction.backward, functions/filter_sample_depthwise.py:53-87, does
+ * with three).  Any of the three outputs may be NULL to skip it.  Workspace as for
+ * dk_sample_depthwise_backward_filter (only needed when grad_filter != NULL). */
+int dk_sample_depthwise_backward(const void *grad_output, const void *input, const void *rotation,
+                                 const void *filter, void *grad_input, void *grad_rotation, void *grad_filter,
+                                 const dk_geom *g, int dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------- DK + DCN
+ * as above, with x read by zero-extended bilinear sampling at
+ * (oh*s-p+fh*d + off_h, ow*s-p+fw*d + off_w); a tap is used only if -1 < pos < size. */
+
+/* replaces deformable_sample_depthwise_forward_cuda, csrc/filter_sample_depthwise_cuda.cpp:237-294 */
+int dk_deform_sample_depthwise_forward(const void *input, const void *offset, const void *rotation,
+                                       const void *filter, void *output, const dk_geom *g, int dtype, void *stream);
+
+/* replaces deformable_sample_depthwise_backward_data_cuda, csrc/filter_sample_depthwise_cuda.cpp:296-354.
+ * For DK_F16 the scatter accumulates in an fp32 workspace of
+ * dk_deform_sample_depthwise_backward_data_workspace_bytes() bytes (0 for F32/F64). */
+size_t dk_deform_sample_depthwise_backward_data_workspace_bytes(const dk_geom *g, int dtype);
+int dk_deform_sample_depthwise_backward_data(const void *grad_output, const void *offset, const void *rotation,
+                                             const void *filter, void *grad_input, const dk_geom *g, int dtype,
+                                             void *workspace, size_t workspace_bytes, void *stream);
+
+/* replaces deformable_sample_depthwise_backward_filter_cuda, csrc/filter_sample_depthwise_cuda.cpp:356-414 */
+size_t dk_deform_sample_depthwise_backward_filter_workspace_bytes(const dk_geom *g, int dtype);
+int dk_deform_sample_depthwise_backward_filter(const void *grad_output, const void *input, const void *offset,
+                                               const void *rotation, void *grad_filter, const dk_geom *g, int dtype,
+                                               void *workspace, size_t workspace_bytes, void *stream);
+
+/* replaces deformable_sample_depthwise_backward_offset_cuda, csrc/filter_sample_depthwise_cuda.cpp:416-476 */
+int dk_deform_sample_depthwise_backward_offset(const void *grad_output, const void *input, const void *offset,
+                                               const void *rotation, const void *filter, void *grad_offset,
+                                               const dk_geom *g, int dtype, void *stream);
+
+/* replaces deformable_sample_depthwise_backward_rotation_cuda, csrc/filter_sample_depthwise_cuda.cpp:478-538 */
+int dk_deform_sample_depthwise_backward_rotation(const void *grad_output, const void *input, const void *offset,
+                                                 const void *rotation, const void *filter, void *grad_rotation,
+                                                 const dk_geom *g, int dtype, void *stream);
+
+/* All gradients of DK+DCN in one call (DeformableSampleDepthwiseFunction.backward,
+ * functions/filter_sample_depthwise.py:142-191, uses four).  Outputs may be NULL.
+ * Workspace: dk_deform_sample_depthwise_backward_workspace_bytes(). */
+size_t dk_deform_sample_depthwise_backward_workspace_bytes(const dk_geom *g, int dtype);
+int dk_deform_sample_depthwise_backward(const void *grad_output, const void *input, const void *offset,
+                                        const void *rotation, const void *filter, void *grad_input,
+                                        void *grad_offset, void *grad_rotation, void *grad_filter, const dk_geom *g,
+                                        int dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------- N-d linear sample
+ * data [channels, shape[0..dims-1]], coord [batch, dims], output [batch, channels];
+ * `shape` is a HOST array of `dims` ints (the reference passes a floating device
+ * tensor and casts it per use, csrc/nd_linear_sample_cuda_kernel.cu:49).  dims <= 8. */
+
+/* replaces nd_linear_sample_forward_cuda, csrc/nd_linear_sample_cuda.cpp:10-26 */
+int dk_nd_linear_sample_forward(const void *data, const void *coord, void *output, int batch, int channels,
+                                int dims, const int *shape, int dtype, void *stream);
+
+/* replaces nd_linear_sample_backward_data_cuda, csrc/nd_linear_sample_cuda.cpp:29-45
+ * (gather form: no atomics, grad_data needs no zeroing) */
+int dk_nd_linear_sample_backward_data(const void *grad_output, const void *coord, void *grad_data, int batch,
+                                      int channels, int dims, const int *shape, int dtype, void *stream);
+
+/* replaces nd_linear_sample_backward_coord_cuda, csrc/nd_linear_sample_cuda.cpp:47-64:
+ * per-channel coordinate gradient [batch, dims, channels] */
+int dk_nd_linear_sample_backward_coord(const void *grad_output, const void *data, const void *coord,
+                                       void *grad_coord_per_channel, int batch, int channels, int dims,
+                                       const int *shape, int dtype, void *stream);
+
+/* The same summed over channels inside the kernel: grad_coord [batch, dims] (the
+ * reference sums in Python, functions/nd_linear_sample.py:55). */
+int dk_nd_linear_sample_backward_coord_sum(const void *grad_output, const void *data, const void *coord,
+                                           void *grad_coord, int batch, int channels, int dims, const int *shape,
+                                           int dtype, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DK_B200_H */

@@ -1,0 +1,143 @@
+"""CPU-side checks of the C-ABI library: it loads, it exports every symbol that
+include/dk_b200.h declares, and its host-side argument validation answers without a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def cabi():
+    from deformable_kernels import _cabi
+    return _cabi
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "dk_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(dk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(cabi):
+    names = _declared()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(cabi.lib, n), n
+    assert set(cabi.EXPORTS) == set(names)
+
+
+def test_version_and_status_strings(cabi):
+    assert b"sm_100a" in cabi.lib.dk_version()
+    assert cabi.lib.dk_status_string(0) == b"ok"
+    for s in range(1, 5):
+        assert cabi.lib.dk_status_string(s) not in (b"ok", b"unknown status")
+
+
+def test_output_size_matches_reference_formula(cabi):
+    g = cabi.geom((2, 8, 28, 30), (3, 3), (2, 1), (1, 1), (1, 2), (4, 4), 1)
+    h, w = ctypes.c_int(), ctypes.c_int()
+    assert cabi.lib.dk_output_size(g, ctypes.byref(h), ctypes.byref(w)) == 0
+    assert h.value == (28 + 2 - 3) // 2 + 1
+    assert w.value == (30 + 2 - (2 * 2 + 1)) // 1 + 1
+    bad = cabi.geom((2, 8, 2, 2), (5, 5), (1, 1), (0, 0), (1, 1), (4, 4), 1)   # input too small
+    assert cabi.lib.dk_output_size(bad, ctypes.byref(h), ctypes.byref(w)) == 1
+
+
+def test_bad_arguments_are_refused_before_any_launch(cabi):
+    g = cabi.geom((1, 4, 8, 8), (3, 3), (1, 1), (1, 1), (1, 1), (4, 4), 1)
+    null = ctypes.c_void_p(0)
+    assert cabi.lib.dk_sample_depthwise_forward(null, null, null, null, g, 0, null) == 1
+    g3 = cabi.geom((1, 4, 8, 8), (3, 3), (1, 1), (1, 1), (1, 1), (4, 4), 3)          # 4 % 3 != 0
+    one = ctypes.c_void_p(16)
+    assert cabi.lib.dk_sample_depthwise_forward(one, one, one, one, g3, 0, null) == 1
+    assert cabi.lib.dk_sample_depthwise_forward(one, one, one, one, g, 7, null) == 1    # unknown dtype
+    shape = (ctypes.c_int * 9)(*([2] * 9))
+    assert cabi.lib.dk_nd_linear_sample_forward(one, one, one, 1, 1, 9, shape, 0, null) == 2  # > 8 dims
+
+
+def test_workspace_queries(cabi):
+    g = cabi.geom((4, 64, 28, 28), (3, 3), (1, 1), (1, 1), (1, 1), (4, 4), 1)
+    n32 = cabi.lib.dk_sample_depthwise_backward_filter_workspace_bytes(g, cabi.DK_F32)
+    assert n32 > 0 and n32 % 256 == 0 and n32 % (64 * 16 * 4) == 0
+    assert cabi.lib.dk_deform_sample_depthwise_backward_data_workspace_bytes(g, cabi.DK_F32) == 0
+    assert cabi.lib.dk_deform_sample_depthwise_backward_data_workspace_bytes(g, cabi.DK_F16) >= 4 * 64 * 28 * 28 * 4
+
+
+def test_cpu_tensors_raise_like_the_reference():
+    import torch
+    from deformable_kernels.ops.deform_kernel.functions import sample_depthwise, nd_linear_sample
+    with pytest.raises(NotImplementedError):
+        sample_depthwise(torch.randn(1, 2, 5, 5), torch.zeros(1, 18, 5, 5), torch.randn(2, 1, 4, 4))
+    with pytest.raises(NotImplementedError):
+        nd_linear_sample(torch.randn(3, 2, 2), torch.rand(4, 2))
+
+
+def test_modules_keep_reference_names_and_shapes():
+    import torch
+    from deformable_kernels.modules import (DeformConv2d, DeformKernel2d, DeformKernelConv2d, GlobalDeformKernel2d,
+                                            LocalDeformKernel2d)
+    assert DeformKernel2d is LocalDeformKernel2d
+    m = DeformKernel2d((4, 4), 8, 8, 3, 1, 1, groups=8, rotation_groups=2)
+    sd = m.state_dict()
+    assert sd["inner_conv.weight"].shape == (8, 1, 4, 4)
+    assert sd["rotation_conv.weight"].shape == (2 * 9 * 2, 8, 3, 3) and "rotation_conv.bias" in sd
+    assert float(sd["inner_conv.weight"].abs().max()) <= 1.0 / 3 + 1e-6
+    m = DeformKernelConv2d((4, 4), 8, 8, 3, 2, 1, groups=8)
+    assert m.state_dict()["offset_conv.weight"].shape == (18, 8, 3, 3)
+    m = DeformConv2d(8, 8, 3, 1, 1, groups=8)
+    assert m.state_dict()["inner_conv.weight"].shape == (8, 1, 3, 3)
+    m = GlobalDeformKernel2d((2, 2), 8, 8, groups=8)
+    assert set(m.state_dict()) == {"weight", "fc.weight", "fc.bias"}
+    assert m.fc_bias == [0.5, 0.5]
+    with pytest.raises(ValueError):
+        DeformKernel2d((4, 4), 4, 4, 5, 1, 0, groups=4).inner_conv._output_size(torch.zeros(1, 4, 3, 3))
+
+
+def test_reference_layers_import_unchanged_on_top_of_this_package():
+    """The reference's own modules/deform_kernel.py and modules/deform_conv.py, loaded from
+    the reference tree as they are, resolve their imports against this package's ops."""
+    import importlib.util
+    import sys
+    import types
+    ref_root = os.environ.get("DK_REFERENCE_ROOT", "/root/reference")
+    mod_dir = os.path.join(ref_root, "deformable_kernels", "modules")
+    if not os.path.isdir(mod_dir):
+        pytest.skip("reference tree not present")
+    import deformable_kernels  # noqa: F401
+    amp = types.ModuleType("apex.amp")
+    amp.float_function = lambda f: f      # identity while amp is not initialised
+    apex = types.ModuleType("apex")
+    apex.amp = amp
+    saved = {k: sys.modules.get(k) for k in ("apex", "apex.amp")}
+    sys.modules["apex"], sys.modules["apex.amp"] = apex, amp
+    try:
+        pkg = types.ModuleType("deformable_kernels._ref_layers")
+        pkg.__path__ = [mod_dir]
+        sys.modules["deformable_kernels._ref_layers"] = pkg
+        mods = {}
+        for name in ("deform_kernel", "deform_conv"):
+            full = "deformable_kernels._ref_layers." + name
+            spec = importlib.util.spec_from_file_location(full, os.path.join(mod_dir, name + ".py"))
+            mod = importlib.util.module_from_spec(spec)
+            sys.modules[full] = mod
+            spec.loader.exec_module(mod)
+            mods[name] = mod
+        from deformable_kernels.ops.deform_kernel.modules import SampleDepthwise
+        layer = mods["deform_kernel"].DeformKernel2d((4, 4), 8, 8, 3, 1, 1, groups=8)
+        assert isinstance(layer.inner_conv, SampleDepthwise)
+        assert set(layer.state_dict()) == {"rotation_conv.weight", "rotation_conv.bias", "inner_conv.weight"}
+        import torch
+        with pytest.raises(NotImplementedError):      # reaches this package's op, which has no CPU path
+            layer(torch.randn(1, 8, 6, 6))
+        assert mods["deform_conv"].DeformConv2d(8, 8, 3, 1, 1, groups=8).inner_conv.weight.shape == (8, 1, 3, 3)
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
+        for k in [k for k in sys.modules if k.startswith("deformable_kernels._ref_layers")]:
+            sys.modules.pop(k, None)

@@ -1,0 +1,389 @@
+"""GPU parity tests: the CUDA kernels, called through the C ABI, against the CPU oracle,
+against the committed golden vectors (outputs of the reference's own CUDA kernels), and,
+at full size, against the reference extension itself when its build travelled with the
+repository (oracle/_ref/) plus size-independent properties.
+
+Tolerances (max|a-b| / max|b| per tensor): 1e-5 for fp32, 2e-3 for fp16 (fp16 results are
+compared with the fp32 oracle evaluated on the fp16-rounded inputs), 1e-11 for fp64.
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+import dk_cases
+from dk_cases import make_case, make_nd_case, rel_err
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TOL = {torch.float64: 1e-11, torch.float32: 1e-5, torch.float16: 2e-3}
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from deformable_kernels.ops.deform_kernel import functions
+    return functions
+
+
+@pytest.fixture(scope="module")
+def oracle():
+    from oracle import dk_oracle
+    return dk_oracle
+
+
+def _ref_modules():
+    from oracle import build_ref
+    try:
+        return (build_ref.load_module("filter_sample_depthwise_cuda"), build_ref.load_module("nd_linear_sample_cuda"))
+    except (FileNotFoundError, ImportError, OSError):
+        return None
+
+
+def snap(t, frac=0.25, seed=1):
+    gen = torch.Generator().manual_seed(seed)
+    pick = torch.rand(t.shape, generator=gen) < frac
+    return torch.where(pick, torch.round(t * 2) / 2, t)
+
+
+def mine_local(ops, case, dtype):
+    x, r, w, dy = (case[k].to(dtype).to(DEV) for k in ("input", "rotation", "weight", "grad_output"))
+    x.requires_grad_(True), r.requires_grad_(True), w.requires_grad_(True)
+    y = ops.sample_depthwise(x, r, w, **case["args"])
+    dx, dr, dw = torch.autograd.grad(y, [x, r, w], dy)
+    return dict(output=y.detach(), grad_input=dx, grad_rotation=dr, grad_weight=dw)
+
+
+def mine_deform(ops, case, dtype):
+    x, o, r, w, dy = (case[k].to(dtype).to(DEV) for k in ("input", "offset", "rotation", "weight", "grad_output"))
+    for t in (x, o, r, w):
+        t.requires_grad_(True)
+    y = ops.deform_sample_depthwise(x, o, r, w, **case["args"])
+    dx, do, dr, dw = torch.autograd.grad(y, [x, o, r, w], dy)
+    return dict(output=y.detach(), grad_input=dx, grad_offset=do, grad_rotation=dr, grad_weight=dw)
+
+
+def mine_nd(ops, case, dtype):
+    data, coord, dy = (case[k].to(dtype).to(DEV) for k in ("data", "coord", "grad_output"))
+    data.requires_grad_(True), coord.requires_grad_(True)
+    y = ops.nd_linear_sample(data, coord)
+    dd, dc = torch.autograd.grad(y, [data, coord], dy)
+    return dict(output=y.detach(), grad_data=dd, grad_coord=dc)
+
+
+def oracle_inputs(case, dtype):
+    """What the oracle computes on: fp64 copies for fp64/fp32 runs (the truth both are judged
+    against), fp32 copies of the fp16-rounded inputs for fp16 runs."""
+    odt = torch.float32 if dtype == torch.float16 else torch.float64
+    return {k: (v.to(dtype).to(odt) if torch.is_tensor(v) else v) for k, v in case.items()}
+
+
+def oracle_local(O, case, dtype):
+    c = oracle_inputs(case, dtype)
+    y = O.sample_depthwise_forward(c["input"], c["rotation"], c["weight"], **c["args"])
+    dx, dr, dw = O.sample_depthwise_backward(c["grad_output"], c["input"], c["rotation"], c["weight"], **c["args"])
+    return dict(output=y, grad_input=dx, grad_rotation=dr, grad_weight=dw)
+
+
+def oracle_deform(O, case, dtype):
+    c = oracle_inputs(case, dtype)
+    y = O.deform_sample_depthwise_forward(c["input"], c["offset"], c["rotation"], c["weight"], **c["args"])
+    dx, do, dr, dw = O.deform_sample_depthwise_backward(c["grad_output"], c["input"], c["offset"], c["rotation"],
+                                                        c["weight"], **c["args"])
+    return dict(output=y, grad_input=dx, grad_offset=do, grad_rotation=dr, grad_weight=dw)
+
+
+def oracle_nd(O, case, dtype):
+    c = oracle_inputs(case, dtype)
+    y = O.nd_linear_sample_forward(c["data"], c["coord"])
+    dd, dc = O.nd_linear_sample_backward(c["grad_output"], c["data"], c["coord"])
+    return dict(output=y, grad_data=dd, grad_coord=dc)
+
+
+def compare(got, want, dtype, what=""):
+    for k, v in want.items():
+        if dtype == torch.float16:
+            v = v.to(torch.float16)
+        err = rel_err(got[k], v)
+        assert err < TOL[dtype], "%s %s: rel err %.3e (tol %.0e)" % (what, k, err, TOL[dtype])
+
+
+SMALL = [
+    dict(n=2, c=6, h=9, w=7, scope=(4, 4), k=3, stride=1, pad=1, dil=1, groups=1, rot_std=1.0),
+    dict(n=2, c=6, h=9, w=8, scope=(4, 4), k=3, stride=2, pad=1, dil=1, groups=2, rot_std=1.0),
+    dict(n=1, c=4, h=11, w=10, scope=(3, 5), k=3, stride=1, pad=2, dil=2, groups=4, rot_std=1.5),
+    dict(n=2, c=4, h=8, w=8, scope=(2, 2), k=1, stride=1, pad=0, dil=1, groups=1, rot_std=0.7),
+    dict(n=1, c=3, h=12, w=9, scope=(6, 4), k=5, stride=2, pad=2, dil=1, groups=3, rot_std=1.0),
+    dict(n=1, c=2, h=10, w=10, scope=(4, 4), k=(3, 1), stride=(1, 2), pad=(1, 0), dil=1, groups=1, rot_std=1.0),
+    dict(n=3, c=40, h=17, w=13, scope=(4, 4), k=3, stride=1, pad=1, dil=1, groups=1, rot_std=1.0),   # > one channel chunk
+    dict(n=2, c=70, h=7, w=7, scope=(4, 4), k=3, stride=2, pad=1, dil=1, groups=1, rot_std=2.5),     # many invalid samples
+    dict(n=1, c=33, h=6, w=5, scope=(4, 4), k=3, stride=1, pad=1, dil=1, groups=33, rot_std=1.0),    # one group per channel
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32, torch.float16])
+@pytest.mark.parametrize("cfg", SMALL)
+def test_local_dk_matches_oracle(ops, oracle, cfg, dtype):
+    case = make_case(seed=31, **cfg)
+    case["rotation"] = snap(case["rotation"])
+    compare(mine_local(ops, case, dtype), oracle_local(oracle, case, dtype), dtype, "local")
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32, torch.float16])
+@pytest.mark.parametrize("cfg", SMALL)
+def test_deform_dk_matches_oracle(ops, oracle, cfg, dtype):
+    case = make_case(seed=32, off_std=2.0, **cfg)
+    case["rotation"] = snap(case["rotation"])
+    case["offset"] = snap(case["offset"], seed=2)
+    compare(mine_deform(ops, case, dtype), oracle_deform(oracle, case, dtype), dtype, "deform")
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(2, 2), (4, 4), (3, 5), (5,), (2, 3, 4), (2, 2, 2, 3)])
+def test_nd_linear_matches_oracle(ops, oracle, shape, dtype):
+    case = make_nd_case(70, shape, 50, seed=33)
+    compare(mine_nd(ops, case, dtype), oracle_nd(oracle, case, dtype), dtype, "nd")
+
+
+def test_empty_and_degenerate_inputs(ops):
+    from deformable_kernels._cabi import DkError
+    x = torch.randn(1, 4, 2, 2, device=DEV)
+    w = torch.randn(4, 1, 4, 4, device=DEV)
+    with pytest.raises(ValueError):      # convolution input is too small
+        ops.sample_depthwise(x, torch.zeros(1, 18, 1, 1, device=DEV), w, (5, 5), (1, 1), (0, 0), (1, 1), 1)
+    with pytest.raises(ValueError):      # offsets of the wrong shape
+        ops.sample_depthwise(x, torch.zeros(1, 18, 3, 3, device=DEV), w)
+    with pytest.raises(TypeError):       # mixed dtypes at the Function level
+        from deformable_kernels.ops.deform_kernel.functions.filter_sample_depthwise import SampleDepthwiseFunction
+        SampleDepthwiseFunction.apply(x, torch.zeros(1, 18, 2, 2, device=DEV).half(), w)
+    assert issubclass(DkError, RuntimeError)
+    # all samples outside the bank -> exact zeros in value and every gradient
+    r = torch.full((1, 18, 2, 2), 50.0, device=DEV)
+    x.requires_grad_(True), r.requires_grad_(True), w.requires_grad_(True)
+    y = ops.sample_depthwise(x, r, w)
+    assert torch.count_nonzero(y) == 0
+    gx, gr, gw = torch.autograd.grad(y, [x, r, w], torch.ones_like(y))
+    assert torch.count_nonzero(gx) == 0 and torch.count_nonzero(gr) == 0 and torch.count_nonzero(gw) == 0
+    # NaN offsets sample nothing (comparisons are false in the reference too)
+    r2 = torch.full((1, 18, 2, 2), float("nan"), device=DEV)
+    assert torch.count_nonzero(ops.sample_depthwise(x.detach(), r2, w.detach())) == 0
+
+
+def _golden_files():
+    return sorted(glob.glob(os.path.join(GOLDEN, "*.npz")))
+
+
+@pytest.mark.parametrize("path", _golden_files() or [None])
+def test_kernels_match_reference_cuda_golden(ops, path):
+    if path is None:
+        pytest.skip("no golden vectors committed yet")
+    z = np.load(path)
+    kind = str(z["kind"])
+    t = {k: torch.from_numpy(z[k]) for k in z.files if k not in ("kind", "args")}
+    dtype = t["grad_output"].dtype
+    tol = 1e-11 if dtype == torch.float64 else 2e-5
+    if kind == "nd":
+        got = mine_nd(ops, t, dtype)
+    else:
+        a = [int(v) for v in z["args"]]
+        t["args"] = dict(kernel_size=(a[0], a[1]), stride=(a[2], a[3]), padding=(a[4], a[5]), dilation=(a[6], a[7]),
+                         rotation_groups=a[8])
+        got = mine_local(ops, t, dtype) if kind == "local" else mine_deform(ops, t, dtype)
+    for k, v in got.items():
+        err = rel_err(v, t["ref_" + k])
+        assert err < tol, "%s %s: %.3e" % (os.path.basename(path), k, err)
+
+
+def test_reference_named_entry_points_agree_with_fused_calls(ops):
+    """The nine + three functions named like the reference's pybind11 functions, called the
+    way the reference's own autograd code calls them, give the fused path's results."""
+    from deformable_kernels.ops.deform_kernel import filter_sample_depthwise_cuda as fs
+    from deformable_kernels.ops.deform_kernel import nd_linear_sample_cuda as nd
+    case = make_case(2, 40, 12, 11, stride=2, groups=2, rot_std=1.0, off_std=2.0, seed=34)
+    for dtype in (torch.float32, torch.float16):
+        fused = mine_deform(ops, case, dtype)
+        x, o, r, w, dy = (case[k].to(dtype).to(DEV) for k in ("input", "offset", "rotation", "weight", "grad_output"))
+        tail = (3, 3, 2, 2, 1, 1, 1, 1, 4, 4, 2)
+        y = torch.empty_like(dy)
+        fs.deformable_sample_depthwise_forward_cuda(x, o, r, w, y, *tail)
+        dx, do, dr, dw = torch.zeros_like(x), torch.zeros_like(o), torch.zeros_like(r), torch.zeros_like(w)
+        fs.deformable_sample_depthwise_backward_data_cuda(dy, x, o, r, w, dx, *tail)
+        fs.deformable_sample_depthwise_backward_offset_cuda(dy, x, o, r, w, do, *tail)
+        fs.deformable_sample_depthwise_backward_rotation_cuda(dy, x, o, r, w, dr, *tail)
+        fs.deformable_sample_depthwise_backward_filter_cuda(dy, x, o, r, w, dw, *tail)
+        for a, b in ((y, "output"), (dx, "grad_input"), (do, "grad_offset"), (dr, "grad_rotation"), (dw, "grad_weight")):
+            assert rel_err(a, fused[b]) < (1e-6 if dtype == torch.float32 else 1e-3), b
+        fusedl = mine_local(ops, case, dtype)
+        y = torch.empty_like(dy)
+        fs.sample_depthwise_forward_cuda(x, r, w, y, *tail)
+        dx, dr, dw = torch.zeros_like(x), torch.zeros_like(r), torch.zeros_like(w)
+        fs.sample_depthwise_backward_data_cuda(dy, x, r, w, dx, *tail)
+        fs.sample_depthwise_backward_rotation_cuda(dy, x, r, w, dr, *tail)
+        fs.sample_depthwise_backward_filter_cuda(dy, x, r, w, dw, *tail)
+        for a, b in ((y, "output"), (dx, "grad_input"), (dr, "grad_rotation"), (dw, "grad_weight")):
+            assert rel_err(a, fusedl[b]) < (1e-6 if dtype == torch.float32 else 1e-3), b
+    ndc = make_nd_case(20, (4, 4), 30, seed=35)
+    fused = mine_nd(ops, ndc, torch.float32)
+    data, coord, dy = (ndc[k].to(DEV) for k in ("data", "coord", "grad_output"))
+    shape = torch.tensor(data.shape[1:], dtype=data.dtype, device=DEV)
+    y = data.new_empty(30, 20)
+    nd.nd_linear_sample_forward_cuda(data, shape, coord, y)
+    dd = data.new_empty(*data.size())
+    nd.nd_linear_sample_backward_data_cuda(dy, data, shape, coord, dd)
+    dcc = coord.new_empty(30, 2, 20)
+    nd.nd_linear_sample_backward_coord_cuda(dy, data, shape, coord, dcc)
+    assert rel_err(y, fused["output"]) < 1e-6
+    assert rel_err(dd, fused["grad_data"]) < 1e-6
+    assert rel_err(dcc.sum(2), fused["grad_coord"]) < 1e-5
+
+
+# ------------------------------------------------------------------ BASELINE configs
+
+def test_cfg1_full_size_matches_oracle(ops, oracle):
+    case = dk_cases.cfg1()
+    for dtype in (torch.float32, torch.float64):
+        compare(mine_local(ops, case, dtype), oracle_local(oracle, case, dtype), dtype, "cfg1")
+
+
+def test_cfg2_full_size_matches_oracle_and_module_runs(ops, oracle):
+    case = dk_cases.cfg2()
+    compare(mine_nd(ops, case, torch.float32), oracle_nd(oracle, case, torch.float32), torch.float32, "cfg2")
+    from deformable_kernels.modules import GlobalDeformKernel2d
+    torch.manual_seed(0)
+    m = GlobalDeformKernel2d((2, 2), 256, 256, kernel_size=1, groups=256).to(DEV)
+    with torch.no_grad():
+        m.weight.copy_(case["weight"].to(DEV))
+        m.fc.weight.normal_(0, 0.05)
+    x = case["input"].to(DEV).requires_grad_(True)
+    y = m(x)
+    y.sum().backward()
+    # per-sample 1x1 depthwise kernel: y = x * k[n, c]
+    with torch.no_grad():
+        avg = x.view(32, 256, -1).mean(2)
+        coord = torch.clamp(m.fc(avg) + 0.5, 0, 1).cpu()
+        k = oracle.nd_linear_sample_forward(case["data"], coord).to(DEV)
+    assert rel_err(y, x.detach() * k.view(32, 256, 1, 1)) < 1e-5
+    assert m.weight.grad is not None and m.fc.weight.grad is not None and x.grad is not None
+
+
+@pytest.mark.parametrize("c,hw,stride,n", [(96, 112, 1, 2), (144, 56, 2, 3), (960, 7, 1, 8), (384, 14, 2, 4)])
+def test_cfg3_reduced_batch_fp16_matches_oracle(ops, oracle, c, hw, stride, n):
+    case = dk_cases.cfg3(c, hw, stride, n=n)
+    compare(mine_local(ops, case, torch.float16), oracle_local(oracle, case, torch.float16), torch.float16, "cfg3")
+
+
+def test_cfg4_reduced_fp16_matches_oracle(ops, oracle):
+    case = dk_cases.cfg4(n=2, c=64, hw=56)
+    compare(mine_deform(ops, case, torch.float16), oracle_deform(oracle, case, torch.float16), torch.float16, "cfg4")
+
+
+def _ref_local(fs, case, dtype):
+    x, r, w, dy = (case[k].to(dtype).to(DEV) for k in ("input", "rotation", "weight", "grad_output"))
+    a = case["args"]
+    tail = (*a["kernel_size"], *a["stride"], *a["padding"], *a["dilation"], w.size(2), w.size(3), a["rotation_groups"])
+    y = torch.empty_like(dy)
+    fs.sample_depthwise_forward_cuda(x, r, w, y, *tail)
+    dx, dr, dw = torch.zeros_like(x), torch.zeros_like(r), torch.zeros_like(w)
+    fs.sample_depthwise_backward_data_cuda(dy, x, r, w, dx, *tail)
+    fs.sample_depthwise_backward_rotation_cuda(dy, x, r, w, dr, *tail)
+    fs.sample_depthwise_backward_filter_cuda(dy, x, r, w, dw, *tail)
+    torch.cuda.synchronize()
+    return dict(output=y, grad_input=dx, grad_rotation=dr, grad_weight=dw)
+
+
+def _ref_deform(fs, case, dtype):
+    x, o, r, w, dy = (case[k].to(dtype).to(DEV) for k in ("input", "offset", "rotation", "weight", "grad_output"))
+    a = case["args"]
+    tail = (*a["kernel_size"], *a["stride"], *a["padding"], *a["dilation"], w.size(2), w.size(3), a["rotation_groups"])
+    y = torch.empty_like(dy)
+    fs.deformable_sample_depthwise_forward_cuda(x, o, r, w, y, *tail)
+    dx, do, dr, dw = torch.zeros_like(x), torch.zeros_like(o), torch.zeros_like(r), torch.zeros_like(w)
+    fs.deformable_sample_depthwise_backward_data_cuda(dy, x, o, r, w, dx, *tail)
+    fs.deformable_sample_depthwise_backward_offset_cuda(dy, x, o, r, w, do, *tail)
+    fs.deformable_sample_depthwise_backward_rotation_cuda(dy, x, o, r, w, dr, *tail)
+    fs.deformable_sample_depthwise_backward_filter_cuda(dy, x, o, r, w, dw, *tail)
+    torch.cuda.synchronize()
+    return dict(output=y, grad_input=dx, grad_offset=do, grad_rotation=dr, grad_weight=dw)
+
+
+def _half_inputs_as_float(case):
+    return {k: (v.half().float() if torch.is_tensor(v) else v) for k, v in case.items()}
+
+
+@pytest.mark.parametrize("c,hw,stride", [(96, 112, 1), (960, 7, 2), (192, 28, 1)])
+def test_cfg3_full_size_fp16_against_live_reference(ops, c, hw, stride):
+    """Full batch (128).  The reference runs in fp32 on the fp16-rounded inputs, which is what
+    it does under Apex (functions/filter_sample_depthwise.py:209-211)."""
+    mods = _ref_modules()
+    if mods is None:
+        pytest.skip("reference build (oracle/_ref) not present")
+    case = dk_cases.cfg3(c, hw, stride, n=128)
+    got = mine_local(ops, case, torch.float16)
+    want = _ref_local(mods[0], _half_inputs_as_float(case), torch.float32)
+    compare(got, want, torch.float16, "cfg3-full")
+
+
+def test_cfg4_full_size_fp16_against_live_reference(ops):
+    mods = _ref_modules()
+    if mods is None:
+        pytest.skip("reference build (oracle/_ref) not present")
+    case = dk_cases.cfg4()
+    got = mine_deform(ops, case, torch.float16)
+    want = _ref_deform(mods[0], _half_inputs_as_float(case), torch.float32)
+    compare(got, want, torch.float16, "cfg4-full")
+
+
+def test_cfg1_cfg2_fp32_against_live_reference(ops):
+    mods = _ref_modules()
+    if mods is None:
+        pytest.skip("reference build (oracle/_ref) not present")
+    case = dk_cases.cfg1()
+    got = mine_local(ops, case, torch.float32)
+    want = _ref_local(mods[0], case, torch.float32)
+    for k in want:
+        assert rel_err(got[k], want[k]) < 2e-5, k     # both sides carry fp32 rounding
+    c2 = dk_cases.cfg2()
+    data, coord, dy = (c2[k].to(DEV) for k in ("data", "coord", "grad_output"))
+    shape = torch.tensor(data.shape[1:], dtype=data.dtype, device=DEV)
+    y = data.new_empty(32, 256)
+    mods[1].nd_linear_sample_forward_cuda(data, shape, coord, y)
+    dd = data.new_empty(*data.size())
+    mods[1].nd_linear_sample_backward_data_cuda(dy, data, shape, coord, dd)
+    dcc = coord.new_empty(32, 2, 256)
+    mods[1].nd_linear_sample_backward_coord_cuda(dy, data, shape, coord, dcc)
+    got = mine_nd(ops, c2, torch.float32)
+    assert rel_err(got["output"], y) < 1e-6
+    assert rel_err(got["grad_data"], dd) < 1e-5
+    assert rel_err(got["grad_coord"], dcc.sum(2)) < 1e-5
+
+
+# ------------------------------------------------------------------ full-size properties (no oracle)
+
+def test_full_size_properties_largest_layer_fp32(ops):
+    """C=96, 112x112, batch 32, fp32: zero offsets reduce to a stock depthwise convolution with the
+    2x2-averaged bank; the operator is linear in x and in W, so <dy, y> = <dx, x> = <dW, W>; the
+    offset gradient agrees with a central difference along a random direction."""
+    n, c, hw = 32, 96, 112
+    case = dk_cases.cfg3(c, hw, 1, n=n)
+    x, r, w, dy = (case[k].to(DEV) for k in ("input", "rotation", "weight", "grad_output"))
+    y0 = ops.sample_depthwise(x, torch.zeros_like(r), w)
+    ref = F.conv2d(x, F.avg_pool2d(w, 2, stride=1), padding=1, groups=c)
+    assert rel_err(y0, ref) < 1e-5
+    x.requires_grad_(True), r.requires_grad_(True), w.requires_grad_(True)
+    y = ops.sample_depthwise(x, r, w)
+    dx, dr, dw = torch.autograd.grad(y, [x, r, w], dy)
+    lhs = (dy.double() * y.detach().double()).sum()
+    assert abs(float((dx.double() * x.detach().double()).sum() / lhs) - 1) < 1e-5
+    assert abs(float((dw.double() * w.detach().double()).sum() / lhs) - 1) < 1e-5
+    v = torch.randn_like(r)
+    eps = 1e-3
+    with torch.no_grad():
+        yp = ops.sample_depthwise(x, r + eps * v, w).double()
+        ym = ops.sample_depthwise(x, r - eps * v, w).double()
+        fd = ((yp - ym) * dy.double()).sum() / (2 * eps)
+    an = (dr.double() * v.double()).sum()
+    assert abs(float(fd / an) - 1) < 2e-2
