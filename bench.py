@@ -126,6 +126,30 @@ def cpu_sweep(n_img, threads=None):
     return total
 
 
+def time_reference_gpu(layers, n, time_call):
+    """The reference's own CUDA kernels (unmodified extension from oracle/_ref/) on the same
+    tensors: forward and the three backward launches per layer, device-timed.  A side
+    measurement; never part of `value`."""
+    try:
+        from oracle import build_ref
+        fs = build_ref.load_module("filter_sample_depthwise_cuda")
+    except Exception as e:
+        return {"unavailable": str(e)[:200]}
+    out, tot = [], 0.0
+    for t in layers:
+        tail = (K, K, t["s"], t["s"], PAD, PAD, 1, 1, SCOPE, SCOPE, 1)
+        x, rot, dy, w = t["x"].detach(), t["rot"].detach(), t["dy"], t["w"].detach()
+        y, gx, gr, gw = torch.empty_like(dy), torch.zeros_like(x), torch.zeros_like(rot), torch.zeros_like(w)
+        tf = time_call(lambda: fs.sample_depthwise_forward_cuda(x, rot, w, y, *tail), 3)
+        tb = (time_call(lambda: fs.sample_depthwise_backward_data_cuda(dy, x, rot, w, gx, *tail), 3) +
+              time_call(lambda: fs.sample_depthwise_backward_rotation_cuda(dy, x, rot, w, gr, *tail), 3) +
+              time_call(lambda: fs.sample_depthwise_backward_filter_cuda(dy, x, rot, w, gw, *tail), 3))
+        out.append({"C": t["c"], "HW": t["hw"], "stride": t["s"], "fwd_ms": round(tf, 3), "bwd_ms": round(tb, 3)})
+        tot += tf + tb
+    return {"images_per_s": n / (tot * 1e-3), "ms_per_step": tot, "dtype": "f16 (the reference computes in half for half "
+            "tensors)", "per_layer": out}
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
@@ -160,6 +184,10 @@ def main():
     ap.add_argument("--batch", type=int, default=128, help="images per GPU")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", default="", help="comma-separated indices into the ten-layer sweep (default: all)")
+    ap.add_argument("--ref-gpu", action="store_true",
+                    help="also time the reference's own CUDA kernels (oracle/_ref build) on this GPU")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
 
@@ -183,7 +211,8 @@ def main():
     n = args.batch
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     layers = []
-    for (c, hw, s) in LAYERS:
+    chosen = [LAYERS[int(i)] for i in args.layers.split(",")] if args.layers else LAYERS
+    for (c, hw, s) in chosen:
         ho = out_hw(hw, s)
         t = dict(c=c, hw=hw, s=s, ho=ho)
         t["w"] = (torch.randn(c, 1, SCOPE, SCOPE, device=dev, generator=gen) * (2.0 / 16) ** 0.5).half()
@@ -264,9 +293,10 @@ def main():
     bt, bkt = big
     kb = kernel_bytes(dom, n, bt["c"], bt["hw"], bt["s"])
     achieved = kb / (bkt[dom] * 1e-3) / 1e9
-    tot_bytes = sum(sum(layer_bytes(n, c, hw, s)) for (c, hw, s) in LAYERS)
+    tot_bytes = sum(sum(layer_bytes(n, c, hw, s)) for (c, hw, s) in chosen)
     sweep_gbs = tot_bytes / (ms_step * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "local DK " + dom + " (C=96, 112x112, stride 1, batch %d)" % n,
+    roofline = {"bound": "hbm", "kernel": "local DK %s (C=%d, %dx%d, stride %d, batch %d)" % (dom, bt["c"], bt["hw"], bt["hw"],
+                                                                                             bt["s"], n),
                 "achieved": round(achieved, 1), "peak": peak, "peak_source": peak_kind, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "frac_of_nominal_8TBs": round(achieved / HBM_NOMINAL_GBS, 4),
                 "traffic": None, "kernel_ms": round(bkt[dom], 4),
@@ -297,19 +327,25 @@ def main():
             h["gw"].copy_(gw, non_blocking=True)
         torch.cuda.synchronize()
 
-    e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    e0.record()
-    for _ in range(args.e2e_steps):
+    e2e_val = None
+    if not args.no_e2e:
         e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
-    tms = torch.tensor([e2e_ms], device=dev)
-    if world > 1:
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-    e2e_val = world * n / (float(tms.item()) / args.e2e_steps * 1e-3)
+        barrier()
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
+        tms = torch.tensor([e2e_ms], device=dev)
+        if world > 1:
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        e2e_val = world * n / (float(tms.item()) / args.e2e_steps * 1e-3)
+
+    ref_gpu = None
+    if args.ref_gpu and rank == 0:
+        ref_gpu = time_reference_gpu(layers, n, time_call)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -333,7 +369,8 @@ def main():
                              "are evicted between steps" % (tot_bytes / 1e9)},
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * len(LAYERS) * 5, "clocks": clocks, "per_layer": per_layer,
+            "gpu_launches": args.steps * len(layers) * 5, "clocks": clocks, "per_layer": per_layer,
+            "reference_cuda_on_this_gpu": ref_gpu,
             "kernel_ms_sum_over_layers": {k: round(v, 4) for k, v in kern_tot.items()},
         }
         print(json.dumps(line))

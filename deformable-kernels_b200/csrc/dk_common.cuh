@@ -37,7 +37,7 @@ __device__ __forceinline__ double dk_floor(double v) { return floor(v); }
 
 // Zero-extended bilinear sampling of a rows x cols grid at (u, v): the four corner
 // indices (clamped into the grid so that they are always loadable) and, per corner,
-// a 0/1 mask telling whether the corner lies inside the grid.  `outer` is the
+// a flag telling whether the corner lies inside the grid.  `outer` is the
 // caller's validity test of the sample as a whole (-1 < u < rows, -1 < v < cols).
 // Value coefficients are {hh*hw, hh*lw, lh*hw, lh*lw} * mask; the derivative wrt u is
 // {-hw, -lw, +hw, +lw} * mask and wrt v {-hh, +hh, -lh, +lh} * mask: floor-based, so
@@ -46,7 +46,7 @@ __device__ __forceinline__ double dk_floor(double v) { return floor(v); }
 template <typename A>
 struct Bilinear {
   int idx[4];
-  A m[4];
+  bool m[4];
   A lh, lw, hh, hw;
 };
 
@@ -66,10 +66,10 @@ __device__ __forceinline__ void bilinear_setup(A u, A v, int rows, int cols, boo
   const bool a1 = outer && h1 >= 0 && h1 <= rows - 1;
   const bool c0 = w0 >= 0 && w0 <= cols - 1;
   const bool c1 = w1 >= 0 && w1 <= cols - 1;
-  b.m[0] = (a0 && c0) ? (A)1 : (A)0;
-  b.m[1] = (a0 && c1) ? (A)1 : (A)0;
-  b.m[2] = (a1 && c0) ? (A)1 : (A)0;
-  b.m[3] = (a1 && c1) ? (A)1 : (A)0;
+  b.m[0] = a0 && c0;
+  b.m[1] = a0 && c1;
+  b.m[2] = a1 && c0;
+  b.m[3] = a1 && c1;
   const int h0c = min(max(h0, 0), rows - 1), h1c = min(max(h1, 0), rows - 1);
   const int w0c = min(max(w0, 0), cols - 1), w1c = min(max(w1, 0), cols - 1);
   b.idx[0] = h0c * cols + w0c;
@@ -80,24 +80,25 @@ __device__ __forceinline__ void bilinear_setup(A u, A v, int rows, int cols, boo
 
 template <typename A>
 __device__ __forceinline__ void bilinear_value_coefs(const Bilinear<A>& b, A (&c)[4]) {
-  c[0] = b.hh * b.hw * b.m[0];
-  c[1] = b.hh * b.lw * b.m[1];
-  c[2] = b.lh * b.hw * b.m[2];
-  c[3] = b.lh * b.lw * b.m[3];
+  // selects, not products with the mask: a NaN or infinite offset must sample nothing
+  c[0] = b.m[0] ? b.hh * b.hw : (A)0;
+  c[1] = b.m[1] ? b.hh * b.lw : (A)0;
+  c[2] = b.m[2] ? b.lh * b.hw : (A)0;
+  c[3] = b.m[3] ? b.lh * b.lw : (A)0;
 }
 template <typename A>
 __device__ __forceinline__ void bilinear_du_coefs(const Bilinear<A>& b, A (&c)[4]) {
-  c[0] = -b.hw * b.m[0];
-  c[1] = -b.lw * b.m[1];
-  c[2] = b.hw * b.m[2];
-  c[3] = b.lw * b.m[3];
+  c[0] = b.m[0] ? -b.hw : (A)0;
+  c[1] = b.m[1] ? -b.lw : (A)0;
+  c[2] = b.m[2] ? b.hw : (A)0;
+  c[3] = b.m[3] ? b.lw : (A)0;
 }
 template <typename A>
 __device__ __forceinline__ void bilinear_dv_coefs(const Bilinear<A>& b, A (&c)[4]) {
-  c[0] = -b.hh * b.m[0];
-  c[1] = b.hh * b.m[1];
-  c[2] = -b.lh * b.m[2];
-  c[3] = b.lh * b.m[3];
+  c[0] = b.m[0] ? -b.hh : (A)0;
+  c[1] = b.m[1] ? b.hh : (A)0;
+  c[2] = b.m[2] ? -b.lh : (A)0;
+  c[3] = b.m[3] ? b.lh : (A)0;
 }
 
 // Bank coordinate of one tap: u = f + r + (scope - kernel)/2.  (The reference adds

@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(BLOCK) deform_data_kernel(const T* __restrict_
           A* dp = dx_n + j * cstride;
 #pragma unroll
           for (int q = 0; q < 4; ++q)
-            if (bi.m[q] != (A)0) atomicAdd(dp + bi.idx[q], ci[q] * v);
+            if (bi.m[q]) atomicAdd(dp + bi.idx[q], ci[q] * v);
         }
       }
     }
