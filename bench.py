@@ -138,7 +138,7 @@ def time_reference_gpu(layers, n, time_call):
     out, tot = [], 0.0
     for t in layers:
         tail = (K, K, t["s"], t["s"], PAD, PAD, 1, 1, SCOPE, SCOPE, 1)
-        x, rot, dy, w = t["x"].detach(), t["rot"].detach(), t["dy"], t["w"].detach()
+        x, rot, dy, w = t["x"].detach().float(), t["rot"].detach().float(), t["dy"].float(), t["w"].detach().float()
         y, gx, gr, gw = torch.empty_like(dy), torch.zeros_like(x), torch.zeros_like(rot), torch.zeros_like(w)
         tf = time_call(lambda: fs.sample_depthwise_forward_cuda(x, rot, w, y, *tail), 3)
         tb = (time_call(lambda: fs.sample_depthwise_backward_data_cuda(dy, x, rot, w, gx, *tail), 3) +
@@ -146,8 +146,8 @@ def time_reference_gpu(layers, n, time_call):
               time_call(lambda: fs.sample_depthwise_backward_filter_cuda(dy, x, rot, w, gw, *tail), 3))
         out.append({"C": t["c"], "HW": t["hw"], "stride": t["s"], "fwd_ms": round(tf, 3), "bwd_ms": round(tb, 3)})
         tot += tf + tb
-    return {"images_per_s": n / (tot * 1e-3), "ms_per_step": tot, "dtype": "f16 (the reference computes in half for half "
-            "tensors)", "per_layer": out}
+    return {"images_per_s": n / (tot * 1e-3), "ms_per_step": tot, "dtype": "f32 tensors, which is how the reference runs "
+            "under Apex (amp.float_function)", "per_layer": out}
 
 
 def run_reference(args, rank):
