@@ -283,7 +283,9 @@ def main():
         fb, bb = layer_bytes(n, t["c"], t["hw"], t["s"])
         tf, tb = kt["forward"], sum(v for k, v in kt.items() if k != "forward")
         per_layer.append({"C": t["c"], "HW": t["hw"], "stride": t["s"], "fwd_ms": round(tf, 4), "bwd_ms": round(tb, 4),
-                          "GBps": round((fb + bb) / ((tf + tb) * 1e-3) / 1e9, 1)})
+                          "GBps": round((fb + bb) / ((tf + tb) * 1e-3) / 1e9, 1),
+                          "bwd_data_rot_filter_ms": [round(kt["backward_data"], 4), round(kt["backward_rotation"], 4),
+                                                     round(kt["backward_filter"], 4)]})
         for k, v in kt.items():
             kern_tot[k] = kern_tot.get(k, 0.0) + v
         if big is None:

@@ -134,7 +134,12 @@ int dk_sample_depthwise_backward_data(const void* grad_output, const void* rotat
 size_t dk_sample_depthwise_backward_filter_workspace_bytes(const dk_geom* g, int dtype) {
   Geom gg;
   if (!make_geom(g, &gg) || !dtype_ok(dtype)) return 0;
-  return align256(filter_plan(gg, acc_bytes(dtype)).ws_bytes);
+  size_t need = filter_plan(gg, acc_bytes(dtype)).ws_bytes;
+  if (dtype == DK_F16) {
+    const size_t fast = local_filter_mma_workspace(gg);
+    if (fast > need) need = fast;
+  }
+  return align256(need);
 }
 
 int dk_sample_depthwise_backward_filter(const void* grad_output, const void* input, const void* rotation,

@@ -168,6 +168,16 @@ template <typename T>
 int deform_backward_filter(const T* dy, const T* x, const T* off, const T* rot, T* dw, const Geom&, void* ws,
                            size_t ws_bytes, cudaStream_t);
 
+// fp16 tensor-core fast path (dk_local_mma.cu); DK_ERR_UNSUPPORTED = shape outside the fast path
+bool mma_path_enabled();
+int local_conv_mma(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, bool transposed,
+                   cudaStream_t s);
+int local_rot_mma(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, const Geom& g,
+                  cudaStream_t s);
+size_t local_filter_mma_workspace(const Geom& g);
+int local_filter_mma(const __half* dy, const __half* x, const __half* rot, __half* dw, const Geom& g, void* ws,
+                     size_t ws_bytes, cudaStream_t s);
+
 // Plan of the two-stage bank-gradient reduction, shared by the workspace query and the launch.
 struct FilterPlan {
   int warps;         // warps per block, each owning 32 channels

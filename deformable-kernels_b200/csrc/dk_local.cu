@@ -7,9 +7,21 @@
 //     reuses it for every channel it handles (the reference recomputes it per channel);
 //   * the weight banks of the block's channels live in shared memory as fp32;
 //   * all arithmetic is in the compute type (fp32 for fp16/fp32 storage).
+#include <cstdlib>
+#include <type_traits>
+
 #include "dk_common.cuh"
 
 namespace dk {
+
+// The fp16 fast path can be switched off (DK_B200_DISABLE_MMA=1) to compare against the SIMT kernels.
+bool mma_path_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("DK_B200_DISABLE_MMA");
+    return !(v && v[0] && v[0] != '0');
+  }();
+  return on;
+}
 
 // ------------------------------------------------------------------ forward / grad-input
 // One thread = one (n, pixel); a block covers BLOCK consecutive pixels of the flattened
@@ -104,6 +116,12 @@ __global__ void __launch_bounds__(BLOCK) local_conv_kernel(const T* __restrict__
 template <typename T, bool TRANSPOSED>
 static int launch_local_conv(const T* src, const T* rot, const T* w, T* dst, const Geom& g, cudaStream_t s) {
   using A = typename Compute<T>::type;
+  if constexpr (std::is_same<T, __half>::value) {
+    if (mma_path_enabled()) {
+      const int rc = local_conv_mma(src, rot, w, dst, g, TRANSPOSED, s);
+      if (rc != DK_ERR_UNSUPPORTED) return rc;
+    }
+  }
   constexpr int CC = 16, BLOCK = 256;
   const long long total = (long long)g.N * (TRANSPOSED ? g.HW : g.P);
   const long long bx = (total + BLOCK - 1) / BLOCK;
@@ -211,6 +229,12 @@ __global__ void __launch_bounds__(32 * NW) local_rot_kernel(const T* __restrict_
 template <typename T>
 int local_backward_rotation(const T* dy, const T* x, const T* rot, const T* w, T* drot, const Geom& g, cudaStream_t s) {
   using A = typename Compute<T>::type;
+  if constexpr (std::is_same<T, __half>::value) {
+    if (mma_path_enabled()) {
+      const int rc = local_rot_mma(dy, x, rot, w, drot, g, s);
+      if (rc != DK_ERR_UNSUPPORTED) return rc;
+    }
+  }
   constexpr int NW = 8;
   const long long bx = ((long long)g.N * g.P + 31) / 32;
   if (bx > 0x7fffffffLL || g.G > 65535) return DK_ERR_UNSUPPORTED;
@@ -408,6 +432,12 @@ static int filter_backward(const T* dy, const T* x, const T* off, const T* rot, 
 template <typename T>
 int local_backward_filter(const T* dy, const T* x, const T* rot, T* dw, const Geom& g, void* ws, size_t ws_bytes,
                           cudaStream_t s) {
+  if constexpr (std::is_same<T, __half>::value) {
+    if (mma_path_enabled()) {
+      const int rc = local_filter_mma(dy, x, rot, dw, g, ws, ws_bytes, s);
+      if (rc != DK_ERR_UNSUPPORTED) return rc;
+    }
+  }
   return filter_backward<T, false>(dy, x, nullptr, rot, dw, g, ws, ws_bytes, s);
 }
 template <typename T>

@@ -1,0 +1,579 @@
+// fp16 fast path of the local deformable kernel on the tensor cores.
+//
+// Zero-extended bilinear sampling of a bank equals a contraction with hat functions:
+//   B(W[c]; u, v) = sum_{a,b} W[c,a,b] * hat(u - a) * hat(v - b),   hat(t) = max(0, 1 - |t|)
+// (two of the hats per axis are non-zero, all vanish when u <= -1 or u >= scope: the
+// reference's validity rule, csrc/filter_sample_depthwise_cuda_kernel.cu:59).  The hat products
+// beta[(pixel, tap), cell] do not depend on the channel, which turns the three expensive parts
+// of the operator into small dense products over the 16 bank cells / 16 channels / 16 (pixel,
+// tap) pairs, each one mma.sync.m16n8k16 (fp16 in, fp32 accumulate):
+//   forward, grad-input   K[16 ch x 8 px]       = W[16 ch x 16 cells]  * beta^T[16 cells x 8 px]
+//                         y[c,p] += x[c,p+tap] * K[c,p]                     (1 FMA per pixel, tap, channel)
+//   grad-bank             dW[16 ch x 16 cells] += dK[16 ch x 16 (px,tap)] * beta[16 (px,tap) x 16 cells]
+//   grad-offsets          G^T[16 cells x 8 px] += W^T[16 cells x 16 ch]  * dK[16 ch x 8 px]
+//                         d(offset)[p,tap] = sum_cell G[p,tap,cell] * d(beta)/d(u or v)   (4 corners)
+// with dK[c,(p,tap)] = dy[c,p] * x[c,p+tap].  The SIMT formulation needs four gathered bank
+// values and five FMAs per (pixel, tap, channel) and is bound by instruction issue.
+//
+// Covers: fp16, 3x3 kernel, dilation 1, pad 1, stride 1 or 2 (equal in h and w), one rotation
+// group, at most 16 bank cells, channels a multiple of 16 (grad-input: stride 1 only).
+// Everything else stays on the SIMT kernels of dk_local.cu.
+#include "dk_mma_common.cuh"
+
+namespace dk {
+
+using namespace mma;
+
+namespace {
+
+// ================================================================== forward / grad-input
+struct ConvPlan {
+  int BH, CG, groups, warps, bands;
+  size_t smem;
+};
+
+template <int S, bool TRANSPOSED>
+__global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restrict__ src, const __half* __restrict__ rot,
+                                                          const __half* __restrict__ w, __half* __restrict__ dst, const Geom g,
+                                                          const ConvPlan pl) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int Hd = TRANSPOSED ? g.H : g.Ho, Wd = TRANSPOSED ? g.W : g.Wo;
+  const int Hs = TRANSPOSED ? g.Ho : g.H, Ws = TRANSPOSED ? g.Wo : g.W;
+  const int n = blockIdx.z;
+  const int c0 = blockIdx.y * pl.CG;
+  const int cnt = min(pl.CG, g.C - c0);
+  const int d_row0 = blockIdx.x * pl.BH;
+  const int RB = (TRANSPOSED ? pl.BH : (pl.BH - 1) * S + 1) + 2;
+  const Band bx = make_band(TRANSPOSED ? d_row0 - 1 : d_row0 * S - 1, RB, Hs, Ws);
+
+  __half* band = reinterpret_cast<__half*>(smem_raw);
+  __half* bank = band + pl.CG * bx.pitch_c;                                  // [CG][kBankPitch]
+  unsigned* tables = reinterpret_cast<unsigned*>(bank + pl.CG * kBankPitch);  // [warps][kBetaWords]
+
+  for (int i = threadIdx.x; i < cnt * 16; i += blockDim.x) {
+    const int j = i >> 4, cell = i & 15;
+    bank[j * kBankPitch + cell] = cell < g.cells ? __ldg(w + (size_t)(c0 + j) * g.cells + cell) : __float2half(0.f);
+  }
+  load_band(band, bx, src, n, g.C, c0, cnt, Hs, Ws);
+  __syncthreads();
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int gq = lane >> 2, q = lane & 3;
+  const int NB = (Wd + 7) >> 3;
+  const int items = pl.BH * NB;
+  unsigned* T = tables + warp * kBetaWords;
+  const __half* rot_n = rot + (size_t)n * 18 * g.P;
+  const bool dst_even = (Wd & 1) == 0;
+
+  for (int item = warp; item < items; item += nwarps) {
+    const int dr = item / NB;
+    const int drow = d_row0 + dr;
+    if (drow >= Hd) break;
+    const int ow0 = (item - dr * NB) << 3;
+    unsigned bf[9][2];
+    build_beta<S, TRANSPOSED, false>(bf, T, nullptr, rot_n, g, drow, ow0, Hs, Ws, Wd, lane);
+
+    const int ow = ow0 + 2 * q;
+    const int wbase = window_offset(bx, TRANSPOSED ? drow - 1 : drow * S - 1, ow, S);
+    for (int cb16 = 0; cb16 < cnt; cb16 += 16) {
+      unsigned a[4];
+      {
+        const unsigned* bk0 = reinterpret_cast<const unsigned*>(bank + (cb16 + gq) * kBankPitch);
+        const unsigned* bk1 = reinterpret_cast<const unsigned*>(bank + (cb16 + gq + 8) * kBankPitch);
+        a[0] = bk0[q];
+        a[1] = bk1[q];
+        a[2] = bk0[q + 4];
+        a[3] = bk1[q + 4];
+      }
+      const __half* x0 = band + (size_t)(cb16 + gq) * bx.pitch_c + wbase;
+      const __half* x1 = x0 + (size_t)8 * bx.pitch_c;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int fh = 0; fh < 3; ++fh) {
+        const int rsel = TRANSPOSED ? 2 - fh : fh;
+        const unsigned* p0 = reinterpret_cast<const unsigned*>(x0 + rsel * bx.Wp);
+        const unsigned* p1 = reinterpret_cast<const unsigned*>(x1 + rsel * bx.Wp);
+        const unsigned w0 = p0[0], w1 = p0[1], w2 = p0[2];
+        const unsigned v0 = p1[0], v1 = p1[1], v2 = p1[2];
+        float f0[6], f1[6];  // halves 1..5 of the window [ow*S-2, ow*S+3]
+        f0[1] = hi2f(w0); f0[2] = lo2f(w1); f0[3] = hi2f(w1); f0[4] = lo2f(w2); f0[5] = hi2f(w2);
+        f1[1] = hi2f(v0); f1[2] = lo2f(v1); f1[3] = hi2f(v1); f1[4] = lo2f(v2); f1[5] = hi2f(v2);
+#pragma unroll
+        for (int fw = 0; fw < 3; ++fw) {
+          float d[4];
+          mma16816(d, a, bf[fh * 3 + fw][0], bf[fh * 3 + fw][1]);
+          const int csel = TRANSPOSED ? 2 - fw : fw;
+          acc[0] += f0[1 + csel] * d[0];
+          acc[1] += f0[1 + S + csel] * d[1];
+          acc[2] += f1[1 + csel] * d[2];
+          acc[3] += f1[1 + S + csel] * d[3];
+        }
+      }
+      if (ow < Wd) {
+        __half* y0 = dst + (((size_t)n * g.C + c0 + cb16 + gq) * Hd + drow) * Wd + ow;
+        __half* y1 = y0 + (size_t)8 * Hd * Wd;
+        if (dst_even) {
+          *reinterpret_cast<__half2*>(y0) = __floats2half2_rn(acc[0], acc[1]);
+          *reinterpret_cast<__half2*>(y1) = __floats2half2_rn(acc[2], acc[3]);
+        } else {
+          y0[0] = __float2half_rn(acc[0]);
+          y1[0] = __float2half_rn(acc[2]);
+          if (ow + 1 < Wd) {
+            y0[1] = __float2half_rn(acc[1]);
+            y1[1] = __float2half_rn(acc[3]);
+          }
+        }
+      }
+    }
+  }
+}
+
+// shared memory per block that still lets two blocks share an SM (228 KB per SM, 1 KB reserved per block)
+constexpr size_t kTwoPerSm = 113 * 1024;
+constexpr size_t kOnePerSm = 226 * 1024;
+
+bool fast_shape(const Geom& g) {
+  if (g.kH != 3 || g.kW != 3 || g.dH != 1 || g.dW != 1 || g.pH != 1 || g.pW != 1) return false;
+  if (g.sH != g.sW || (g.sH != 1 && g.sH != 2)) return false;
+  if (g.G != 1 || g.cells > 16 || (g.C & 15) || g.N > 65535) return false;
+  return true;
+}
+
+int pick_warps(int items, int maxw) {
+  if (items <= 2) return 2;
+  if (items < 4) return items;
+  int bw = maxw, bwaste = 1 << 30;
+  for (int wv = maxw; wv >= 4; --wv) {
+    const int waste = ((items + wv - 1) / wv) * wv - items;
+    if (waste < bwaste) { bwaste = waste; bw = wv; }
+  }
+  return bw;
+}
+
+ConvPlan conv_plan(const Geom& g, bool transposed) {
+  ConvPlan pl;
+  const int S = g.sH;
+  const int Hd = transposed ? g.H : g.Ho, Wd = transposed ? g.W : g.Wo;
+  const int Ws = transposed ? g.Wo : g.W;
+  const int Wp = Ws + (Ws & 1);
+  const int ngrp = (g.C + 127) / 128;
+  pl.CG = (((g.C + ngrp - 1) / ngrp) + 15) & ~15;
+  pl.groups = (g.C + pl.CG - 1) / pl.CG;
+  const int NB = (Wd + 7) / 8;
+  const size_t budget = kTwoPerSm;
+  int best = 1;
+  for (int bh = 1; bh <= Hd; ++bh) {
+    const int rb = (transposed ? bh : (bh - 1) * S + 1) + 2;
+    const size_t smem = (size_t)pl.CG * band_pitch(rb, Wp) * 2 + (size_t)pl.CG * kBankPitch * 2 +
+                        (size_t)pick_warps(bh * NB, 8) * kBetaWords * 4;
+    if (smem > budget) break;
+    const long long ctas = (long long)((Hd + bh - 1) / bh) * pl.groups * g.N;
+    if (bh > 1 && ctas < 2 * 148) break;
+    best = bh;
+    if (bh * NB >= 32) break;
+  }
+  pl.BH = best;
+  pl.bands = (Hd + pl.BH - 1) / pl.BH;
+  pl.warps = pick_warps(pl.BH * NB, 8);
+  const int rb = (transposed ? pl.BH : (pl.BH - 1) * S + 1) + 2;
+  pl.smem = (size_t)pl.CG * band_pitch(rb, Wp) * 2 + (size_t)pl.CG * kBankPitch * 2 + (size_t)pl.warps * kBetaWords * 4;
+  return pl;
+}
+
+template <int S, bool TRANSPOSED>
+int launch_conv(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, cudaStream_t s) {
+  const ConvPlan pl = conv_plan(g, TRANSPOSED);
+  if (pl.smem > (size_t)device_smem_optin() || pl.groups > 65535) return DK_ERR_UNSUPPORTED;
+  auto kern = mma_conv_kernel<S, TRANSPOSED>;
+  int rc = enable_smem(kern, pl.smem);
+  if (rc) return rc;
+  kern<<<dim3(pl.bands, pl.groups, g.N), pl.warps * 32, pl.smem, s>>>(src, rot, w, dst, g, pl);
+  return check_launch();
+}
+
+// ================================================================== grad-offsets and grad-bank
+// Shared by both kernels: the products dK[c, (pixel pair, tap)] = dy[c, pixel pair] * x[c, pixel pair + tap]
+// of the two channels (gq, gq+8 of a 16-channel slab) this thread holds in A fragments.
+template <int S>
+__device__ __forceinline__ void dk_products(unsigned (&dk0)[9], unsigned (&dk1)[9], const __half* __restrict__ x0, int xpitch8,
+                                            int Wp, unsigned dy0, unsigned dy1) {
+  const __half* x1 = x0 + xpitch8;
+#pragma unroll
+  for (int fh = 0; fh < 3; ++fh) {
+    const unsigned* p0 = reinterpret_cast<const unsigned*>(x0 + fh * Wp);
+    const unsigned* p1 = reinterpret_cast<const unsigned*>(x1 + fh * Wp);
+    const unsigned w0 = p0[0], w1 = p0[1], w2 = p0[2];
+    const unsigned v0 = p1[0], v1 = p1[1], v2 = p1[2];
+#pragma unroll
+    for (int fw = 0; fw < 3; ++fw) {
+      dk0[fh * 3 + fw] = hmul2u(dy0, tap_pair<S>(w0, w1, w2, fw));
+      dk1[fh * 3 + fw] = hmul2u(dy1, tap_pair<S>(v0, v1, v2, fw));
+    }
+  }
+}
+
+struct RotPlan {
+  int BH, warps, bands;
+  bool big;  // one block of up to 16 warps per SM instead of two of up to 8
+  size_t smem;
+};
+constexpr int kRotScratch = kBetaWords * 4 + 72 * 8;  // beta table (reused for G, 3 taps at a time) + (u, v)
+
+template <int S, int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB) mma_rot_kernel(const __half* __restrict__ dy, const __half* __restrict__ x,
+                                                         const __half* __restrict__ rot, const __half* __restrict__ w,
+                                                         __half* __restrict__ drot, const Geom g, const RotPlan pl) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int n = blockIdx.y;
+  const int oh0 = blockIdx.x * pl.BH;
+  const Band bx = make_band(oh0 * S - 1, (pl.BH - 1) * S + 3, g.H, g.W);
+  const Band by = make_band(oh0, pl.BH, g.Ho, g.Wo);
+  const int pitchT = g.C + 8;  // halves per cell row of the transposed bank
+
+  __half* xband = reinterpret_cast<__half*>(smem_raw);
+  __half* yband = xband + (size_t)g.C * bx.pitch_c;
+  __half* bankT = yband + (size_t)g.C * by.pitch_c;                       // [16 cells][C + 8]
+  unsigned char* scratch = reinterpret_cast<unsigned char*>(bankT + 16 * pitchT);
+
+  for (int i = threadIdx.x; i < 16 * g.C; i += blockDim.x) {
+    const int cell = i / g.C, c = i - cell * g.C;
+    bankT[cell * pitchT + c] = cell < g.cells ? __ldg(w + (size_t)c * g.cells + cell) : __float2half(0.f);
+  }
+  load_band(xband, bx, x, n, g.C, 0, g.C, g.H, g.W);
+  load_band(yband, by, dy, n, g.C, 0, g.C, g.Ho, g.Wo);
+  __syncthreads();
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int gq = lane >> 2, q = lane & 3;
+  const int NB = (g.Wo + 7) >> 3;
+  const int items = pl.BH * NB;
+  unsigned* T = reinterpret_cast<unsigned*>(scratch + (size_t)warp * kRotScratch);
+  float* Gs = reinterpret_cast<float*>(T);                       // [3 taps][16 cells][8 px], after the fragments are read
+  float2* uv = reinterpret_cast<float2*>(T + kBetaWords);        // [9 taps][8 px]
+  const __half* rot_n = rot + (size_t)n * 18 * g.P;
+  __half* drot_n = drot + (size_t)n * 18 * g.P;
+
+  for (int item = warp; item < items; item += nwarps) {
+    const int dr = item / NB;
+    const int oh = oh0 + dr;
+    if (oh >= g.Ho) break;
+    const int ow0 = (item - dr * NB) << 3;
+    {
+      unsigned bf[9][2];  // not needed here: only (u, v) is kept
+      build_beta<S, false, true>(bf, T, uv, rot_n, g, oh, ow0, g.H, g.W, g.Wo, lane);
+    }
+    const int ow = ow0 + 2 * q;
+    const int xoff = window_offset(bx, oh * S - 1, ow, S);
+    const int yoff = kSlack + oh * by.Wp + ow - by.org;
+
+    float G[9][4];
+#pragma unroll
+    for (int t = 0; t < 9; ++t) G[t][0] = G[t][1] = G[t][2] = G[t][3] = 0.f;
+
+    for (int cb16 = 0; cb16 < g.C; cb16 += 16) {
+      const unsigned dy0 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq) * by.pitch_c + yoff);
+      const unsigned dy1 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq + 8) * by.pitch_c + yoff);
+      unsigned dk0[9], dk1[9];
+      dk_products<S>(dk0, dk1, xband + (size_t)(cb16 + gq) * bx.pitch_c + xoff, 8 * bx.pitch_c, bx.Wp, dy0, dy1);
+      // A = W^T slab: rows = cells (gq, gq+8), k = channels (2q,2q+1) and (2q+8,2q+9)
+      const unsigned* wt0 = reinterpret_cast<const unsigned*>(bankT + gq * pitchT + cb16);
+      const unsigned* wt1 = reinterpret_cast<const unsigned*>(bankT + (gq + 8) * pitchT + cb16);
+      const unsigned a0 = wt0[q], a1 = wt1[q], a2 = wt0[q + 4], a3 = wt1[q + 4];
+#pragma unroll
+      for (int t = 0; t < 9; ++t) mma16816_acc(G[t], a0, a1, a2, a3, movmatrix_trans(dk0[t]), movmatrix_trans(dk1[t]));
+    }
+
+    // d(offset)[pixel, tap, dir] = sum over the four corner cells of G * d(coefficient)/d(u or v)
+#pragma unroll
+    for (int pass = 0; pass < 3; ++pass) {
+      __syncwarp();
+#pragma unroll
+      for (int tt = 0; tt < 3; ++tt) {
+        const int t = pass * 3 + tt;
+        *reinterpret_cast<float2*>(Gs + (tt * 16 + gq) * 8 + 2 * q) = make_float2(G[t][0], G[t][1]);
+        *reinterpret_cast<float2*>(Gs + (tt * 16 + gq + 8) * 8 + 2 * q) = make_float2(G[t][2], G[t][3]);
+      }
+      __syncwarp();
+      if (lane < 24) {
+        const int px = lane & 7, tt = lane >> 3;
+        const int t = pass * 3 + tt;
+        const float2 c = uv[t * 8 + px];
+        float gu = 0.f, gv = 0.f;
+        if (c.x < 1e29f) {
+          const float fu = floorf(c.x), fv = floorf(c.y);
+          const int h0 = (int)fu, w0 = (int)fv;
+          const float lh = c.x - fu, lw = c.y - fv;
+          const float hh = 1.f - lh, hw = 1.f - lw;
+          const float* Gp = Gs + tt * 128 + px;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int a = h0 + (k >> 1), b = w0 + (k & 1);
+            if (a >= 0 && a < g.scH && b >= 0 && b < g.scW) {
+              const float gval = Gp[(a * g.scW + b) * 8];
+              const float du = (k >> 1) ? ((k & 1) ? lw : hw) : ((k & 1) ? -lw : -hw);
+              const float dv = (k & 1) ? ((k >> 1) ? lh : hh) : ((k >> 1) ? -lh : -hh);
+              gu += du * gval;
+              gv += dv * gval;
+            }
+          }
+        }
+        if (ow0 + px < g.Wo) {
+          __half* o = drot_n + (size_t)(2 * t) * g.P + oh * g.Wo + ow0 + px;
+          o[0] = __float2half_rn(gu);
+          o[g.P] = __float2half_rn(gv);
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// Two blocks of at most 8 warps per SM when the bands of ALL channels fit twice, else one block
+// of up to 16 warps per SM.
+RotPlan rot_plan(const Geom& g) {
+  RotPlan pl;
+  const int S = g.sH;
+  const int NB = (g.Wo + 7) / 8;
+  const int Wp = g.W + (g.W & 1), Wpo = g.Wo + (g.Wo & 1);
+  pl.BH = 0;
+  pl.big = false;
+  for (int attempt = 0; attempt < 2 && !pl.BH; ++attempt) {
+    const size_t budget = attempt == 0 ? kTwoPerSm : kOnePerSm;
+    const int maxw = attempt == 0 ? 8 : 16;
+    for (int bh = 1; bh <= g.Ho; ++bh) {
+      const int warps = pick_warps(bh * NB, maxw);
+      const size_t smem = (size_t)g.C * (band_pitch((bh - 1) * S + 3, Wp) + band_pitch(bh, Wpo)) * 2 +
+                          (size_t)16 * (g.C + 8) * 2 + (size_t)warps * kRotScratch;
+      if (smem > budget) break;
+      const long long ctas = (long long)((g.Ho + bh - 1) / bh) * g.N;
+      if (bh > 1 && ctas < 2 * 148) break;
+      pl.BH = bh;
+      pl.warps = warps;
+      pl.smem = smem;
+      pl.big = attempt == 1;
+      if (bh * NB >= 2 * maxw) break;
+    }
+  }
+  if (pl.BH) pl.bands = (g.Ho + pl.BH - 1) / pl.BH;
+  return pl;
+}
+
+// ------------------------------------------------------------------ grad-bank
+struct FiltPlan {
+  int BH, CG, groups, warps, bands, units_per_block, blocks_x;
+  size_t smem, ws_bytes;
+};
+
+template <int S>
+__global__ void __launch_bounds__(256, 2) mma_filter_kernel(const __half* __restrict__ dy, const __half* __restrict__ x,
+                                                            const __half* __restrict__ rot, float* __restrict__ partial,
+                                                            const Geom g, const FiltPlan pl) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int c0 = blockIdx.y * pl.CG;
+  const int cnt = min(pl.CG, g.C - c0);
+  const int nslab = cnt >> 4;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int gq = lane >> 2, q = lane & 3;
+  const int NB = (g.Wo + 7) >> 3;
+  const int items = pl.BH * NB;
+  const int Wp = g.W + (g.W & 1), Wpo = g.Wo + (g.Wo & 1);
+  const int xpitch = band_pitch((pl.BH - 1) * S + 3, Wp), ypitch = band_pitch(pl.BH, Wpo);
+
+  __half* xband = reinterpret_cast<__half*>(smem_raw);
+  __half* yband = xband + (size_t)pl.CG * xpitch;
+  unsigned* tables = reinterpret_cast<unsigned*>(yband + (size_t)pl.CG * ypitch);
+  unsigned* T = tables + warp * kBetaWords;
+
+  float acc[4][2][4];  // up to 4 slabs of 16 channels x (cells 0-7 | cells 8-15)
+#pragma unroll
+  for (int sidx = 0; sidx < 4; ++sidx)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[sidx][0][k] = acc[sidx][1][k] = 0.f;
+
+  const int total_units = g.N * pl.bands;
+  const int u_begin = blockIdx.x * pl.units_per_block;
+  const int u_end = min(u_begin + pl.units_per_block, total_units);
+  for (int unit = u_begin; unit < u_end; ++unit) {
+    const int n = unit / pl.bands;
+    const int oh0 = (unit - n * pl.bands) * pl.BH;
+    const Band bx = make_band(oh0 * S - 1, (pl.BH - 1) * S + 3, g.H, g.W);
+    const Band by = make_band(oh0, pl.BH, g.Ho, g.Wo);
+    __syncthreads();  // previous unit's readers are done
+    load_band(xband, bx, x, n, g.C, c0, cnt, g.H, g.W);
+    load_band(yband, by, dy, n, g.C, c0, cnt, g.Ho, g.Wo);
+    __syncthreads();
+    const __half* rot_n = rot + (size_t)n * 18 * g.P;
+    for (int item = warp; item < items; item += nwarps) {
+      const int dr = item / NB;
+      const int oh = oh0 + dr;
+      if (oh >= g.Ho) break;
+      const int ow0 = (item - dr * NB) << 3;
+      unsigned bw[10][2];  // beta as B fragments of the grad-bank product: [tap][cells 0-7 | cells 8-15]
+      {
+        unsigned bf[9][2];
+        build_beta<S, false, false>(bf, T, nullptr, rot_n, g, oh, ow0, g.H, g.W, g.Wo, lane);
+#pragma unroll
+        for (int t = 0; t < 9; ++t) {
+          bw[t][0] = movmatrix_trans(bf[t][0]);
+          bw[t][1] = movmatrix_trans(bf[t][1]);
+        }
+        bw[9][0] = bw[9][1] = 0u;
+      }
+      const int ow = ow0 + 2 * q;
+      const int xoff = window_offset(bx, oh * S - 1, ow, S);
+      const int yoff = kSlack + oh * by.Wp + ow - by.org;
+#pragma unroll
+      for (int sidx = 0; sidx < 4; ++sidx) {
+        if (sidx < nslab) {
+          const int cb16 = sidx << 4;
+          const unsigned dy0 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq) * by.pitch_c + yoff);
+          const unsigned dy1 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq + 8) * by.pitch_c + yoff);
+          unsigned dk0[10], dk1[10];
+          {
+            unsigned a9[9], b9[9];
+            dk_products<S>(a9, b9, xband + (size_t)(cb16 + gq) * bx.pitch_c + xoff, 8 * bx.pitch_c, bx.Wp, dy0, dy1);
+#pragma unroll
+            for (int t = 0; t < 9; ++t) { dk0[t] = a9[t]; dk1[t] = b9[t]; }
+            dk0[9] = dk1[9] = 0u;
+          }
+#pragma unroll
+          for (int j = 0; j < 5; ++j) {  // k = 16 = 8 pixels x taps (2j, 2j+1)
+            mma16816_acc(acc[sidx][0], dk0[2 * j], dk1[2 * j], dk0[2 * j + 1], dk1[2 * j + 1], bw[2 * j][0],
+                         bw[2 * j + 1][0]);
+            mma16816_acc(acc[sidx][1], dk0[2 * j], dk1[2 * j], dk0[2 * j + 1], dk1[2 * j + 1], bw[2 * j][1],
+                         bw[2 * j + 1][1]);
+          }
+        }
+      }
+    }
+  }
+  // reduce the warps' accumulators and write this block's partial bank gradient [cnt][16]
+  __syncthreads();
+  float* red = reinterpret_cast<float*>(smem_raw);  // [nwarps][CG][16]
+#pragma unroll
+  for (int sidx = 0; sidx < 4; ++sidx) {
+    if (sidx < nslab) {
+      float* r0 = red + ((size_t)warp * pl.CG + (sidx << 4) + gq) * 16;
+      float* r1 = r0 + 8 * 16;
+      r0[2 * q] = acc[sidx][0][0]; r0[2 * q + 1] = acc[sidx][0][1];
+      r1[2 * q] = acc[sidx][0][2]; r1[2 * q + 1] = acc[sidx][0][3];
+      r0[8 + 2 * q] = acc[sidx][1][0]; r0[8 + 2 * q + 1] = acc[sidx][1][1];
+      r1[8 + 2 * q] = acc[sidx][1][2]; r1[8 + 2 * q + 1] = acc[sidx][1][3];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < cnt * 16; i += blockDim.x) {
+    float sum = 0.f;
+    for (int wv = 0; wv < nwarps; ++wv) sum += red[(size_t)wv * pl.CG * 16 + i];
+    partial[((size_t)blockIdx.x * g.C + c0) * 16 + i] = sum;
+  }
+}
+
+// out[c][cell] = sum over blocks of partial[block][c][16], fixed order
+__global__ void reduce_bank_partials_kernel(const float* __restrict__ partial, __half* __restrict__ out, int C, int cells,
+                                            int nblocks) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= C * cells) return;
+  const int c = i / cells, cell = i - c * cells;
+  float s = 0.f;
+  for (int k = 0; k < nblocks; ++k) s += partial[((size_t)k * C + c) * 16 + cell];
+  out[i] = __float2half_rn(s);
+}
+
+FiltPlan filt_plan(const Geom& g) {
+  FiltPlan pl;
+  const int S = g.sH;
+  pl.CG = (g.C % 64 == 0) ? 64 : (g.C % 48 == 0) ? 48 : (g.C % 32 == 0) ? 32 : 16;
+  pl.groups = g.C / pl.CG;
+  const int NB = (g.Wo + 7) / 8;
+  const int Wp = g.W + (g.W & 1), Wpo = g.Wo + (g.Wo & 1);
+  const size_t budget = kTwoPerSm;
+  pl.BH = 0;
+  for (int bh = 1; bh <= g.Ho; ++bh) {
+    const int warps = pick_warps(bh * NB, 8);
+    size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + band_pitch(bh, Wpo)) * 2 + (size_t)warps * kBetaWords * 4;
+    const size_t red = (size_t)warps * pl.CG * 16 * 4;
+    if (smem < red) smem = red;
+    if (smem > budget) break;
+    pl.BH = bh;
+    pl.warps = warps;
+    pl.smem = smem;
+    if (bh * NB >= 24) break;
+  }
+  if (!pl.BH) return pl;
+  pl.bands = (g.Ho + pl.BH - 1) / pl.BH;
+  const long long units = (long long)g.N * pl.bands;
+  long long want = (4LL * 148 + pl.groups - 1) / pl.groups;  // ~4 blocks per SM over the grid
+  if (want > units) want = units;
+  if (want < 1) want = 1;
+  pl.units_per_block = (int)((units + want - 1) / want);
+  pl.blocks_x = (int)((units + pl.units_per_block - 1) / pl.units_per_block);
+  pl.ws_bytes = (size_t)pl.blocks_x * g.C * 16 * sizeof(float);
+  return pl;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ entry points used by dk_local.cu
+// Each returns DK_ERR_UNSUPPORTED when the shape is outside the fast path.
+
+int local_conv_mma(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, bool transposed,
+                   cudaStream_t s) {
+  if (!fast_shape(g) || (transposed && g.sH != 1)) return DK_ERR_UNSUPPORTED;
+  if (transposed) return launch_conv<1, true>(src, rot, w, dst, g, s);
+  if (g.sH == 1) return launch_conv<1, false>(src, rot, w, dst, g, s);
+  return launch_conv<2, false>(src, rot, w, dst, g, s);
+}
+
+int local_rot_mma(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, const Geom& g,
+                  cudaStream_t s) {
+  if (!fast_shape(g)) return DK_ERR_UNSUPPORTED;
+  const RotPlan pl = rot_plan(g);
+  if (!pl.BH || pl.smem > (size_t)device_smem_optin()) return DK_ERR_UNSUPPORTED;
+  int rc;
+  const dim3 grid(pl.bands, g.N);
+#define DK_LAUNCH_ROT(SS, MAXT, MINB)                                                     \
+  {                                                                                       \
+    auto kern = mma_rot_kernel<SS, MAXT, MINB>;                                           \
+    if ((rc = enable_smem(kern, pl.smem))) return rc;                                     \
+    kern<<<grid, pl.warps * 32, pl.smem, s>>>(dy, x, rot, w, drot, g, pl);                \
+  }
+  if (g.sH == 1) {
+    if (pl.big) DK_LAUNCH_ROT(1, 512, 1) else DK_LAUNCH_ROT(1, 256, 2)
+  } else {
+    if (pl.big) DK_LAUNCH_ROT(2, 512, 1) else DK_LAUNCH_ROT(2, 256, 2)
+  }
+#undef DK_LAUNCH_ROT
+  return check_launch();
+}
+
+size_t local_filter_mma_workspace(const Geom& g) {
+  if (!fast_shape(g)) return 0;
+  const FiltPlan pl = filt_plan(g);
+  return pl.BH ? pl.ws_bytes : 0;
+}
+
+int local_filter_mma(const __half* dy, const __half* x, const __half* rot, __half* dw, const Geom& g, void* ws,
+                     size_t ws_bytes, cudaStream_t s) {
+  if (!fast_shape(g)) return DK_ERR_UNSUPPORTED;
+  const FiltPlan pl = filt_plan(g);
+  if (!pl.BH || pl.smem > (size_t)device_smem_optin() || pl.groups > 65535) return DK_ERR_UNSUPPORTED;
+  if (ws == nullptr || ws_bytes < pl.ws_bytes) return DK_ERR_WORKSPACE;
+  int rc;
+  float* partial = reinterpret_cast<float*>(ws);
+  if (g.sH == 1) {
+    auto kern = mma_filter_kernel<1>;
+    if ((rc = enable_smem(kern, pl.smem))) return rc;
+    kern<<<dim3(pl.blocks_x, pl.groups), pl.warps * 32, pl.smem, s>>>(dy, x, rot, partial, g, pl);
+  } else {
+    auto kern = mma_filter_kernel<2>;
+    if ((rc = enable_smem(kern, pl.smem))) return rc;
+    kern<<<dim3(pl.blocks_x, pl.groups), pl.warps * 32, pl.smem, s>>>(dy, x, rot, partial, g, pl);
+  }
+  if ((rc = check_launch())) return rc;
+  const int n_out = g.C * g.cells;
+  reduce_bank_partials_kernel<<<(n_out + 255) / 256, 256, 0, s>>>(partial, dw, g.C, g.cells, pl.blocks_x);
+  return check_launch();
+}
+
+}  // namespace dk

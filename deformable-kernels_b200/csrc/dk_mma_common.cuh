@@ -1,0 +1,221 @@
+// Building blocks of the fp16 tensor-core kernels (dk_local_mma.cu).
+//
+// Conventions.  lane = 4*gq + q (gq = lane >> 2 in 0..7, q = lane & 3).  An "item" is a block
+// of 8 horizontally adjacent destination pixels ow0 .. ow0+7 of one row; in accumulator
+// fragments a thread owns the pixel pair (ow0 + 2q, ow0 + 2q + 1), in B fragments of the
+// kernel GEMM it supplies pixel ow0 + gq.  A "band" is the set of source rows a block of
+// destination rows needs, kept in shared memory as fp16 in the global row layout.
+#pragma once
+
+#include "dk_common.cuh"
+
+namespace dk {
+namespace mma {
+
+constexpr int kSlack = 8;       // zeroed halves in front of each channel's band
+constexpr int kBankPitch = 24;  // halves per channel row of the bank copy (12 words: conflict-free A loads)
+constexpr int kBetaWords = 9 * 8 * 8;  // per-warp table: [tap][pixel][8 words of two cells], swizzled
+
+// d = a * b (+ c): m16n8k16, fp16 inputs, fp32 accumulate.
+__device__ __forceinline__ void mma16816(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ void mma16816_acc(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                             unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// transpose of an 8x8 block of 16-bit values held one row per 4 lanes (standard fragment layout)
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
+  unsigned d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+  return d;
+}
+
+__device__ __forceinline__ float lo2f(unsigned w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
+__device__ __forceinline__ float hi2f(unsigned w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
+__device__ __forceinline__ unsigned hmul2u(unsigned a, unsigned b) {
+  __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<unsigned*>(&r);
+}
+
+// The pair (source value of pixel 0, source value of pixel 1) for tap column fw, cut out of the
+// 6-half window [ow*S-2, ow*S+3] held in three words: halves 1+fw and 1+S+fw.
+template <int S>
+__device__ __forceinline__ unsigned tap_pair(unsigned w0, unsigned w1, unsigned w2, int fw) {
+  if (S == 1) {
+    if (fw == 0) return __byte_perm(w0, w1, 0x5432);  // (w0.hi, w1.lo)
+    if (fw == 1) return w1;
+    return __byte_perm(w1, w2, 0x5432);               // (w1.hi, w2.lo)
+  } else {
+    if (fw == 0) return __byte_perm(w0, w1, 0x7632);  // (w0.hi, w1.hi)
+    if (fw == 1) return __byte_perm(w1, w2, 0x5410);  // (w1.lo, w2.lo)
+    return __byte_perm(w1, w2, 0x7632);               // (w1.hi, w2.hi)
+  }
+}
+
+// ---------------------------------------------------------------- band loader
+struct Band {
+  int row_lo;   // first source row held
+  int RB;       // rows held
+  int Wp;       // row pitch in shared memory (halves, even)
+  int pitch_c;  // channel pitch (halves), = 8 (mod 16): conflict-free across the 8 channels of a fragment
+  int mode;     // 2 = 16-byte vectors, 1 = 4-byte pairs, 0 = scalars
+  int org;      // element (row, col) of local channel j sits at j*pitch_c + kSlack + row*Wp + col - org
+};
+
+__host__ __device__ inline int band_pitch(int RB, int Wp) {
+  const int need = RB * Wp + kSlack + 16;
+  int pitch = ((need + 7) & ~15) + 8;
+  if (pitch < need) pitch += 16;
+  return pitch;
+}
+__host__ __device__ inline int band_mode(int plane, int Ws) {
+  return ((plane & 7) == 0 && (Ws & 1) == 0) ? 2 : ((Ws & 1) == 0 ? 1 : 0);
+}
+__device__ __forceinline__ Band make_band(int row_lo, int RB, int Hs, int Ws) {
+  Band b;
+  b.row_lo = row_lo;
+  b.RB = RB;
+  b.Wp = Ws + (Ws & 1);
+  b.pitch_c = band_pitch(RB, b.Wp);
+  b.mode = band_mode(Hs * Ws, Ws);
+  b.org = (b.mode == 2) ? ((row_lo * Ws) & ~7) : row_lo * b.Wp;
+  return b;
+}
+
+// Zero `cnt` channel bands, then copy the in-range source rows [row_lo, row_lo+RB) of channels
+// c0 .. c0+cnt-1 of sample n.  Must be called by the whole block; ends with the data visible
+// to the calling thread only after the caller's __syncthreads().
+__device__ __forceinline__ void load_band(__half* __restrict__ band, const Band& b, const __half* __restrict__ src, int n, int C,
+                                          int c0, int cnt, int Hs, int Ws) {
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
+  {
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    uint4* b4 = reinterpret_cast<uint4*>(band);
+    const int nv = cnt * b.pitch_c / 8;
+    for (int i = tid; i < nv; i += nt) b4[i] = z;
+  }
+  __syncthreads();
+  const int r_s = max(b.row_lo, 0), r_e = min(b.row_lo + b.RB, Hs);
+  if (r_e <= r_s) return;
+  const size_t plane = (size_t)Hs * Ws;
+  const __half* s0 = src + ((size_t)n * C + c0) * plane;
+  if (b.mode == 2) {
+    const int gs = (r_s * Ws) & ~7, ge = min((r_e * Ws + 7) & ~7, (int)plane);
+    const int nvec = (ge - gs) >> 3;
+    for (int j = warp; j < cnt; j += nwarps) {
+      const uint4* sp = reinterpret_cast<const uint4*>(s0 + (size_t)j * plane + gs);
+      uint4* dp = reinterpret_cast<uint4*>(band + (size_t)j * b.pitch_c + kSlack + (gs - b.org));
+      for (int v = lane; v < nvec; v += 32) dp[v] = __ldg(sp + v);
+    }
+  } else if (b.mode == 1) {
+    const int per = (r_e - r_s) * Ws / 2;
+    for (int j = warp; j < cnt; j += nwarps) {
+      const unsigned* sp = reinterpret_cast<const unsigned*>(s0 + (size_t)j * plane + r_s * Ws);
+      unsigned* dp = reinterpret_cast<unsigned*>(band + (size_t)j * b.pitch_c + kSlack + (r_s * b.Wp - b.org));
+      for (int v = lane; v < per; v += 32) dp[v] = __ldg(sp + v);
+    }
+  } else {
+    for (int j = warp; j < cnt; j += nwarps) {
+      for (int r = r_s; r < r_e; ++r) {
+        const __half* sp = s0 + (size_t)j * plane + (size_t)r * Ws;
+        __half* dp = band + (size_t)j * b.pitch_c + kSlack + (r * b.Wp - b.org);
+        for (int v = lane; v < Ws; v += 32) dp[v] = __ldg(sp + v);
+      }
+    }
+  }
+}
+
+// Offset (in halves, even) of the window of pixel pair (ow, ow+1), row selector 0, inside a channel band.
+__device__ __forceinline__ int window_offset(const Band& b, int srow0, int ow, int S) {
+  return kSlack + srow0 * b.Wp + (ow * S - 2) - b.org;
+}
+
+// ---------------------------------------------------------------- hat-product (beta) fragments
+// For the 8 pixels of an item and the 9 taps: beta[(pixel, tap)][cell] = hat(u - a) * hat(v - b),
+// i.e. the four bilinear coefficients scattered into a row of 16 cells, zero when the tap is
+// unused (outside the image / the bank).  Built cooperatively by the warp -- one lane per
+// (pixel, tap), three rounds -- into a swizzled table, then read back as mma B fragments:
+//   bf[t][0] = cells (2q, 2q+1) of pixel gq, bf[t][1] = cells (2q+8, 2q+9) of pixel gq.
+// With KEEP_UV the bank coordinates are left in uv[tap*8 + pixel] (u = 1e30 marks an unused tap).
+template <int S, bool TRANSPOSED, bool KEEP_UV>
+__device__ __forceinline__ void build_beta(unsigned (&bf)[9][2], unsigned* __restrict__ T, float2* __restrict__ uv,
+                                           const __half* __restrict__ rot_n, const Geom& g, int drow, int ow0, int Hs, int Ws,
+                                           int Wd, int lane) {
+  {
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    uint4* t4 = reinterpret_cast<uint4*>(T);
+#pragma unroll
+    for (int i = 0; i < (kBetaWords / 4 + 31) / 32; ++i) {
+      const int k = i * 32 + lane;
+      if (k < kBetaWords / 4) t4[k] = z;
+    }
+  }
+  __syncwarp();
+  const float uh0 = (float)(g.scH - 3) * 0.5f, uw0 = (float)(g.scW - 3) * 0.5f;
+  __half* Th = reinterpret_cast<__half*>(T);
+#pragma unroll
+  for (int r = 0; r < 3; ++r) {
+    const int idx = r * 32 + lane;
+    if (idx < 72) {
+      const int px = idx & 7, t = idx >> 3;
+      const int fh = t / 3, fw = t - fh * 3;
+      const int pc = ow0 + px;
+      int orow, ocol;
+      bool ok;
+      if (!TRANSPOSED) {
+        const int sr = drow * S - 1 + fh, sc = pc * S - 1 + fw;
+        ok = pc < Wd && sr >= 0 && sr < Hs && sc >= 0 && sc < Ws;
+        orow = drow;
+        ocol = pc;
+      } else {
+        orow = drow + 1 - fh;
+        ocol = pc + 1 - fw;
+        ok = pc < Wd && orow >= 0 && orow < Hs && ocol >= 0 && ocol < Ws;
+      }
+      const int off = ok ? orow * g.Wo + ocol : 0;
+      const __half* rp = rot_n + (size_t)(2 * t) * g.P + off;
+      const float u = ((float)fh + __half2float(__ldg(rp))) + uh0;
+      const float v = ((float)fw + __half2float(__ldg(rp + g.P))) + uw0;
+      const bool valid = ok && u > -1.f && v > -1.f && u < (float)g.scH && v < (float)g.scW;
+      if (KEEP_UV) uv[idx] = make_float2(valid ? u : 1e30f, v);
+      if (valid) {
+        const float fu = floorf(u), fv = floorf(v);
+        const int h0 = (int)fu, w0 = (int)fv;
+        const float lh = u - fu, lw = v - fv;
+        const int sw = (px >> 2) << 2;
+        __half* row = Th + (t * 8 + px) * 16;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int a = h0 + (k >> 1), b = w0 + (k & 1);
+          if (a >= 0 && a < g.scH && b >= 0 && b < g.scW) {
+            const int cell = a * g.scW + b;
+            const float coef = ((k >> 1) ? lh : 1.f - lh) * ((k & 1) ? lw : 1.f - lw);
+            row[(((cell >> 1) ^ sw) << 1) + (cell & 1)] = __float2half_rn(coef);
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  {
+    const int gq = lane >> 2, q = lane & 3;
+    const int sw = (gq >> 2) << 2;
+#pragma unroll
+    for (int t = 0; t < 9; ++t) {
+      bf[t][0] = T[(t * 8 + gq) * 8 + (q ^ sw)];
+      bf[t][1] = T[(t * 8 + gq) * 8 + ((q + 4) ^ sw)];
+    }
+  }
+  __syncwarp();
+}
+
+}  // namespace mma
+}  // namespace dk
