@@ -151,13 +151,25 @@ int dk_sample_depthwise_backward_filter(const void* grad_output, const void* inp
                                               workspace, workspace_bytes, (cudaStream_t)stream))
 }
 
+size_t dk_sample_depthwise_backward_rotation_workspace_bytes(const dk_geom* g, int dtype) {
+  Geom gg;
+  if (!make_geom(g, &gg) || !dtype_ok(dtype)) return 0;
+  return dtype == DK_F16 ? align256(local_rot_mma_workspace(gg)) : 0;
+}
+
 int dk_sample_depthwise_backward_rotation(const void* grad_output, const void* input, const void* rotation,
                                           const void* filter, void* grad_rotation, const dk_geom* g, int dtype,
-                                          void* stream) {
+                                          void* workspace, size_t workspace_bytes, void* stream) {
   Geom gg;
   if (!grad_output || !input || !rotation || !filter || !grad_rotation || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
   DK_DISPATCH(dtype, local_backward_rotation<T>(P_(T, grad_output), P_(T, input), P_(T, rotation), P_(T, filter),
-                                                M_(T, grad_rotation), gg, (cudaStream_t)stream))
+                                                M_(T, grad_rotation), gg, workspace, workspace_bytes, (cudaStream_t)stream))
+}
+
+size_t dk_sample_depthwise_backward_workspace_bytes(const dk_geom* g, int dtype) {
+  const size_t a = dk_sample_depthwise_backward_filter_workspace_bytes(g, dtype);
+  const size_t b = dk_sample_depthwise_backward_rotation_workspace_bytes(g, dtype);
+  return a > b ? a : b;  // the two passes run one after the other on the stream and share the buffer
 }
 
 int dk_sample_depthwise_backward(const void* grad_output, const void* input, const void* rotation, const void* filter,
@@ -170,7 +182,8 @@ int dk_sample_depthwise_backward(const void* grad_output, const void* input, con
     if (rc) return rc;
   }
   if (grad_rotation) {
-    rc = dk_sample_depthwise_backward_rotation(grad_output, input, rotation, filter, grad_rotation, g, dtype, stream);
+    rc = dk_sample_depthwise_backward_rotation(grad_output, input, rotation, filter, grad_rotation, g, dtype, workspace,
+                                               workspace_bytes, stream);
     if (rc) return rc;
   }
   if (grad_filter) {

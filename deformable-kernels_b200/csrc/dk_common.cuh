@@ -153,7 +153,8 @@ inline int enable_smem(K kernel, size_t bytes) {
 // typed launchers implemented in dk_local.cu / dk_deform.cu / dk_nd.cu
 template <typename T> int local_forward(const T*, const T*, const T*, T*, const Geom&, cudaStream_t);
 template <typename T> int local_backward_data(const T*, const T*, const T*, T*, const Geom&, cudaStream_t);
-template <typename T> int local_backward_rotation(const T*, const T*, const T*, const T*, T*, const Geom&, cudaStream_t);
+template <typename T>
+int local_backward_rotation(const T*, const T*, const T*, const T*, T*, const Geom&, void* ws, size_t ws_bytes, cudaStream_t);
 template <typename T>
 int local_backward_filter(const T* dy, const T* x, const T* rot, T* dw, const Geom&, void* ws, size_t ws_bytes, cudaStream_t);
 
@@ -172,8 +173,9 @@ int deform_backward_filter(const T* dy, const T* x, const T* off, const T* rot, 
 bool mma_path_enabled();
 int local_conv_mma(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, bool transposed,
                    cudaStream_t s);
+size_t local_rot_mma_workspace(const Geom& g);
 int local_rot_mma(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, const Geom& g,
-                  cudaStream_t s);
+                  void* ws, size_t ws_bytes, cudaStream_t s);
 size_t local_filter_mma_workspace(const Geom& g);
 int local_filter_mma(const __half* dy, const __half* x, const __half* rot, __half* dw, const Geom& g, void* ws,
                      size_t ws_bytes, cudaStream_t s);

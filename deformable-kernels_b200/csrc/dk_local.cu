@@ -227,11 +227,12 @@ __global__ void __launch_bounds__(32 * NW) local_rot_kernel(const T* __restrict_
 }
 
 template <typename T>
-int local_backward_rotation(const T* dy, const T* x, const T* rot, const T* w, T* drot, const Geom& g, cudaStream_t s) {
+int local_backward_rotation(const T* dy, const T* x, const T* rot, const T* w, T* drot, const Geom& g, void* ws,
+                            size_t ws_bytes, cudaStream_t s) {
   using A = typename Compute<T>::type;
   if constexpr (std::is_same<T, __half>::value) {
     if (mma_path_enabled()) {
-      const int rc = local_rot_mma(dy, x, rot, w, drot, g, s);
+      const int rc = local_rot_mma(dy, x, rot, w, drot, g, ws, ws_bytes, s);
       if (rc != DK_ERR_UNSUPPORTED) return rc;
     }
   }
@@ -449,7 +450,8 @@ int deform_backward_filter(const T* dy, const T* x, const T* off, const T* rot, 
 #define DK_INSTANTIATE_LOCAL(T)                                                                                  \
   template int local_forward<T>(const T*, const T*, const T*, T*, const Geom&, cudaStream_t);                     \
   template int local_backward_data<T>(const T*, const T*, const T*, T*, const Geom&, cudaStream_t);               \
-  template int local_backward_rotation<T>(const T*, const T*, const T*, const T*, T*, const Geom&, cudaStream_t); \
+  template int local_backward_rotation<T>(const T*, const T*, const T*, const T*, T*, const Geom&, void*, size_t, \
+                                          cudaStream_t);                                                           \
   template int local_backward_filter<T>(const T*, const T*, const T*, T*, const Geom&, void*, size_t, cudaStream_t); \
   template int deform_backward_filter<T>(const T*, const T*, const T*, const T*, T*, const Geom&, void*, size_t,      \
                                          cudaStream_t);

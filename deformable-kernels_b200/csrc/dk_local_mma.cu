@@ -16,7 +16,7 @@
 // values and five FMAs per (pixel, tap, channel) and is bound by instruction issue.
 //
 // Covers: fp16, 3x3 kernel, dilation 1, pad 1, stride 1 or 2 (equal in h and w), one rotation
-// group, at most 16 bank cells, channels a multiple of 16 (grad-input: stride 1 only).
+// group, at most 16 bank cells, channels a multiple of 16.
 // Everything else stays on the SIMT kernels of dk_local.cu.
 #include "dk_mma_common.cuh"
 
@@ -29,8 +29,16 @@ namespace {
 // ================================================================== forward / grad-input
 struct ConvPlan {
   int BH, CG, groups, warps, bands;
+  int mode_src, mode_rot;  // copy widths the base pointers allow
+  bool pair_store;         // destination rows are even and the pointer is 4-byte aligned
   size_t smem;
 };
+
+// source rows a band of BH destination rows needs
+__host__ __device__ inline int conv_band_rows(int bh, int S, bool transposed) {
+  if (!transposed) return (bh - 1) * S + 3;
+  return S == 1 ? bh + 2 : (bh >> 1) + 2;
+}
 
 template <int S, bool TRANSPOSED>
 __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restrict__ src, const __half* __restrict__ rot,
@@ -43,11 +51,16 @@ __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restri
   const int c0 = blockIdx.y * pl.CG;
   const int cnt = min(pl.CG, g.C - c0);
   const int d_row0 = blockIdx.x * pl.BH;
-  const int RB = (TRANSPOSED ? pl.BH : (pl.BH - 1) * S + 1) + 2;
-  const Band bx = make_band(TRANSPOSED ? d_row0 - 1 : d_row0 * S - 1, RB, Hs, Ws);
+  const int RB = conv_band_rows(pl.BH, S, TRANSPOSED);
+  const int src_row_lo = TRANSPOSED ? (S == 1 ? d_row0 - 1 : d_row0 >> 1) : d_row0 * S - 1;
+  const Band bx = make_band(src_row_lo, RB, Hs, Ws, pl.mode_src);
+  // offset planes: the rows of the output pixels whose offsets drive the band's taps
+  const Band br = TRANSPOSED ? make_band(src_row_lo, RB, g.Ho, g.Wo, pl.mode_rot)
+                             : make_band(d_row0, pl.BH, g.Ho, g.Wo, pl.mode_rot);
 
   __half* band = reinterpret_cast<__half*>(smem_raw);
-  __half* bank = band + pl.CG * bx.pitch_c;                                  // [CG][kBankPitch]
+  __half* rband = band + pl.CG * bx.pitch_c;                                 // [18][br.pitch_c]
+  __half* bank = rband + 18 * br.pitch_c;                                    // [CG][kBankPitch]
   unsigned* tables = reinterpret_cast<unsigned*>(bank + pl.CG * kBankPitch);  // [warps][kBetaWords]
 
   for (int i = threadIdx.x; i < cnt * 16; i += blockDim.x) {
@@ -55,6 +68,8 @@ __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restri
     bank[j * kBankPitch + cell] = cell < g.cells ? __ldg(w + (size_t)(c0 + j) * g.cells + cell) : __float2half(0.f);
   }
   load_band(band, bx, src, n, g.C, c0, cnt, Hs, Ws);
+  load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
+  cp_async_wait_all();
   __syncthreads();
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -62,8 +77,7 @@ __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restri
   const int NB = (Wd + 7) >> 3;
   const int items = pl.BH * NB;
   unsigned* T = tables + warp * kBetaWords;
-  const __half* rot_n = rot + (size_t)n * 18 * g.P;
-  const bool dst_even = (Wd & 1) == 0;
+  const bool dst_even = pl.pair_store;
 
   for (int item = warp; item < items; item += nwarps) {
     const int dr = item / NB;
@@ -71,10 +85,14 @@ __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restri
     if (drow >= Hd) break;
     const int ow0 = (item - dr * NB) << 3;
     unsigned bf[9][2];
-    build_beta<S, TRANSPOSED, false>(bf, T, nullptr, rot_n, g, drow, ow0, Hs, Ws, Wd, lane);
+    build_beta<S, TRANSPOSED, false>(bf, T, nullptr, rband, br, g, drow, ow0, Hs, Ws, Wd, lane);
 
     const int ow = ow0 + 2 * q;
-    const int wbase = window_offset(bx, TRANSPOSED ? drow - 1 : drow * S - 1, ow, S);
+    // TRANSPOSED with stride 2: pixel 0 (even column) takes tap column 1 from grad-output column ow/2,
+    // pixel 1 takes tap columns 0 and 2 from columns ow/2 + 1 and ow/2; only tap rows of matching parity count.
+    const int j0 = ow >> 1;
+    const int wbase = (TRANSPOSED && S == 2) ? kSlack + (j0 & ~1) - bx.org
+                                             : window_offset(bx, TRANSPOSED ? drow - 1 : drow * S - 1, ow, S);
     for (int cb16 = 0; cb16 < cnt; cb16 += 16) {
       unsigned a[4];
       {
@@ -88,6 +106,30 @@ __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restri
       const __half* x0 = band + (size_t)(cb16 + gq) * bx.pitch_c + wbase;
       const __half* x1 = x0 + (size_t)8 * bx.pitch_c;
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (TRANSPOSED && S == 2) {
+#pragma unroll
+        for (int fh = 0; fh < 3; ++fh) {
+          const int tr = drow + 1 - fh;
+          if (tr < 0 || (tr & 1)) continue;  // uniform over the warp
+          const int orow = tr >> 1;
+          const unsigned* p0 = reinterpret_cast<const unsigned*>(x0 + orow * bx.Wp);
+          const unsigned* p1 = reinterpret_cast<const unsigned*>(x1 + orow * bx.Wp);
+          const unsigned w0 = p0[0], w1 = p0[1], v0 = p1[0], v1 = p1[1];
+          const bool odd = j0 & 1;
+          const float a0 = odd ? hi2f(w0) : lo2f(w0), b0 = odd ? lo2f(w1) : hi2f(w0);  // dy[j0], dy[j0 + 1]
+          const float a1 = odd ? hi2f(v0) : lo2f(v0), b1 = odd ? lo2f(v1) : hi2f(v0);
+          float d[4];
+          mma16816(d, a, bf[fh * 3 + 0][0], bf[fh * 3 + 0][1]);
+          acc[1] += b0 * d[1];
+          acc[3] += b1 * d[3];
+          mma16816(d, a, bf[fh * 3 + 1][0], bf[fh * 3 + 1][1]);
+          acc[0] += a0 * d[0];
+          acc[2] += a1 * d[2];
+          mma16816(d, a, bf[fh * 3 + 2][0], bf[fh * 3 + 2][1]);
+          acc[1] += a0 * d[1];
+          acc[3] += a1 * d[3];
+        }
+      } else {
 #pragma unroll
       for (int fh = 0; fh < 3; ++fh) {
         const int rsel = TRANSPOSED ? 2 - fh : fh;
@@ -108,6 +150,7 @@ __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restri
           acc[2] += f1[1 + csel] * d[2];
           acc[3] += f1[1 + S + csel] * d[3];
         }
+      }
       }
       if (ow < Wd) {
         __half* y0 = dst + (((size_t)n * g.C + c0 + cb16 + gq) * Hd + drow) * Wd + ow;
@@ -155,7 +198,7 @@ ConvPlan conv_plan(const Geom& g, bool transposed) {
   const int S = g.sH;
   const int Hd = transposed ? g.H : g.Ho, Wd = transposed ? g.W : g.Wo;
   const int Ws = transposed ? g.Wo : g.W;
-  const int Wp = Ws + (Ws & 1);
+  const int Wp = Ws + (Ws & 1), Wpo = g.Wo + (g.Wo & 1);
   const int ngrp = (g.C + 127) / 128;
   pl.CG = (((g.C + ngrp - 1) / ngrp) + 15) & ~15;
   pl.groups = (g.C + pl.CG - 1) / pl.CG;
@@ -163,9 +206,9 @@ ConvPlan conv_plan(const Geom& g, bool transposed) {
   const size_t budget = kTwoPerSm;
   int best = 1;
   for (int bh = 1; bh <= Hd; ++bh) {
-    const int rb = (transposed ? bh : (bh - 1) * S + 1) + 2;
-    const size_t smem = (size_t)pl.CG * band_pitch(rb, Wp) * 2 + (size_t)pl.CG * kBankPitch * 2 +
-                        (size_t)pick_warps(bh * NB, 8) * kBetaWords * 4;
+    const int rb = conv_band_rows(bh, S, transposed);
+    const size_t smem = (size_t)pl.CG * band_pitch(rb, Wp) * 2 + (size_t)18 * band_pitch(transposed ? rb : bh, Wpo) * 2 +
+                        (size_t)pl.CG * kBankPitch * 2 + (size_t)pick_warps(bh * NB, 8) * kBetaWords * 4;
     if (smem > budget) break;
     const long long ctas = (long long)((Hd + bh - 1) / bh) * pl.groups * g.N;
     if (bh > 1 && ctas < 2 * 148) break;
@@ -175,15 +218,19 @@ ConvPlan conv_plan(const Geom& g, bool transposed) {
   pl.BH = best;
   pl.bands = (Hd + pl.BH - 1) / pl.BH;
   pl.warps = pick_warps(pl.BH * NB, 8);
-  const int rb = (transposed ? pl.BH : (pl.BH - 1) * S + 1) + 2;
-  pl.smem = (size_t)pl.CG * band_pitch(rb, Wp) * 2 + (size_t)pl.CG * kBankPitch * 2 + (size_t)pl.warps * kBetaWords * 4;
+  const int rb = conv_band_rows(pl.BH, S, transposed);
+  pl.smem = (size_t)pl.CG * band_pitch(rb, Wp) * 2 + (size_t)18 * band_pitch(transposed ? rb : pl.BH, Wpo) * 2 +
+            (size_t)pl.CG * kBankPitch * 2 + (size_t)pl.warps * kBetaWords * 4;
   return pl;
 }
 
 template <int S, bool TRANSPOSED>
 int launch_conv(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, cudaStream_t s) {
-  const ConvPlan pl = conv_plan(g, TRANSPOSED);
+  ConvPlan pl = conv_plan(g, TRANSPOSED);
   if (pl.smem > (size_t)device_smem_optin() || pl.groups > 65535) return DK_ERR_UNSUPPORTED;
+  pl.mode_src = ptr_mode(src);
+  pl.mode_rot = ptr_mode(rot);
+  pl.pair_store = (((TRANSPOSED ? g.W : g.Wo) & 1) == 0) && ptr_mode(dst) >= 1;
   auto kern = mma_conv_kernel<S, TRANSPOSED>;
   int rc = enable_smem(kern, pl.smem);
   if (rc) return rc;
@@ -214,33 +261,42 @@ __device__ __forceinline__ void dk_products(unsigned (&dk0)[9], unsigned (&dk1)[
 
 struct RotPlan {
   int BH, warps, bands;
-  bool big;  // one block of up to 16 warps per SM instead of two of up to 8
-  size_t smem;
+  int CG, groups;  // channels per block; with more than one group the blocks write fp32 partial sums
+  bool big;        // one block of up to 16 warps per SM instead of two of up to 8
+  int mode_x, mode_dy, mode_rot;
+  size_t smem, ws_bytes;
 };
-constexpr int kRotScratch = kBetaWords * 4 + 72 * 8;  // beta table (reused for G, 3 taps at a time) + (u, v)
+constexpr int kRotScratch = 3 * 16 * 8 * 4 + 72 * 8;  // G of three taps (aliases the beta table) + (u, v)
 
 template <int S, int MAXT, int MINB>
 __global__ void __launch_bounds__(MAXT, MINB) mma_rot_kernel(const __half* __restrict__ dy, const __half* __restrict__ x,
                                                          const __half* __restrict__ rot, const __half* __restrict__ w,
-                                                         __half* __restrict__ drot, const Geom g, const RotPlan pl) {
+                                                         __half* __restrict__ drot, float* __restrict__ partial,
+                                                         const Geom g, const RotPlan pl) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int n = blockIdx.y;
   const int oh0 = blockIdx.x * pl.BH;
-  const Band bx = make_band(oh0 * S - 1, (pl.BH - 1) * S + 3, g.H, g.W);
-  const Band by = make_band(oh0, pl.BH, g.Ho, g.Wo);
-  const int pitchT = g.C + 8;  // halves per cell row of the transposed bank
+  const int c0 = blockIdx.z * pl.CG;
+  const int cnt = min(pl.CG, g.C - c0);
+  const Band bx = make_band(oh0 * S - 1, (pl.BH - 1) * S + 3, g.H, g.W, pl.mode_x);
+  const Band by = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_dy);
+  const Band br = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_rot);
+  const int pitchT = pl.CG + 8;  // halves per cell row of the transposed bank
 
   __half* xband = reinterpret_cast<__half*>(smem_raw);
-  __half* yband = xband + (size_t)g.C * bx.pitch_c;
-  __half* bankT = yband + (size_t)g.C * by.pitch_c;                       // [16 cells][C + 8]
+  __half* yband = xband + (size_t)pl.CG * bx.pitch_c;
+  __half* rband = yband + (size_t)pl.CG * by.pitch_c;                      // [18][br.pitch_c]
+  __half* bankT = rband + (size_t)18 * br.pitch_c;                         // [16 cells][CG + 8]
   unsigned char* scratch = reinterpret_cast<unsigned char*>(bankT + 16 * pitchT);
 
-  for (int i = threadIdx.x; i < 16 * g.C; i += blockDim.x) {
-    const int cell = i / g.C, c = i - cell * g.C;
-    bankT[cell * pitchT + c] = cell < g.cells ? __ldg(w + (size_t)c * g.cells + cell) : __float2half(0.f);
+  for (int i = threadIdx.x; i < 16 * cnt; i += blockDim.x) {
+    const int cell = i / cnt, c = i - cell * cnt;
+    bankT[cell * pitchT + c] = cell < g.cells ? __ldg(w + (size_t)(c0 + c) * g.cells + cell) : __float2half(0.f);
   }
-  load_band(xband, bx, x, n, g.C, 0, g.C, g.H, g.W);
-  load_band(yband, by, dy, n, g.C, 0, g.C, g.Ho, g.Wo);
+  load_band(xband, bx, x, n, g.C, c0, cnt, g.H, g.W);
+  load_band(yband, by, dy, n, g.C, c0, cnt, g.Ho, g.Wo);
+  load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
+  cp_async_wait_all();
   __syncthreads();
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -249,9 +305,9 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_rot_kernel(const __half* __res
   const int items = pl.BH * NB;
   unsigned* T = reinterpret_cast<unsigned*>(scratch + (size_t)warp * kRotScratch);
   float* Gs = reinterpret_cast<float*>(T);                       // [3 taps][16 cells][8 px], after the fragments are read
-  float2* uv = reinterpret_cast<float2*>(T + kBetaWords);        // [9 taps][8 px]
-  const __half* rot_n = rot + (size_t)n * 18 * g.P;
+  float2* uv = reinterpret_cast<float2*>(T + 3 * 16 * 8);        // [9 taps][8 px]
   __half* drot_n = drot + (size_t)n * 18 * g.P;
+  float* part_n = partial + ((size_t)blockIdx.z * g.N + n) * 18 * g.P;
 
   for (int item = warp; item < items; item += nwarps) {
     const int dr = item / NB;
@@ -260,7 +316,7 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_rot_kernel(const __half* __res
     const int ow0 = (item - dr * NB) << 3;
     {
       unsigned bf[9][2];  // not needed here: only (u, v) is kept
-      build_beta<S, false, true>(bf, T, uv, rot_n, g, oh, ow0, g.H, g.W, g.Wo, lane);
+      build_beta<S, false, true>(bf, T, uv, rband, br, g, oh, ow0, g.H, g.W, g.Wo, lane);
     }
     const int ow = ow0 + 2 * q;
     const int xoff = window_offset(bx, oh * S - 1, ow, S);
@@ -270,7 +326,7 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_rot_kernel(const __half* __res
 #pragma unroll
     for (int t = 0; t < 9; ++t) G[t][0] = G[t][1] = G[t][2] = G[t][3] = 0.f;
 
-    for (int cb16 = 0; cb16 < g.C; cb16 += 16) {
+    for (int cb16 = 0; cb16 < cnt; cb16 += 16) {
       const unsigned dy0 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq) * by.pitch_c + yoff);
       const unsigned dy1 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq + 8) * by.pitch_c + yoff);
       unsigned dk0[9], dk1[9];
@@ -318,9 +374,14 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_rot_kernel(const __half* __res
           }
         }
         if (ow0 + px < g.Wo) {
-          __half* o = drot_n + (size_t)(2 * t) * g.P + oh * g.Wo + ow0 + px;
-          o[0] = __float2half_rn(gu);
-          o[g.P] = __float2half_rn(gv);
+          const size_t o = (size_t)(2 * t) * g.P + oh * g.Wo + ow0 + px;
+          if (pl.groups == 1) {
+            drot_n[o] = __float2half_rn(gu);
+            drot_n[o + g.P] = __float2half_rn(gv);
+          } else {
+            part_n[o] = gu;
+            part_n[o + g.P] = gv;
+          }
         }
       }
     }
@@ -328,39 +389,89 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_rot_kernel(const __half* __res
   }
 }
 
-// Two blocks of at most 8 warps per SM when the bands of ALL channels fit twice, else one block
-// of up to 16 warps per SM.
+// out[i] = sum over channel groups of partial[group][i], fixed order
+__global__ void reduce_rot_partials_kernel(const float* __restrict__ partial, __half* __restrict__ out, size_t n_out,
+                                           int groups) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_out) return;
+  float s = 0.f;
+  for (int k = 0; k < groups; ++k) s += partial[(size_t)k * n_out + i];
+  out[i] = __float2half_rn(s);
+}
+
+// Plan of the grad-offsets kernel.  A block needs the bands of every channel it sums over, and
+// the sum over channels must be complete before the four-corner contraction, so:
+//   1. all channels in one block, two blocks (<= 8 warps) per SM, if that fits and fills the GPU;
+//   2. else all channels in one block of up to 16 warps, one per SM (large planes);
+//   3. else (small planes, many channels) split the channels into groups that each write an
+//      fp32 partial sum, reduced by a second pass: cheap there because the offset tensor is
+//      small next to the activations.
+static size_t rot_smem(const Geom& g, int cg, int bh, int warps) {
+  const int S = g.sH;
+  const int Wp = g.W + (g.W & 1), Wpo = g.Wo + (g.Wo & 1);
+  return (size_t)cg * (band_pitch((bh - 1) * S + 3, Wp) + band_pitch(bh, Wpo)) * 2 + (size_t)18 * band_pitch(bh, Wpo) * 2 +
+         (size_t)16 * (cg + 8) * 2 + (size_t)warps * kRotScratch;
+}
+
 RotPlan rot_plan(const Geom& g) {
   RotPlan pl;
-  const int S = g.sH;
   const int NB = (g.Wo + 7) / 8;
-  const int Wp = g.W + (g.W & 1), Wpo = g.Wo + (g.Wo & 1);
+  const long long min_ctas = 2 * 148;
   pl.BH = 0;
   pl.big = false;
+  pl.groups = 1;
+  pl.CG = g.C;
   for (int attempt = 0; attempt < 2 && !pl.BH; ++attempt) {
     const size_t budget = attempt == 0 ? kTwoPerSm : kOnePerSm;
     const int maxw = attempt == 0 ? 8 : 16;
+    int best = 0;
     for (int bh = 1; bh <= g.Ho; ++bh) {
-      const int warps = pick_warps(bh * NB, maxw);
-      const size_t smem = (size_t)g.C * (band_pitch((bh - 1) * S + 3, Wp) + band_pitch(bh, Wpo)) * 2 +
-                          (size_t)16 * (g.C + 8) * 2 + (size_t)warps * kRotScratch;
-      if (smem > budget) break;
-      const long long ctas = (long long)((g.Ho + bh - 1) / bh) * g.N;
-      if (bh > 1 && ctas < 2 * 148) break;
-      pl.BH = bh;
-      pl.warps = warps;
-      pl.smem = smem;
-      pl.big = attempt == 1;
+      if (rot_smem(g, g.C, bh, pick_warps(bh * NB, maxw)) > budget) break;
+      best = bh;
       if (bh * NB >= 2 * maxw) break;
     }
+    if (!best) continue;
+    const int items = best * NB;
+    const long long ctas = (long long)((g.Ho + best - 1) / best) * g.N;
+    if (items >= 7 && ctas >= min_ctas) {
+      pl.BH = best;
+      pl.warps = pick_warps(items, maxw);
+      pl.big = attempt == 1;
+    }
   }
-  if (pl.BH) pl.bands = (g.Ho + pl.BH - 1) / pl.BH;
+  if (!pl.BH) {
+    const int slabs = g.C / 16;
+    int bh = (14 + NB - 1) / NB;
+    if (bh > g.Ho) bh = g.Ho;
+    for (; bh >= 1 && !pl.BH; --bh) {
+      const int warps = pick_warps(bh * NB, 8);
+      for (int groups = 1; groups <= slabs; ++groups) {
+        const int cg = ((slabs + groups - 1) / groups) * 16;
+        if ((g.C + cg - 1) / cg != groups) continue;
+        if (rot_smem(g, cg, bh, warps) > kTwoPerSm) continue;
+        const long long ctas = (long long)((g.Ho + bh - 1) / bh) * g.N * groups;
+        if (ctas < min_ctas && cg > 32) continue;
+        if (cg < 64 && bh > 1 && groups > 1) break;  // too little work per item: try a shorter band first
+        pl.BH = bh;
+        pl.warps = warps;
+        pl.CG = cg;
+        pl.groups = groups;
+        break;
+      }
+    }
+  }
+  if (pl.BH) {
+    pl.smem = rot_smem(g, pl.CG, pl.BH, pl.warps);
+    pl.bands = (g.Ho + pl.BH - 1) / pl.BH;
+    pl.ws_bytes = pl.groups > 1 ? (size_t)pl.groups * g.N * 18 * g.P * sizeof(float) : 0;
+  }
   return pl;
 }
 
 // ------------------------------------------------------------------ grad-bank
 struct FiltPlan {
   int BH, CG, groups, warps, bands, units_per_block, blocks_x;
+  int mode_x, mode_dy, mode_rot;
   size_t smem, ws_bytes;
 };
 
@@ -381,7 +492,8 @@ __global__ void __launch_bounds__(256, 2) mma_filter_kernel(const __half* __rest
 
   __half* xband = reinterpret_cast<__half*>(smem_raw);
   __half* yband = xband + (size_t)pl.CG * xpitch;
-  unsigned* tables = reinterpret_cast<unsigned*>(yband + (size_t)pl.CG * ypitch);
+  __half* rband = yband + (size_t)pl.CG * ypitch;  // [18][ypitch]
+  unsigned* tables = reinterpret_cast<unsigned*>(rband + (size_t)18 * ypitch);
   unsigned* T = tables + warp * kBetaWords;
 
   float acc[4][2][4];  // up to 4 slabs of 16 channels x (cells 0-7 | cells 8-15)
@@ -396,13 +508,15 @@ __global__ void __launch_bounds__(256, 2) mma_filter_kernel(const __half* __rest
   for (int unit = u_begin; unit < u_end; ++unit) {
     const int n = unit / pl.bands;
     const int oh0 = (unit - n * pl.bands) * pl.BH;
-    const Band bx = make_band(oh0 * S - 1, (pl.BH - 1) * S + 3, g.H, g.W);
-    const Band by = make_band(oh0, pl.BH, g.Ho, g.Wo);
+    const Band bx = make_band(oh0 * S - 1, (pl.BH - 1) * S + 3, g.H, g.W, pl.mode_x);
+    const Band by = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_dy);
+    const Band br = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_rot);
     __syncthreads();  // previous unit's readers are done
     load_band(xband, bx, x, n, g.C, c0, cnt, g.H, g.W);
     load_band(yband, by, dy, n, g.C, c0, cnt, g.Ho, g.Wo);
+    load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
+    cp_async_wait_all();
     __syncthreads();
-    const __half* rot_n = rot + (size_t)n * 18 * g.P;
     for (int item = warp; item < items; item += nwarps) {
       const int dr = item / NB;
       const int oh = oh0 + dr;
@@ -411,7 +525,7 @@ __global__ void __launch_bounds__(256, 2) mma_filter_kernel(const __half* __rest
       unsigned bw[10][2];  // beta as B fragments of the grad-bank product: [tap][cells 0-7 | cells 8-15]
       {
         unsigned bf[9][2];
-        build_beta<S, false, false>(bf, T, nullptr, rot_n, g, oh, ow0, g.H, g.W, g.Wo, lane);
+        build_beta<S, false, false>(bf, T, nullptr, rband, br, g, oh, ow0, g.H, g.W, g.Wo, lane);
 #pragma unroll
         for (int t = 0; t < 9; ++t) {
           bw[t][0] = movmatrix_trans(bf[t][0]);
@@ -491,7 +605,8 @@ FiltPlan filt_plan(const Geom& g) {
   pl.BH = 0;
   for (int bh = 1; bh <= g.Ho; ++bh) {
     const int warps = pick_warps(bh * NB, 8);
-    size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + band_pitch(bh, Wpo)) * 2 + (size_t)warps * kBetaWords * 4;
+    size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + band_pitch(bh, Wpo)) * 2 +
+                  (size_t)18 * band_pitch(bh, Wpo) * 2 + (size_t)warps * kBetaWords * 4;
     const size_t red = (size_t)warps * pl.CG * 16 * 4;
     if (smem < red) smem = red;
     if (smem > budget) break;
@@ -519,24 +634,35 @@ FiltPlan filt_plan(const Geom& g) {
 
 int local_conv_mma(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, bool transposed,
                    cudaStream_t s) {
-  if (!fast_shape(g) || (transposed && g.sH != 1)) return DK_ERR_UNSUPPORTED;
-  if (transposed) return launch_conv<1, true>(src, rot, w, dst, g, s);
+  if (!fast_shape(g)) return DK_ERR_UNSUPPORTED;
+  if (transposed) return g.sH == 1 ? launch_conv<1, true>(src, rot, w, dst, g, s) : launch_conv<2, true>(src, rot, w, dst, g, s);
   if (g.sH == 1) return launch_conv<1, false>(src, rot, w, dst, g, s);
   return launch_conv<2, false>(src, rot, w, dst, g, s);
 }
 
-int local_rot_mma(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, const Geom& g,
-                  cudaStream_t s) {
-  if (!fast_shape(g)) return DK_ERR_UNSUPPORTED;
+size_t local_rot_mma_workspace(const Geom& g) {
+  if (!fast_shape(g)) return 0;
   const RotPlan pl = rot_plan(g);
-  if (!pl.BH || pl.smem > (size_t)device_smem_optin()) return DK_ERR_UNSUPPORTED;
+  return pl.BH ? pl.ws_bytes : 0;
+}
+
+int local_rot_mma(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, const Geom& g,
+                  void* ws, size_t ws_bytes, cudaStream_t s) {
+  if (!fast_shape(g)) return DK_ERR_UNSUPPORTED;
+  RotPlan pl = rot_plan(g);
+  if (!pl.BH || pl.smem > (size_t)device_smem_optin() || pl.groups > 65535) return DK_ERR_UNSUPPORTED;
+  if (pl.ws_bytes && (ws == nullptr || ws_bytes < pl.ws_bytes)) return DK_ERR_WORKSPACE;
+  pl.mode_x = ptr_mode(x);
+  pl.mode_dy = ptr_mode(dy);
+  pl.mode_rot = ptr_mode(rot);
   int rc;
-  const dim3 grid(pl.bands, g.N);
+  const dim3 grid(pl.bands, g.N, pl.groups);
+  float* partial = reinterpret_cast<float*>(ws);
 #define DK_LAUNCH_ROT(SS, MAXT, MINB)                                                     \
   {                                                                                       \
     auto kern = mma_rot_kernel<SS, MAXT, MINB>;                                           \
     if ((rc = enable_smem(kern, pl.smem))) return rc;                                     \
-    kern<<<grid, pl.warps * 32, pl.smem, s>>>(dy, x, rot, w, drot, g, pl);                \
+    kern<<<grid, pl.warps * 32, pl.smem, s>>>(dy, x, rot, w, drot, partial, g, pl);       \
   }
   if (g.sH == 1) {
     if (pl.big) DK_LAUNCH_ROT(1, 512, 1) else DK_LAUNCH_ROT(1, 256, 2)
@@ -544,7 +670,15 @@ int local_rot_mma(const __half* dy, const __half* x, const __half* rot, const __
     if (pl.big) DK_LAUNCH_ROT(2, 512, 1) else DK_LAUNCH_ROT(2, 256, 2)
   }
 #undef DK_LAUNCH_ROT
-  return check_launch();
+  if ((rc = check_launch())) return rc;
+  if (pl.groups > 1) {
+    const size_t n_out = (size_t)g.N * 18 * g.P;
+    const size_t blocks = (n_out + 255) / 256;
+    if (blocks > 0x7fffffffULL) return DK_ERR_UNSUPPORTED;
+    reduce_rot_partials_kernel<<<(unsigned)blocks, 256, 0, s>>>(partial, drot, n_out, pl.groups);
+    rc = check_launch();
+  }
+  return rc;
 }
 
 size_t local_filter_mma_workspace(const Geom& g) {
@@ -556,9 +690,12 @@ size_t local_filter_mma_workspace(const Geom& g) {
 int local_filter_mma(const __half* dy, const __half* x, const __half* rot, __half* dw, const Geom& g, void* ws,
                      size_t ws_bytes, cudaStream_t s) {
   if (!fast_shape(g)) return DK_ERR_UNSUPPORTED;
-  const FiltPlan pl = filt_plan(g);
+  FiltPlan pl = filt_plan(g);
   if (!pl.BH || pl.smem > (size_t)device_smem_optin() || pl.groups > 65535) return DK_ERR_UNSUPPORTED;
   if (ws == nullptr || ws_bytes < pl.ws_bytes) return DK_ERR_WORKSPACE;
+  pl.mode_x = ptr_mode(x);
+  pl.mode_dy = ptr_mode(dy);
+  pl.mode_rot = ptr_mode(rot);
   int rc;
   float* partial = reinterpret_cast<float*>(ws);
   if (g.sH == 1) {

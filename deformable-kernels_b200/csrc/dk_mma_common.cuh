@@ -14,7 +14,7 @@ namespace mma {
 
 constexpr int kSlack = 8;       // zeroed halves in front of each channel's band
 constexpr int kBankPitch = 24;  // halves per channel row of the bank copy (12 words: conflict-free A loads)
-constexpr int kBetaWords = 9 * 8 * 8;  // per-warp table: [tap][pixel][8 words of two cells], swizzled
+constexpr int kBetaWords = 3 * 8 * 8;  // per-warp table for three taps: [tap][pixel][8 words of two cells], swizzled
 
 // d = a * b (+ c): m16n8k16, fp16 inputs, fp32 accumulate.
 __device__ __forceinline__ void mma16816(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
@@ -43,6 +43,16 @@ __device__ __forceinline__ unsigned hmul2u(unsigned a, unsigned b) {
   __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
   return *reinterpret_cast<unsigned*>(&r);
 }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+  const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(sa), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
 // The pair (source value of pixel 0, source value of pixel 1) for tap column fw, cut out of the
 // 6-half window [ow*S-2, ow*S+3] held in three words: halves 1+fw and 1+S+fw.
@@ -78,58 +88,92 @@ __host__ __device__ inline int band_pitch(int RB, int Wp) {
 __host__ __device__ inline int band_mode(int plane, int Ws) {
   return ((plane & 7) == 0 && (Ws & 1) == 0) ? 2 : ((Ws & 1) == 0 ? 1 : 0);
 }
-__device__ __forceinline__ Band make_band(int row_lo, int RB, int Hs, int Ws) {
+// maxmode caps the copy width by the alignment of the tensor's base pointer (see ptr_mode).
+__device__ __forceinline__ Band make_band(int row_lo, int RB, int Hs, int Ws, int maxmode) {
   Band b;
   b.row_lo = row_lo;
   b.RB = RB;
   b.Wp = Ws + (Ws & 1);
   b.pitch_c = band_pitch(RB, b.Wp);
-  b.mode = band_mode(Hs * Ws, Ws);
+  b.mode = min(band_mode(Hs * Ws, Ws), maxmode);
   b.org = (b.mode == 2) ? ((row_lo * Ws) & ~7) : row_lo * b.Wp;
   return b;
 }
 
-// Zero `cnt` channel bands, then copy the in-range source rows [row_lo, row_lo+RB) of channels
-// c0 .. c0+cnt-1 of sample n.  Must be called by the whole block; ends with the data visible
-// to the calling thread only after the caller's __syncthreads().
+inline int ptr_mode(const void* p) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  return (a & 15) == 0 ? 2 : ((a & 3) == 0 ? 1 : 0);
+}
+
+// Copy the in-range source rows [row_lo, row_lo+RB) of channels c0 .. c0+cnt-1 of sample n into
+// the band with cp.async (16- or 4-byte pieces) and zero everything else of the band (slack,
+// rows outside the image).  Called by the whole block; the caller must execute
+// cp_async_wait_all() and __syncthreads() before reading.  Odd row widths fall back to plain
+// 2-byte copies behind an extra barrier.
 __device__ __forceinline__ void load_band(__half* __restrict__ band, const Band& b, const __half* __restrict__ src, int n, int C,
                                           int c0, int cnt, int Hs, int Ws) {
   const int tid = threadIdx.x, nt = blockDim.x;
   const int lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
-  {
+  const int r_s = max(b.row_lo, 0), r_e = min(b.row_lo + b.RB, Hs);
+  const size_t plane = (size_t)Hs * Ws;
+  const __half* s0 = src + ((size_t)n * C + c0) * plane;
+  if (b.mode == 0 || r_e <= r_s) {
     const uint4 z = make_uint4(0, 0, 0, 0);
     uint4* b4 = reinterpret_cast<uint4*>(band);
     const int nv = cnt * b.pitch_c / 8;
     for (int i = tid; i < nv; i += nt) b4[i] = z;
-  }
-  __syncthreads();
-  const int r_s = max(b.row_lo, 0), r_e = min(b.row_lo + b.RB, Hs);
-  if (r_e <= r_s) return;
-  const size_t plane = (size_t)Hs * Ws;
-  const __half* s0 = src + ((size_t)n * C + c0) * plane;
-  if (b.mode == 2) {
-    const int gs = (r_s * Ws) & ~7, ge = min((r_e * Ws + 7) & ~7, (int)plane);
-    const int nvec = (ge - gs) >> 3;
-    for (int j = warp; j < cnt; j += nwarps) {
-      const uint4* sp = reinterpret_cast<const uint4*>(s0 + (size_t)j * plane + gs);
-      uint4* dp = reinterpret_cast<uint4*>(band + (size_t)j * b.pitch_c + kSlack + (gs - b.org));
-      for (int v = lane; v < nvec; v += 32) dp[v] = __ldg(sp + v);
-    }
-  } else if (b.mode == 1) {
-    const int per = (r_e - r_s) * Ws / 2;
-    for (int j = warp; j < cnt; j += nwarps) {
-      const unsigned* sp = reinterpret_cast<const unsigned*>(s0 + (size_t)j * plane + r_s * Ws);
-      unsigned* dp = reinterpret_cast<unsigned*>(band + (size_t)j * b.pitch_c + kSlack + (r_s * b.Wp - b.org));
-      for (int v = lane; v < per; v += 32) dp[v] = __ldg(sp + v);
-    }
-  } else {
-    for (int j = warp; j < cnt; j += nwarps) {
-      for (int r = r_s; r < r_e; ++r) {
-        const __half* sp = s0 + (size_t)j * plane + (size_t)r * Ws;
-        __half* dp = band + (size_t)j * b.pitch_c + kSlack + (r * b.Wp - b.org);
-        for (int v = lane; v < Ws; v += 32) dp[v] = __ldg(sp + v);
+    if (r_e <= r_s) return;
+    __syncthreads();
+    // 2-byte copies, four independent loads in flight per thread
+    const int rows = r_e - r_s;
+    const int per = rows * Ws, total = cnt * per;
+    for (int i0 = tid; i0 < total; i0 += 4 * nt) {
+      __half val[4];
+      int dst[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = i0 + k * nt;
+        dst[k] = -1;
+        if (i < total) {
+          const int j = i / per, v = i - j * per;
+          const int r = v / Ws, col = v - r * Ws;
+          val[k] = __ldg(s0 + (size_t)j * plane + (size_t)(r_s + r) * Ws + col);
+          dst[k] = j * b.pitch_c + kSlack + ((r_s + r) * b.Wp - b.org) + col;
+        }
       }
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (dst[k] >= 0) band[dst[k]] = val[k];
     }
+    return;
+  }
+  // contiguous span [lo, hi) of each channel band that receives data (in halves, relative to the channel)
+  int gs, lo, hi;
+  if (b.mode == 2) {
+    gs = (r_s * Ws) & ~7;
+    const int ge = min((r_e * Ws + 7) & ~7, (int)plane);
+    lo = kSlack + (gs - b.org);
+    hi = lo + (ge - gs);
+  } else {
+    gs = r_s * Ws;
+    lo = kSlack + (r_s * b.Wp - b.org);
+    hi = lo + (r_e - r_s) * Ws;
+  }
+  const int head = lo >> 1, tail = (b.pitch_c - hi) >> 1;  // 4-byte words to zero in front / behind
+  for (int j = warp; j < cnt; j += nwarps) {
+    __half* ch = band + (size_t)j * b.pitch_c;
+    const __half* sp = s0 + (size_t)j * plane + gs;
+    if (b.mode == 2) {
+      const int nvec = (hi - lo) >> 3;
+      for (int v = lane; v < nvec; v += 32) cp_async16(ch + lo + v * 8, sp + v * 8);
+    } else {
+      const int nw = (hi - lo) >> 1;
+      for (int v = lane; v < nw; v += 32) cp_async4(ch + lo + v * 2, sp + v * 2);
+    }
+    unsigned* zw = reinterpret_cast<unsigned*>(ch);
+    for (int v = lane; v < head; v += 32) zw[v] = 0u;
+    unsigned* zt = reinterpret_cast<unsigned*>(ch + hi);
+    for (int v = lane; v < tail; v += 32) zt[v] = 0u;
   }
 }
 
@@ -141,33 +185,32 @@ __device__ __forceinline__ int window_offset(const Band& b, int srow0, int ow, i
 // ---------------------------------------------------------------- hat-product (beta) fragments
 // For the 8 pixels of an item and the 9 taps: beta[(pixel, tap)][cell] = hat(u - a) * hat(v - b),
 // i.e. the four bilinear coefficients scattered into a row of 16 cells, zero when the tap is
-// unused (outside the image / the bank).  Built cooperatively by the warp -- one lane per
-// (pixel, tap), three rounds -- into a swizzled table, then read back as mma B fragments:
+// unused (outside the image / the bank).  Built cooperatively by the warp, three taps at a
+// time -- one lane per (pixel, tap) -- into a swizzled table, then read back as mma B fragments:
 //   bf[t][0] = cells (2q, 2q+1) of pixel gq, bf[t][1] = cells (2q+8, 2q+9) of pixel gq.
+// The kernel-space offsets come from a band of the 18 offset planes in shared memory (rb, rband).
 // With KEEP_UV the bank coordinates are left in uv[tap*8 + pixel] (u = 1e30 marks an unused tap).
 template <int S, bool TRANSPOSED, bool KEEP_UV>
 __device__ __forceinline__ void build_beta(unsigned (&bf)[9][2], unsigned* __restrict__ T, float2* __restrict__ uv,
-                                           const __half* __restrict__ rot_n, const Geom& g, int drow, int ow0, int Hs, int Ws,
-                                           int Wd, int lane) {
-  {
-    const uint4 z = make_uint4(0, 0, 0, 0);
-    uint4* t4 = reinterpret_cast<uint4*>(T);
-#pragma unroll
-    for (int i = 0; i < (kBetaWords / 4 + 31) / 32; ++i) {
-      const int k = i * 32 + lane;
-      if (k < kBetaWords / 4) t4[k] = z;
-    }
-  }
-  __syncwarp();
+                                           const __half* __restrict__ rband, const Band& rb, const Geom& g, int drow, int ow0,
+                                           int Hs, int Ws, int Wd, int lane) {
   const float uh0 = (float)(g.scH - 3) * 0.5f, uw0 = (float)(g.scW - 3) * 0.5f;
   __half* Th = reinterpret_cast<__half*>(T);
+  const int gq = lane >> 2, q = lane & 3;
+  const int px = lane & 7, tt = lane >> 3;  // builder role (lanes 0..23)
+  const int pc = ow0 + px;
 #pragma unroll
-  for (int r = 0; r < 3; ++r) {
-    const int idx = r * 32 + lane;
-    if (idx < 72) {
-      const int px = idx & 7, t = idx >> 3;
-      const int fh = t / 3, fw = t - fh * 3;
-      const int pc = ow0 + px;
+  for (int pass = 0; pass < 3; ++pass) {
+    {
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      uint4* t4 = reinterpret_cast<uint4*>(T);
+      t4[lane] = z;
+      if (lane < kBetaWords / 4 - 32) t4[32 + lane] = z;
+    }
+    __syncwarp();
+    if (lane < 24) {
+      const int fh = pass, fw = tt;
+      const int t = pass * 3 + tt;
       int orow, ocol;
       bool ok;
       if (!TRANSPOSED) {
@@ -176,22 +219,24 @@ __device__ __forceinline__ void build_beta(unsigned (&bf)[9][2], unsigned* __res
         orow = drow;
         ocol = pc;
       } else {
-        orow = drow + 1 - fh;
-        ocol = pc + 1 - fw;
-        ok = pc < Wd && orow >= 0 && orow < Hs && ocol >= 0 && ocol < Ws;
+        // the output pixel that reaches destination (drow, pc) through tap (fh, fw), if any
+        const int tr = drow + 1 - fh, tc = pc + 1 - fw;
+        orow = tr / S;
+        ocol = tc / S;
+        ok = pc < Wd && tr >= 0 && tc >= 0 && orow * S == tr && ocol * S == tc && orow < Hs && ocol < Ws;
       }
-      const int off = ok ? orow * g.Wo + ocol : 0;
-      const __half* rp = rot_n + (size_t)(2 * t) * g.P + off;
-      const float u = ((float)fh + __half2float(__ldg(rp))) + uh0;
-      const float v = ((float)fw + __half2float(__ldg(rp + g.P))) + uw0;
+      const int off = ok ? kSlack + orow * rb.Wp + ocol - rb.org : kSlack;
+      const __half* rp = rband + (size_t)(2 * t) * rb.pitch_c + off;
+      const float u = ((float)fh + __half2float(rp[0])) + uh0;
+      const float v = ((float)fw + __half2float(rp[rb.pitch_c])) + uw0;
       const bool valid = ok && u > -1.f && v > -1.f && u < (float)g.scH && v < (float)g.scW;
-      if (KEEP_UV) uv[idx] = make_float2(valid ? u : 1e30f, v);
+      if (KEEP_UV) uv[t * 8 + px] = make_float2(valid ? u : 1e30f, v);
       if (valid) {
         const float fu = floorf(u), fv = floorf(v);
         const int h0 = (int)fu, w0 = (int)fv;
         const float lh = u - fu, lw = v - fv;
         const int sw = (px >> 2) << 2;
-        __half* row = Th + (t * 8 + px) * 16;
+        __half* row = Th + (tt * 8 + px) * 16;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int a = h0 + (k >> 1), b = w0 + (k & 1);
@@ -203,18 +248,17 @@ __device__ __forceinline__ void build_beta(unsigned (&bf)[9][2], unsigned* __res
         }
       }
     }
-  }
-  __syncwarp();
-  {
-    const int gq = lane >> 2, q = lane & 3;
-    const int sw = (gq >> 2) << 2;
+    __syncwarp();
+    {
+      const int sw = (gq >> 2) << 2;
 #pragma unroll
-    for (int t = 0; t < 9; ++t) {
-      bf[t][0] = T[(t * 8 + gq) * 8 + (q ^ sw)];
-      bf[t][1] = T[(t * 8 + gq) * 8 + ((q + 4) ^ sw)];
+      for (int k = 0; k < 3; ++k) {
+        bf[pass * 3 + k][0] = T[(k * 8 + gq) * 8 + (q ^ sw)];
+        bf[pass * 3 + k][1] = T[(k * 8 + gq) * 8 + ((q + 4) ^ sw)];
+      }
     }
+    __syncwarp();
   }
-  __syncwarp();
 }
 
 }  // namespace mma

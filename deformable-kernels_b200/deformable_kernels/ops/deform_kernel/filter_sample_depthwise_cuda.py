@@ -63,10 +63,13 @@ def sample_depthwise_backward_filter_cuda(gradOutput, input, rotation, filter, g
 def sample_depthwise_backward_rotation_cuda(gradOutput, input, rotation, filter, gradRotation, *ints):
     gradOutput, input, rotation, filter = _prep(gradOutput, input, rotation, filter)
     g = _geom(input, *ints)
+    code = C.dtype_code(input)
     with torch.cuda.device(input.device):
+        nbytes = C.lib.dk_sample_depthwise_backward_rotation_workspace_bytes(g, code)
+        ws = C.workspace(nbytes, input.device)
         C.check(C.lib.dk_sample_depthwise_backward_rotation(C.ptr(gradOutput), C.ptr(input), C.ptr(rotation),
-                                                            C.ptr(filter), C.ptr(_out(gradRotation)), g,
-                                                            C.dtype_code(input), C.stream_ptr(input.device)),
+                                                            C.ptr(filter), C.ptr(_out(gradRotation)), g, code,
+                                                            C.ptr(ws), nbytes, C.stream_ptr(input.device)),
                 "sample_depthwise_backward_rotation")
     return 1
 

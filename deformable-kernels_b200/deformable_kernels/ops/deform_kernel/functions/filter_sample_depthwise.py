@@ -77,7 +77,7 @@ class SampleDepthwiseFunction(Function):
         grad_weight = torch.empty_like(weight) if need[2] else None
         code = C.dtype_code(input)
         with torch.cuda.device(input.device):
-            nbytes = C.lib.dk_sample_depthwise_backward_filter_workspace_bytes(ctx.geom, code) if need[2] else 0
+            nbytes = C.lib.dk_sample_depthwise_backward_workspace_bytes(ctx.geom, code)
             ws = C.workspace(nbytes, input.device)
             C.check(C.lib.dk_sample_depthwise_backward(
                 C.ptr(grad_output), C.ptr(input), C.ptr(rotation), C.ptr(weight), C.ptr(grad_input),

@@ -91,15 +91,19 @@ int dk_sample_depthwise_backward_filter(const void *grad_output, const void *inp
                                         void *grad_filter, const dk_geom *g, int dtype, void *workspace,
                                         size_t workspace_bytes, void *stream);
 
-/* replaces sample_depthwise_backward_rotation_cuda, csrc/filter_sample_depthwise_cuda.cpp:178-235 */
+/* replaces sample_depthwise_backward_rotation_cuda, csrc/filter_sample_depthwise_cuda.cpp:178-235.
+ * The workspace (fp32 partial sums over channel groups, used for fp16 tensors on small planes)
+ * may be 0 bytes; ask dk_sample_depthwise_backward_rotation_workspace_bytes(). */
+size_t dk_sample_depthwise_backward_rotation_workspace_bytes(const dk_geom *g, int dtype);
 int dk_sample_depthwise_backward_rotation(const void *grad_output, const void *input, const void *rotation,
                                           const void *filter, void *grad_rotation, const dk_geom *g, int dtype,
-                                          void *stream);
+                                          void *workspace, size_t workspace_bytes, void *stream);
 
 /* All gradients of the local operator in one call (what
  * SampleDepthwiseFunction.backward, functions/filter_sample_depthwise.py:53-87, does
- * with three).  Any of the three outputs may be NULL to skip it.  Workspace as for
- * dk_sample_depthwise_backward_filter (only needed when grad_filter != NULL). */
+ * with three).  Any of the three outputs may be NULL to skip it.  Workspace:
+ * dk_sample_depthwise_backward_workspace_bytes() (shared by the passes). */
+size_t dk_sample_depthwise_backward_workspace_bytes(const dk_geom *g, int dtype);
 int dk_sample_depthwise_backward(const void *grad_output, const void *input, const void *rotation,
                                  const void *filter, void *grad_input, void *grad_rotation, void *grad_filter,
                                  const dk_geom *g, int dtype, void *workspace, size_t workspace_bytes, void *stream);
