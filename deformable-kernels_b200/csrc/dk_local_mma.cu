@@ -61,7 +61,6 @@ __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restri
   __half* band = reinterpret_cast<__half*>(smem_raw);
   __half* rband = band + pl.CG * bx.pitch_c;                                 // [18][br.pitch_c]
   __half* bank = rband + 18 * br.pitch_c;                                    // [CG][kBankPitch]
-  unsigned* tables = reinterpret_cast<unsigned*>(bank + pl.CG * kBankPitch);  // [warps][kBetaWords]
 
   for (int i = threadIdx.x; i < cnt * 16; i += blockDim.x) {
     const int j = i >> 4, cell = i & 15;
@@ -76,8 +75,9 @@ __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restri
   const int gq = lane >> 2, q = lane & 3;
   const int NB = (Wd + 7) >> 3;
   const int items = pl.BH * NB;
-  unsigned* T = tables + warp * kBetaWords;
   const bool dst_even = pl.pair_store;
+  const LaneCells lc = lane_cells(g, q);
+  const bool sc44 = g.scH == 4 && g.scW == 4;
 
   for (int item = warp; item < items; item += nwarps) {
     const int dr = item / NB;
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restri
     if (drow >= Hd) break;
     const int ow0 = (item - dr * NB) << 3;
     unsigned bf[9][2];
-    build_beta<S, TRANSPOSED, false>(bf, T, nullptr, rband, br, g, drow, ow0, Hs, Ws, Wd, lane);
+    beta_direct<S, TRANSPOSED>(bf, rband, br, g, lc, sc44, drow, ow0, Hs, Ws, Wd, gq);
 
     const int ow = ow0 + 2 * q;
     // TRANSPOSED with stride 2: pixel 0 (even column) takes tap column 1 from grad-output column ow/2,
@@ -93,20 +93,21 @@ __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restri
     const int j0 = ow >> 1;
     const int wbase = (TRANSPOSED && S == 2) ? kSlack + (j0 & ~1) - bx.org
                                              : window_offset(bx, TRANSPOSED ? drow - 1 : drow * S - 1, ow, S);
-    for (int cb16 = 0; cb16 < cnt; cb16 += 16) {
+    const unsigned* bkp = reinterpret_cast<const unsigned*>(bank + gq * kBankPitch) + q;
+    const __half* x0 = band + gq * bx.pitch_c + wbase;
+    const int xstep = 16 * bx.pitch_c, x8 = 8 * bx.pitch_c;
+    const size_t dplane = (size_t)Hd * Wd;
+    __half* y0 = dst + ((size_t)n * g.C + c0 + gq) * dplane + (size_t)drow * Wd + ow;
+    for (int cb16 = 0; cb16 < cnt; cb16 += 16, bkp += 16 * kBankPitch / 2, x0 += xstep, y0 += 16 * dplane) {
       unsigned a[4];
-      {
-        const unsigned* bk0 = reinterpret_cast<const unsigned*>(bank + (cb16 + gq) * kBankPitch);
-        const unsigned* bk1 = reinterpret_cast<const unsigned*>(bank + (cb16 + gq + 8) * kBankPitch);
-        a[0] = bk0[q];
-        a[1] = bk1[q];
-        a[2] = bk0[q + 4];
-        a[3] = bk1[q + 4];
-      }
-      const __half* x0 = band + (size_t)(cb16 + gq) * bx.pitch_c + wbase;
-      const __half* x1 = x0 + (size_t)8 * bx.pitch_c;
+      a[0] = bkp[0];
+      a[1] = bkp[8 * kBankPitch / 2];
+      a[2] = bkp[4];
+      a[3] = bkp[8 * kBankPitch / 2 + 4];
+      const __half* x1 = x0 + x8;
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       if (TRANSPOSED && S == 2) {
+        const unsigned sel = (j0 & 1) ? 0x5432u : 0x3210u;  // -> (dy[j0], dy[j0 + 1]) in one word
 #pragma unroll
         for (int fh = 0; fh < 3; ++fh) {
           const int tr = drow + 1 - fh;
@@ -114,47 +115,47 @@ __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restri
           const int orow = tr >> 1;
           const unsigned* p0 = reinterpret_cast<const unsigned*>(x0 + orow * bx.Wp);
           const unsigned* p1 = reinterpret_cast<const unsigned*>(x1 + orow * bx.Wp);
-          const unsigned w0 = p0[0], w1 = p0[1], v0 = p1[0], v1 = p1[1];
-          const bool odd = j0 & 1;
-          const float a0 = odd ? hi2f(w0) : lo2f(w0), b0 = odd ? lo2f(w1) : hi2f(w0);  // dy[j0], dy[j0 + 1]
-          const float a1 = odd ? hi2f(v0) : lo2f(v0), b1 = odd ? lo2f(v1) : hi2f(v0);
-          float d[4];
-          mma16816(d, a, bf[fh * 3 + 0][0], bf[fh * 3 + 0][1]);
-          acc[1] += b0 * d[1];
-          acc[3] += b1 * d[3];
-          mma16816(d, a, bf[fh * 3 + 1][0], bf[fh * 3 + 1][1]);
-          acc[0] += a0 * d[0];
-          acc[2] += a1 * d[2];
-          mma16816(d, a, bf[fh * 3 + 2][0], bf[fh * 3 + 2][1]);
-          acc[1] += a0 * d[1];
-          acc[3] += a1 * d[3];
+          const unsigned ab0 = __byte_perm(p0[0], p0[1], sel), ab1 = __byte_perm(p1[0], p1[1], sel);
+          unsigned d[2];
+          mma16816_h(d, a, bf[fh * 3 + 0][0], bf[fh * 3 + 0][1]);
+          fma_hh<1, 1>(acc[1], ab0, d[0]);
+          fma_hh<1, 1>(acc[3], ab1, d[1]);
+          mma16816_h(d, a, bf[fh * 3 + 1][0], bf[fh * 3 + 1][1]);
+          fma_hh<0, 0>(acc[0], ab0, d[0]);
+          fma_hh<0, 0>(acc[2], ab1, d[1]);
+          mma16816_h(d, a, bf[fh * 3 + 2][0], bf[fh * 3 + 2][1]);
+          fma_hh<0, 1>(acc[1], ab0, d[0]);
+          fma_hh<0, 1>(acc[3], ab1, d[1]);
         }
       } else {
 #pragma unroll
-      for (int fh = 0; fh < 3; ++fh) {
-        const int rsel = TRANSPOSED ? 2 - fh : fh;
-        const unsigned* p0 = reinterpret_cast<const unsigned*>(x0 + rsel * bx.Wp);
-        const unsigned* p1 = reinterpret_cast<const unsigned*>(x1 + rsel * bx.Wp);
-        const unsigned w0 = p0[0], w1 = p0[1], w2 = p0[2];
-        const unsigned v0 = p1[0], v1 = p1[1], v2 = p1[2];
-        float f0[6], f1[6];  // halves 1..5 of the window [ow*S-2, ow*S+3]
-        f0[1] = hi2f(w0); f0[2] = lo2f(w1); f0[3] = hi2f(w1); f0[4] = lo2f(w2); f0[5] = hi2f(w2);
-        f1[1] = hi2f(v0); f1[2] = lo2f(v1); f1[3] = hi2f(v1); f1[4] = lo2f(v2); f1[5] = hi2f(v2);
+        for (int fh = 0; fh < 3; ++fh) {
+          const int rsel = TRANSPOSED ? 2 - fh : fh;
+          const unsigned* p0 = reinterpret_cast<const unsigned*>(x0 + rsel * bx.Wp);
+          const unsigned* p1 = reinterpret_cast<const unsigned*>(x1 + rsel * bx.Wp);
+          const unsigned w0 = p0[0], w1 = p0[1], w2 = p0[2];
+          const unsigned v0 = p1[0], v1 = p1[1], v2 = p1[2];
+          unsigned d[3][2];
 #pragma unroll
-        for (int fw = 0; fw < 3; ++fw) {
-          float d[4];
-          mma16816(d, a, bf[fh * 3 + fw][0], bf[fh * 3 + fw][1]);
-          const int csel = TRANSPOSED ? 2 - fw : fw;
-          acc[0] += f0[1 + csel] * d[0];
-          acc[1] += f0[1 + S + csel] * d[1];
-          acc[2] += f1[1 + csel] * d[2];
-          acc[3] += f1[1 + S + csel] * d[3];
+          for (int fw = 0; fw < 3; ++fw) mma16816_h(d[fw], a, bf[fh * 3 + fw][0], bf[fh * 3 + fw][1]);
+          // tap column fw reads window half 1 + c (pixel 0) and 1 + S + c (pixel 1), c = fw (forward) or 2 - fw
+          constexpr int C0 = TRANSPOSED ? 2 : 0, C1 = 1, C2 = TRANSPOSED ? 0 : 2;
+          fma_win<1 + C0, 0>(acc[0], w0, w1, w2, d[0][0]);
+          fma_win<1 + S + C0, 1>(acc[1], w0, w1, w2, d[0][0]);
+          fma_win<1 + C0, 0>(acc[2], v0, v1, v2, d[0][1]);
+          fma_win<1 + S + C0, 1>(acc[3], v0, v1, v2, d[0][1]);
+          fma_win<1 + C1, 0>(acc[0], w0, w1, w2, d[1][0]);
+          fma_win<1 + S + C1, 1>(acc[1], w0, w1, w2, d[1][0]);
+          fma_win<1 + C1, 0>(acc[2], v0, v1, v2, d[1][1]);
+          fma_win<1 + S + C1, 1>(acc[3], v0, v1, v2, d[1][1]);
+          fma_win<1 + C2, 0>(acc[0], w0, w1, w2, d[2][0]);
+          fma_win<1 + S + C2, 1>(acc[1], w0, w1, w2, d[2][0]);
+          fma_win<1 + C2, 0>(acc[2], v0, v1, v2, d[2][1]);
+          fma_win<1 + S + C2, 1>(acc[3], v0, v1, v2, d[2][1]);
         }
       }
-      }
       if (ow < Wd) {
-        __half* y0 = dst + (((size_t)n * g.C + c0 + cb16 + gq) * Hd + drow) * Wd + ow;
-        __half* y1 = y0 + (size_t)8 * Hd * Wd;
+        __half* y1 = y0 + 8 * dplane;
         if (dst_even) {
           *reinterpret_cast<__half2*>(y0) = __floats2half2_rn(acc[0], acc[1]);
           *reinterpret_cast<__half2*>(y1) = __floats2half2_rn(acc[2], acc[3]);
@@ -208,7 +209,7 @@ ConvPlan conv_plan(const Geom& g, bool transposed) {
   for (int bh = 1; bh <= Hd; ++bh) {
     const int rb = conv_band_rows(bh, S, transposed);
     const size_t smem = (size_t)pl.CG * band_pitch(rb, Wp) * 2 + (size_t)18 * band_pitch(transposed ? rb : bh, Wpo) * 2 +
-                        (size_t)pl.CG * kBankPitch * 2 + (size_t)pick_warps(bh * NB, 8) * kBetaWords * 4;
+                        (size_t)pl.CG * kBankPitch * 2;
     if (smem > budget) break;
     const long long ctas = (long long)((Hd + bh - 1) / bh) * pl.groups * g.N;
     if (bh > 1 && ctas < 2 * 148) break;
@@ -220,7 +221,7 @@ ConvPlan conv_plan(const Geom& g, bool transposed) {
   pl.warps = pick_warps(pl.BH * NB, 8);
   const int rb = conv_band_rows(pl.BH, S, transposed);
   pl.smem = (size_t)pl.CG * band_pitch(rb, Wp) * 2 + (size_t)18 * band_pitch(transposed ? rb : pl.BH, Wpo) * 2 +
-            (size_t)pl.CG * kBankPitch * 2 + (size_t)pl.warps * kBetaWords * 4;
+            (size_t)pl.CG * kBankPitch * 2;
   return pl;
 }
 
@@ -314,10 +315,7 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_rot_kernel(const __half* __res
     const int oh = oh0 + dr;
     if (oh >= g.Ho) break;
     const int ow0 = (item - dr * NB) << 3;
-    {
-      unsigned bf[9][2];  // not needed here: only (u, v) is kept
-      build_beta<S, false, true>(bf, T, uv, rband, br, g, oh, ow0, g.H, g.W, g.Wo, lane);
-    }
+    item_uv<S>(uv, rband, br, g, oh, ow0, lane);
     const int ow = ow0 + 2 * q;
     const int xoff = window_offset(bx, oh * S - 1, ow, S);
     const int yoff = kSlack + oh * by.Wp + ow - by.org;
@@ -493,8 +491,8 @@ __global__ void __launch_bounds__(256, 2) mma_filter_kernel(const __half* __rest
   __half* xband = reinterpret_cast<__half*>(smem_raw);
   __half* yband = xband + (size_t)pl.CG * xpitch;
   __half* rband = yband + (size_t)pl.CG * ypitch;  // [18][ypitch]
-  unsigned* tables = reinterpret_cast<unsigned*>(rband + (size_t)18 * ypitch);
-  unsigned* T = tables + warp * kBetaWords;
+  const LaneCells lc = lane_cells(g, q);
+  const bool sc44 = g.scH == 4 && g.scW == 4;
 
   float acc[4][2][4];  // up to 4 slabs of 16 channels x (cells 0-7 | cells 8-15)
 #pragma unroll
@@ -525,7 +523,7 @@ __global__ void __launch_bounds__(256, 2) mma_filter_kernel(const __half* __rest
       unsigned bw[10][2];  // beta as B fragments of the grad-bank product: [tap][cells 0-7 | cells 8-15]
       {
         unsigned bf[9][2];
-        build_beta<S, false, false>(bf, T, nullptr, rband, br, g, oh, ow0, g.H, g.W, g.Wo, lane);
+        beta_direct<S, false>(bf, rband, br, g, lc, sc44, oh, ow0, g.H, g.W, g.Wo, gq);
 #pragma unroll
         for (int t = 0; t < 9; ++t) {
           bw[t][0] = movmatrix_trans(bf[t][0]);
@@ -606,7 +604,7 @@ FiltPlan filt_plan(const Geom& g) {
   for (int bh = 1; bh <= g.Ho; ++bh) {
     const int warps = pick_warps(bh * NB, 8);
     size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + band_pitch(bh, Wpo)) * 2 +
-                  (size_t)18 * band_pitch(bh, Wpo) * 2 + (size_t)warps * kBetaWords * 4;
+                  (size_t)18 * band_pitch(bh, Wpo) * 2;
     const size_t red = (size_t)warps * pl.CG * 16 * 4;
     if (smem < red) smem = red;
     if (smem > budget) break;

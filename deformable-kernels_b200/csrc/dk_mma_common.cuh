@@ -30,6 +30,35 @@ __device__ __forceinline__ void mma16816_acc(float (&d)[4], unsigned a0, unsigne
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// d = a * b with fp16 output: d[0] = row gq, columns (2q, 2q+1); d[1] = row gq + 8.
+__device__ __forceinline__ void mma16816_h(unsigned (&d)[2], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f16.f16.f16.f16 {%0,%1}, {%2,%3,%4,%5}, {%6,%7}, {%8,%8};\n"
+      : "=r"(d[0]), "=r"(d[1])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0u));
+}
+// acc += half HA of a * half HB of b, product and sum in fp32 (sm_100 mixed-precision FMA)
+template <int HA, int HB>
+__device__ __forceinline__ void fma_hh(float& acc, unsigned a, unsigned b) {
+  if (HA == 0 && HB == 0)
+    asm("{\n .reg .b16 al, ah, bl, bh;\n mov.b32 {al, ah}, %1;\n mov.b32 {bl, bh}, %2;\n fma.rn.f32.f16 %0, al, bl, %0;\n}\n"
+        : "+f"(acc) : "r"(a), "r"(b));
+  else if (HA == 0 && HB == 1)
+    asm("{\n .reg .b16 al, ah, bl, bh;\n mov.b32 {al, ah}, %1;\n mov.b32 {bl, bh}, %2;\n fma.rn.f32.f16 %0, al, bh, %0;\n}\n"
+        : "+f"(acc) : "r"(a), "r"(b));
+  else if (HA == 1 && HB == 0)
+    asm("{\n .reg .b16 al, ah, bl, bh;\n mov.b32 {al, ah}, %1;\n mov.b32 {bl, bh}, %2;\n fma.rn.f32.f16 %0, ah, bl, %0;\n}\n"
+        : "+f"(acc) : "r"(a), "r"(b));
+  else
+    asm("{\n .reg .b16 al, ah, bl, bh;\n mov.b32 {al, ah}, %1;\n mov.b32 {bl, bh}, %2;\n fma.rn.f32.f16 %0, ah, bh, %0;\n}\n"
+        : "+f"(acc) : "r"(a), "r"(b));
+}
+// acc += (half IDX of the 6-half window held in w0, w1, w2) * (half KH of k)
+template <int IDX, int KH>
+__device__ __forceinline__ void fma_win(float& acc, unsigned w0, unsigned w1, unsigned w2, unsigned k) {
+  fma_hh<(IDX & 1), KH>(acc, IDX < 2 ? w0 : (IDX < 4 ? w1 : w2), k);
+}
+
 // transpose of an 8x8 block of 16-bit values held one row per 4 lanes (standard fragment layout)
 __device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
   unsigned d;
@@ -37,8 +66,8 @@ __device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
   return d;
 }
 
-__device__ __forceinline__ float lo2f(unsigned w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
-__device__ __forceinline__ float hi2f(unsigned w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
+__device__ __forceinline__ float lo2f(unsigned w) { return __low2float(*reinterpret_cast<const __half2*>(&w)); }
+__device__ __forceinline__ float hi2f(unsigned w) { return __high2float(*reinterpret_cast<const __half2*>(&w)); }
 __device__ __forceinline__ unsigned hmul2u(unsigned a, unsigned b) {
   __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
   return *reinterpret_cast<unsigned*>(&r);
@@ -160,20 +189,24 @@ __device__ __forceinline__ void load_band(__half* __restrict__ band, const Band&
     hi = lo + (r_e - r_s) * Ws;
   }
   const int head = lo >> 1, tail = (b.pitch_c - hi) >> 1;  // 4-byte words to zero in front / behind
-  for (int j = warp; j < cnt; j += nwarps) {
-    __half* ch = band + (size_t)j * b.pitch_c;
-    const __half* sp = s0 + (size_t)j * plane + gs;
+  const int esz = b.mode == 2 ? 8 : 2;                       // halves per copy
+  const int npiece = (hi - lo) / esz;
+  __half* ch = band + (size_t)warp * b.pitch_c;
+  const __half* sp = s0 + (size_t)warp * plane + gs;
+  const size_t sstep = (size_t)nwarps * plane;
+  const int dstep = nwarps * b.pitch_c;
+  for (int j = warp; j < cnt; j += nwarps, ch += dstep, sp += sstep) {
     if (b.mode == 2) {
-      const int nvec = (hi - lo) >> 3;
-      for (int v = lane; v < nvec; v += 32) cp_async16(ch + lo + v * 8, sp + v * 8);
+      for (int v = lane; v < npiece; v += 32) cp_async16(ch + lo + v * 8, sp + v * 8);
     } else {
-      const int nw = (hi - lo) >> 1;
-      for (int v = lane; v < nw; v += 32) cp_async4(ch + lo + v * 2, sp + v * 2);
+      for (int v = lane; v < npiece; v += 32) cp_async4(ch + lo + v * 2, sp + v * 2);
     }
     unsigned* zw = reinterpret_cast<unsigned*>(ch);
-    for (int v = lane; v < head; v += 32) zw[v] = 0u;
+    if (lane < head) zw[lane] = 0u;
+    for (int v = lane + 32; v < head; v += 32) zw[v] = 0u;
     unsigned* zt = reinterpret_cast<unsigned*>(ch + hi);
-    for (int v = lane; v < tail; v += 32) zt[v] = 0u;
+    if (lane < tail) zt[lane] = 0u;
+    for (int v = lane + 32; v < tail; v += 32) zt[v] = 0u;
   }
 }
 
@@ -258,6 +291,110 @@ __device__ __forceinline__ void build_beta(unsigned (&bf)[9][2], unsigned* __res
       }
     }
     __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------- beta fragments, computed per lane
+// Same fragments as build_beta, without the table: lane (gq, q) evaluates the hat products of
+// pixel ow0 + gq at its own four cells (2q, 2q+1, 2q+8, 2q+9) for each tap.  ca/cb are the (row,
+// column) of those cells as floats, cellok marks cells that exist (scope smaller than 16 cells);
+// SC44 = 4x4 scope, where the four cells share two rows and two columns.
+struct LaneCells {
+  float ca[4], cb[4];
+  bool ok[4];
+};
+__device__ __forceinline__ LaneCells lane_cells(const Geom& g, int q) {
+  LaneCells lc;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int cell = 2 * q + (k & 1) + (k >> 1) * 8;
+    lc.ok[k] = cell < g.cells;
+    const int a = cell / g.scW;
+    lc.ca[k] = (float)a;
+    lc.cb[k] = (float)(cell - a * g.scW);
+  }
+  return lc;
+}
+__device__ __forceinline__ float hat(float t) { return fmaxf(0.f, 1.f - fabsf(t)); }
+__device__ __forceinline__ unsigned pack2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const unsigned*>(&h);
+}
+
+template <int S, bool TRANSPOSED>
+__device__ __forceinline__ void beta_direct(unsigned (&bf)[9][2], const __half* __restrict__ rband, const Band& rb,
+                                            const Geom& g, const LaneCells& lc, bool sc44, int drow, int ow0, int Hs, int Ws,
+                                            int Wd, int gq) {
+  const int pc = ow0 + gq;
+  int roff[3], coff[3];
+  bool rok[3], cok[3];
+#pragma unroll
+  for (int f = 0; f < 3; ++f) {
+    if (!TRANSPOSED) {
+      const int sr = drow * S - 1 + f, sc = pc * S - 1 + f;
+      rok[f] = sr >= 0 && sr < Hs;
+      cok[f] = pc < Wd && sc >= 0 && sc < Ws;
+      roff[f] = drow * rb.Wp;
+      coff[f] = pc;
+    } else {
+      const int tr = drow + 1 - f, tc = pc + 1 - f;
+      const int orow = S == 1 ? tr : tr >> 1, ocol = S == 1 ? tc : tc >> 1;
+      rok[f] = tr >= 0 && (S == 1 || !(tr & 1)) && orow < Hs;
+      cok[f] = pc < Wd && tc >= 0 && (S == 1 || !(tc & 1)) && ocol < Ws;
+      roff[f] = rok[f] ? orow * rb.Wp : 0;
+      coff[f] = cok[f] ? ocol : 0;
+    }
+  }
+  const float uh0 = (float)(g.scH - 3) * 0.5f, uw0 = (float)(g.scW - 3) * 0.5f;
+  const __half* base = rband + kSlack - rb.org;
+  const int p2 = 2 * rb.pitch_c;
+#pragma unroll
+  for (int fh = 0; fh < 3; ++fh) {
+#pragma unroll
+    for (int fw = 0; fw < 3; ++fw) {
+      const int t = fh * 3 + fw;
+      const bool ok = rok[fh] && cok[fw];
+      const __half* rp = base + t * p2 + roff[fh] + coff[fw];
+      const float u = ((float)fh + __half2float(rp[0])) + uh0;
+      const float v = ok ? ((float)fw + __half2float(rp[rb.pitch_c])) + uw0 : 1e30f;  // unused tap: every hat is 0
+      if (sc44) {
+        const float hh0 = hat(u - lc.ca[0]), hh1 = hat(u - lc.ca[2]);
+        const float hw0 = hat(v - lc.cb[0]), hw1 = hat(v - lc.cb[1]);
+        bf[t][0] = pack2(hh0 * hw0, hh0 * hw1);
+        bf[t][1] = pack2(hh1 * hw0, hh1 * hw1);
+      } else {
+        float b4[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) b4[k] = lc.ok[k] ? hat(u - lc.ca[k]) * hat(v - lc.cb[k]) : 0.f;
+        bf[t][0] = pack2(b4[0], b4[1]);
+        bf[t][1] = pack2(b4[2], b4[3]);
+      }
+    }
+  }
+}
+
+// Bank coordinates (u, v) of the 72 (pixel, tap) pairs of an item, left in uv[tap*8 + pixel]
+// (u = 1e30 marks a tap that is unused: in the padding or outside the bank).  Lanes 0..23, three passes.
+template <int S>
+__device__ __forceinline__ void item_uv(float2* __restrict__ uv, const __half* __restrict__ rband, const Band& rb, const Geom& g,
+                                        int drow, int ow0, int lane) {
+  const float uh0 = (float)(g.scH - 3) * 0.5f, uw0 = (float)(g.scW - 3) * 0.5f;
+  const int px = lane & 7, fw = lane >> 3;
+  const int pc = ow0 + px;
+  const int sc = pc * S - 1 + fw;
+  const bool cok = pc < g.Wo && sc >= 0 && sc < g.W;
+  const __half* base = rband + kSlack - rb.org + drow * rb.Wp + pc;
+  if (lane < 24) {
+#pragma unroll
+    for (int fh = 0; fh < 3; ++fh) {
+      const int t = fh * 3 + fw;
+      const int sr = drow * S - 1 + fh;
+      const __half* rp = base + (size_t)(2 * t) * rb.pitch_c;
+      const float u = ((float)fh + __half2float(rp[0])) + uh0;
+      const float v = ((float)fw + __half2float(rp[rb.pitch_c])) + uw0;
+      const bool valid = cok && sr >= 0 && sr < g.H && u > -1.f && v > -1.f && u < (float)g.scH && v < (float)g.scW;
+      uv[t * 8 + px] = make_float2(valid ? u : 1e30f, v);
+    }
   }
 }
 
