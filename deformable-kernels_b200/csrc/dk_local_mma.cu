@@ -98,6 +98,7 @@ __global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restri
     const int xstep = 16 * bx.pitch_c, x8 = 8 * bx.pitch_c;
     const size_t dplane = (size_t)Hd * Wd;
     __half* y0 = dst + ((size_t)n * g.C + c0 + gq) * dplane + (size_t)drow * Wd + ow;
+#pragma unroll 2
     for (int cb16 = 0; cb16 < cnt; cb16 += 16, bkp += 16 * kBankPitch / 2, x0 += xstep, y0 += 16 * dplane) {
       unsigned a[4];
       a[0] = bkp[0];
