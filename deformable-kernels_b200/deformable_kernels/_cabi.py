@@ -39,6 +39,8 @@ _PROTOS = {
     "dk_sample_depthwise_backward_data": (_int, [_vp, _vp, _vp, _vp, _gp, _int, _vp]),
     "dk_sample_depthwise_backward_filter_workspace_bytes": (_sz, [_gp, _int]),
     "dk_sample_depthwise_backward_filter": (_int, [_vp, _vp, _vp, _vp, _gp, _int, _vp, _sz, _vp]),
+    "dk_sample_depthwise_backward_filter_noalloc_max_bytes": (_sz, []),
+    "dk_sample_depthwise_backward_filter_noalloc": (_int, [_vp, _vp, _vp, _vp, _gp, _int, _vp]),
     "dk_sample_depthwise_backward_rotation_workspace_bytes": (_sz, [_gp, _int]),
     "dk_sample_depthwise_backward_rotation": (_int, [_vp, _vp, _vp, _vp, _vp, _gp, _int, _vp, _sz, _vp]),
     "dk_sample_depthwise_backward_workspace_bytes": (_sz, [_gp, _int]),

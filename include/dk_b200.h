@@ -91,6 +91,19 @@ int dk_sample_depthwise_backward_filter(const void *grad_output, const void *inp
                                         void *grad_filter, const dk_geom *g, int dtype, void *workspace,
                                         size_t workspace_bytes, void *stream);
 
+/* No counterpart in the reference.  Same result as dk_sample_depthwise_backward_filter, for callers
+ * that cannot supply a workspace because they may not allocate device memory at call time (plugins
+ * inside a memory-planned runtime, fixed-memory control loops, FFI hosts without a CUDA allocator):
+ * the partial sums go to a fixed array built into the library, at most
+ * dk_sample_depthwise_backward_filter_noalloc_max_bytes() (8 MiB, held by every GPU that loads the
+ * library until the process exits).  Nothing is allocated or freed on this path.  Shapes that need
+ * more return DK_ERR_WORKSPACE.  All calls on one device share that array, so calls that overlap
+ * on the GPU race: serialise them.  The first call on a device queries the array's address; make
+ * it before any stream capture begins. */
+size_t dk_sample_depthwise_backward_filter_noalloc_max_bytes(void);
+int dk_sample_depthwise_backward_filter_noalloc(const void *grad_output, const void *input, const void *rotation,
+                                                void *grad_filter, const dk_geom *g, int dtype, void *stream);
+
 /* replaces sample_depthwise_backward_rotation_cuda, csrc/filter_sample_depthwise_cuda.cpp:178-235.
  * The workspace (fp32 partial sums over channel groups, used for fp16 tensors on small planes)
  * may be 0 bytes; ask dk_sample_depthwise_backward_rotation_workspace_bytes(). */
