@@ -126,6 +126,127 @@ def cpu_sweep(n_img, threads=None):
     return total
 
 
+def other_configs(dev, time_call):
+    """BASELINE.json configs 1, 2 and 4 (parity-test cases, not the headline): device-timed forward + backward."""
+    import dk_cases
+    from deformable_kernels.modules import GlobalDeformKernel2d
+    from deformable_kernels.ops.deform_kernel.functions import deform_sample_depthwise, nd_linear_sample, sample_depthwise
+    out = {}
+
+    def fb(fn, ins, dy):
+        def run():
+            y = fn(*ins)
+            torch.autograd.grad(y, ins, dy)
+        return run
+
+    c1 = dk_cases.cfg1()
+    ins = [c1[k].to(dev).requires_grad_(True) for k in ("input", "rotation", "weight")]
+    t = time_call(fb(lambda x, r, w: sample_depthwise(x, r, w, **c1["args"]), ins, c1["grad_output"].to(dev)), 20)
+    out["cfg1 local DK N=2 C=64 28x28 fp32"] = {"fwd_bwd_us": round(t * 1e3, 1), "algorithmic_MB": 2.36}
+
+    c2 = dk_cases.cfg2()
+    ins = [c2[k].to(dev).requires_grad_(True) for k in ("data", "coord")]
+    t = time_call(fb(nd_linear_sample, ins, c2["grad_output"].to(dev)), 20)
+    out["cfg2 nd_linear_sample C=256 2x2, 32 samples fp32"] = {"fwd_bwd_us": round(t * 1e3, 1), "algorithmic_MB": 0.079}
+    m = GlobalDeformKernel2d((2, 2), 256, 256, kernel_size=1, groups=256).to(dev)
+    x2 = c2["input"].to(dev).requires_grad_(True)
+
+    def mod():
+        y = m(x2)
+        torch.autograd.grad(y.sum(), [x2, m.weight, m.fc.weight])
+    t = time_call(mod, 10)
+    out["cfg2 GlobalDeformKernel2d module N=32 C=256 14x14 fp32"] = {"fwd_bwd_us": round(t * 1e3, 1), "algorithmic_MB": 32.3}
+
+    n4 = 64
+    g = torch.Generator(device=dev).manual_seed(4)
+    w = (torch.randn(256, 1, 4, 4, device=dev, generator=g) * 0.354).half().requires_grad_(True)
+    x = torch.randn(n4, 256, 56, 56, device=dev, generator=g).half().requires_grad_(True)
+    rot = (torch.randn(n4, 18, 56, 56, device=dev, generator=g) * 0.5).half().requires_grad_(True)
+    off = (torch.randn(n4, 18, 56, 56, device=dev, generator=g) * 2.0).half().requires_grad_(True)
+    dy = torch.randn(n4, 256, 56, 56, device=dev, generator=g).half()
+    t = time_call(fb(lambda a, o, r, b: deform_sample_depthwise(a, o, r, b), [x, off, rot, w], dy), 3)
+    out["cfg4 DK+DCN N=64 C=256 56x56 fp16"] = {"fwd_bwd_ms": round(t, 3), "images_per_s": round(n4 / (t * 1e-3), 1),
+                                                  "GBps": round(557.2e6 / (t * 1e-3) / 1e9, 1), "algorithmic_MB": 557.2}
+    return out
+
+
+def build_mobilenet_dk():
+    """torchvision's MobileNetV2-1.0 skeleton (random init; the reference ships no model) with each of its 17
+    depthwise 3x3 convolutions replaced by DeformKernel2d((4, 4), C, C, 3, stride, 1, groups=C)."""
+    import torchvision
+    from deformable_kernels.modules import DeformKernel2d
+    model = torchvision.models.mobilenet_v2(weights=None)
+    replaced = 0
+    for mod in model.modules():
+        for name, child in list(mod.named_children()):
+            if isinstance(child, torch.nn.Conv2d) and child.kernel_size == (3, 3) and child.groups == child.in_channels \
+                    and child.groups > 1:
+                dk = DeformKernel2d((4, 4), child.in_channels, child.out_channels, 3, child.stride[0], 1, groups=child.groups)
+                torch.nn.init.normal_(dk.rotation_conv.weight, std=0.01)
+                torch.nn.init.zeros_(dk.rotation_conv.bias)
+                setattr(mod, name, dk)
+                replaced += 1
+    return model, replaced
+
+
+def run_training_step(args, rank, world, local, dev):
+    """BASELINE.json config 5: forward + backward + SGD step of MobileNetV2-DK on synthetic 224x224 images, fp16
+    autocast, global batch sharded over the ranks, gradients all-reduced by NCCL through DDP."""
+    import torch.distributed as dist
+    torch.manual_seed(0)
+    model, replaced = build_mobilenet_dk()
+    model = model.to(dev).to(memory_format=torch.contiguous_format)
+    if world > 1:
+        model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local])
+    opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+    per_gpu = args.global_batch // world
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    x = torch.randn(per_gpu, 3, 224, 224, device=dev, generator=gen)
+    labels = torch.randint(0, 1000, (per_gpu,), device=dev, generator=gen)
+    loss_fn = torch.nn.CrossEntropyLoss()
+    scaler = torch.amp.GradScaler("cuda", init_scale=1024.0)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.float16):
+            loss = loss_fn(model(x), labels)
+        scaler.scale(loss).backward()
+        scaler.step(opt)
+        scaler.update()
+        return loss
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0.record()
+    for _ in range(args.steps):
+        loss = step()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    tms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms_step = float(tms.item()) / args.steps
+    if rank == 0:
+        print(json.dumps({
+            "metric": "MobileNetV2-DK training step images/sec (global batch %d, fp16 autocast)" % args.global_batch,
+            "value": args.global_batch / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16 autocast, f32 master weights", "data": "synthetic",
+            "config": {"workload": "cfg5: MobileNetV2-1.0 with %d DeformKernel2d layers (scope 4x4), 224x224, SGD step, "
+                                   "DDP/NCCL gradient all-reduce" % replaced, "per_gpu_batch": per_gpu},
+            "loss": float(loss.item()), "clocks": clocks, "peak_mem_GB": round(torch.cuda.max_memory_allocated() / 1e9, 1)}))
+
+
 def time_reference_gpu(layers, n, time_call):
     """The reference's own CUDA kernels (unmodified extension from oracle/_ref/) on the same
     tensors: forward and the three backward launches per layer, device-timed.  A side
@@ -154,6 +275,7 @@ def run_reference(args, rank):
     if rank != 0:
         return
     from oracle import dk_oracle as O
+    O.set_threads(os.cpu_count() or 1)  # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every host core
     cores = O.max_threads()
     n_img = 4
     for _ in range(args.warmup):
@@ -185,6 +307,10 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-other-configs", action="store_true")
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "train"],
+                    help="sweep: the DK layer sweep (headline); train: MobileNetV2-DK training step, global batch 1024")
+    ap.add_argument("--global-batch", type=int, default=1024)
     ap.add_argument("--layers", default="", help="comma-separated indices into the ten-layer sweep (default: all)")
     ap.add_argument("--ref-gpu", action="store_true",
                     help="also time the reference's own CUDA kernels (oracle/_ref build) on this GPU")
@@ -207,6 +333,11 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "train":
+        run_training_step(args, rank, world, local, dev)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     n = args.batch
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -349,9 +480,14 @@ def main():
     if args.ref_gpu and rank == 0:
         ref_gpu = time_reference_gpu(layers, n, time_call)
 
+    others = None
+    if rank == 0 and world == 1 and not args.no_other_configs:
+        others = other_configs(dev, time_call)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import dk_oracle as O
+        O.set_threads(os.cpu_count() or 1)
         n_img = 16
         cpu_sweep(1)
         sec = cpu_sweep(n_img)
@@ -372,7 +508,7 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * len(layers) * 5, "clocks": clocks, "per_layer": per_layer,
-            "reference_cuda_on_this_gpu": ref_gpu,
+            "reference_cuda_on_this_gpu": ref_gpu, "other_configs": others,
             "kernel_ms_sum_over_layers": {k: round(v, 4) for k, v in kern_tot.items()},
         }
         print(json.dumps(line))
