@@ -18,6 +18,8 @@
 // Covers: fp16, 3x3 kernel, dilation 1, pad 1, stride 1 or 2 (equal in h and w), one rotation
 // group, at most 16 bank cells, channels a multiple of 16.
 // Everything else stays on the SIMT kernels of dk_local.cu.
+#include <cstdlib>
+
 #include "dk_mma_common.cuh"
 
 namespace dk {
@@ -41,7 +43,7 @@ __host__ __device__ inline int conv_band_rows(int bh, int S, bool transposed) {
 }
 
 template <int S, bool TRANSPOSED>
-__global__ void __launch_bounds__(256, 2) mma_conv_kernel(const __half* __restrict__ src, const __half* __restrict__ rot,
+__global__ void __launch_bounds__(448, 2) mma_conv_kernel(const __half* __restrict__ src, const __half* __restrict__ rot,
                                                           const __half* __restrict__ w, __half* __restrict__ dst, const Geom g,
                                                           const ConvPlan pl) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -201,11 +203,14 @@ ConvPlan conv_plan(const Geom& g, bool transposed) {
   const int Hd = transposed ? g.H : g.Ho, Wd = transposed ? g.W : g.Wo;
   const int Ws = transposed ? g.Wo : g.W;
   const int Wp = Ws + (Ws & 1), Wpo = g.Wo + (g.Wo & 1);
-  const int ngrp = (g.C + 127) / 128;
+  int cgmax = 128;
+  if (const char* e = std::getenv("DK_B200_CONV_CG")) cgmax = atoi(e) > 0 ? atoi(e) : cgmax;  // tuning knob
+  const int ngrp = (g.C + cgmax - 1) / cgmax;
   pl.CG = (((g.C + ngrp - 1) / ngrp) + 15) & ~15;
   pl.groups = (g.C + pl.CG - 1) / pl.CG;
   const int NB = (Wd + 7) / 8;
-  const size_t budget = kTwoPerSm;
+  size_t budget = kTwoPerSm;
+  if (const char* e = std::getenv("DK_B200_CONV_SMEM_KB")) budget = (size_t)atoi(e) * 1024;  // tuning knob
   int best = 1;
   for (int bh = 1; bh <= Hd; ++bh) {
     const int rb = conv_band_rows(bh, S, transposed);
@@ -219,7 +224,7 @@ ConvPlan conv_plan(const Geom& g, bool transposed) {
   }
   pl.BH = best;
   pl.bands = (Hd + pl.BH - 1) / pl.BH;
-  pl.warps = pick_warps(pl.BH * NB, 8);
+  pl.warps = pick_warps(pl.BH * NB, 14);
   const int rb = conv_band_rows(pl.BH, S, transposed);
   pl.smem = (size_t)pl.CG * band_pitch(rb, Wp) * 2 + (size_t)18 * band_pitch(transposed ? rb : pl.BH, Wpo) * 2 +
             (size_t)pl.CG * kBankPitch * 2;
