@@ -58,6 +58,12 @@ def kernel_bytes(name, n, c, hw, s, e=2):
                 "backward_filter": y + x + rot + w}[name]
 
 
+# DRAM bytes (read + write) per launch of each fast-path kernel on the largest layer, from one ncu capture at batch 64
+# (dram__bytes_read.sum + dram__bytes_write.sum, profiles/local_dk_mma_kernels_C96_112x112_batch64.md); traffic grows in
+# proportion to the batch, so it is scaled by batch / 64.
+NCU_TRAFFIC_BATCH64 = {"forward": 298.2e6, "backward_data": 298.2e6, "backward_rotation": 361.8e6, "backward_filter": 387.1e6}
+
+
 def measured_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -432,7 +438,8 @@ def main():
                                                                                              bt["s"], n),
                 "achieved": round(achieved, 1), "peak": peak, "peak_source": peak_kind, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "frac_of_nominal_8TBs": round(achieved / HBM_NOMINAL_GBS, 4),
-                "traffic": None, "kernel_ms": round(bkt[dom], 4),
+                "traffic": (NCU_TRAFFIC_BATCH64[dom] * n / 64.0) if (bt["c"], bt["hw"], bt["s"]) == (96, 112, 1) else None,
+                "algorithmic_bytes": kb, "kernel_ms": round(bkt[dom], 4),
                 "sweep_fwd_bwd_GBps": round(sweep_gbs, 1), "sweep_frac": round(sweep_gbs / peak, 4)}
 
     # end to end: pinned host inputs -> device, forward + backward, all results -> pinned host
