@@ -455,16 +455,33 @@ def main():
     h2d = sum(h[k].numel() * 2 for h in host for k in ("x", "rot", "dy"))
     d2h = sum(h[k].numel() * 2 for h in host for k in ("y", "gx", "gr", "gw"))
 
+    # Three streams so that PCIe carries inputs and results at the same time as the kernels run: copy-in of
+    # layer k+1, compute of layer k and copy-out of layer k-1 overlap; everything still happens inside the timed step.
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    s_cmp = torch.cuda.current_stream(dev)
+    dev_in = [{k: torch.empty_like(t[k]) for k in ("x", "rot", "dy")} for t in layers]
+
     def e2e_step():
-        for t, h in zip(layers, host):
-            x = h["x"].to(dev, non_blocking=True)
-            rot = h["rot"].to(dev, non_blocking=True)
-            dy = h["dy"].to(dev, non_blocking=True)
-            y, gx, gr, gw = fwd_bwd(t, x, rot, dy)
-            h["y"].copy_(y.detach(), non_blocking=True)
-            h["gx"].copy_(gx, non_blocking=True)
-            h["gr"].copy_(gr, non_blocking=True)
-            h["gw"].copy_(gw, non_blocking=True)
+        ready = []
+        for t, h, d in zip(layers, host, dev_in):
+            with torch.cuda.stream(s_in):
+                for k in ("x", "rot", "dy"):
+                    d[k].copy_(h[k], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(s_in)
+            ready.append(ev)
+        for t, h, d, ev in zip(layers, host, dev_in, ready):
+            s_cmp.wait_event(ev)
+            y, gx, gr, gw = fwd_bwd(t, d["x"].detach(), d["rot"].detach(), d["dy"])
+            done = torch.cuda.Event()
+            done.record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                for src, key in ((y.detach(), "y"), (gx, "gx"), (gr, "gr"), (gw, "gw")):
+                    src.record_stream(s_out)
+                    h[key].copy_(src, non_blocking=True)
+        s_cmp.wait_stream(s_out)
+        s_in.wait_stream(s_cmp)
         torch.cuda.synchronize()
 
     e2e_val = None
