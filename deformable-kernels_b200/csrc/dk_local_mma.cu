@@ -474,13 +474,14 @@ RotPlan rot_plan(const Geom& g) {
 
 // ------------------------------------------------------------------ grad-bank
 struct FiltPlan {
+  bool big;  // six channel slabs per block, one block of up to 14 warps per SM
   int BH, CG, groups, warps, bands, units_per_block, blocks_x;
   int mode_x, mode_dy, mode_rot;
   size_t smem, ws_bytes;
 };
 
-template <int S>
-__global__ void __launch_bounds__(256, 2) mma_filter_kernel(const __half* __restrict__ dy, const __half* __restrict__ x,
+template <int S, int NS, int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __restrict__ dy, const __half* __restrict__ x,
                                                             const __half* __restrict__ rot, float* __restrict__ partial,
                                                             const Geom g, const FiltPlan pl) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -500,9 +501,9 @@ __global__ void __launch_bounds__(256, 2) mma_filter_kernel(const __half* __rest
   const LaneCells lc = lane_cells(g, q);
   const bool sc44 = g.scH == 4 && g.scW == 4;
 
-  float acc[4][2][4];  // up to 4 slabs of 16 channels x (cells 0-7 | cells 8-15)
+  float acc[NS][2][4];  // up to NS slabs of 16 channels x (cells 0-7 | cells 8-15)
 #pragma unroll
-  for (int sidx = 0; sidx < 4; ++sidx)
+  for (int sidx = 0; sidx < NS; ++sidx)
 #pragma unroll
     for (int k = 0; k < 4; ++k) acc[sidx][0][k] = acc[sidx][1][k] = 0.f;
 
@@ -541,7 +542,7 @@ __global__ void __launch_bounds__(256, 2) mma_filter_kernel(const __half* __rest
       const int xoff = window_offset(bx, oh * S - 1, ow, S);
       const int yoff = kSlack + oh * by.Wp + ow - by.org;
 #pragma unroll
-      for (int sidx = 0; sidx < 4; ++sidx) {
+      for (int sidx = 0; sidx < NS; ++sidx) {
         if (sidx < nslab) {
           const int cb16 = sidx << 4;
           const unsigned dy0 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq) * by.pitch_c + yoff);
@@ -569,7 +570,7 @@ __global__ void __launch_bounds__(256, 2) mma_filter_kernel(const __half* __rest
   __syncthreads();
   float* red = reinterpret_cast<float*>(smem_raw);  // [nwarps][CG][16]
 #pragma unroll
-  for (int sidx = 0; sidx < 4; ++sidx) {
+  for (int sidx = 0; sidx < NS; ++sidx) {
     if (sidx < nslab) {
       float* r0 = red + ((size_t)warp * pl.CG + (sidx << 4) + gq) * 16;
       float* r1 = r0 + 8 * 16;
@@ -587,28 +588,38 @@ __global__ void __launch_bounds__(256, 2) mma_filter_kernel(const __half* __rest
   }
 }
 
-// out[c][cell] = sum over blocks of partial[block][c][16], fixed order
+// out[c][cell] = sum over blocks of partial[block][c][16]; one warp per output, fixed summation tree
 __global__ void reduce_bank_partials_kernel(const float* __restrict__ partial, __half* __restrict__ out, int C, int cells,
                                             int nblocks) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
   if (i >= C * cells) return;
   const int c = i / cells, cell = i - c * cells;
   float s = 0.f;
-  for (int k = 0; k < nblocks; ++k) s += partial[((size_t)k * C + c) * 16 + cell];
-  out[i] = __float2half_rn(s);
+  for (int k = lane; k < nblocks; k += 32) s += partial[((size_t)k * C + c) * 16 + cell];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) out[i] = __float2half_rn(s);
 }
 
 FiltPlan filt_plan(const Geom& g) {
   FiltPlan pl;
   const int S = g.sH;
-  pl.CG = (g.C % 64 == 0) ? 64 : (g.C % 48 == 0) ? 48 : (g.C % 32 == 0) ? 32 : 16;
+  // Two shapes of block: up to four channel slabs and two blocks per SM, or six slabs in one block of up to
+  // 14 warps per SM.  The second halves the hat-product work per slab; it pays on wide rows where the first
+  // would be stuck with three slabs (measured: C = 96 at 112 x 112).
+  const int cg_small = (g.C % 64 == 0) ? 64 : (g.C % 48 == 0) ? 48 : (g.C % 32 == 0) ? 32 : 16;
+  const int cg_big = (g.C % 96 == 0) ? 96 : (g.C % 80 == 0) ? 80 : cg_small;
+  pl.big = cg_big >= 2 * cg_small && (g.Wo + 7) / 8 >= 14;
+  if (const char* e = std::getenv("DK_B200_FILT_BIG")) pl.big = atoi(e) != 0;  // tuning knob
+  pl.CG = pl.big ? cg_big : cg_small;
   pl.groups = g.C / pl.CG;
   const int NB = (g.Wo + 7) / 8;
   const int Wp = g.W + (g.W & 1), Wpo = g.Wo + (g.Wo & 1);
-  const size_t budget = kTwoPerSm;
+  const size_t budget = pl.big ? kOnePerSm : kTwoPerSm;
   pl.BH = 0;
   for (int bh = 1; bh <= g.Ho; ++bh) {
-    const int warps = pick_warps(bh * NB, 8);
+    const int warps = pick_warps(bh * NB, pl.big ? 14 : 8);
     size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + band_pitch(bh, Wpo)) * 2 +
                   (size_t)18 * band_pitch(bh, Wpo) * 2;
     const size_t red = (size_t)warps * pl.CG * 16 * 4;
@@ -622,7 +633,7 @@ FiltPlan filt_plan(const Geom& g) {
   if (!pl.BH) return pl;
   pl.bands = (g.Ho + pl.BH - 1) / pl.BH;
   const long long units = (long long)g.N * pl.bands;
-  long long want = (4LL * 148 + pl.groups - 1) / pl.groups;  // ~4 blocks per SM over the grid
+  long long want = ((pl.big ? 2LL : 4LL) * 148 + pl.groups - 1) / pl.groups;  // a few blocks per SM over the grid
   if (want > units) want = units;
   if (want < 1) want = 1;
   pl.units_per_block = (int)((units + want - 1) / want);
@@ -702,18 +713,21 @@ int local_filter_mma(const __half* dy, const __half* x, const __half* rot, __hal
   pl.mode_rot = ptr_mode(rot);
   int rc;
   float* partial = reinterpret_cast<float*>(ws);
-  if (g.sH == 1) {
-    auto kern = mma_filter_kernel<1>;
-    if ((rc = enable_smem(kern, pl.smem))) return rc;
-    kern<<<dim3(pl.blocks_x, pl.groups), pl.warps * 32, pl.smem, s>>>(dy, x, rot, partial, g, pl);
-  } else {
-    auto kern = mma_filter_kernel<2>;
-    if ((rc = enable_smem(kern, pl.smem))) return rc;
-    kern<<<dim3(pl.blocks_x, pl.groups), pl.warps * 32, pl.smem, s>>>(dy, x, rot, partial, g, pl);
+#define DK_LAUNCH_FILT(SS, NS, MAXT, MINB)                                                            \
+  {                                                                                                 \
+    auto kern = mma_filter_kernel<SS, NS, MAXT, MINB>;                                              \
+    if ((rc = enable_smem(kern, pl.smem))) return rc;                                               \
+    kern<<<dim3(pl.blocks_x, pl.groups), pl.warps * 32, pl.smem, s>>>(dy, x, rot, partial, g, pl);  \
   }
+  if (g.sH == 1) {
+    if (pl.big) DK_LAUNCH_FILT(1, 6, 448, 1) else DK_LAUNCH_FILT(1, 4, 256, 2)
+  } else {
+    if (pl.big) DK_LAUNCH_FILT(2, 6, 448, 1) else DK_LAUNCH_FILT(2, 4, 256, 2)
+  }
+#undef DK_LAUNCH_FILT
   if ((rc = check_launch())) return rc;
   const int n_out = g.C * g.cells;
-  reduce_bank_partials_kernel<<<(n_out + 255) / 256, 256, 0, s>>>(partial, dw, g.C, g.cells, pl.blocks_x);
+  reduce_bank_partials_kernel<<<(n_out + 7) / 8, 256, 0, s>>>(partial, dw, g.C, g.cells, pl.blocks_x);
   return check_launch();
 }
 

@@ -9,7 +9,7 @@ state dicts are interchangeable: ``weight``, ``fc.*``; ``rotation_conv.*``,
 import torch
 from torch import nn
 
-from ..ops.deform_kernel.functions import nd_linear_sample
+from ..ops.deform_kernel.functions import nd_linear_sample, plane_scale
 from ..ops.deform_kernel.modules import SampleDepthwise, DeformableSampleDepthwise
 
 __all__ = ['GlobalDeformKernel2d', 'LocalDeformKernel2d', 'DeformKernel2d', 'DeformKernelConv2d']
@@ -67,9 +67,16 @@ class GlobalDeformKernel2d(nn.Module):
         return sample.transpose(1, 2).reshape(n * self.out_planes, self.in_planes // self.group, self.kernel_size,
                                               self.kernel_size)
 
+    def _is_plane_scale(self):
+        return (self.kernel_size == 1 and self.stride in (1, (1, 1)) and self.padding in (0, (0, 0)) and
+                self.group == self.in_planes == self.out_planes)
+
     def forward(self, x):
         n, c, h, w = x.shape
         weight = self.dynamic_weight(x, self.weight).to(x.dtype)
+        if self._is_plane_scale() and x.is_cuda:
+            # 1x1 depthwise: the per-sample grouped convolution is a per-plane scale
+            return plane_scale(x, weight.view(n, c))
         out = nn.functional.conv2d(x.reshape(1, n * c, h, w), weight, stride=self.stride, padding=self.padding,
                                    dilation=self.dilation, groups=n * self.group)
         return out.view(n, self.out_planes, out.shape[2], out.shape[3])

@@ -1,4 +1,5 @@
 from .filter_sample_depthwise import sample_depthwise, deform_sample_depthwise
 from .nd_linear_sample import nd_linear_sample
+from .plane_scale import plane_scale
 
-__all__ = ['sample_depthwise', 'deform_sample_depthwise', 'nd_linear_sample']
+__all__ = ['sample_depthwise', 'deform_sample_depthwise', 'nd_linear_sample', 'plane_scale']

@@ -188,6 +188,16 @@ int dk_nd_linear_sample_backward_coord_sum(const void *grad_output, const void *
                                            void *grad_coord, int batch, int channels, int dims, const int *shape,
                                            int dtype, void *stream);
 
+/* ---------------------------------------------------------------- global DK with a 1x1 depthwise kernel
+ * The reference evaluates it as F.conv2d(x.view(1, N*C, H, W), weight[N*C,1,1,1], groups=N*C)
+ * (modules/deform_kernel.py:105-118): y[plane, :] = x[plane, :] * scale[plane], plane = n*C + c.
+ * Backward gives grad_input = grad_output * scale and grad_scale[plane] = sum(grad_output * input);
+ * either output may be NULL. */
+int dk_plane_scale_forward(const void *input, const void *scale, void *output, long long planes, int plane_size,
+                           int dtype, void *stream);
+int dk_plane_scale_backward(const void *grad_output, const void *input, const void *scale, void *grad_input,
+                            void *grad_scale, long long planes, int plane_size, int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -168,6 +168,21 @@ def test_local_dk_fp16_fast_path_matches_oracle(ops, oracle, cfg):
     compare(mine_local(ops, case, torch.float16), oracle_local(oracle, case, torch.float16), torch.float16, "fast")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.float64])
+def test_plane_scale_is_the_per_sample_grouped_1x1_conv(ops, dtype):
+    gen = torch.Generator().manual_seed(37)
+    x = torch.randn(5, 12, 7, 9, generator=gen).to(dtype).to(DEV).requires_grad_(True)
+    k = torch.randn(5, 12, generator=gen).to(dtype).to(DEV).requires_grad_(True)
+    dy = torch.randn(5, 12, 7, 9, generator=gen).to(dtype).to(DEV)
+    y = ops.plane_scale(x, k)
+    gx, gk = torch.autograd.grad(y, [x, k], dy)
+    xr, kr = x.detach().double().requires_grad_(True), k.detach().double().requires_grad_(True)
+    ref = F.conv2d(xr.view(1, 60, 7, 9), kr.view(60, 1, 1, 1), groups=60).view(5, 12, 7, 9)   # reference formulation
+    rx, rk = torch.autograd.grad(ref, [xr, kr], dy.double())
+    tol = TOL[dtype]
+    assert rel_err(y, ref.to(dtype)) < tol and rel_err(gx, rx.to(dtype)) < tol and rel_err(gk, rk.to(dtype)) < tol
+
+
 def test_empty_and_degenerate_inputs(ops):
     from deformable_kernels._cabi import DkError
     x = torch.randn(1, 4, 2, 2, device=DEV)
