@@ -220,7 +220,12 @@ int dk_deform_sample_depthwise_backward_data(const void* grad_output, const void
 }
 
 size_t dk_deform_sample_depthwise_backward_filter_workspace_bytes(const dk_geom* g, int dtype) {
-  return dk_sample_depthwise_backward_filter_workspace_bytes(g, dtype);
+  Geom gg;
+  if (!make_geom(g, &gg) || !dtype_ok(dtype)) return 0;
+  size_t need = filter_plan(gg, acc_bytes(dtype)).ws_bytes;
+  const size_t plane = deform_filter_plane_workspace(gg, dtype);
+  if (plane > need) need = plane;
+  return align256(need);
 }
 
 int dk_deform_sample_depthwise_backward_filter(const void* grad_output, const void* input, const void* offset,

@@ -189,6 +189,7 @@ struct FilterPlan {
   size_t ws_bytes;   // pix_blocks * C * cells * sizeof(acc)
 };
 FilterPlan filter_plan(const Geom& g, size_t acc_bytes);
+size_t deform_filter_plane_workspace(const Geom& g, int dtype);  // 0 when the shared-memory-plane variant does not apply
 
 constexpr int kMaxNdDims = 8;
 struct NdShape {

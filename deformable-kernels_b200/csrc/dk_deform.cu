@@ -159,6 +159,75 @@ __global__ void __launch_bounds__(BLOCK) deform_data_kernel(const T* __restrict_
   }
 }
 
+// Variant for planes that fit in shared memory: a block owns sample n and CP channels, keeps their
+// grad-input planes on chip in the compute type, scatters into them with shared-memory atomics and
+// writes each plane out once, coalesced and already rounded -- no global atomics, no zero-fill
+// pass, no fp32 scratch tensor, no conversion pass.
+template <typename T, int CP, int BLOCK>
+__global__ void __launch_bounds__(BLOCK) deform_data_plane_kernel(const T* __restrict__ dy, const T* __restrict__ off,
+                                                                  const T* __restrict__ rot, const T* __restrict__ w,
+                                                                  T* __restrict__ dx, const Geom g) {
+  using A = typename Compute<T>::type;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  A* bank = reinterpret_cast<A*>(smem_raw);  // [CP][cells]
+  A* planes = bank + CP * g.cells;           // [CP][HW]
+  const int grp = blockIdx.z;
+  const int j0 = blockIdx.y * CP;
+  const int cnt = min(CP, g.Cg - j0);
+  const int n = blockIdx.x;
+  for (int i = threadIdx.x; i < CP * g.cells; i += BLOCK) {
+    const int j = i / g.cells, cell = i - j * g.cells;
+    bank[i] = (j < cnt) ? ld<A>(w + (size_t)(grp + g.G * (j0 + j)) * g.cells + cell) : (A)0;
+  }
+  for (int i = threadIdx.x; i < CP * g.HW; i += BLOCK) planes[i] = (A)0;
+  __syncthreads();
+
+  const T* dy_n = dy + ((size_t)n * g.C + grp + (size_t)g.G * j0) * g.P;
+  const T* off_n = off + (size_t)n * g.taps * 2 * g.P;
+  const T* rot_n = rot + (size_t)(n * g.G + grp) * g.taps * 2 * g.P;
+  for (int p = threadIdx.x; p < g.P; p += BLOCK) {
+    const int oh = p / g.Wo, ow = p - oh * g.Wo;
+    A dyv[CP];
+#pragma unroll
+    for (int j = 0; j < CP; ++j) dyv[j] = (j < cnt) ? ld<A>(dy_n + (size_t)j * g.G * g.P + p) : (A)0;
+    for (int fh = 0; fh < g.kH; ++fh) {
+      const int ih = oh * g.sH - g.pH + fh * g.dH;
+      for (int fw = 0; fw < g.kW; ++fw) {
+        const int iw = ow * g.sW - g.pW + fw * g.dW;
+        const int t = fh * g.kW + fw;
+        Bilinear<A> bi;
+        if (!image_setup<A>((A)ih + ld<A>(off_n + (size_t)t * 2 * g.P + p), (A)iw + ld<A>(off_n + (size_t)(t * 2 + 1) * g.P + p),
+                            g, bi))
+          continue;
+        Bilinear<A> bb;
+        if (!bank_setup<A>(ld<A>(rot_n + (size_t)t * 2 * g.P + p), ld<A>(rot_n + (size_t)(t * 2 + 1) * g.P + p), fh, fw, g, bb))
+          continue;
+        A ci[4], cb[4];
+        bilinear_value_coefs(bi, ci);
+        bilinear_value_coefs(bb, cb);
+#pragma unroll
+        for (int j = 0; j < CP; ++j) {
+          if (j < cnt) {
+            const A* bk = bank + j * g.cells;
+            const A k = cb[0] * bk[bb.idx[0]] + cb[1] * bk[bb.idx[1]] + cb[2] * bk[bb.idx[2]] + cb[3] * bk[bb.idx[3]];
+            const A v = k * dyv[j];
+            A* dp = planes + j * g.HW;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              if (bi.m[q]) atomicAdd(dp + bi.idx[q], ci[q] * v);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int j = 0; j < cnt; ++j) {
+    T* o = dx + ((size_t)n * g.C + grp + (size_t)g.G * (j0 + j)) * g.HW;
+    const A* sp = planes + j * g.HW;
+    for (int i = threadIdx.x; i < g.HW; i += BLOCK) st<T, A>(o + i, sp[i]);
+  }
+}
+
 template <typename T, typename A>
 __global__ void convert_kernel(const A* __restrict__ src, T* __restrict__ dst, const size_t n) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -170,6 +239,19 @@ int deform_backward_data(const T* dy, const T* off, const T* rot, const T* w, T*
                          size_t ws_bytes, cudaStream_t s) {
   using A = typename Compute<T>::type;
   constexpr int CC = 16, BLOCK = 256;
+  {
+    // planes of 8 channels in shared memory, when they fit
+    constexpr int CP = 8;
+    const size_t psmem = (size_t)CP * (g.HW + g.cells) * sizeof(A);
+    const int byp = (g.Cg + CP - 1) / CP;
+    if (psmem <= 110 * 1024 && psmem <= (size_t)device_smem_optin() && byp <= 65535 && g.G <= 65535 && g.P >= 64) {
+      auto kern = deform_data_plane_kernel<T, CP, 512>;
+      int rc = enable_smem(kern, psmem);
+      if (rc) return rc;
+      kern<<<dim3(g.N, byp, g.G), 512, psmem, s>>>(dy, off, rot, w, dx, g);
+      return check_launch();
+    }
+  }
   constexpr bool direct = sizeof(T) == sizeof(A);
   const size_t count = (size_t)g.N * g.C * g.HW;
   A* accbuf;

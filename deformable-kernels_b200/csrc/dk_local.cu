@@ -375,6 +375,161 @@ __global__ void filter_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   }
 }
 
+// Variant for DK + DCN on planes that fit in shared memory: the block keeps the whole input plane of
+// its 32 channels on chip ([channel][pixel], pitch chosen so that the 32 lanes of a warp -- one
+// channel each -- hit 32 different banks), so the four data-dependent image samples of a tap are
+// shared-memory reads instead of 32 scattered global lines per warp load.  Warps split the pixels of
+// a batch; each has private accumulators; a block walks several samples and writes one partial.
+template <typename T, bool DEFORM>
+__global__ void filter_plane_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ off,
+                                    const T* __restrict__ rot, typename Compute<T>::type* __restrict__ partial,
+                                    const Geom g, const int pitch, const int batch) {
+  using A = typename Compute<T>::type;
+  using Entry = TapEntry<A, DEFORM>;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warps = blockDim.x >> 5;
+  A* acc_all = reinterpret_cast<A*>(smem_raw);                                      // [warps][cells][32]
+  Entry* table = reinterpret_cast<Entry*>(acc_all + (size_t)warps * g.cells * 32);  // [batch][taps]
+  T* planes = reinterpret_cast<T*>(table + (size_t)batch * g.taps);                 // [32][pitch]
+
+  const int grp = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int j0 = blockIdx.y * 32;
+  const bool chan_ok = j0 + lane < g.Cg;
+  const size_t c = (size_t)grp + (size_t)g.G * (chan_ok ? j0 + lane : 0);
+  A* acc = acc_all + (size_t)warp * g.cells * 32;
+  for (int i = lane; i < g.cells * 32; i += 32) acc[i] = (A)0;
+  const T* myplane = planes + (size_t)lane * pitch;
+
+  for (int n = blockIdx.x; n < g.N; n += gridDim.x) {
+    __syncthreads();
+    for (int ch = warp; ch < 32; ch += warps) {
+      if (j0 + ch < g.Cg) {
+        const T* sp = x + ((size_t)n * g.C + grp + (size_t)g.G * (j0 + ch)) * g.HW;
+        T* dp = planes + (size_t)ch * pitch;
+        for (int i = lane; i < g.HW; i += 32) dp[i] = __ldg(sp + i);
+      }
+    }
+    for (int base = 0; base < g.P; base += batch) {
+      const int nb = min(batch, g.P - base);
+      __syncthreads();
+      for (int i = threadIdx.x; i < nb * g.taps; i += blockDim.x) {
+        const int pl = i / g.taps, t = i - pl * g.taps;
+        const int p = base + pl;
+        const int oh = p / g.Wo, ow = p - oh * g.Wo;
+        const int fh = t / g.kW, fw = t - fh * g.kW;
+        const int ih = oh * g.sH - g.pH + fh * g.dH, iw = ow * g.sW - g.pW + fw * g.dW;
+        Entry e;
+        e.src[0] = -1;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { e.idx[q] = 0; e.c[q] = (A)0; }
+        bool used;
+        Bilinear<A> bi;
+        if (DEFORM) {
+          const T* o = off + ((size_t)n * g.taps + t) * 2 * g.P + p;
+          used = image_setup<A>((A)ih + ld<A>(o), (A)iw + ld<A>(o + g.P), g, bi);
+        } else {
+          used = ih >= 0 && ih < g.H && iw >= 0 && iw < g.W;
+        }
+        if (used) {
+          const T* r = rot + ((size_t)(n * g.G + grp) * g.taps + t) * 2 * g.P + p;
+          Bilinear<A> b;
+          if (bank_setup<A>(ld<A>(r), ld<A>(r + g.P), fh, fw, g, b)) {
+            bilinear_value_coefs(b, e.c);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) e.idx[q] = b.idx[q];
+            if (DEFORM) {
+              A sc[4];
+              bilinear_value_coefs(bi, sc);
+#pragma unroll
+              for (int q = 0; q < (DEFORM ? 4 : 1); ++q) { e.src[q] = bi.idx[q]; e.sc[q] = sc[q]; }
+            } else {
+              e.src[0] = ih * g.W + iw;
+            }
+          }
+        }
+        table[i] = e;
+      }
+      __syncthreads();
+      if (chan_ok) {
+        for (int pl = warp; pl < nb; pl += warps) {
+          const A dyv = ld<A>(dy + ((size_t)n * g.C + c) * g.P + base + pl);
+          for (int t = 0; t < g.taps; ++t) {
+            const Entry& e = table[pl * g.taps + t];
+            if (e.src[0] >= 0) {
+              A xv;
+              if (DEFORM) {
+                xv = (A)0;
+#pragma unroll
+                for (int q = 0; q < (DEFORM ? 4 : 1); ++q) xv += e.sc[q] * static_cast<A>(myplane[e.src[q]]);
+              } else {
+                xv = static_cast<A>(myplane[e.src[0]]);
+              }
+              const A sv = xv * dyv;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                A* a = acc + e.idx[q] * 32 + lane;
+                *a += e.c[q] * sv;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (chan_ok) {
+    A* out = partial + ((size_t)blockIdx.x * g.C + c) * g.cells;
+    for (int cell = warp; cell < g.cells; cell += warps) {
+      A sum = (A)0;
+      for (int wv = 0; wv < warps; ++wv) sum += acc_all[((size_t)wv * g.cells + cell) * 32 + lane];
+      out[cell] = sum;
+    }
+  }
+}
+
+struct PlanePlan {
+  bool ok;
+  int warps, batch, pitch, slots, chan_blocks;
+  size_t smem, ws_bytes;
+};
+
+template <typename T, bool DEFORM>
+static PlanePlan plane_plan(const Geom& g) {
+  using A = typename Compute<T>::type;
+  PlanePlan pl;
+  pl.batch = 16;
+  // lanes = channels read element i of 32 planes: the plane pitch in 32-bit words must be odd
+  if (sizeof(T) == 2) {
+    pl.pitch = (g.HW + 3) & ~3;
+    pl.pitch += 2;
+  } else {
+    pl.pitch = g.HW | 1;
+  }
+  for (pl.warps = 16; pl.warps >= 4; pl.warps >>= 1) {
+    pl.smem = (size_t)pl.warps * g.cells * 32 * sizeof(A) + (size_t)pl.batch * g.taps * sizeof(TapEntry<A, DEFORM>) +
+              (size_t)32 * pl.pitch * sizeof(T);
+    if (pl.smem <= 226 * 1024 || pl.warps == 4) break;
+  }
+  pl.chan_blocks = (g.Cg + 31) / 32;
+  const long long chan_ctas = (long long)pl.chan_blocks * g.G;
+  long long slots = (2LL * 148 + chan_ctas - 1) / chan_ctas;
+  if (slots > g.N) slots = g.N;
+  if (slots < 1) slots = 1;
+  pl.slots = (int)slots;
+  pl.ws_bytes = (size_t)pl.slots * g.C * g.cells * sizeof(A);
+  pl.ok = pl.smem <= 226 * 1024 && pl.chan_blocks <= 65535 && g.G <= 65535 && g.Cg >= 32;
+  return pl;
+}
+
+size_t deform_filter_plane_workspace(const Geom& g, int dtype) {
+  PlanePlan pl;
+  if (dtype == DK_F16) pl = plane_plan<__half, true>(g);
+  else if (dtype == DK_F64) pl = plane_plan<double, true>(g);
+  else pl = plane_plan<float, true>(g);
+  return pl.ok ? pl.ws_bytes : 0;
+}
+
 // out[i] = sum over partial blocks, fixed order.
 template <typename T>
 __global__ void reduce_partials_kernel(const typename Compute<T>::type* __restrict__ partial, T* __restrict__ out,
@@ -412,6 +567,22 @@ template <typename T, bool DEFORM>
 static int filter_backward(const T* dy, const T* x, const T* off, const T* rot, T* dw, const Geom& g, void* ws,
                            size_t ws_bytes, cudaStream_t s) {
   using A = typename Compute<T>::type;
+  if (DEFORM) {
+    const PlanePlan pp = plane_plan<T, DEFORM>(g);
+    if (pp.ok && pp.smem <= (size_t)device_smem_optin()) {
+      if (ws == nullptr || ws_bytes < pp.ws_bytes) return DK_ERR_WORKSPACE;
+      auto kern = filter_plane_kernel<T, DEFORM>;
+      int rc = enable_smem(kern, pp.smem);
+      if (rc) return rc;
+      kern<<<dim3(pp.slots, pp.chan_blocks, g.G), pp.warps * 32, pp.smem, s>>>(dy, x, off, rot, reinterpret_cast<A*>(ws), g,
+                                                                            pp.pitch, pp.batch);
+      rc = check_launch();
+      if (rc) return rc;
+      const int n_out = g.C * g.cells;
+      reduce_partials_kernel<T><<<(n_out + 255) / 256, 256, 0, s>>>(reinterpret_cast<const A*>(ws), dw, n_out, pp.slots);
+      return check_launch();
+    }
+  }
   const FilterPlan pl = filter_plan(g, sizeof(A));
   if (ws == nullptr || ws_bytes < pl.ws_bytes) return DK_ERR_WORKSPACE;
   if (pl.chan_blocks > 65535 || g.G > 65535) return DK_ERR_UNSUPPORTED;
