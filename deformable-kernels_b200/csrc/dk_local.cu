@@ -553,7 +553,7 @@ FilterPlan filter_plan(const Geom& g, size_t acc_bytes) {
   const long long total = (long long)g.N * g.P;
   const long long chan_ctas = (long long)pl.chan_blocks * g.G;
   long long want = (4LL * 148 + chan_ctas - 1) / chan_ctas;  // ~4 blocks per SM over the grid
-  const long long max_by_work = (total + 4 * kFilterPixBatch - 1) / (4 * kFilterPixBatch);
+  const long long max_by_work = (total + 7) / 8;  // at least eight pixels per block, so that small problems still spread out
   if (want > max_by_work) want = max_by_work;
   if (want > 2048) want = 2048;
   if (want < 1) want = 1;

@@ -102,8 +102,35 @@ def ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr(device):
+    """cudaStream_t of torch's current stream on `device` (the raw-handle query is several times cheaper than
+    building a Stream object, which matters for the small latency-bound calls)."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(device.index if device.index is not None else torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+class device_of:
+    """Device guard that does nothing when the tensor already lives on the current device."""
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, tensor):
+        self.idx = tensor.device.index
+
+    def __enter__(self):
+        self.prev = torch.cuda.current_device()
+        if self.idx is not None and self.idx != self.prev:
+            torch.cuda.set_device(self.idx)
+        else:
+            self.prev = None
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def require_cuda(*tensors):

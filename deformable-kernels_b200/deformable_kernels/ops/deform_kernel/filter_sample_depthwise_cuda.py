@@ -30,7 +30,7 @@ def _out(out):
 def sample_depthwise_forward_cuda(input, rotation, filter, output, *ints):
     input, rotation, filter = _prep(input, rotation, filter)
     g = _geom(input, *ints)
-    with torch.cuda.device(input.device):
+    with C.device_of(input):
         C.check(C.lib.dk_sample_depthwise_forward(C.ptr(input), C.ptr(rotation), C.ptr(filter), C.ptr(_out(output)), g,
                                                   C.dtype_code(input), C.stream_ptr(input.device)),
                 "sample_depthwise_forward")
@@ -40,7 +40,7 @@ def sample_depthwise_forward_cuda(input, rotation, filter, output, *ints):
 def sample_depthwise_backward_data_cuda(gradOutput, input, rotation, filter, gradInput, *ints):
     gradOutput, rotation, filter = _prep(gradOutput, rotation, filter)
     g = _geom(input, *ints)
-    with torch.cuda.device(input.device):
+    with C.device_of(input):
         C.check(C.lib.dk_sample_depthwise_backward_data(C.ptr(gradOutput), C.ptr(rotation), C.ptr(filter),
                                                         C.ptr(_out(gradInput)), g, C.dtype_code(gradOutput),
                                                         C.stream_ptr(input.device)), "sample_depthwise_backward_data")
@@ -51,7 +51,7 @@ def sample_depthwise_backward_filter_cuda(gradOutput, input, rotation, filter, g
     gradOutput, input, rotation = _prep(gradOutput, input, rotation)
     g = _geom(input, *ints)
     code = C.dtype_code(input)
-    with torch.cuda.device(input.device):
+    with C.device_of(input):
         nbytes = C.lib.dk_sample_depthwise_backward_filter_workspace_bytes(g, code)
         ws = C.workspace(nbytes, input.device)
         C.check(C.lib.dk_sample_depthwise_backward_filter(C.ptr(gradOutput), C.ptr(input), C.ptr(rotation),
@@ -64,7 +64,7 @@ def sample_depthwise_backward_rotation_cuda(gradOutput, input, rotation, filter,
     gradOutput, input, rotation, filter = _prep(gradOutput, input, rotation, filter)
     g = _geom(input, *ints)
     code = C.dtype_code(input)
-    with torch.cuda.device(input.device):
+    with C.device_of(input):
         nbytes = C.lib.dk_sample_depthwise_backward_rotation_workspace_bytes(g, code)
         ws = C.workspace(nbytes, input.device)
         C.check(C.lib.dk_sample_depthwise_backward_rotation(C.ptr(gradOutput), C.ptr(input), C.ptr(rotation),
@@ -77,7 +77,7 @@ def sample_depthwise_backward_rotation_cuda(gradOutput, input, rotation, filter,
 def deformable_sample_depthwise_forward_cuda(input, offset, rotation, filter, output, *ints):
     input, offset, rotation, filter = _prep(input, offset, rotation, filter)
     g = _geom(input, *ints)
-    with torch.cuda.device(input.device):
+    with C.device_of(input):
         C.check(C.lib.dk_deform_sample_depthwise_forward(C.ptr(input), C.ptr(offset), C.ptr(rotation), C.ptr(filter),
                                                          C.ptr(_out(output)), g, C.dtype_code(input),
                                                          C.stream_ptr(input.device)), "deform_sample_depthwise_forward")
@@ -88,7 +88,7 @@ def deformable_sample_depthwise_backward_data_cuda(gradOutput, input, offset, ro
     gradOutput, offset, rotation, filter = _prep(gradOutput, offset, rotation, filter)
     g = _geom(input, *ints)
     code = C.dtype_code(gradOutput)
-    with torch.cuda.device(input.device):
+    with C.device_of(input):
         nbytes = C.lib.dk_deform_sample_depthwise_backward_data_workspace_bytes(g, code)
         ws = C.workspace(nbytes, input.device)
         C.check(C.lib.dk_deform_sample_depthwise_backward_data(C.ptr(gradOutput), C.ptr(offset), C.ptr(rotation),
@@ -102,7 +102,7 @@ def deformable_sample_depthwise_backward_filter_cuda(gradOutput, input, offset, 
     gradOutput, input, offset, rotation = _prep(gradOutput, input, offset, rotation)
     g = _geom(input, *ints)
     code = C.dtype_code(input)
-    with torch.cuda.device(input.device):
+    with C.device_of(input):
         nbytes = C.lib.dk_deform_sample_depthwise_backward_filter_workspace_bytes(g, code)
         ws = C.workspace(nbytes, input.device)
         C.check(C.lib.dk_deform_sample_depthwise_backward_filter(C.ptr(gradOutput), C.ptr(input), C.ptr(offset),
@@ -115,7 +115,7 @@ def deformable_sample_depthwise_backward_filter_cuda(gradOutput, input, offset, 
 def deformable_sample_depthwise_backward_offset_cuda(gradOutput, input, offset, rotation, filter, gradOffset, *ints):
     gradOutput, input, offset, rotation, filter = _prep(gradOutput, input, offset, rotation, filter)
     g = _geom(input, *ints)
-    with torch.cuda.device(input.device):
+    with C.device_of(input):
         C.check(C.lib.dk_deform_sample_depthwise_backward_offset(C.ptr(gradOutput), C.ptr(input), C.ptr(offset),
                                                                  C.ptr(rotation), C.ptr(filter), C.ptr(_out(gradOffset)),
                                                                  g, C.dtype_code(input), C.stream_ptr(input.device)),
@@ -127,7 +127,7 @@ def deformable_sample_depthwise_backward_rotation_cuda(gradOutput, input, offset
                                                        *ints):
     gradOutput, input, offset, rotation, filter = _prep(gradOutput, input, offset, rotation, filter)
     g = _geom(input, *ints)
-    with torch.cuda.device(input.device):
+    with C.device_of(input):
         C.check(C.lib.dk_deform_sample_depthwise_backward_rotation(C.ptr(gradOutput), C.ptr(input), C.ptr(offset),
                                                                    C.ptr(rotation), C.ptr(filter),
                                                                    C.ptr(_out(gradRotation)), g, C.dtype_code(input),

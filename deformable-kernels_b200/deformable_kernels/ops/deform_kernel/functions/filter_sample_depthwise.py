@@ -58,7 +58,7 @@ class SampleDepthwiseFunction(Function):
         ctx.geom = C.geom(input.shape, kernel_size, stride, padding, dilation, weight.shape[2:], rotation_groups)
         ctx.save_for_backward(input, rotation, weight)
         output = input.new_empty(out_size)
-        with torch.cuda.device(input.device):
+        with C.device_of(input):
             C.check(C.lib.dk_sample_depthwise_forward(C.ptr(input), C.ptr(rotation), C.ptr(weight), C.ptr(output),
                                                       ctx.geom, C.dtype_code(input), C.stream_ptr(input.device)),
                     "sample_depthwise forward")
@@ -76,7 +76,7 @@ class SampleDepthwiseFunction(Function):
         grad_rotation = torch.empty_like(rotation) if need[1] else None
         grad_weight = torch.empty_like(weight) if need[2] else None
         code = C.dtype_code(input)
-        with torch.cuda.device(input.device):
+        with C.device_of(input):
             nbytes = C.lib.dk_sample_depthwise_backward_workspace_bytes(ctx.geom, code)
             ws = C.workspace(nbytes, input.device)
             C.check(C.lib.dk_sample_depthwise_backward(
@@ -100,7 +100,7 @@ class DeformableSampleDepthwiseFunction(Function):
         ctx.geom = C.geom(input.shape, kernel_size, stride, padding, dilation, weight.shape[2:], rotation_groups)
         ctx.save_for_backward(input, offset, rotation, weight)
         output = input.new_empty(out_size)
-        with torch.cuda.device(input.device):
+        with C.device_of(input):
             C.check(C.lib.dk_deform_sample_depthwise_forward(
                 C.ptr(input), C.ptr(offset), C.ptr(rotation), C.ptr(weight), C.ptr(output), ctx.geom,
                 C.dtype_code(input), C.stream_ptr(input.device)), "deform_sample_depthwise forward")
@@ -119,7 +119,7 @@ class DeformableSampleDepthwiseFunction(Function):
         grad_rotation = torch.empty_like(rotation) if need[2] else None
         grad_weight = torch.empty_like(weight) if need[3] else None
         code = C.dtype_code(input)
-        with torch.cuda.device(input.device):
+        with C.device_of(input):
             nbytes = C.lib.dk_deform_sample_depthwise_backward_workspace_bytes(ctx.geom, code)
             ws = C.workspace(nbytes, input.device)
             C.check(C.lib.dk_deform_sample_depthwise_backward(

@@ -27,7 +27,7 @@ class NdLinearSampleFunction(Function):
         dims = input.dim() - 1
         shape = (ctypes.c_int * dims)(*input.shape[1:])
         output = input.new_empty(coord.size(0), input.size(0))
-        with torch.cuda.device(input.device):
+        with C.device_of(input):
             C.check(C.lib.dk_nd_linear_sample_forward(C.ptr(input), C.ptr(coord), C.ptr(output), coord.size(0),
                                                       input.size(0), dims, shape, C.dtype_code(input),
                                                       C.stream_ptr(input.device)), "nd_linear_sample forward")
@@ -42,7 +42,7 @@ class NdLinearSampleFunction(Function):
         shape = (ctypes.c_int * dims)(*input.shape[1:])
         grad_input = grad_coord = None
         code = C.dtype_code(input)
-        with torch.cuda.device(input.device):
+        with C.device_of(input):
             if ctx.needs_input_grad[0]:
                 grad_input = torch.empty_like(input)
                 C.check(C.lib.dk_nd_linear_sample_backward_data(

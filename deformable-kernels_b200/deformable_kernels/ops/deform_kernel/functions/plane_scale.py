@@ -20,7 +20,7 @@ class PlaneScaleFunction(Function):
         ctx.save_for_backward(input, scale)
         output = torch.empty_like(input)
         n, c, h, w = input.shape
-        with torch.cuda.device(input.device):
+        with C.device_of(input):
             C.check(C.lib.dk_plane_scale_forward(C.ptr(input), C.ptr(scale), C.ptr(output), n * c, h * w,
                                                  C.dtype_code(input), C.stream_ptr(input.device)), "plane_scale forward")
         return output
@@ -32,7 +32,7 @@ class PlaneScaleFunction(Function):
         n, c, h, w = input.shape
         grad_input = torch.empty_like(input) if ctx.needs_input_grad[0] else None
         grad_scale = torch.empty_like(scale) if ctx.needs_input_grad[1] else None
-        with torch.cuda.device(input.device):
+        with C.device_of(input):
             C.check(C.lib.dk_plane_scale_backward(C.ptr(grad_output), C.ptr(input), C.ptr(scale), C.ptr(grad_input),
                                                   C.ptr(grad_scale), n * c, h * w, C.dtype_code(input),
                                                   C.stream_ptr(input.device)), "plane_scale backward")

@@ -19,7 +19,7 @@ def nd_linear_sample_forward_cuda(data, shape, coord, output):
     C.same_dtype(data, coord, output)
     data, coord = data.contiguous(), coord.contiguous()
     dims, sh = _shape(data)
-    with torch.cuda.device(data.device):
+    with C.device_of(data):
         C.check(C.lib.dk_nd_linear_sample_forward(C.ptr(data), C.ptr(coord), C.ptr(output), coord.size(0), data.size(0),
                                                   dims, sh, C.dtype_code(data), C.stream_ptr(data.device)),
                 "nd_linear_sample_forward")
@@ -31,7 +31,7 @@ def nd_linear_sample_backward_data_cuda(out_grad, data, shape, coord, in_grad):
     C.same_dtype(out_grad, coord, in_grad)
     out_grad, coord = out_grad.contiguous(), coord.contiguous()
     dims, sh = _shape(data)
-    with torch.cuda.device(data.device):
+    with C.device_of(data):
         C.check(C.lib.dk_nd_linear_sample_backward_data(C.ptr(out_grad), C.ptr(coord), C.ptr(in_grad), coord.size(0),
                                                         data.size(0), dims, sh, C.dtype_code(out_grad),
                                                         C.stream_ptr(data.device)), "nd_linear_sample_backward_data")
@@ -43,7 +43,7 @@ def nd_linear_sample_backward_coord_cuda(out_grad, data, shape, coord, coord_gra
     C.same_dtype(out_grad, data, coord, coord_grad_c)
     out_grad, data, coord = out_grad.contiguous(), data.contiguous(), coord.contiguous()
     dims, sh = _shape(data)
-    with torch.cuda.device(data.device):
+    with C.device_of(data):
         C.check(C.lib.dk_nd_linear_sample_backward_coord(C.ptr(out_grad), C.ptr(data), C.ptr(coord), C.ptr(coord_grad_c),
                                                          coord.size(0), data.size(0), dims, sh, C.dtype_code(data),
                                                          C.stream_ptr(data.device)), "nd_linear_sample_backward_coord")
