@@ -225,6 +225,10 @@ size_t dk_deform_sample_depthwise_backward_filter_workspace_bytes(const dk_geom*
   size_t need = filter_plan(gg, acc_bytes(dtype)).ws_bytes;
   const size_t plane = deform_filter_plane_workspace(gg, dtype);
   if (plane > need) need = plane;
+  if (dtype == DK_F16) {
+    const size_t fast = deform_filter_mma_workspace(gg);
+    if (fast > need) need = fast;
+  }
   return align256(need);
 }
 

@@ -615,6 +615,12 @@ int local_backward_filter(const T* dy, const T* x, const T* rot, T* dw, const Ge
 template <typename T>
 int deform_backward_filter(const T* dy, const T* x, const T* off, const T* rot, T* dw, const Geom& g, void* ws,
                            size_t ws_bytes, cudaStream_t s) {
+  if constexpr (std::is_same<T, __half>::value) {
+    if (mma_path_enabled()) {
+      const int rc = deform_filter_mma(dy, x, off, rot, dw, g, ws, ws_bytes, s);
+      if (rc != DK_ERR_UNSUPPORTED) return rc;
+    }
+  }
   return filter_backward<T, true>(dy, x, off, rot, dw, g, ws, ws_bytes, s);
 }
 

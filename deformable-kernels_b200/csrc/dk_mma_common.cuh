@@ -321,7 +321,9 @@ __device__ __forceinline__ unsigned pack2(float a, float b) {
   return *reinterpret_cast<const unsigned*>(&h);
 }
 
-template <int S, bool TRANSPOSED>
+// IMAGE_MASK = false keeps the taps whose integer source position lies in the padding (the DK + DCN
+// operator decides validity on the deformed position instead).
+template <int S, bool TRANSPOSED, bool IMAGE_MASK = true>
 __device__ __forceinline__ void beta_direct(unsigned (&bf)[9][2], const __half* __restrict__ rband, const Band& rb,
                                             const Geom& g, const LaneCells& lc, bool sc44, int drow, int ow0, int Hs, int Ws,
                                             int Wd, int gq) {
@@ -332,8 +334,8 @@ __device__ __forceinline__ void beta_direct(unsigned (&bf)[9][2], const __half* 
   for (int f = 0; f < 3; ++f) {
     if (!TRANSPOSED) {
       const int sr = drow * S - 1 + f, sc = pc * S - 1 + f;
-      rok[f] = sr >= 0 && sr < Hs;
-      cok[f] = pc < Wd && sc >= 0 && sc < Ws;
+      rok[f] = !IMAGE_MASK || (sr >= 0 && sr < Hs);
+      cok[f] = pc < Wd && (!IMAGE_MASK || (sc >= 0 && sc < Ws));
       roff[f] = drow * rb.Wp;
       coff[f] = pc;
     } else {

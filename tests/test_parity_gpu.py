@@ -168,6 +168,14 @@ def test_local_dk_fp16_fast_path_matches_oracle(ops, oracle, cfg):
     compare(mine_local(ops, case, torch.float16), oracle_local(oracle, case, torch.float16), torch.float16, "fast")
 
 
+@pytest.mark.parametrize("cfg", FAST)
+def test_deform_dk_fp16_fast_shapes_match_oracle(ops, oracle, cfg):
+    case = make_case(seed=38, off_std=2.0, **cfg)
+    case["rotation"] = snap(case["rotation"])
+    case["offset"] = snap(case["offset"], seed=3)
+    compare(mine_deform(ops, case, torch.float16), oracle_deform(oracle, case, torch.float16), torch.float16, "deform-fast")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.float64])
 def test_plane_scale_is_the_per_sample_grouped_1x1_conv(ops, dtype):
     gen = torch.Generator().manual_seed(37)
