@@ -78,6 +78,12 @@ __global__ void __launch_bounds__(BLOCK) deform_fwd_kernel(const T* __restrict__
 
 template <typename T>
 int deform_forward(const T* x, const T* off, const T* rot, const T* w, T* y, const Geom& g, cudaStream_t s) {
+  if constexpr (std::is_same<T, __half>::value) {
+    if (mma_path_enabled()) {
+      const int rc = deform_forward_mma(x, off, rot, w, y, g, s);
+      if (rc != DK_ERR_UNSUPPORTED) return rc;
+    }
+  }
   using A = typename Compute<T>::type;
   constexpr int CC = 16, BLOCK = 256;
   const long long bx = ((long long)g.N * g.P + BLOCK - 1) / BLOCK;
