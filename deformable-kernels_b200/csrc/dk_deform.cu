@@ -245,6 +245,12 @@ int deform_backward_data(const T* dy, const T* off, const T* rot, const T* w, T*
                          size_t ws_bytes, cudaStream_t s) {
   using A = typename Compute<T>::type;
   constexpr int CC = 16, BLOCK = 256;
+  if constexpr (std::is_same<T, __half>::value) {
+    if (mma_path_enabled()) {
+      const int rc = deform_data_mma(dy, off, rot, w, dx, g, ws, ws_bytes, s);
+      if (rc != DK_ERR_UNSUPPORTED) return rc;
+    }
+  }
   {
     // planes of 8 channels in shared memory, when they fit
     constexpr int CP = 8;

@@ -69,37 +69,59 @@ constexpr int kPairTabWords = 3 * 80;  // per warp: 3 taps x 4 pixel pairs x (2 
 // Sampling table of the three taps of kernel row fh for the 8 pixels of an item: per (pixel, tap) the byte
 // offsets of the four corner chunks and the four corner coefficients, each duplicated into both halves of a
 // word.  A tap whose deformed position is outside (-1, H) x (-1, W) gets zero coefficients.  Lanes 0..23.
+// With ACC_PLANE the entries address the accumulator planes of the grad-input kernel instead (the shared-memory
+// address of the pixel's first group of eight channels, see acc_word) and the coefficients are fp32.
+template <int S>
+__device__ __forceinline__ unsigned acc_word(int i, int ch) {  // word of (pixel i, channel ch) in the fp32 planes
+  const int row = i >> 1, r = (S == 1 ? row : row >> 1) & 3;
+  return (unsigned)(row * 32 + (((((ch >> 3) << 1) | (i & 1)) ^ r) << 3) + (ch & 7));
+}
+template <int S, bool ACC_PLANE>
+__device__ __forceinline__ void pair_table_entry(unsigned* __restrict__ tab, const Geom& g, int fh, int oh, int ow0, int lane,
+                                                 float o_h, float o_w, unsigned acc_saddr) {
+  const int px = lane & 7, fw = lane >> 3;
+  const int pc = ow0 + px;
+  const float ph = (float)(oh * S - 1 + fh) + o_h;
+  const float pw = (float)(pc * S - 1 + fw) + o_w;
+  const bool used = pc < g.Wo && ph > -1.f && pw > -1.f && ph < (float)g.H && pw < (float)g.W;
+  uint4 o4 = make_uint4(0, 0, 0, 0), c4 = make_uint4(0, 0, 0, 0);
+  if (ACC_PLANE) {  // an unused tap adds zeros at its undeformed position (distinct addresses per lane)
+    const int hn = min(max(oh * S - 1 + fh, 0), g.H - 1), wn = min(max(pc * S - 1 + fw, 0), g.W - 1);
+    const unsigned a = acc_saddr + acc_word<S>(hn * g.W + wn, 0) * 4u;
+    o4 = make_uint4(a, a, a, a);
+  }
+  if (used) {
+    const float fph = floorf(ph), fpw = floorf(pw);
+    const int h0 = (int)fph, w0 = (int)fpw;
+    const float lh = ph - fph, lw = pw - fpw;
+    const float hh = 1.f - lh, hw = 1.f - lw;
+    const bool r0 = h0 >= 0, r1 = h0 + 1 <= g.H - 1, k0 = w0 >= 0, k1 = w0 + 1 <= g.W - 1;
+    const int h0c = max(h0, 0), h1c = min(h0 + 1, g.H - 1), w0c = max(w0, 0), w1c = min(w0 + 1, g.W - 1);
+    auto where = [&](int hh_, int ww_) {
+      const int i = hh_ * g.W + ww_;
+      return ACC_PLANE ? acc_saddr + acc_word<S>(i, 0) * 4u : (unsigned)chunk_of<S>(i) * 32u;
+    };
+    auto coef = [&](bool ok, float v) { return !ok ? 0u : (ACC_PLANE ? __float_as_uint(v) : pack2(v, v)); };
+    o4.x = where(h0c, w0c);
+    o4.y = where(h0c, w1c);
+    o4.z = where(h1c, w0c);
+    o4.w = where(h1c, w1c);
+    c4.x = coef(r0 && k0, hh * hw);
+    c4.y = coef(r0 && k1, hh * lw);
+    c4.z = coef(r1 && k0, lh * hw);
+    c4.w = coef(r1 && k1, lh * lw);
+  }
+  uint4* e = reinterpret_cast<uint4*>(tab + fw * 80 + (px >> 1) * 20 + (px & 1) * 8);
+  e[0] = o4;
+  e[1] = c4;
+}
 template <int S>
 __device__ __forceinline__ void build_pair_table(unsigned* __restrict__ tab, const __half* __restrict__ oband, const Band& bo,
                                                  const Geom& g, int fh, int oh, int ow0, int lane) {
   if (lane < 24) {
-    const int px = lane & 7, fw = lane >> 3;
-    const int pc = ow0 + px;
-    const int t = fh * 3 + fw;
-    const __half* op = oband + (size_t)(2 * t) * bo.pitch_c + kSlack + oh * bo.Wp + pc - bo.org;
-    const float ph = (float)(oh * S - 1 + fh) + __half2float(op[0]);
-    const float pw = (float)(pc * S - 1 + fw) + __half2float(op[bo.pitch_c]);
-    const bool used = pc < g.Wo && ph > -1.f && pw > -1.f && ph < (float)g.H && pw < (float)g.W;
-    uint4 o4 = make_uint4(0, 0, 0, 0), c4 = make_uint4(0, 0, 0, 0);
-    if (used) {
-      const float fph = floorf(ph), fpw = floorf(pw);
-      const int h0 = (int)fph, w0 = (int)fpw;
-      const float lh = ph - fph, lw = pw - fpw;
-      const float hh = 1.f - lh, hw = 1.f - lw;
-      const bool r0 = h0 >= 0, r1 = h0 + 1 <= g.H - 1, k0 = w0 >= 0, k1 = w0 + 1 <= g.W - 1;
-      const int h0c = max(h0, 0), h1c = min(h0 + 1, g.H - 1), w0c = max(w0, 0), w1c = min(w0 + 1, g.W - 1);
-      o4.x = (unsigned)chunk_of<S>(h0c * g.W + w0c) * 32u;
-      o4.y = (unsigned)chunk_of<S>(h0c * g.W + w1c) * 32u;
-      o4.z = (unsigned)chunk_of<S>(h1c * g.W + w0c) * 32u;
-      o4.w = (unsigned)chunk_of<S>(h1c * g.W + w1c) * 32u;
-      c4.x = (r0 && k0) ? pack2(hh * hw, hh * hw) : 0u;
-      c4.y = (r0 && k1) ? pack2(hh * lw, hh * lw) : 0u;
-      c4.z = (r1 && k0) ? pack2(lh * hw, lh * hw) : 0u;
-      c4.w = (r1 && k1) ? pack2(lh * lw, lh * lw) : 0u;
-    }
-    uint4* e = reinterpret_cast<uint4*>(tab + fw * 80 + (px >> 1) * 20 + (px & 1) * 8);
-    e[0] = o4;
-    e[1] = c4;
+    const int t = fh * 3 + (lane >> 3);
+    const __half* op = oband + (size_t)(2 * t) * bo.pitch_c + kSlack + oh * bo.Wp + ow0 + (lane & 7) - bo.org;
+    pair_table_entry<S, false>(tab, g, fh, oh, ow0, lane, __half2float(op[0]), __half2float(op[bo.pitch_c]), 0u);
   }
 }
 
@@ -372,6 +394,302 @@ __global__ void __launch_bounds__(512, 1) mma_deform_filter_kernel(const __half*
   }
 }
 
+// ------------------------------------------------------------------ grad-input
+// dx[c, corner] += coefficient * K[c, p, tap] * dy[c, p]: a data-dependent scatter.  The block keeps the gradient
+// planes of its 16 channels in shared memory, processes whole samples and writes each plane once.
+//
+// Accumulation is in 32-bit FIXED POINT with native integer atomics: on this GPU a shared-memory float add is a
+// compare-and-swap loop (measured 5-10 updates per clock per SM, and two lanes of a warp on one address make the
+// loser retry), an integer add is one instruction (27 per clock per SM) and indifferent to collisions.  Per sample
+// and channel the scale is the power of two that maps B = max|dy| * max|W| (no single contribution can exceed it:
+// |K| <= max|W| because the hat weights are non-negative and sum to at most 1, and a tap's four corner coefficients
+// sum to at most 1) to 2^(30 - ceil(log2(M))), where M is the largest number of (pixel, tap) samples that touch one
+// input pixel of this sample, counted beforehand by dcn_hit_count_kernel from the offsets alone: the accumulator
+// cannot overflow whatever the offsets are.  With M of a few dozen a contribution is resolved to 2^-23 B or better,
+// the level of an fp32 sum of values up to B; the sum itself is exact and order-independent, so the gradient is
+// bit-reproducible from run to run.
+//
+// Layout: a row of 32 words per pixel pair = four groups of eight channels (channel half x pixel parity), the
+// group index XOR-ed with the low bits of the row (acc_word): a lane quartet's four pixels, 2 (or 4) source pixels
+// apart when the offsets are smooth, then fall into four different bank groups.
+// Offsets are read straight from global memory one item ahead of their use, so the warps never wait on each
+// other between the zeroing and the write-out of a sample.
+struct DDataPlan {
+  int warps, samples_per_block, blocks_x;
+  bool pair_dy;
+  size_t smem;
+};
+
+// hits[n] = max over input pixels of the number of (output pixel, tap) samples of sample n with a corner on it
+template <int S>
+__global__ void __launch_bounds__(256) dcn_hit_count_kernel(const __half* __restrict__ off, int* __restrict__ hits, const Geom g) {
+  extern __shared__ int cnt[];
+  __shared__ int wmax[8];
+  const int n = blockIdx.x;
+  for (int i = threadIdx.x; i < g.HW; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  const __half* off_n = off + (size_t)n * 18 * g.P;
+  for (int idx = threadIdx.x; idx < 9 * g.P; idx += blockDim.x) {
+    const int t = idx / g.P, p = idx - t * g.P;
+    const int oh = p / g.Wo, ow = p - oh * g.Wo;
+    const float ph = (float)(oh * S - 1 + t / 3) + __half2float(__ldg(off_n + (size_t)(2 * t) * g.P + p));
+    const float pw = (float)(ow * S - 1 + t % 3) + __half2float(__ldg(off_n + (size_t)(2 * t + 1) * g.P + p));
+    if (ph > -1.f && pw > -1.f && ph < (float)g.H && pw < (float)g.W) {
+      const int h0 = (int)floorf(ph), w0 = (int)floorf(pw);
+      const int h0c = max(h0, 0), h1c = min(h0 + 1, g.H - 1), w0c = max(w0, 0), w1c = min(w0 + 1, g.W - 1);
+      atomicAdd(&cnt[h0c * g.W + w0c], 1);
+      atomicAdd(&cnt[h0c * g.W + w1c], 1);
+      atomicAdd(&cnt[h1c * g.W + w0c], 1);
+      atomicAdd(&cnt[h1c * g.W + w1c], 1);
+    }
+  }
+  __syncthreads();
+  int m = 1;
+  for (int i = threadIdx.x; i < g.HW; i += blockDim.x) m = max(m, cnt[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int k = 1; k < 8; ++k) m = max(m, wmax[k]);
+    hits[n] = m;
+  }
+}
+
+__device__ __forceinline__ void red_shared_s32(unsigned a, int v) {
+  asm volatile("red.shared.add.s32 [%0], %1;\n" ::"r"(a), "r"(v) : "memory");
+}
+
+// o: shared addresses of the four corners' first channel group; lane_off = 4 * (channel & 7);
+// ga, gb: scaled K * dy of this pixel for channel rows gq and gq + 8
+__device__ __forceinline__ void scatter8(const uint4 o, const uint4 cf, float ga, float gb, unsigned lane_off) {
+  constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: (v + kMagic) has rint(v) in its low mantissa bits for |v| < 2^22
+  constexpr int kMagicBits = 0x4B400000;
+  const unsigned ok[4] = {o.x, o.y, o.z, o.w};
+  const unsigned ck[4] = {cf.x, cf.y, cf.z, cf.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const unsigned a = ok[k] + lane_off;
+    const float c = __uint_as_float(ck[k]);
+    red_shared_s32(a, __float_as_int(fmaf(c, ga, kMagic)) - kMagicBits);
+    red_shared_s32(a ^ 64u, __float_as_int(fmaf(c, gb, kMagic)) - kMagicBits);  // channels 8..15: group index ^ 2
+  }
+}
+
+// everything an item needs from global memory: kernel-space offsets of pixel gq (9 taps, h | w << 16), image-space
+// offsets of the table builder's (pixel, tap column) for the three kernel rows, dy of the lane's two pixels
+struct ItemRegs {
+  unsigned rp[9], op[3], dy0, dy1;
+};
+__device__ __forceinline__ void fetch_item(ItemRegs& r, const __half* __restrict__ dy, const __half* __restrict__ off,
+                                           const __half* __restrict__ rot, const Geom& g, int n, int c0, int oh, int ow0, int lane,
+                                           bool pair_dy) {
+  const int gq = lane >> 2, q = lane & 3;
+  const size_t row = (size_t)oh * g.Wo;
+  {
+    const int pc = ow0 + gq;
+    const __half* rp = rot + (size_t)n * 18 * g.P + row + pc;
+#pragma unroll
+    for (int t = 0; t < 9; ++t) {
+      r.rp[t] = 0u;
+      if (pc < g.Wo)
+        r.rp[t] = (unsigned)__half_as_ushort(__ldg(rp + (size_t)(2 * t) * g.P)) |
+                  ((unsigned)__half_as_ushort(__ldg(rp + (size_t)(2 * t + 1) * g.P)) << 16);
+    }
+  }
+  {
+    const int pc = ow0 + (lane & 7), fw = lane >> 3;
+    const __half* op = off + (size_t)n * 18 * g.P + row + pc;
+#pragma unroll
+    for (int fh = 0; fh < 3; ++fh) {
+      r.op[fh] = 0u;
+      if (lane < 24 && pc < g.Wo) {
+        const int t = fh * 3 + fw;
+        r.op[fh] = (unsigned)__half_as_ushort(__ldg(op + (size_t)(2 * t) * g.P)) |
+                   ((unsigned)__half_as_ushort(__ldg(op + (size_t)(2 * t + 1) * g.P)) << 16);
+      }
+    }
+  }
+  r.dy0 = r.dy1 = 0u;
+  const int ow = ow0 + 2 * q;
+  if (ow < g.Wo) {
+    const __half* p0 = dy + ((size_t)n * g.C + c0 + gq) * g.P + row + ow;
+    const __half* p1 = p0 + (size_t)8 * g.P;
+    if (pair_dy) {
+      r.dy0 = __ldg(reinterpret_cast<const unsigned*>(p0));
+      r.dy1 = __ldg(reinterpret_cast<const unsigned*>(p1));
+    } else {
+      r.dy0 = __half_as_ushort(__ldg(p0));
+      r.dy1 = __half_as_ushort(__ldg(p1));
+      if (ow + 1 < g.Wo) {
+        r.dy0 |= (unsigned)__half_as_ushort(__ldg(p0 + 1)) << 16;
+        r.dy1 |= (unsigned)__half_as_ushort(__ldg(p1 + 1)) << 16;
+      }
+    }
+  }
+}
+
+// hat-product fragments (as beta_direct without the image mask) from offsets held in registers
+__device__ __forceinline__ void beta_from_regs(unsigned (&bf)[9][2], const unsigned (&rp)[9], const Geom& g, const LaneCells& lc,
+                                               bool sc44, bool valid) {
+  const float uh0 = (float)(g.scH - 3) * 0.5f, uw0 = (float)(g.scW - 3) * 0.5f;
+#pragma unroll
+  for (int fh = 0; fh < 3; ++fh) {
+#pragma unroll
+    for (int fw = 0; fw < 3; ++fw) {
+      const int t = fh * 3 + fw;
+      const float u = ((float)fh + lo2f(rp[t])) + uh0;
+      const float v = valid ? ((float)fw + hi2f(rp[t])) + uw0 : 1e30f;
+      if (sc44) {
+        const float hh0 = hat(u - lc.ca[0]), hh1 = hat(u - lc.ca[2]);
+        const float hw0 = hat(v - lc.cb[0]), hw1 = hat(v - lc.cb[1]);
+        bf[t][0] = pack2(hh0 * hw0, hh0 * hw1);
+        bf[t][1] = pack2(hh1 * hw0, hh1 * hw1);
+      } else {
+        float b4[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) b4[k] = lc.ok[k] ? hat(u - lc.ca[k]) * hat(v - lc.cb[k]) : 0.f;
+        bf[t][0] = pack2(b4[0], b4[1]);
+        bf[t][1] = pack2(b4[2], b4[3]);
+      }
+    }
+  }
+}
+
+template <int S>
+__global__ void __launch_bounds__(512, 1) mma_deform_data_kernel(const __half* __restrict__ dy, const __half* __restrict__ off,
+                                                                const __half* __restrict__ rot, const __half* __restrict__ w,
+                                                                const int* __restrict__ hits, __half* __restrict__ dx,
+                                                                const Geom g, const DDataPlan pl) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int c0 = blockIdx.y * 16;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int gq = lane >> 2, q = lane & 3;
+  const int NB = (g.Wo + 7) >> 3;
+  const int items = g.Ho * NB;
+  const int rows = (g.HW + 1) >> 1;  // pixel pairs
+
+  // planes on a 128-byte boundary: the channel-half select is an XOR of the address with 64
+  const unsigned raw_saddr = (unsigned)__cvta_generic_to_shared(smem_raw);
+  const unsigned pad = (128u - (raw_saddr & 127u)) & 127u;
+  int* acc = reinterpret_cast<int*>(smem_raw + pad);  // [rows][32]
+  const unsigned acc_saddr = raw_saddr + pad;
+  float* scales = reinterpret_cast<float*>(acc + (size_t)rows * 32);  // [16] scale, [16] 1 / scale
+  unsigned* tab = reinterpret_cast<unsigned*>(scales + 32) + warp * kPairTabWords;
+  const LaneCells lc = lane_cells(g, q);
+  const bool sc44 = g.scH == 4 && g.scW == 4;
+
+  unsigned wa[4];  // A fragments of the bank slab (see the forward)
+  {
+    const __half* w0 = w + (size_t)(c0 + gq) * g.cells;
+    const __half* w1 = w0 + (size_t)8 * g.cells;
+    auto cell2 = [&](const __half* p, int k) {
+      const unsigned lo = k < g.cells ? (unsigned)__half_as_ushort(__ldg(p + k)) : 0u;
+      const unsigned hi = k + 1 < g.cells ? (unsigned)__half_as_ushort(__ldg(p + k + 1)) : 0u;
+      return lo | (hi << 16);
+    };
+    wa[0] = cell2(w0, 2 * q);
+    wa[1] = cell2(w1, 2 * q);
+    wa[2] = cell2(w0, 2 * q + 8);
+    wa[3] = cell2(w1, 2 * q + 8);
+  }
+  const unsigned lane_off = gq * 4;
+  const int n_begin = blockIdx.x * pl.samples_per_block;
+  const int n_end = min(n_begin + pl.samples_per_block, g.N);
+  for (int n = n_begin; n < n_end; ++n) {
+    ItemRegs cur;
+    if (warp < items) fetch_item(cur, dy, off, rot, g, n, c0, warp / NB, (warp % NB) << 3, lane, pl.pair_dy);
+    __syncthreads();  // the previous sample's planes have been written out
+    {
+      uint4* a4 = reinterpret_cast<uint4*>(acc);
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int i = threadIdx.x; i < rows * 8; i += blockDim.x) a4[i] = z;
+    }
+    // scale of each channel from max |dy| over its plane: warp k scans channel k
+    for (int ch = warp; ch < 16; ch += nwarps) {
+      const __half* p = dy + ((size_t)n * g.C + c0 + ch) * g.P;
+      float m = 0.f;
+      if (pl.pair_dy) {
+        const unsigned* p2 = reinterpret_cast<const unsigned*>(p);
+        for (int i = lane; i < (g.P >> 1); i += 32) {
+          const unsigned v = __ldg(p2 + i);
+          m = fmaxf(m, fmaxf(fabsf(lo2f(v)), fabsf(hi2f(v))));
+        }
+      } else {
+        for (int i = lane; i < g.P; i += 32) m = fmaxf(m, fabsf(__half2float(__ldg(p + i))));
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      if (lane == 0) {
+        float wm = 0.f;
+        for (int k = 0; k < g.cells; ++k) wm = fmaxf(wm, fabsf(__half2float(__ldg(w + (size_t)(c0 + ch) * g.cells + k))));
+        const float bound = m * wm * 1.01f;
+        // at most hits[n] contributions per accumulator, each at most 2^limit: no overflow of 31 bits; and each
+        // below 2^22, the range of the float -> integer conversion in scatter8
+        const int limit_log2 = min(21, 30 - (32 - __clz(max(__ldg(hits + n), 1) - 1)));
+        int e = 0;  // scale = 2^e with bound * 2^e <= 2^limit_log2
+        if (bound > 0.f && bound < 3e38f) {
+          const float lim = ldexpf(1.f, limit_log2) / bound;
+          e = ((__float_as_int(lim) >> 23) & 0xff) - 127;  // floor(log2(lim))
+          e = max(-100, min(100, e));
+        }
+        scales[ch] = __int_as_float((e + 127) << 23);
+        scales[16 + ch] = __int_as_float((127 - e) << 23);
+      }
+    }
+    __syncthreads();
+    const float sa = scales[gq], sb = scales[gq + 8];
+    for (int item = warp; item < items; item += nwarps) {
+      const int oh = item / NB;
+      const int ow0 = (item - oh * NB) << 3;
+      ItemRegs nxt;
+      const int item2 = item + nwarps;
+      if (item2 < items) {
+        const int oh2 = item2 / NB;
+        fetch_item(nxt, dy, off, rot, g, n, c0, oh2, (item2 - oh2 * NB) << 3, lane, pl.pair_dy);
+      }
+      unsigned bf[9][2];
+      beta_from_regs(bf, cur.rp, g, lc, sc44, ow0 + gq < g.Wo);
+#pragma unroll
+      for (int fh = 0; fh < 3; ++fh) {
+        __syncwarp();
+        if (lane < 24) pair_table_entry<S, true>(tab, g, fh, oh, ow0, lane, lo2f(cur.op[fh]), hi2f(cur.op[fh]), acc_saddr);
+        __syncwarp();
+#pragma unroll
+        for (int fw = 0; fw < 3; ++fw) {
+          const int t = fh * 3 + fw;
+          const uint4* e0 = reinterpret_cast<const uint4*>(tab + fw * 80 + q * 20);
+          const uint4 oA = e0[0], cA = e0[1], oB = e0[2], cB = e0[3];  // pixel 2q, pixel 2q + 1
+          unsigned kk[2];
+          mma16816_h(kk, wa, bf[t][0], bf[t][1]);
+          const unsigned g0 = hmul2u(kk[0], cur.dy0), g1 = hmul2u(kk[1], cur.dy1);  // K * dy of channel gq, gq + 8
+          scatter8(oA, cA, lo2f(g0) * sa, lo2f(g1) * sb, lane_off);
+          scatter8(oB, cB, hi2f(g0) * sa, hi2f(g1) * sb, lane_off);
+        }
+      }
+      if (item2 < items) cur = nxt;
+    }
+    __syncthreads();
+    // write the planes: a warp covers 8 channels x 4 pixel pairs, which sit in 32 different banks
+    __half* dx_n = dx + ((size_t)n * g.C + c0) * g.HW;
+    const bool pair_dx = (g.HW & 1) == 0 && pl.pair_dy;
+    for (int task = threadIdx.x; task < rows * 16; task += blockDim.x) {
+      const int rw = task >> 3;
+      const int half = rw / rows, row = rw - half * rows;
+      const int ch = half * 8 + (task & 7), i = row * 2;
+      const float inv = scales[16 + ch];
+      const float v0 = (float)acc[acc_word<S>(i, ch)] * inv, v1 = (float)acc[acc_word<S>(i + 1, ch)] * inv;
+      __half* o = dx_n + (size_t)ch * g.HW + i;
+      if (pair_dx) {
+        *reinterpret_cast<unsigned*>(o) = pack2(v0, v1);
+      } else {
+        o[0] = __float2half_rn(v0);
+        if (i + 1 < g.HW) o[1] = __float2half_rn(v1);
+      }
+    }
+  }
+}
+
 __global__ void reduce_dcn_bank_partials_kernel(const float* __restrict__ partial, __half* __restrict__ out, int C, int cells,
                                                 int nblocks) {
   const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -446,6 +764,29 @@ DcnPlan dcn_plan(const Geom& g, int ns_cap, int dy_rows) {
   return pl;
 }
 
+DDataPlan ddata_plan(const Geom& g) {
+  DDataPlan pl;
+  pl.warps = 0;
+  if (!dcn_fast_shape(g)) return pl;
+  const int groups = g.C / 16;
+  if ((long long)g.N * groups < 96) return pl;  // whole samples per block: too few of them to fill the GPU
+  const int NB = (g.Wo + 7) / 8;
+  const int items = g.Ho * NB;
+  pl.warps = items < 16 ? (items < 2 ? 2 : items) : 16;
+  pl.smem = 128 + (size_t)((g.HW + 1) / 2) * 128 + 128 + (size_t)pl.warps * kPairTabWords * 4;
+
+  if (pl.smem > kOnePerSm) {
+    pl.warps = 0;
+    return pl;
+  }
+  int want = 148 / groups;
+  if (want > g.N) want = g.N;
+  if (want < 1) want = 1;
+  pl.samples_per_block = (g.N + want - 1) / want;
+  pl.blocks_x = (g.N + pl.samples_per_block - 1) / pl.samples_per_block;
+  return pl;
+}
+
 int slab_cap() {  // DK_B200_DCN_SLABS = 1, 2 or 4 caps the channel slabs per block (tuning knob)
   static const int cap = [] {
     const char* e = getenv("DK_B200_DCN_SLABS");
@@ -515,6 +856,28 @@ int deform_forward_mma(const __half* x, const __half* off, const __half* rot, co
                                                                         : launch(mma_deform_fwd_kernel<1, 1>);
   return pl.NS == 4 ? launch(mma_deform_fwd_kernel<2, 4>) : pl.NS == 2 ? launch(mma_deform_fwd_kernel<2, 2>)
                                                                       : launch(mma_deform_fwd_kernel<2, 1>);
+}
+
+size_t deform_data_mma_workspace(const Geom& g) { return ddata_plan(g).warps ? (size_t)g.N * sizeof(int) : 0; }
+
+int deform_data_mma(const __half* dy, const __half* off, const __half* rot, const __half* w, __half* dx, const Geom& g,
+                    void* ws, size_t ws_bytes, cudaStream_t s) {
+  DDataPlan pl = ddata_plan(g);
+  if (!pl.warps || pl.smem > (size_t)device_smem_optin() || g.C / 16 > 65535) return DK_ERR_UNSUPPORTED;
+  if ((size_t)g.HW * sizeof(int) > 48 * 1024) return DK_ERR_UNSUPPORTED;
+  if (ws == nullptr || ws_bytes < (size_t)g.N * sizeof(int)) return DK_ERR_WORKSPACE;
+  int* hits = reinterpret_cast<int*>(ws);
+  if (g.sH == 1) dcn_hit_count_kernel<1><<<g.N, 256, (size_t)g.HW * sizeof(int), s>>>(off, hits, g);
+  else dcn_hit_count_kernel<2><<<g.N, 256, (size_t)g.HW * sizeof(int), s>>>(off, hits, g);
+  if (int rc = check_launch()) return rc;
+  pl.pair_dy = (g.Wo & 1) == 0 && ptr_mode(dy) >= 1 && ptr_mode(dx) >= 1;
+  const dim3 grid(pl.blocks_x, g.C / 16);
+  auto launch = [&](auto kern) -> int {
+    if (int e = enable_smem(kern, pl.smem)) return e;
+    kern<<<grid, pl.warps * 32, pl.smem, s>>>(dy, off, rot, w, hits, dx, g, pl);
+    return check_launch();
+  };
+  return g.sH == 1 ? launch(mma_deform_data_kernel<1>) : launch(mma_deform_data_kernel<2>);
 }
 
 }  // namespace dk

@@ -139,9 +139,14 @@ inline int ptr_mode(const void* p) {
 // rows outside the image).  Called by the whole block; the caller must execute
 // cp_async_wait_all() and __syncthreads() before reading.  Odd row widths fall back to plain
 // 2-byte copies behind an extra barrier.
-__device__ __forceinline__ void load_band(__half* __restrict__ band, const Band& b, const __half* __restrict__ src, int n, int C,
-                                          int c0, int cnt, int Hs, int Ws) {
-  const int tid = threadIdx.x, nt = blockDim.x;
+// load_band_group: the same for a group of nt threads (whole warps) numbered tid = 0 .. nt-1 that synchronises on
+// named barrier bar_id (bar_id 0: the whole block, __syncthreads).
+__device__ __forceinline__ void group_sync(int bar_id, int nt) {
+  if (bar_id == 0) __syncthreads();
+  else asm volatile("bar.sync %0, %1;\n" ::"r"(bar_id), "r"(nt) : "memory");
+}
+__device__ __forceinline__ void load_band_group(__half* __restrict__ band, const Band& b, const __half* __restrict__ src, int n,
+                                                int C, int c0, int cnt, int Hs, int Ws, int tid, int nt, int bar_id) {
   const int lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
   const int r_s = max(b.row_lo, 0), r_e = min(b.row_lo + b.RB, Hs);
   const size_t plane = (size_t)Hs * Ws;
@@ -152,7 +157,7 @@ __device__ __forceinline__ void load_band(__half* __restrict__ band, const Band&
     const int nv = cnt * b.pitch_c / 8;
     for (int i = tid; i < nv; i += nt) b4[i] = z;
     if (r_e <= r_s) return;
-    __syncthreads();
+    group_sync(bar_id, nt);
     // 2-byte copies, four independent loads in flight per thread
     const int rows = r_e - r_s;
     const int per = rows * Ws, total = cnt * per;
@@ -208,6 +213,10 @@ __device__ __forceinline__ void load_band(__half* __restrict__ band, const Band&
     if (lane < tail) zt[lane] = 0u;
     for (int v = lane + 32; v < tail; v += 32) zt[v] = 0u;
   }
+}
+__device__ __forceinline__ void load_band(__half* __restrict__ band, const Band& b, const __half* __restrict__ src, int n, int C,
+                                          int c0, int cnt, int Hs, int Ws) {
+  load_band_group(band, b, src, n, C, c0, cnt, Hs, Ws, threadIdx.x, blockDim.x, 0);
 }
 
 // Offset (in halves, even) of the window of pixel pair (ow, ow+1), row selector 0, inside a channel band.

@@ -176,6 +176,53 @@ def test_deform_dk_fp16_fast_shapes_match_oracle(ops, oracle, cfg):
     compare(mine_deform(ops, case, torch.float16), oracle_deform(oracle, case, torch.float16), torch.float16, "deform-fast")
 
 
+# DK + DCN shapes with enough (sample, 16-channel group) pairs for the whole-sample grad-input kernel
+DCN_BATCHED = [
+    dict(n=6, c=256, h=14, w=14, scope=(4, 4), k=3, stride=1, pad=1, rot_std=0.7),
+    dict(n=12, c=128, h=9, w=7, scope=(4, 4), k=3, stride=1, pad=1, rot_std=0.7),      # odd sizes: scalar loads and stores
+    dict(n=8, c=192, h=20, w=16, scope=(4, 4), k=3, stride=2, pad=1, rot_std=1.0),
+    dict(n=24, c=64, h=12, w=12, scope=(3, 5), k=3, stride=1, pad=1, rot_std=1.0),     # 15 cells
+]
+
+
+@pytest.mark.parametrize("cfg", DCN_BATCHED)
+def test_deform_dk_fp16_batched_shapes_match_oracle(ops, oracle, cfg):
+    case = make_case(seed=39, off_std=2.0, **cfg)
+    case["rotation"] = snap(case["rotation"])
+    case["offset"] = snap(case["offset"], seed=3)
+    compare(mine_deform(ops, case, torch.float16), oracle_deform(oracle, case, torch.float16), torch.float16, "deform-batched")
+
+
+def test_deform_grad_input_fixed_point_accumulation(ops, oracle):
+    """The fp16 grad-input kernel sums in fixed point.  Bit-reproducible; an outlier in dy coarsens only its own
+    (sample, channel) plane and the result still holds the tolerance on every plane taken by itself; offsets that
+    send every sample of an image to one pixel (the worst case for the accumulator's headroom) do not overflow."""
+    cfg = dict(n=6, c=256, h=14, w=14, scope=(4, 4), k=3, stride=1, pad=1, rot_std=0.7)
+    case = make_case(seed=40, off_std=2.0, **cfg)
+    case["grad_output"][1, 5, 3, 4] *= 1024.0
+    case["grad_output"][4, 200, 9, 9] *= -300.0
+    # sample 2: every tap of every pixel lands next to input pixel (6, 7)
+    ho = wo = 14
+    oh = torch.arange(ho).view(ho, 1).expand(ho, wo).float()
+    ow = torch.arange(wo).view(1, wo).expand(ho, wo).float()
+    for t in range(9):
+        case["offset"][2, 2 * t] = 6.3 - (oh - 1 + t // 3)
+        case["offset"][2, 2 * t + 1] = 7.6 - (ow - 1 + t % 3)
+    got = mine_deform(ops, case, torch.float16)
+    again = mine_deform(ops, case, torch.float16)
+    assert torch.equal(got["grad_input"], again["grad_input"])
+    want = oracle_deform(oracle, case, torch.float16)
+    compare(got, want, torch.float16, "deform-fixed-point")
+    g, w = got["grad_input"].float().cpu(), want["grad_input"].to(torch.float16).float()
+    err = (g - w).abs()
+    plane_max = w.abs().amax(dim=(2, 3), keepdim=True).clamp_min(1e-6)
+    keep = [0, 1, 3, 4, 5]
+    worst = float((err / plane_max)[keep].max())
+    assert worst < TOL[torch.float16], "per-plane rel err %.3e" % worst
+    # sample 2: 1764 terms per pixel, sums that cancel to almost nothing on some channels; judged against the sample
+    worst2 = float(err[2].max() / w[2].abs().max())
+    assert worst2 < TOL[torch.float16], "concentrated sample rel err %.3e" % worst2
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.float64])
 def test_plane_scale_is_the_per_sample_grouped_1x1_conv(ops, dtype):
     gen = torch.Generator().manual_seed(37)
