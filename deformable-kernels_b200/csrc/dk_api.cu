@@ -261,9 +261,19 @@ int dk_deform_sample_depthwise_backward_rotation(const void* grad_output, const 
                                                P_(T, filter), (T*)nullptr, M_(T, grad_rotation), gg, (cudaStream_t)stream))
 }
 
+/* First region of the fused backward's workspace: used by grad-input, then (same stream) by the offset gradients. */
+static size_t deform_front_ws(const dk_geom* g, int dtype) {
+  size_t need = dk_deform_sample_depthwise_backward_data_workspace_bytes(g, dtype);
+  Geom gg;
+  if (dtype == DK_F16 && make_geom(g, &gg)) {
+    const size_t c = align256(deform_coords_mma_workspace(gg));
+    if (c > need) need = c;
+  }
+  return need;
+}
+
 size_t dk_deform_sample_depthwise_backward_workspace_bytes(const dk_geom* g, int dtype) {
-  return dk_deform_sample_depthwise_backward_data_workspace_bytes(g, dtype) +
-         dk_deform_sample_depthwise_backward_filter_workspace_bytes(g, dtype);
+  return deform_front_ws(g, dtype) + dk_deform_sample_depthwise_backward_filter_workspace_bytes(g, dtype);
 }
 
 static int deform_coords_dispatch(const void* grad_output, const void* input, const void* offset, const void* rotation,
@@ -281,7 +291,7 @@ int dk_deform_sample_depthwise_backward(const void* grad_output, const void* inp
   Geom gg;
   if (!grad_output || !input || !offset || !rotation || !filter || !make_geom(g, &gg) || !dtype_ok(dtype))
     return DK_ERR_BAD_ARGUMENT;
-  const size_t data_ws = dk_deform_sample_depthwise_backward_data_workspace_bytes(g, dtype);
+  const size_t data_ws = deform_front_ws(g, dtype);
   const size_t filt_ws = dk_deform_sample_depthwise_backward_filter_workspace_bytes(g, dtype);
   int rc = DK_OK;
   if (grad_input) {
@@ -291,7 +301,13 @@ int dk_deform_sample_depthwise_backward(const void* grad_output, const void* inp
     if (rc) return rc;
   }
   if (grad_offset || grad_rotation) {
-    rc = deform_coords_dispatch(grad_output, input, offset, rotation, filter, grad_offset, grad_rotation, gg, dtype, stream);
+    rc = DK_ERR_UNSUPPORTED;
+    if (dtype == DK_F16 && mma_path_enabled() && workspace && workspace_bytes >= data_ws)
+      rc = deform_coords_mma(P_(__half, grad_output), P_(__half, input), P_(__half, offset), P_(__half, rotation),
+                             P_(__half, filter), M_(__half, grad_offset), M_(__half, grad_rotation), gg, workspace, data_ws,
+                             (cudaStream_t)stream);
+    if (rc == DK_ERR_UNSUPPORTED)
+      rc = deform_coords_dispatch(grad_output, input, offset, rotation, filter, grad_offset, grad_rotation, gg, dtype, stream);
     if (rc) return rc;
   }
   if (grad_filter) {

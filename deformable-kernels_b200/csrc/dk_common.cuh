@@ -190,6 +190,9 @@ struct FilterPlan {
 };
 FilterPlan filter_plan(const Geom& g, size_t acc_bytes);
 size_t deform_filter_mma_workspace(const Geom& g);
+size_t deform_coords_mma_workspace(const Geom& g);
+int deform_coords_mma(const __half* dy, const __half* x, const __half* off, const __half* rot, const __half* w, __half* doff,
+                      __half* drot, const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s);
 int deform_data_mma(const __half* dy, const __half* off, const __half* rot, const __half* w, __half* dx, const Geom& g,
                     void* ws, size_t ws_bytes, cudaStream_t s);
 int deform_forward_mma(const __half* x, const __half* off, const __half* rot, const __half* w, __half* y, const Geom& g,

@@ -690,6 +690,268 @@ __global__ void __launch_bounds__(512, 1) mma_deform_data_kernel(const __half* _
   }
 }
 
+// ------------------------------------------------------------------ gradients of the two offset fields
+// d(kernel offset)[p, tap, dir] = sum_c dy * xs * dK/d(u|v)   and   d(image offset)[p, tap, dir] = sum_c dy * K * dxs/d(h|w).
+// The first goes through G = W^T * (dy * xs) and the derivative hat weights exactly as in the local operator
+// (dk_local_mma.cu).  For the second, K comes from one mma per tap as in the forward, dxs/dh and dxs/dw are two more
+// coefficient sets over the same four image reads, and the sum over channels of E = dy * K * dxs is an mma with a
+// matrix of ones: the transposed E fragments (rows = 8 pixels x 2 directions, k = 16 channels) are its A operand.
+// A block owns 16 * NS channels; when that is not all of them, blocks add their partial sums into an fp32 buffer
+// [sample][36 planes][pixel] (image offsets first) with red.global.add.f32 and a second kernel rounds it.
+struct DCoordPlan {
+  int NS, BH, warps, bands, units_per_block, blocks_x, groups;
+  int mode_dy, mode_rot, mode_off;
+  bool vec;
+  size_t smem, ws_bytes;
+};
+constexpr int kCoordTabWords = 3 * 144;                   // 3 taps x 4 pixel pairs x (2 x 16 words + 4 of padding)
+constexpr int kCoordWarpWords = kCoordTabWords + 2 * 72;  // + the (u, v) of the item's 72 (pixel, tap) pairs
+constexpr int kBankPitch = 24;                            // halves per channel row of the bank copy (conflict-free fragments)
+
+// Sampling table with derivatives: per (pixel, tap) four corner offsets, then three sets of four coefficients
+// (value, d/dh, d/dw), each duplicated into both halves of a word.  Lanes 0..23.
+template <int S>
+__device__ __forceinline__ void build_coord_table(unsigned* __restrict__ tab, const __half* __restrict__ oband, const Band& bo,
+                                                  const Geom& g, int fh, int oh, int ow0, int lane) {
+  if (lane < 24) {
+    const int px = lane & 7, fw = lane >> 3;
+    const int pc = ow0 + px;
+    const int t = fh * 3 + fw;
+    const __half* op = oband + (size_t)(2 * t) * bo.pitch_c + kSlack + oh * bo.Wp + pc - bo.org;
+    const float ph = (float)(oh * S - 1 + fh) + __half2float(op[0]);
+    const float pw = (float)(pc * S - 1 + fw) + __half2float(op[bo.pitch_c]);
+    const bool used = pc < g.Wo && ph > -1.f && pw > -1.f && ph < (float)g.H && pw < (float)g.W;
+    uint4 o4 = make_uint4(0, 0, 0, 0), cv = o4, ch = o4, cw = o4;
+    if (used) {
+      const float fph = floorf(ph), fpw = floorf(pw);
+      const int h0 = (int)fph, w0 = (int)fpw;
+      const float lh = ph - fph, lw = pw - fpw;
+      const float hh = 1.f - lh, hw = 1.f - lw;
+      const bool r0 = h0 >= 0, r1 = h0 + 1 <= g.H - 1, k0 = w0 >= 0, k1 = w0 + 1 <= g.W - 1;
+      const int h0c = max(h0, 0), h1c = min(h0 + 1, g.H - 1), w0c = max(w0, 0), w1c = min(w0 + 1, g.W - 1);
+      o4.x = (unsigned)chunk_of<S>(h0c * g.W + w0c) * 32u;
+      o4.y = (unsigned)chunk_of<S>(h0c * g.W + w1c) * 32u;
+      o4.z = (unsigned)chunk_of<S>(h1c * g.W + w0c) * 32u;
+      o4.w = (unsigned)chunk_of<S>(h1c * g.W + w1c) * 32u;
+      auto dup = [](bool ok, float v) { return ok ? pack2(v, v) : 0u; };
+      cv = make_uint4(dup(r0 && k0, hh * hw), dup(r0 && k1, hh * lw), dup(r1 && k0, lh * hw), dup(r1 && k1, lh * lw));
+      ch = make_uint4(dup(r0 && k0, -hw), dup(r0 && k1, -lw), dup(r1 && k0, hw), dup(r1 && k1, lw));
+      cw = make_uint4(dup(r0 && k0, -hh), dup(r0 && k1, hh), dup(r1 && k0, -lh), dup(r1 && k1, lh));
+    }
+    uint4* e = reinterpret_cast<uint4*>(tab + fw * 144 + (px >> 1) * 36 + (px & 1) * 16);
+    e[0] = o4;
+    e[1] = cv;
+    e[2] = ch;
+    e[3] = cw;
+  }
+}
+
+// value and both derivatives of (channel j | channel j + 8) at one (pixel, tap)
+__device__ __forceinline__ void sample_pair3(unsigned& v, unsigned& dh, unsigned& dw, const char* __restrict__ base,
+                                             const uint4* __restrict__ e) {
+  const uint4 o = e[0], cv = e[1], ch = e[2], cw = e[3];
+  const unsigned x0 = *reinterpret_cast<const unsigned*>(base + o.x), x1 = *reinterpret_cast<const unsigned*>(base + o.y);
+  const unsigned x2 = *reinterpret_cast<const unsigned*>(base + o.z), x3 = *reinterpret_cast<const unsigned*>(base + o.w);
+  v = hfma2u(x3, cv.w, hfma2u(x2, cv.z, hfma2u(x1, cv.y, hmul2u(x0, cv.x))));
+  dh = hfma2u(x3, ch.w, hfma2u(x2, ch.z, hfma2u(x1, ch.y, hmul2u(x0, ch.x))));
+  dw = hfma2u(x3, cw.w, hfma2u(x2, cw.z, hfma2u(x1, cw.y, hmul2u(x0, cw.x))));
+}
+
+template <int S, int NS>
+__global__ void __launch_bounds__(512, 1)
+    mma_deform_coords_kernel(const __half* __restrict__ dy, const __half* __restrict__ x, const __half* __restrict__ off,
+                             const __half* __restrict__ rot, const __half* __restrict__ w, __half* __restrict__ doff,
+                             __half* __restrict__ drot, float* __restrict__ partial, const Geom g, const DCoordPlan pl) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int CG = 16 * NS;
+  constexpr int pitchT = CG + 8;
+  const int c0 = blockIdx.y * CG;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int gq = lane >> 2, q = lane & 3;
+  const int NB = (g.Wo + 7) >> 3;
+  const int items = pl.BH * NB;
+  const int Wpo = g.Wo + (g.Wo & 1);
+  const int HW16 = (g.HW + 15) & ~15;
+  const int ypitch = band_pitch(pl.BH, Wpo);
+
+  unsigned* xw = reinterpret_cast<unsigned*>(smem_raw);                      // [NS][HW16 * 8]
+  __half* yband = reinterpret_cast<__half*>(xw + (size_t)NS * HW16 * 8);     // [CG][ypitch]
+  __half* rband = yband + (size_t)CG * ypitch;                               // [18][ypitch]
+  __half* oband = rband + (size_t)18 * ypitch;                               // [18][ypitch]
+  __half* bankT = oband + (size_t)18 * ypitch;                               // [16 cells][CG + 8]
+  __half* bank = bankT + 16 * pitchT;                                        // [CG][kBankPitch]
+  unsigned* tab = reinterpret_cast<unsigned*>(bank + CG * kBankPitch) + warp * kCoordWarpWords;
+  float* Gs = reinterpret_cast<float*>(tab);                   // [3 taps][16 cells][8 px], aliases the table
+  float2* uv = reinterpret_cast<float2*>(tab + kCoordTabWords);  // [9 taps][8 px]
+  const LaneCells lc = lane_cells(g, q);
+  const bool sc44 = g.scH == 4 && g.scW == 4;
+
+  for (int i = threadIdx.x; i < 16 * CG; i += blockDim.x) {
+    const int cell = i / CG, c = i - cell * CG;
+    const __half v = cell < g.cells ? __ldg(w + (size_t)(c0 + c) * g.cells + cell) : __float2half(0.f);
+    bankT[cell * pitchT + c] = v;
+    bank[c * kBankPitch + cell] = v;
+  }
+
+  const int total_units = g.N * pl.bands;
+  const int u_begin = blockIdx.x * pl.units_per_block;
+  const int u_end = min(u_begin + pl.units_per_block, total_units);
+  int cur_n = -1;
+  for (int unit = u_begin; unit < u_end; ++unit) {
+    const int n = unit / pl.bands;
+    const int oh0 = (unit - n * pl.bands) * pl.BH;
+    const Band by = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_dy);
+    const Band br = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_rot);
+    const Band bo = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_off);
+    __syncthreads();  // readers of the previous unit are done
+    load_band(yband, by, dy, n, g.C, c0, CG, g.Ho, g.Wo);
+    load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
+    load_band(oband, bo, off, n, 18, 0, 18, g.Ho, g.Wo);
+    if (n != cur_n) {
+#pragma unroll
+      for (int sidx = 0; sidx < NS; ++sidx) load_pair_planes<S>(xw + (size_t)sidx * HW16 * 8, x, n, g.C, c0 + 16 * sidx, g.HW, pl.vec);
+      cur_n = n;
+    }
+    cp_async_wait_all();
+    __syncthreads();
+
+    __half* doff_n = doff ? doff + (size_t)n * 18 * g.P : nullptr;
+    __half* drot_n = drot ? drot + (size_t)n * 18 * g.P : nullptr;
+    float* part_n = partial + (size_t)n * 36 * g.P;
+    for (int item = warp; item < items; item += nwarps) {
+      const int dr = item / NB;
+      const int oh = oh0 + dr;
+      if (oh >= g.Ho) break;
+      const int ow0 = (item - dr * NB) << 3;
+      unsigned bf[9][2];
+      beta_direct<S, false, false>(bf, rband, br, g, lc, sc44, oh, ow0, g.H, g.W, g.Wo, gq);
+      __syncwarp();
+      item_uv<S, false>(uv, rband, br, g, oh, ow0, lane);
+      const int yoff = kSlack + oh * by.Wp + ow0 + 2 * q - by.org;
+      unsigned dy0[NS], dy1[NS];
+#pragma unroll
+      for (int sidx = 0; sidx < NS; ++sidx) {
+        dy0[sidx] = *reinterpret_cast<const unsigned*>(yband + (size_t)(16 * sidx + gq) * by.pitch_c + yoff);
+        dy1[sidx] = *reinterpret_cast<const unsigned*>(yband + (size_t)(16 * sidx + gq + 8) * by.pitch_c + yoff);
+      }
+      const char* lane_base = reinterpret_cast<const char*>(xw) + gq * 4;
+      const size_t row = (size_t)oh * g.Wo + ow0;
+#pragma unroll
+      for (int fh = 0; fh < 3; ++fh) {
+        __syncwarp();  // the previous pass has read Gs (the table's storage)
+        build_coord_table<S>(tab, oband, bo, g, fh, oh, ow0, lane);
+        __syncwarp();
+        float G[3][4], D[3][4];
+#pragma unroll
+        for (int fw = 0; fw < 3; ++fw)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) G[fw][k] = D[fw][k] = 0.f;
+#pragma unroll
+        for (int sidx = 0; sidx < NS; ++sidx) {
+          const int cb16 = 16 * sidx;
+          // A = W slab (rows = channels gq, gq + 8; k = cells) and A = W^T slab (rows = cells; k = channels)
+          const unsigned* b0 = reinterpret_cast<const unsigned*>(bank + (cb16 + gq) * kBankPitch);
+          const unsigned* b1 = reinterpret_cast<const unsigned*>(bank + (cb16 + gq + 8) * kBankPitch);
+          const unsigned wa[4] = {b0[q], b1[q], b0[q + 4], b1[q + 4]};
+          const unsigned* wt0 = reinterpret_cast<const unsigned*>(bankT + gq * pitchT + cb16);
+          const unsigned* wt1 = reinterpret_cast<const unsigned*>(bankT + (gq + 8) * pitchT + cb16);
+          const unsigned t0 = wt0[q], t1 = wt1[q], t2 = wt0[q + 4], t3 = wt1[q + 4];
+          const char* base = lane_base + (size_t)sidx * HW16 * 32;
+#pragma unroll
+          for (int fw = 0; fw < 3; ++fw) {
+            const uint4* e0 = reinterpret_cast<const uint4*>(tab + fw * 144 + q * 36);
+            unsigned vA, hA, wA, vB, hB, wB;  // pixel 2q and pixel 2q + 1: (channel gq | channel gq + 8)
+            sample_pair3(vA, hA, wA, base, e0);
+            sample_pair3(vB, hB, wB, base, e0 + 4);
+            // kernel offsets: G += W^T * (dy * xs)
+            const unsigned ka = hmul2u(dy0[sidx], __byte_perm(vA, vB, 0x5410));
+            const unsigned kb = hmul2u(dy1[sidx], __byte_perm(vA, vB, 0x7632));
+            mma16816_acc(G[fw], t0, t1, t2, t3, movmatrix_trans(ka), movmatrix_trans(kb));
+            // image offsets: D[pixel, dir] += sum over the slab's channels of dy * K * dxs
+            unsigned kk[2];
+            mma16816_h(kk, wa, bf[fh * 3 + fw][0], bf[fh * 3 + fw][1]);
+            const unsigned ya = hmul2u(kk[0], dy0[sidx]), yb = hmul2u(kk[1], dy1[sidx]);
+            const unsigned eha = hmul2u(ya, __byte_perm(hA, hB, 0x5410)), ehb = hmul2u(yb, __byte_perm(hA, hB, 0x7632));
+            const unsigned ewa = hmul2u(ya, __byte_perm(wA, wB, 0x5410)), ewb = hmul2u(yb, __byte_perm(wA, wB, 0x7632));
+            mma16816_acc(D[fw], movmatrix_trans(eha), movmatrix_trans(ewa), movmatrix_trans(ehb), movmatrix_trans(ewb),
+                         0x3C003C00u, 0x3C003C00u);
+          }
+        }
+        // image offsets: row gq of D = pixel gq, direction h; row gq + 8 = direction w (every column holds the sum)
+        if (q == 0 && ow0 + gq < g.Wo) {
+#pragma unroll
+          for (int fw = 0; fw < 3; ++fw) {
+            const size_t o = (size_t)(2 * (fh * 3 + fw)) * g.P + row + gq;
+            if (pl.groups == 1) {
+              if (doff_n) {
+                doff_n[o] = __float2half_rn(D[fw][0]);
+                doff_n[o + g.P] = __float2half_rn(D[fw][2]);
+              }
+            } else {
+              atomicAdd(part_n + o, D[fw][0]);
+              atomicAdd(part_n + o + g.P, D[fw][2]);
+            }
+          }
+        }
+        // kernel offsets: sum over the four corner cells of G * d(hat weight)/d(u or v)
+        __syncwarp();  // the table has been read by every lane
+#pragma unroll
+        for (int fw = 0; fw < 3; ++fw) {
+          *reinterpret_cast<float2*>(Gs + (fw * 16 + gq) * 8 + 2 * q) = make_float2(G[fw][0], G[fw][1]);
+          *reinterpret_cast<float2*>(Gs + (fw * 16 + gq + 8) * 8 + 2 * q) = make_float2(G[fw][2], G[fw][3]);
+        }
+        __syncwarp();
+        if (lane < 24) {
+          const int px = lane & 7, fw = lane >> 3;
+          const int t = fh * 3 + fw;
+          const float2 c = uv[t * 8 + px];
+          float gu = 0.f, gv = 0.f;
+          if (c.x < 1e29f) {
+            const float fu = floorf(c.x), fv = floorf(c.y);
+            const int h0 = (int)fu, w0 = (int)fv;
+            const float lh = c.x - fu, lw = c.y - fv;
+            const float hh = 1.f - lh, hw = 1.f - lw;
+            const float* Gp = Gs + fw * 128 + px;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int a = h0 + (k >> 1), b = w0 + (k & 1);
+              if (a >= 0 && a < g.scH && b >= 0 && b < g.scW) {
+                const float gval = Gp[(a * g.scW + b) * 8];
+                const float du = (k >> 1) ? ((k & 1) ? lw : hw) : ((k & 1) ? -lw : -hw);
+                const float dv = (k & 1) ? ((k >> 1) ? lh : hh) : ((k >> 1) ? -lh : -hh);
+                gu += du * gval;
+                gv += dv * gval;
+              }
+            }
+          }
+          if (ow0 + px < g.Wo) {
+            const size_t o = (size_t)(2 * t) * g.P + row + px;
+            if (pl.groups == 1) {
+              if (drot_n) {
+                drot_n[o] = __float2half_rn(gu);
+                drot_n[o + g.P] = __float2half_rn(gv);
+              }
+            } else {
+              atomicAdd(part_n + 18 * g.P + o, gu);
+              atomicAdd(part_n + 18 * g.P + o + g.P, gv);
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// out = fp16(partial) for one of the two offset fields: partial is [N][36][P], the field's 18 planes start at `first`
+__global__ void round_coord_partials_kernel(const float* __restrict__ partial, __half* __restrict__ out, int N, size_t plane18,
+                                            int first) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)N * plane18) return;
+  const size_t n = i / plane18, r = i - n * plane18;
+  out[i] = __float2half_rn(partial[n * 2 * plane18 + (size_t)first * (plane18 / 18) + r]);
+}
+
 __global__ void reduce_dcn_bank_partials_kernel(const float* __restrict__ partial, __half* __restrict__ out, int C, int cells,
                                                 int nblocks) {
   const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -787,6 +1049,57 @@ DDataPlan ddata_plan(const Geom& g) {
   return pl;
 }
 
+DCoordPlan dcoord_plan(const Geom& g, int ns_cap) {
+  DCoordPlan pl;
+  pl.BH = 0;
+  if (!dcn_fast_shape(g)) return pl;
+  const int NB = (g.Wo + 7) / 8;
+  const int Wpo = g.Wo + (g.Wo & 1);
+  const int HW16 = (g.HW + 15) & ~15;
+  const size_t plane = (size_t)HW16 * 32;
+  const int slabs = g.C / 16;
+  for (int ns = 2; ns >= 1; ns >>= 1) {  // four slabs would spill the accumulators
+    if (ns > ns_cap || slabs % ns) continue;
+    if (ns > 1 && (long long)(slabs / ns) * g.N < 148) continue;
+    const int cg = 16 * ns;
+    auto need = [&](int bh, int& warps) {
+      warps = bh * NB;
+      if (warps > 16) warps = 16;
+      if (warps < 2) warps = 2;
+      return ns * plane + (size_t)(36 + cg) * band_pitch(bh, Wpo) * 2 + (size_t)16 * (cg + 8) * 2 + (size_t)cg * kBankPitch * 2 +
+             (size_t)warps * kCoordWarpWords * 4;
+    };
+    int bh_max = 0, wv;
+    for (int bh = 1; bh <= g.Ho; ++bh) {
+      if (need(bh, wv) > kOnePerSm) break;
+      bh_max = bh;
+    }
+    if (!bh_max || (ns > 1 && bh_max * NB < 28 && bh_max < g.Ho)) continue;
+    const int groups = slabs / ns;
+    int bands = (g.Ho + bh_max - 1) / bh_max;
+    const long long base_units = (long long)g.N * groups;
+    if (base_units * bands < 148) {
+      long long wantb = (148 + base_units - 1) / base_units;
+      if (wantb > g.Ho) wantb = g.Ho;
+      if (wantb > bands) bands = (int)wantb;
+    }
+    pl.NS = ns;
+    pl.groups = groups;
+    pl.BH = (g.Ho + bands - 1) / bands;
+    pl.bands = (g.Ho + pl.BH - 1) / pl.BH;
+    pl.smem = need(pl.BH, pl.warps);
+    const long long units = (long long)g.N * pl.bands;
+    long long want = 148 / groups;
+    if (want > units) want = units;
+    if (want < 1) want = 1;
+    pl.units_per_block = (int)((units + want - 1) / want);
+    pl.blocks_x = (int)((units + pl.units_per_block - 1) / pl.units_per_block);
+    pl.ws_bytes = groups > 1 ? (size_t)g.N * 36 * g.P * sizeof(float) : 0;
+    return pl;
+  }
+  return pl;
+}
+
 int slab_cap() {  // DK_B200_DCN_SLABS = 1, 2 or 4 caps the channel slabs per block (tuning knob)
   static const int cap = [] {
     const char* e = getenv("DK_B200_DCN_SLABS");
@@ -878,6 +1191,51 @@ int deform_data_mma(const __half* dy, const __half* off, const __half* rot, cons
     return check_launch();
   };
   return g.sH == 1 ? launch(mma_deform_data_kernel<1>) : launch(mma_deform_data_kernel<2>);
+}
+
+size_t deform_coords_mma_workspace(const Geom& g) {
+  size_t need = 0;
+  for (int cap = 1; cap <= 2; cap <<= 1) {
+    const DCoordPlan pl = dcoord_plan(g, cap);
+    if (pl.BH && pl.ws_bytes > need) need = pl.ws_bytes;
+  }
+  return need;
+}
+
+int deform_coords_mma(const __half* dy, const __half* x, const __half* off, const __half* rot, const __half* w, __half* doff,
+                      __half* drot, const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s) {
+  DCoordPlan pl = dcoord_plan(g, slab_cap());
+  if (!pl.BH || pl.smem > (size_t)device_smem_optin() || g.C / (16 * pl.NS) > 65535) return DK_ERR_UNSUPPORTED;
+  if (pl.ws_bytes && (ws == nullptr || ws_bytes < pl.ws_bytes)) return DK_ERR_UNSUPPORTED;  // no scratch: the SIMT kernel
+  pl.mode_dy = ptr_mode(dy);
+  pl.mode_rot = ptr_mode(rot);
+  pl.mode_off = ptr_mode(off);
+  pl.vec = (g.HW & 7) == 0 && ptr_mode(x) == 2;
+  float* partial = reinterpret_cast<float*>(ws);
+  if (pl.ws_bytes) {
+    const cudaError_t e = cudaMemsetAsync(partial, 0, pl.ws_bytes, s);
+    if (e != cudaSuccess) {
+      set_last_cuda_error(e);
+      return DK_ERR_CUDA;
+    }
+  }
+  const dim3 grid(pl.blocks_x, g.C / (16 * pl.NS));
+  auto launch = [&](auto kern) -> int {
+    if (int e = enable_smem(kern, pl.smem)) return e;
+    kern<<<grid, pl.warps * 32, pl.smem, s>>>(dy, x, off, rot, w, doff, drot, partial, g, pl);
+    return check_launch();
+  };
+  int rc;
+  if (g.sH == 1)
+    rc = pl.NS == 2 ? launch(mma_deform_coords_kernel<1, 2>) : launch(mma_deform_coords_kernel<1, 1>);
+  else
+    rc = pl.NS == 2 ? launch(mma_deform_coords_kernel<2, 2>) : launch(mma_deform_coords_kernel<2, 1>);
+  if (rc || !pl.ws_bytes) return rc;
+  const size_t plane18 = (size_t)18 * g.P, count = (size_t)g.N * plane18;
+  const unsigned blocks = (unsigned)((count + 255) / 256);
+  if (doff) round_coord_partials_kernel<<<blocks, 256, 0, s>>>(partial, doff, g.N, plane18, 0);
+  if (drot) round_coord_partials_kernel<<<blocks, 256, 0, s>>>(partial, drot, g.N, plane18, 18);
+  return check_launch();
 }
 
 }  // namespace dk

@@ -386,14 +386,14 @@ __device__ __forceinline__ void beta_direct(unsigned (&bf)[9][2], const __half* 
 
 // Bank coordinates (u, v) of the 72 (pixel, tap) pairs of an item, left in uv[tap*8 + pixel]
 // (u = 1e30 marks a tap that is unused: in the padding or outside the bank).  Lanes 0..23, three passes.
-template <int S>
+template <int S, bool IMAGE_MASK = true>
 __device__ __forceinline__ void item_uv(float2* __restrict__ uv, const __half* __restrict__ rband, const Band& rb, const Geom& g,
                                         int drow, int ow0, int lane) {
   const float uh0 = (float)(g.scH - 3) * 0.5f, uw0 = (float)(g.scW - 3) * 0.5f;
   const int px = lane & 7, fw = lane >> 3;
   const int pc = ow0 + px;
   const int sc = pc * S - 1 + fw;
-  const bool cok = pc < g.Wo && sc >= 0 && sc < g.W;
+  const bool cok = pc < g.Wo && (!IMAGE_MASK || (sc >= 0 && sc < g.W));
   const __half* base = rband + kSlack - rb.org + drow * rb.Wp + pc;
   if (lane < 24) {
 #pragma unroll
@@ -403,7 +403,7 @@ __device__ __forceinline__ void item_uv(float2* __restrict__ uv, const __half* _
       const __half* rp = base + (size_t)(2 * t) * rb.pitch_c;
       const float u = ((float)fh + __half2float(rp[0])) + uh0;
       const float v = ((float)fw + __half2float(rp[rb.pitch_c])) + uw0;
-      const bool valid = cok && sr >= 0 && sr < g.H && u > -1.f && v > -1.f && u < (float)g.scH && v < (float)g.scW;
+      const bool valid = cok && (!IMAGE_MASK || (sr >= 0 && sr < g.H)) && u > -1.f && v > -1.f && u < (float)g.scH && v < (float)g.scW;
       uv[t * 8 + px] = make_float2(valid ? u : 1e30f, v);
     }
   }
