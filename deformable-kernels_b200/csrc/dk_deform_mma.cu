@@ -422,9 +422,9 @@ struct DDataPlan {
 
 // hits[n] = max over input pixels of the number of (output pixel, tap) samples of sample n with a corner on it
 template <int S>
-__global__ void __launch_bounds__(256) dcn_hit_count_kernel(const __half* __restrict__ off, int* __restrict__ hits, const Geom g) {
+__global__ void __launch_bounds__(1024) dcn_hit_count_kernel(const __half* __restrict__ off, int* __restrict__ hits, const Geom g) {
   extern __shared__ int cnt[];
-  __shared__ int wmax[8];
+  __shared__ int wmax[32];
   const int n = blockIdx.x;
   for (int i = threadIdx.x; i < g.HW; i += blockDim.x) cnt[i] = 0;
   __syncthreads();
@@ -451,7 +451,7 @@ __global__ void __launch_bounds__(256) dcn_hit_count_kernel(const __half* __rest
   if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int k = 1; k < 8; ++k) m = max(m, wmax[k]);
+    for (int k = 1; k < (int)(blockDim.x >> 5); ++k) m = max(m, wmax[k]);
     hits[n] = m;
   }
 }
@@ -1180,8 +1180,8 @@ int deform_data_mma(const __half* dy, const __half* off, const __half* rot, cons
   if ((size_t)g.HW * sizeof(int) > 48 * 1024) return DK_ERR_UNSUPPORTED;
   if (ws == nullptr || ws_bytes < (size_t)g.N * sizeof(int)) return DK_ERR_WORKSPACE;
   int* hits = reinterpret_cast<int*>(ws);
-  if (g.sH == 1) dcn_hit_count_kernel<1><<<g.N, 256, (size_t)g.HW * sizeof(int), s>>>(off, hits, g);
-  else dcn_hit_count_kernel<2><<<g.N, 256, (size_t)g.HW * sizeof(int), s>>>(off, hits, g);
+  if (g.sH == 1) dcn_hit_count_kernel<1><<<g.N, 1024, (size_t)g.HW * sizeof(int), s>>>(off, hits, g);
+  else dcn_hit_count_kernel<2><<<g.N, 1024, (size_t)g.HW * sizeof(int), s>>>(off, hits, g);
   if (int rc = check_launch()) return rc;
   pl.pair_dy = (g.Wo & 1) == 0 && ptr_mode(dy) >= 1 && ptr_mode(dx) >= 1;
   const dim3 grid(pl.blocks_x, g.C / 16);
