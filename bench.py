@@ -253,6 +253,63 @@ def run_training_step(args, rank, world, local, dev):
             "loss": float(loss.item()), "clocks": clocks, "peak_mem_GB": round(torch.cuda.max_memory_allocated() / 1e9, 1)}))
 
 
+def run_dcn_layer(args, rank, world, local, dev):
+    """BASELINE.json config 4: one DK + DCN layer (C=256, 56x56, 3x3, scope 4x4, fp16), forward + backward through the
+    autograd API, each rank on its own batch shard (weak scaling, no collective)."""
+    import torch.distributed as dist
+    from deformable_kernels.ops.deform_kernel.functions import deform_sample_depthwise
+    n = args.dcn_batch
+    g = torch.Generator(device=dev).manual_seed(4 + rank)
+    w = (torch.randn(256, 1, 4, 4, device=dev, generator=g) * 0.354).half().requires_grad_(True)
+    x = torch.randn(n, 256, 56, 56, device=dev, generator=g).half().requires_grad_(True)
+    rot = (torch.randn(n, 18, 56, 56, device=dev, generator=g) * 0.5).half().requires_grad_(True)
+    off = (torch.randn(n, 18, 56, 56, device=dev, generator=g) * 2.0).half().requires_grad_(True)
+    dy = torch.randn(n, 256, 56, 56, device=dev, generator=g).half()
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=dev)  # larger than the 126 MB L2
+
+    def step():
+        y = deform_sample_depthwise(x, off, rot, w)
+        return torch.autograd.grad(y, [x, off, rot, w], dy)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    total = 0.0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(args.steps):
+        flush.zero_()
+        e0.record()
+        step()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    tms = torch.tensor([total], device=dev)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms_step = float(tms.item()) / args.steps
+    bytes_step = 557.2e6 * n / 64
+    peak, peak_kind = measured_peak()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "DK+DCN layer fwd+bwd images/sec (C=256, 56x56, fp16)", "value": world * n / (ms_step * 1e-3),
+            "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "cfg4: DeformableSampleDepthwise C=256 56x56 k3 scope 4x4, batch %d per GPU, offsets "
+                                   "~N(0,2^2), kernel offsets ~N(0,0.5^2)" % n,
+                       "l2": "a 160 MB buffer is written between timed iterations"},
+            "roofline": {"bound": "hbm", "achieved": round(bytes_step / (ms_step * 1e-3) / 1e9, 1), "peak": peak,
+                         "peak_source": peak_kind, "unit": "GB/s",
+                         "frac": round(bytes_step / (ms_step * 1e-3) / 1e9 / peak, 4), "traffic": None,
+                         "algorithmic_bytes": bytes_step, "kernel": "whole layer, forward + backward (6 kernels)"},
+            "gpu_launches": 10 * args.steps, "clocks": clocks}))
+
+
 def time_reference_gpu(layers, n, time_call):
     """The reference's own CUDA kernels (unmodified extension from oracle/_ref/) on the same
     tensors: forward and the three backward launches per layer, device-timed.  A side
@@ -314,9 +371,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true")
-    ap.add_argument("--workload", default="sweep", choices=["sweep", "train"],
-                    help="sweep: the DK layer sweep (headline); train: MobileNetV2-DK training step, global batch 1024")
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "train", "dcn"],
+                    help="sweep: the DK layer sweep (headline); train: MobileNetV2-DK training step, global batch 1024; "
+                         "dcn: one DK + DCN layer (BASELINE config 4)")
     ap.add_argument("--global-batch", type=int, default=1024)
+    ap.add_argument("--dcn-batch", type=int, default=64, help="images per GPU of the dcn workload")
     ap.add_argument("--layers", default="", help="comma-separated indices into the ten-layer sweep (default: all)")
     ap.add_argument("--ref-gpu", action="store_true",
                     help="also time the reference's own CUDA kernels (oracle/_ref build) on this GPU")
@@ -339,8 +398,8 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-    if args.workload == "train":
-        run_training_step(args, rank, world, local, dev)
+    if args.workload in ("train", "dcn"):
+        (run_training_step if args.workload == "train" else run_dcn_layer)(args, rank, world, local, dev)
         if world > 1:
             dist.destroy_process_group()
         return
