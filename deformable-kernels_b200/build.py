@@ -15,7 +15,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libdk_b200.so")
-SOURCES = ["dk_api.cu", "dk_local.cu", "dk_local_mma.cu", "dk_deform.cu", "dk_deform_mma.cu", "dk_nd.cu", "dk_scale.cu", "dk_static_scratch.cu"]
+SOURCES = ["dk_api.cu", "dk_local.cu", "dk_local_mma.cu", "dk_deform.cu", "dk_deform_mma.cu", "dk_nd.cu", "dk_scale.cu", "dk_global.cu", "dk_static_scratch.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

@@ -380,4 +380,45 @@ int dk_nd_linear_sample_backward_coord_sum(const void* grad_output, const void* 
                                           channels, dims, prod, sh, true, (cudaStream_t)stream))
 }
 
+/* ---------------------------------------------------------------- fused global DK (1x1 depthwise) */
+
+size_t dk_global_dk_backward_workspace_bytes(int batch, int channels, int dims) {
+  if (batch <= 0 || channels <= 0 || dims <= 0) return 0;
+  return align256(((size_t)2 * batch * channels + (size_t)batch * dims) * sizeof(float));
+}
+
+int dk_global_dk_forward(const void* input, const void* bank, const void* fc_weight, const void* fc_bias,
+                         const void* tap_bias, void* output, void* pooled, void* raw_coord, void* coord, void* scale,
+                         int batch, int channels, int plane_size, int dims, const int* shape, int dtype, void* stream) {
+  NdShape sh;
+  int prod;
+  if (!input || !bank || !fc_weight || !fc_bias || !tap_bias || !output || !pooled || !raw_coord || !coord || !scale ||
+      plane_size <= 0)
+    return DK_ERR_BAD_ARGUMENT;
+  int rc = nd_args(batch, channels, dims, shape, &sh, &prod);
+  if (rc) return rc;
+  DK_DISPATCH(dtype, global_dk_forward<T>(P_(T, input), P_(float, bank), P_(float, fc_weight), P_(float, fc_bias),
+                                          P_(float, tap_bias), M_(T, output), M_(float, pooled), M_(float, raw_coord),
+                                          M_(float, coord), M_(float, scale), batch, channels, plane_size, dims, prod, sh,
+                                          (cudaStream_t)stream))
+}
+
+int dk_global_dk_backward(const void* grad_output, const void* input, const void* bank, const void* fc_weight,
+                          const void* pooled, const void* raw_coord, const void* coord, const void* scale, void* grad_input,
+                          void* grad_bank, void* grad_fc_weight, void* grad_fc_bias, int batch, int channels, int plane_size,
+                          int dims, const int* shape, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  NdShape sh;
+  int prod;
+  if (!grad_output || !input || !bank || !fc_weight || !pooled || !raw_coord || !coord || !scale || plane_size <= 0)
+    return DK_ERR_BAD_ARGUMENT;
+  int rc = nd_args(batch, channels, dims, shape, &sh, &prod);
+  if (rc) return rc;
+  if (!workspace || workspace_bytes < dk_global_dk_backward_workspace_bytes(batch, channels, dims)) return DK_ERR_WORKSPACE;
+  DK_DISPATCH(dtype, global_dk_backward<T>(P_(T, grad_output), P_(T, input), P_(float, bank), P_(float, fc_weight),
+                                           P_(float, pooled), P_(float, raw_coord), P_(float, coord), P_(float, scale),
+                                           M_(T, grad_input), M_(float, grad_bank), M_(float, grad_fc_weight),
+                                           M_(float, grad_fc_bias), M_(float, workspace), batch, channels, plane_size, dims,
+                                           prod, sh, (cudaStream_t)stream))
+}
+
 }  // extern "C"

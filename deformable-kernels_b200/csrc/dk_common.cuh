@@ -205,6 +205,14 @@ constexpr int kMaxNdDims = 8;
 struct NdShape {
   int s[kMaxNdDims];
 };
+template <typename T>
+int global_dk_forward(const T* x, const float* bank, const float* fc_w, const float* fc_b, const float* tap_bias, T* y,
+                      float* gap, float* raw, float* coord, float* scale, int N, int C, int hw, int D, int prod,
+                      const NdShape& sh, cudaStream_t s);
+template <typename T>
+int global_dk_backward(const T* dy, const T* x, const float* bank, const float* fc_w, const float* gap, const float* raw,
+                       const float* coord, const float* scale, T* dx, float* dbank, float* dfc_w, float* dfc_b, float* ws,
+                       int N, int C, int hw, int D, int prod, const NdShape& sh, cudaStream_t s);
 template <typename T> int nd_forward(const T*, const T*, T*, int B, int C, int D, int prod, const NdShape&, cudaStream_t);
 template <typename T> int nd_backward_data(const T*, const T*, T*, int B, int C, int D, int prod, const NdShape&, cudaStream_t);
 template <typename T>

@@ -60,6 +60,9 @@ _PROTOS = {
     "dk_nd_linear_sample_backward_coord_sum": (_int, [_vp, _vp, _vp, _vp, _int, _int, _int, _ip, _int, _vp]),
     "dk_plane_scale_forward": (_int, [_vp, _vp, _vp, ctypes.c_longlong, _int, _int, _vp]),
     "dk_plane_scale_backward": (_int, [_vp, _vp, _vp, _vp, _vp, ctypes.c_longlong, _int, _int, _vp]),
+    "dk_global_dk_forward": (_int, [_vp] * 10 + [_int, _int, _int, _int, _ip, _int, _vp]),
+    "dk_global_dk_backward_workspace_bytes": (ctypes.c_size_t, [_int, _int, _int]),
+    "dk_global_dk_backward": (_int, [_vp] * 12 + [_int, _int, _int, _int, _ip, _int, _vp, ctypes.c_size_t, _vp]),
     "dk_output_size": (_int, [_gp, _ip, _ip]),
     "dk_status_string": (ctypes.c_char_p, [_int]),
     "dk_last_cuda_error": (_int, []),

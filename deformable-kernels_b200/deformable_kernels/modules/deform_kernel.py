@@ -9,7 +9,7 @@ state dicts are interchangeable: ``weight``, ``fc.*``; ``rotation_conv.*``,
 import torch
 from torch import nn
 
-from ..ops.deform_kernel.functions import nd_linear_sample, plane_scale
+from ..ops.deform_kernel.functions import global_dk_scale, nd_linear_sample, plane_scale
 from ..ops.deform_kernel.modules import SampleDepthwise, DeformableSampleDepthwise
 
 __all__ = ['GlobalDeformKernel2d', 'LocalDeformKernel2d', 'DeformKernel2d', 'DeformKernelConv2d']
@@ -71,8 +71,16 @@ class GlobalDeformKernel2d(nn.Module):
         return (self.kernel_size == 1 and self.stride in (1, (1, 1)) and self.padding in (0, (0, 0)) and
                 self.group == self.in_planes == self.out_planes)
 
+    def _fused_head_ok(self, x):
+        return (x.is_cuda and self._is_plane_scale() and self.weight_dilate == 1 and len(self.weight_shape) <= 8 and
+                x.dtype in (torch.float16, torch.float32) and self.weight.dtype == torch.float32 and
+                self.fc.weight.dtype == torch.float32 and self.fc.bias is not None and not torch.is_autocast_enabled())
+
     def forward(self, x):
         n, c, h, w = x.shape
+        if self._fused_head_ok(x):
+            # pool, coordinate head, bank sampling and the per-plane scale in one call each way
+            return global_dk_scale(x, self.weight.view(c, *self.weight_shape), self.fc.weight, self.fc.bias, self._tap_bias)
         weight = self.dynamic_weight(x, self.weight).to(x.dtype)
         if self._is_plane_scale() and x.is_cuda:
             # 1x1 depthwise: the per-sample grouped convolution is a per-plane scale

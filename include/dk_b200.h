@@ -198,6 +198,23 @@ int dk_plane_scale_forward(const void *input, const void *scale, void *output, l
 int dk_plane_scale_backward(const void *grad_output, const void *input, const void *scale, void *grad_input,
                             void *grad_scale, long long planes, int plane_size, int dtype, void *stream);
 
+/* ---------------------------------------------------------------- fused global DK with a 1x1 depthwise kernel
+ * GlobalDeformKernel2d.forward for kernel_size 1, groups == channels (modules/deform_kernel.py:76-118) as one call:
+ * global average pool -> linear coordinate head (+ tap_bias) -> clamp to [0, shape[0]-1] -> N-d linear sample of
+ * the bank [channels, shape...] -> y = x * scale.  The head runs in fp32: bank, fc_weight [dims, channels], fc_bias,
+ * tap_bias [dims] and the four saved tensors pooled [batch, channels], raw_coord, coord [batch, dims], scale
+ * [batch, channels] are float whatever `dtype` (that of input/output) is.  The backward call takes the saved
+ * tensors back; any of its four outputs may be NULL. */
+int dk_global_dk_forward(const void *input, const void *bank, const void *fc_weight, const void *fc_bias,
+                         const void *tap_bias, void *output, void *pooled, void *raw_coord, void *coord, void *scale,
+                         int batch, int channels, int plane_size, int dims, const int *shape, int dtype, void *stream);
+size_t dk_global_dk_backward_workspace_bytes(int batch, int channels, int dims);
+int dk_global_dk_backward(const void *grad_output, const void *input, const void *bank, const void *fc_weight,
+                          const void *pooled, const void *raw_coord, const void *coord, const void *scale,
+                          void *grad_input, void *grad_bank, void *grad_fc_weight, void *grad_fc_bias, int batch,
+                          int channels, int plane_size, int dims, const int *shape, int dtype, void *workspace,
+                          size_t workspace_bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -359,6 +359,82 @@ def test_cfg2_full_size_matches_oracle_and_module_runs(ops, oracle):
     assert m.weight.grad is not None and m.fc.weight.grad is not None and x.grad is not None
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("shape,c,n,hw,fc_std", [((2, 2), 256, 32, 14, 0.05), ((3, 3), 40, 5, 9, 0.6), ((2, 3, 2), 24, 7, 6, 0.4)])
+def test_fused_global_dk_matches_its_composition(dtype, shape, c, n, hw, fc_std):
+    """GlobalDeformKernel2d (1x1 depthwise) through the two fused calls against the same module evaluated as the
+    reference composes it (pool, nn.Linear, clamp, nd_linear_sample, per-plane scale), values and all four gradients.
+    fc_std is large enough in two of the cases for part of the coordinates to sit on the clamp."""
+    from deformable_kernels.modules import GlobalDeformKernel2d
+    torch.manual_seed(5)
+    m = GlobalDeformKernel2d(shape, c, c, kernel_size=1, groups=c).to(DEV)
+    with torch.no_grad():
+        m.fc.weight.normal_(0, fc_std)
+        m.fc.bias.normal_(0, 0.2)
+    x = torch.randn(n, c, hw, hw, device=DEV).to(dtype)
+    dy = torch.randn(n, c, hw, hw, device=DEV).to(dtype)
+    params = [m.weight, m.fc.weight, m.fc.bias]
+
+    def run(fused):
+        xi = x.clone().requires_grad_(True)
+        if not fused:
+            m._fused_head_ok = lambda _x: False
+        try:
+            y = m(xi)
+        finally:
+            if not fused:
+                del m._fused_head_ok
+        return [y.detach()] + list(torch.autograd.grad(y, [xi] + params, dy))
+
+    assert m._fused_head_ok(x)
+    got, want = run(True), run(False)
+    tol = 2e-5 if dtype == torch.float32 else 4e-3   # fp16: the composition rounds the scale to fp16 before use
+    for name, a, b in zip(("y", "dx", "dbank", "dfc_weight", "dfc_bias"), got, want):
+        assert rel_err(a, b) < tol, "%s: %.3e" % (name, rel_err(a, b))
+
+
+def test_operators_capture_into_cuda_graphs():
+    """The operators enqueue on the current stream, never synchronise and take their scratch from the caller, so their
+    forward and backward capture into CUDA graphs (torch.cuda.make_graphed_callables) and replay to the same result."""
+    import warnings
+    from deformable_kernels.modules import GlobalDeformKernel2d
+    from deformable_kernels.ops.deform_kernel.modules import DeformableSampleDepthwise, SampleDepthwise
+    gen = torch.Generator(device=DEV).manual_seed(6)
+
+    def rnd(*shape, std=1.0, dtype=torch.float32):
+        return (torch.randn(*shape, device=DEV, generator=gen) * std).to(dtype).requires_grad_(True)
+
+    cases = [
+        (SampleDepthwise((4, 4), 32, 32, 3, 1, 1, groups=32).to(DEV), [rnd(2, 32, 20, 20), rnd(2, 18, 20, 20, std=0.7)]),
+        (SampleDepthwise((4, 4), 64, 64, 3, 1, 1, groups=64).to(DEV).half(),
+         [rnd(4, 64, 28, 28, dtype=torch.float16), rnd(4, 18, 28, 28, std=0.7, dtype=torch.float16)]),
+        (DeformableSampleDepthwise((4, 4), 64, 64, 3, 1, 1, groups=64).to(DEV).half(),
+         [rnd(24, 64, 14, 14, dtype=torch.float16), rnd(24, 18, 14, 14, std=2.0, dtype=torch.float16),
+          rnd(24, 18, 14, 14, std=0.7, dtype=torch.float16)]),
+        (GlobalDeformKernel2d((2, 2), 64, 64, kernel_size=1, groups=64).to(DEV), [rnd(4, 64, 14, 14)]),
+    ]
+    for layer, ins in cases:
+        with torch.no_grad():
+            for p in layer.parameters():
+                if p.abs().max() == 0:
+                    p.normal_(0, 0.1)
+        params = list(layer.parameters())
+        # graph first: an eager backward on the default stream beforehand would tie the parameters' gradient
+        # accumulation to that stream, which PyTorch then cannot capture
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            graphed = torch.cuda.make_graphed_callables(layer, tuple(t.detach().clone().requires_grad_(True) for t in ins))
+            dy = None
+            for _ in range(2):
+                yg = graphed(*ins)
+                dy = torch.randn_like(yg) if dy is None else dy
+                got = [yg.detach().clone()] + [g.clone() for g in torch.autograd.grad(yg, ins + params, dy)]
+            y = layer(*ins)
+            want = [y.detach()] + list(torch.autograd.grad(y, ins + params, dy))
+        for a_, b_ in zip(got, want):
+            assert rel_err(a_, b_) < (1e-5 if a_.dtype == torch.float32 else 1e-3)
+
+
 @pytest.mark.parametrize("c,hw,stride,n", [(96, 112, 1, 2), (144, 56, 2, 3), (960, 7, 1, 8), (384, 14, 2, 4)])
 def test_cfg3_reduced_batch_fp16_matches_oracle(ops, oracle, c, hw, stride, n):
     case = dk_cases.cfg3(c, hw, stride, n=n)
