@@ -158,26 +158,22 @@ __device__ __forceinline__ void load_band_group(__half* __restrict__ band, const
     for (int i = tid; i < nv; i += nt) b4[i] = z;
     if (r_e <= r_s) return;
     group_sync(bar_id, nt);
-    // 2-byte copies, four independent loads in flight per thread
+    // 2-byte copies: a thread takes one (channel, row) and walks along it, eight independent loads in flight
     const int rows = r_e - r_s;
-    const int per = rows * Ws, total = cnt * per;
-    for (int i0 = tid; i0 < total; i0 += 4 * nt) {
-      __half val[4];
-      int dst[4];
+    const int tasks = cnt * rows;
+    for (int t = tid; t < tasks; t += nt) {
+      const int j = t / rows, r = r_s + (t - j * rows);
+      const __half* sp = s0 + (size_t)j * plane + (size_t)r * Ws;
+      __half* dp = band + (size_t)j * b.pitch_c + kSlack + (r * b.Wp - b.org);
+      for (int c0w = 0; c0w < Ws; c0w += 8) {
+        __half val[8];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int i = i0 + k * nt;
-        dst[k] = -1;
-        if (i < total) {
-          const int j = i / per, v = i - j * per;
-          const int r = v / Ws, col = v - r * Ws;
-          val[k] = __ldg(s0 + (size_t)j * plane + (size_t)(r_s + r) * Ws + col);
-          dst[k] = j * b.pitch_c + kSlack + ((r_s + r) * b.Wp - b.org) + col;
-        }
+        for (int k = 0; k < 8; ++k)
+          if (c0w + k < Ws) val[k] = __ldg(sp + c0w + k);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (c0w + k < Ws) dp[c0w + k] = val[k];
       }
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        if (dst[k] >= 0) band[dst[k]] = val[k];
     }
     return;
   }
