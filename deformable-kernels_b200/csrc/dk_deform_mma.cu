@@ -757,7 +757,7 @@ __device__ __forceinline__ void sample_pair3(unsigned& v, unsigned& dh, unsigned
   dw = hfma2u(x3, cw.w, hfma2u(x2, cw.z, hfma2u(x1, cw.y, hmul2u(x0, cw.x))));
 }
 
-template <int S, int NS>
+template <int S, int NS, bool DO_OFF, bool DO_ROT>
 __global__ void __launch_bounds__(512, 1)
     mma_deform_coords_kernel(const __half* __restrict__ dy, const __half* __restrict__ x, const __half* __restrict__ off,
                              const __half* __restrict__ rot, const __half* __restrict__ w, __half* __restrict__ doff,
@@ -815,6 +815,7 @@ __global__ void __launch_bounds__(512, 1)
     cp_async_wait_all();
     __syncthreads();
 
+    constexpr bool want_off = DO_OFF, want_rot = DO_ROT;  // a field nobody asked for is not computed
     __half* doff_n = doff ? doff + (size_t)n * 18 * g.P : nullptr;
     __half* drot_n = drot ? drot + (size_t)n * 18 * g.P : nullptr;
     float* part_n = partial + (size_t)n * 36 * g.P;
@@ -863,22 +864,24 @@ __global__ void __launch_bounds__(512, 1)
             unsigned vA, hA, wA, vB, hB, wB;  // pixel 2q and pixel 2q + 1: (channel gq | channel gq + 8)
             sample_pair3(vA, hA, wA, base, e0);
             sample_pair3(vB, hB, wB, base, e0 + 4);
-            // kernel offsets: G += W^T * (dy * xs)
-            const unsigned ka = hmul2u(dy0[sidx], __byte_perm(vA, vB, 0x5410));
-            const unsigned kb = hmul2u(dy1[sidx], __byte_perm(vA, vB, 0x7632));
-            mma16816_acc(G[fw], t0, t1, t2, t3, movmatrix_trans(ka), movmatrix_trans(kb));
-            // image offsets: D[pixel, dir] += sum over the slab's channels of dy * K * dxs
-            unsigned kk[2];
-            mma16816_h(kk, wa, bf[fh * 3 + fw][0], bf[fh * 3 + fw][1]);
-            const unsigned ya = hmul2u(kk[0], dy0[sidx]), yb = hmul2u(kk[1], dy1[sidx]);
-            const unsigned eha = hmul2u(ya, __byte_perm(hA, hB, 0x5410)), ehb = hmul2u(yb, __byte_perm(hA, hB, 0x7632));
-            const unsigned ewa = hmul2u(ya, __byte_perm(wA, wB, 0x5410)), ewb = hmul2u(yb, __byte_perm(wA, wB, 0x7632));
-            mma16816_acc(D[fw], movmatrix_trans(eha), movmatrix_trans(ewa), movmatrix_trans(ehb), movmatrix_trans(ewb),
-                         0x3C003C00u, 0x3C003C00u);
+            if (want_rot) {  // kernel offsets: G += W^T * (dy * xs)
+              const unsigned ka = hmul2u(dy0[sidx], __byte_perm(vA, vB, 0x5410));
+              const unsigned kb = hmul2u(dy1[sidx], __byte_perm(vA, vB, 0x7632));
+              mma16816_acc(G[fw], t0, t1, t2, t3, movmatrix_trans(ka), movmatrix_trans(kb));
+            }
+            if (want_off) {  // image offsets: D[pixel, dir] += sum over the slab's channels of dy * K * dxs
+              unsigned kk[2];
+              mma16816_h(kk, wa, bf[fh * 3 + fw][0], bf[fh * 3 + fw][1]);
+              const unsigned ya = hmul2u(kk[0], dy0[sidx]), yb = hmul2u(kk[1], dy1[sidx]);
+              const unsigned eha = hmul2u(ya, __byte_perm(hA, hB, 0x5410)), ehb = hmul2u(yb, __byte_perm(hA, hB, 0x7632));
+              const unsigned ewa = hmul2u(ya, __byte_perm(wA, wB, 0x5410)), ewb = hmul2u(yb, __byte_perm(wA, wB, 0x7632));
+              mma16816_acc(D[fw], movmatrix_trans(eha), movmatrix_trans(ewa), movmatrix_trans(ehb), movmatrix_trans(ewb),
+                           0x3C003C00u, 0x3C003C00u);
+            }
           }
         }
         // image offsets: row gq of D = pixel gq, direction h; row gq + 8 = direction w (every column holds the sum)
-        if (q == 0 && ow0 + gq < g.Wo) {
+        if (want_off && q == 0 && ow0 + gq < g.Wo) {
 #pragma unroll
           for (int fw = 0; fw < 3; ++fw) {
             const size_t o = (size_t)(2 * (fh * 3 + fw)) * g.P + row + gq;
@@ -893,6 +896,7 @@ __global__ void __launch_bounds__(512, 1)
             }
           }
         }
+        if (!want_rot) continue;
         // kernel offsets: sum over the four corner cells of G * d(hat weight)/d(u or v)
         __syncwarp();  // the table has been read by every lane
 #pragma unroll
@@ -1204,6 +1208,7 @@ size_t deform_coords_mma_workspace(const Geom& g) {
 
 int deform_coords_mma(const __half* dy, const __half* x, const __half* off, const __half* rot, const __half* w, __half* doff,
                       __half* drot, const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s) {
+  if (!doff && !drot) return DK_OK;
   DCoordPlan pl = dcoord_plan(g, slab_cap());
   if (!pl.BH || pl.smem > (size_t)device_smem_optin() || g.C / (16 * pl.NS) > 65535) return DK_ERR_UNSUPPORTED;
   if (pl.ws_bytes && (ws == nullptr || ws_bytes < pl.ws_bytes)) return DK_ERR_UNSUPPORTED;  // no scratch: the SIMT kernel
@@ -1226,10 +1231,15 @@ int deform_coords_mma(const __half* dy, const __half* x, const __half* off, cons
     return check_launch();
   };
   int rc;
+#define DK_COORDS(SS, NN)                                                              \
+  (doff && drot ? launch(mma_deform_coords_kernel<SS, NN, true, true>)                \
+                : doff ? launch(mma_deform_coords_kernel<SS, NN, true, false>)        \
+                       : launch(mma_deform_coords_kernel<SS, NN, false, true>))
   if (g.sH == 1)
-    rc = pl.NS == 2 ? launch(mma_deform_coords_kernel<1, 2>) : launch(mma_deform_coords_kernel<1, 1>);
+    rc = pl.NS == 2 ? DK_COORDS(1, 2) : DK_COORDS(1, 1);
   else
-    rc = pl.NS == 2 ? launch(mma_deform_coords_kernel<2, 2>) : launch(mma_deform_coords_kernel<2, 1>);
+    rc = pl.NS == 2 ? DK_COORDS(2, 2) : DK_COORDS(2, 1);
+#undef DK_COORDS
   if (rc || !pl.ws_bytes) return rc;
   const size_t plane18 = (size_t)18 * g.P, count = (size_t)g.N * plane18;
   const unsigned blocks = (unsigned)((count + 255) / 256);

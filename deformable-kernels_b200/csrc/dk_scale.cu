@@ -57,6 +57,50 @@ int scale_backward(const T* dy, const T* x, const T* k, T* dx, T* dk, long long 
   return check_launch();
 }
 
+// Offset clipping of the layers that produce the offsets (reference modules/deform_kernel.py:185-218, 273-276), one
+// pass instead of five elementwise ones:  v = r * dilate + bias[channel];  y = (clamp(v, lo, hi) - bias) / dilate * post.
+// The backward passes the gradient where lo <= v <= hi (both ends included, as torch.clamp does).
+template <typename T>
+__global__ void clip_fwd_kernel(const T* __restrict__ r, const float* __restrict__ bias, T* __restrict__ y, long long total,
+                                int channels, int hw, float lo, float hi, float dilate, float post) {
+  using A = typename Compute<T>::type;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const A b = bias ? (A)bias[(i / hw) % channels] : (A)0;
+  const A v = ld<A>(r + i) * (A)dilate + b;
+  const A c = v < (A)lo ? (A)lo : (v > (A)hi ? (A)hi : v);  // NaN stays NaN
+  st<T, A>(y + i, (c - b) / (A)dilate * (A)post);
+}
+template <typename T>
+__global__ void clip_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ r, const float* __restrict__ bias,
+                                T* __restrict__ dr, long long total, int channels, int hw, float lo, float hi, float dilate,
+                                float post) {
+  using A = typename Compute<T>::type;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const A b = bias ? (A)bias[(i / hw) % channels] : (A)0;
+  const A v = ld<A>(r + i) * (A)dilate + b;
+  const bool pass = v >= (A)lo && v <= (A)hi;
+  st<T, A>(dr + i, pass ? ld<A>(dy + i) * (A)post : (A)0);
+}
+
+template <typename T>
+int clip_forward(const T* r, const float* bias, T* y, long long total, int channels, int hw, float lo, float hi, float dilate,
+                 float post, cudaStream_t s) {
+  const long long blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffLL) return DK_ERR_UNSUPPORTED;
+  clip_fwd_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(r, bias, y, total, channels, hw, lo, hi, dilate, post);
+  return check_launch();
+}
+template <typename T>
+int clip_backward(const T* dy, const T* r, const float* bias, T* dr, long long total, int channels, int hw, float lo, float hi,
+                  float dilate, float post, cudaStream_t s) {
+  const long long blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffLL) return DK_ERR_UNSUPPORTED;
+  clip_bwd_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(dy, r, bias, dr, total, channels, hw, lo, hi, dilate, post);
+  return check_launch();
+}
+
 }  // namespace dk
 
 using namespace dk;
@@ -89,6 +133,36 @@ int dk_plane_scale_backward(const void* grad_output, const void* input, const vo
     case DK_F64:
       return scale_backward<double>((const double*)grad_output, (const double*)input, (const double*)scale,
                                     (double*)grad_input, (double*)grad_scale, planes, plane_size, s);
+    default: return DK_ERR_BAD_ARGUMENT;
+  }
+}
+
+int dk_offset_clip_forward(const void* offsets, const void* bias, void* output, int batch, int channels, int plane_size,
+                           float lo, float hi, float dilate, float post_scale, int dtype, void* stream) {
+  if (!offsets || !output || batch <= 0 || channels <= 0 || plane_size <= 0 || dilate == 0.f) return DK_ERR_BAD_ARGUMENT;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long total = (long long)batch * channels * plane_size;
+  const float* b = (const float*)bias;
+  switch (dtype) {
+    case DK_F32: return clip_forward<float>((const float*)offsets, b, (float*)output, total, channels, plane_size, lo, hi, dilate, post_scale, s);
+    case DK_F16: return clip_forward<__half>((const __half*)offsets, b, (__half*)output, total, channels, plane_size, lo, hi, dilate, post_scale, s);
+    case DK_F64: return clip_forward<double>((const double*)offsets, b, (double*)output, total, channels, plane_size, lo, hi, dilate, post_scale, s);
+    default: return DK_ERR_BAD_ARGUMENT;
+  }
+}
+
+int dk_offset_clip_backward(const void* grad_output, const void* offsets, const void* bias, void* grad_offsets, int batch,
+                            int channels, int plane_size, float lo, float hi, float dilate, float post_scale, int dtype,
+                            void* stream) {
+  if (!grad_output || !offsets || !grad_offsets || batch <= 0 || channels <= 0 || plane_size <= 0 || dilate == 0.f)
+    return DK_ERR_BAD_ARGUMENT;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long total = (long long)batch * channels * plane_size;
+  const float* b = (const float*)bias;
+  switch (dtype) {
+    case DK_F32: return clip_backward<float>((const float*)grad_output, (const float*)offsets, b, (float*)grad_offsets, total, channels, plane_size, lo, hi, dilate, post_scale, s);
+    case DK_F16: return clip_backward<__half>((const __half*)grad_output, (const __half*)offsets, b, (__half*)grad_offsets, total, channels, plane_size, lo, hi, dilate, post_scale, s);
+    case DK_F64: return clip_backward<double>((const double*)grad_output, (const double*)offsets, b, (double*)grad_offsets, total, channels, plane_size, lo, hi, dilate, post_scale, s);
     default: return DK_ERR_BAD_ARGUMENT;
   }
 }

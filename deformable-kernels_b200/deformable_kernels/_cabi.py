@@ -63,6 +63,8 @@ _PROTOS = {
     "dk_global_dk_forward": (_int, [_vp] * 10 + [_int, _int, _int, _int, _ip, _int, _vp]),
     "dk_global_dk_backward_workspace_bytes": (ctypes.c_size_t, [_int, _int, _int]),
     "dk_global_dk_backward": (_int, [_vp] * 12 + [_int, _int, _int, _int, _ip, _int, _vp, ctypes.c_size_t, _vp]),
+    "dk_offset_clip_forward": (_int, [_vp, _vp, _vp, _int, _int, _int] + [ctypes.c_float] * 4 + [_int, _vp]),
+    "dk_offset_clip_backward": (_int, [_vp, _vp, _vp, _vp, _int, _int, _int] + [ctypes.c_float] * 4 + [_int, _vp]),
     "dk_output_size": (_int, [_gp, _ip, _ip]),
     "dk_status_string": (ctypes.c_char_p, [_int]),
     "dk_last_cuda_error": (_int, []),

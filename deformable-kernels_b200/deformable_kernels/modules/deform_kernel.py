@@ -9,7 +9,7 @@ state dicts are interchangeable: ``weight``, ``fc.*``; ``rotation_conv.*``,
 import torch
 from torch import nn
 
-from ..ops.deform_kernel.functions import global_dk_scale, nd_linear_sample, plane_scale
+from ..ops.deform_kernel.functions import clip_offsets, global_dk_scale, nd_linear_sample, plane_scale
 from ..ops.deform_kernel.modules import SampleDepthwise, DeformableSampleDepthwise
 
 __all__ = ['GlobalDeformKernel2d', 'LocalDeformKernel2d', 'DeformKernel2d', 'DeformKernelConv2d']
@@ -138,8 +138,23 @@ class LocalDeformKernel2d(nn.Module):
         raise NotImplementedError(
             'Expect rotation_clip to be tuple or "scope", but get {}'.format(self.rotation_clip))
 
+    def _fused_clip(self, rotation):
+        """Clip and scale in one pass on CUDA; None when the configuration is not one the fused op covers."""
+        if not rotation.is_cuda or rotation.dtype not in (torch.float16, torch.float32, torch.float64):
+            return None
+        if isinstance(self.rotation_clip, tuple) and len(self.rotation_clip) == 2:
+            return clip_offsets(rotation, None, self.rotation_clip[0], self.rotation_clip[1], 1.0, self.weight_dilate)
+        if self.rotation_clip == 'scope':
+            bias = rotation.new_tensor(_tap_positions(self.weight_shape, self.kernel_size, self.weight_dilate),
+                                       dtype=torch.float32).repeat(self.rotation_groups)
+            return clip_offsets(rotation, bias, 0.0, self.weight_shape[0] - 1, self.weight_dilate, self.weight_dilate)
+        return None
+
     def forward(self, x):
         rotation = self.rotation_conv(x)
+        fused = self._fused_clip(rotation) if self.rotation_clip is not None else None
+        if fused is not None:
+            return self.inner_conv(x, fused)
         if self.rotation_clip is not None:
             rotation = self._clip_rotation(rotation)
         if self.weight_dilate != 1:
@@ -174,8 +189,15 @@ class DeformKernelConv2d(nn.Module):
 
     def forward(self, x):
         offset = self.offset_conv(x)
-        if self.offset_clip is not None:
-            offset = offset.clamp(**self.offset_clip)
+        clip = self.offset_clip
+        if (clip is not None and offset.is_cuda and isinstance(clip, dict) and set(clip) <= {'min', 'max'} and
+                isinstance(self.dilation, (int, float))):
+            # clamp and dilation scaling in one pass
+            offset = clip_offsets(offset, None, clip.get('min', float('-inf')), clip.get('max', float('inf')), 1.0,
+                                  float(self.dilation))
+            return self.inner_conv(x, offset, None)
+        if clip is not None:
+            offset = offset.clamp(**clip)
         if self.dilation != 1:
             offset = offset * self.dilation
         return self.inner_conv(x, offset, None)

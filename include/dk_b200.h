@@ -215,6 +215,18 @@ int dk_global_dk_backward(const void *grad_output, const void *input, const void
                           int channels, int plane_size, int dims, const int *shape, int dtype, void *workspace,
                           size_t workspace_bytes, void *stream);
 
+/* ---------------------------------------------------------------- offset clipping
+ * What LocalDeformKernel2d._clip_rotation, `rotation * weight_dilate` and DeformKernelConv2d's offset clamp / `* dilation`
+ * (modules/deform_kernel.py:185-218, 165-170, 273-276) do in up to five elementwise passes, as one:
+ *   v = offsets * dilate + bias[channel];   output = (clamp(v, lo, hi) - bias[channel]) / dilate * post_scale
+ * offsets [batch, channels, plane_size]; bias [channels] float or NULL (zero).  The backward passes
+ * grad_output * post_scale where lo <= v <= hi.  No counterpart among the reference's compiled functions. */
+int dk_offset_clip_forward(const void *offsets, const void *bias, void *output, int batch, int channels, int plane_size,
+                           float lo, float hi, float dilate, float post_scale, int dtype, void *stream);
+int dk_offset_clip_backward(const void *grad_output, const void *offsets, const void *bias, void *grad_offsets, int batch,
+                            int channels, int plane_size, float lo, float hi, float dilate, float post_scale, int dtype,
+                            void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -435,6 +435,50 @@ def test_operators_capture_into_cuda_graphs():
             assert rel_err(a_, b_) < (1e-5 if a_.dtype == torch.float32 else 1e-3)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.float64])
+def test_clip_offsets_matches_the_elementwise_composition(ops, dtype):
+    """(clamp(r * d + b, lo, hi) - b) / d * post in one pass, against the five PyTorch passes of
+    LocalDeformKernel2d._clip_rotation, and the plain clamp * dilation of DeformKernelConv2d."""
+    gen = torch.Generator().manual_seed(41)
+    r = (torch.randn(3, 18, 9, 11, generator=gen) * 2).to(dtype).to(DEV)
+    dy = torch.randn(3, 18, 9, 11, generator=gen).to(dtype).to(DEV)
+    bias = (torch.rand(18, generator=gen) * 3).to(DEV)
+    for b, lo, hi, d, post in ((bias, 0.0, 3.0, 1.0, 1.0), (bias, 0.0, 3.0, 2.0, 2.0), (None, -1.5, 0.75, 1.0, 3.0)):
+        a = r.clone().requires_grad_(True)
+        y = ops.clip_offsets(a, b, lo, hi, d, post)
+        ga, = torch.autograd.grad(y, a, dy)
+        # fp16: the composition evaluated in fp32 on the fp16 inputs (in fp16 it rounds r * d + b before clamping
+        # and so decides a few boundary elements differently)
+        wide = torch.float32 if dtype == torch.float16 else dtype
+        c = r.to(wide).requires_grad_(True)
+        bb = 0 if b is None else b.to(wide)[None, :, None, None]
+        want = ((c * d + bb).clamp(lo, hi) - bb) / d * post
+        gc, = torch.autograd.grad(want, c, dy.to(wide))
+        want, gc = want.to(dtype), gc.to(dtype)
+        tol = {torch.float64: 1e-12, torch.float32: 1e-6, torch.float16: 2e-3}[dtype]
+        assert rel_err(y, want) < tol and rel_err(ga, gc) < tol
+
+
+def test_layers_with_offset_clipping_match_the_composition():
+    from deformable_kernels.modules import DeformKernel2d, DeformKernelConv2d
+    torch.manual_seed(7)
+    x = torch.randn(2, 16, 12, 12, device=DEV)
+    for clip in ('scope', (-0.4, 0.6)):
+        m = DeformKernel2d((4, 4), 16, 16, 3, 1, 1, groups=16, rotation_clip=clip).to(DEV)
+        with torch.no_grad():
+            m.rotation_conv.weight.normal_(0, 0.3)
+        got = m(x)
+        m._fused_clip = lambda rot: None
+        want = m(x)
+        assert rel_err(got, want) < 1e-5
+    m = DeformKernelConv2d((4, 4), 16, 16, 3, 1, 1, groups=16, offset_clip=dict(min=-1.0, max=1.5)).to(DEV)
+    with torch.no_grad():
+        m.offset_conv.weight.normal_(0, 0.5)
+    got = m(x)
+    want = m.inner_conv(x, m.offset_conv(x).clamp(min=-1.0, max=1.5), None)
+    assert rel_err(got, want) < 1e-5
+
+
 @pytest.mark.parametrize("c,hw,stride,n", [(96, 112, 1, 2), (144, 56, 2, 3), (960, 7, 1, 8), (384, 14, 2, 4)])
 def test_cfg3_reduced_batch_fp16_matches_oracle(ops, oracle, c, hw, stride, n):
     case = dk_cases.cfg3(c, hw, stride, n=n)
@@ -547,11 +591,12 @@ def test_full_size_properties_largest_layer_fp32(ops):
     gw = dw.double() * w.detach().double()
     assert abs(float(gx.sum() - lhs)) < 1e-6 * float(gx.abs().sum())
     assert abs(float(gw.sum() - lhs)) < 1e-6 * float(gw.abs().sum())
-    v = torch.randn_like(r)
+    v = torch.randn(r.shape, device=DEV, generator=torch.Generator(device=DEV).manual_seed(12))
     eps = 1e-3
     with torch.no_grad():
         yp = ops.sample_depthwise(x, r + eps * v, w).double()
         ym = ops.sample_depthwise(x, r - eps * v, w).double()
         fd = ((yp - ym) * dy.double()).sum() / (2 * eps)
-    an = (dr.double() * v.double()).sum()
-    assert abs(float(fd / an) - 1) < 2e-2
+    an = dr.double() * v.double()
+    # the directional derivative is a heavily cancelling sum too (and the central difference steps over kinks)
+    assert abs(float(fd - an.sum())) < 5e-3 * float(an.abs().sum())
