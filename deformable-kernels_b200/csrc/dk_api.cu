@@ -198,7 +198,12 @@ int dk_sample_depthwise_backward(const void* grad_output, const void* input, con
 int dk_deform_sample_depthwise_forward(const void* input, const void* offset, const void* rotation, const void* filter,
                                        void* output, const dk_geom* g, int dtype, void* stream) {
   Geom gg;
-  if (!input || !offset || !rotation || !filter || !output || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+  if (!input || !offset || !filter || !output || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+  if (!rotation) {  // zero kernel-space offsets: tensor-core path only, the caller falls back to a tensor of zeros
+    if (dtype != DK_F16 || !mma_path_enabled()) return DK_ERR_UNSUPPORTED;
+    return deform_forward_mma(P_(__half, input), P_(__half, offset), nullptr, P_(__half, filter), M_(__half, output), gg,
+                              (cudaStream_t)stream);
+  }
   DK_DISPATCH(dtype, deform_forward<T>(P_(T, input), P_(T, offset), P_(T, rotation), P_(T, filter), M_(T, output), gg,
                                        (cudaStream_t)stream))
 }
@@ -289,11 +294,30 @@ int dk_deform_sample_depthwise_backward(const void* grad_output, const void* inp
                                         void* grad_rotation, void* grad_filter, const dk_geom* g, int dtype,
                                         void* workspace, size_t workspace_bytes, void* stream) {
   Geom gg;
-  if (!grad_output || !input || !offset || !rotation || !filter || !make_geom(g, &gg) || !dtype_ok(dtype))
-    return DK_ERR_BAD_ARGUMENT;
+  if (!grad_output || !input || !offset || !filter || !make_geom(g, &gg) || !dtype_ok(dtype)) return DK_ERR_BAD_ARGUMENT;
   const size_t data_ws = deform_front_ws(g, dtype);
   const size_t filt_ws = dk_deform_sample_depthwise_backward_filter_workspace_bytes(g, dtype);
   int rc = DK_OK;
+  if (!rotation) {  // zero kernel-space offsets (see the forward); nothing to differentiate with respect to them
+    if (grad_rotation) return DK_ERR_BAD_ARGUMENT;
+    if (dtype != DK_F16 || !mma_path_enabled()) return DK_ERR_UNSUPPORTED;
+    if (!workspace || workspace_bytes < data_ws + filt_ws) return DK_ERR_WORKSPACE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (grad_input) {
+      rc = deform_data_mma(P_(__half, grad_output), P_(__half, offset), nullptr, P_(__half, filter), M_(__half, grad_input),
+                           gg, workspace, data_ws, s);
+      if (rc) return rc;
+    }
+    if (grad_offset) {
+      rc = deform_coords_mma(P_(__half, grad_output), P_(__half, input), P_(__half, offset), nullptr, P_(__half, filter),
+                             M_(__half, grad_offset), nullptr, gg, workspace, data_ws, s);
+      if (rc) return rc;
+    }
+    if (grad_filter)
+      rc = deform_filter_mma(P_(__half, grad_output), P_(__half, input), P_(__half, offset), nullptr, M_(__half, grad_filter),
+                             gg, (char*)workspace + data_ws, filt_ws, s);
+    return rc;
+  }
   if (grad_input) {
     if (data_ws && (!workspace || workspace_bytes < data_ws)) return DK_ERR_WORKSPACE;
     rc = dk_deform_sample_depthwise_backward_data(grad_output, offset, rotation, filter, grad_input, g, dtype, workspace,

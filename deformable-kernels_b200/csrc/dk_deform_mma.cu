@@ -139,6 +139,34 @@ __device__ __forceinline__ unsigned sample_pair(const char* __restrict__ base, c
   return r;
 }
 
+// hat-product fragments (as beta_direct without the image mask) from offsets held in registers; with all-zero
+// offsets (rot == nullptr in the kernels below: the kernel is the same for every pixel) they are built once per warp
+__device__ __forceinline__ void beta_from_regs(unsigned (&bf)[9][2], const unsigned (&rp)[9], const Geom& g, const LaneCells& lc,
+                                               bool sc44, bool valid) {
+  const float uh0 = (float)(g.scH - 3) * 0.5f, uw0 = (float)(g.scW - 3) * 0.5f;
+#pragma unroll
+  for (int fh = 0; fh < 3; ++fh) {
+#pragma unroll
+    for (int fw = 0; fw < 3; ++fw) {
+      const int t = fh * 3 + fw;
+      const float u = ((float)fh + lo2f(rp[t])) + uh0;
+      const float v = valid ? ((float)fw + hi2f(rp[t])) + uw0 : 1e30f;
+      if (sc44) {
+        const float hh0 = hat(u - lc.ca[0]), hh1 = hat(u - lc.ca[2]);
+        const float hw0 = hat(v - lc.cb[0]), hw1 = hat(v - lc.cb[1]);
+        bf[t][0] = pack2(hh0 * hw0, hh0 * hw1);
+        bf[t][1] = pack2(hh1 * hw0, hh1 * hw1);
+      } else {
+        float b4[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) b4[k] = lc.ok[k] ? hat(u - lc.ca[k]) * hat(v - lc.cb[k]) : 0.f;
+        bf[t][0] = pack2(b4[0], b4[1]);
+        bf[t][1] = pack2(b4[2], b4[3]);
+      }
+    }
+  }
+}
+
 struct DcnPlan {
   int NS, BH, warps, bands, units_per_block, blocks_x;
   int mode_rot, mode_off, mode_dy;
@@ -149,7 +177,7 @@ struct DcnPlan {
 // y[c, p] = sum over taps of K[c, p, tap] * xs[c, p, tap]:  K = W * beta^T from one mma per tap (as in the local
 // forward), xs sampled from the channel-pair planes.  A block owns 16 * NS channels and walks over units
 // (sample, band of output rows); the planes are reloaded only when the sample changes.
-template <int S, int NS>
+template <int S, int NS, bool ZR>
 __global__ void __launch_bounds__(512, 1) mma_deform_fwd_kernel(const __half* __restrict__ x, const __half* __restrict__ off,
                                                                const __half* __restrict__ rot, const __half* __restrict__ w,
                                                                __half* __restrict__ y, const Geom g, const DcnPlan pl) {
@@ -191,6 +219,12 @@ __global__ void __launch_bounds__(512, 1) mma_deform_fwd_kernel(const __half* __
   const int u_begin = blockIdx.x * pl.units_per_block;
   const int u_end = min(u_begin + pl.units_per_block, total_units);
   const bool even_w = (g.Wo & 1) == 0;
+  constexpr bool zero_rot = ZR;  // rot == nullptr
+  unsigned bf[9][2];
+  if (zero_rot) {
+    const unsigned z[9] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    beta_from_regs(bf, z, g, lc, sc44, true);
+  }
   int cur_n = -1;
   for (int unit = u_begin; unit < u_end; ++unit) {
     const int n = unit / pl.bands;
@@ -198,7 +232,7 @@ __global__ void __launch_bounds__(512, 1) mma_deform_fwd_kernel(const __half* __
     const Band br = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_rot);
     const Band bo = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_off);
     __syncthreads();  // readers of the previous unit are done
-    load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
+    if (!zero_rot) load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
     load_band(oband, bo, off, n, 18, 0, 18, g.Ho, g.Wo);
     if (n != cur_n) {
 #pragma unroll
@@ -213,8 +247,7 @@ __global__ void __launch_bounds__(512, 1) mma_deform_fwd_kernel(const __half* __
       const int oh = oh0 + dr;
       if (oh >= g.Ho) break;
       const int ow0 = (item - dr * NB) << 3;
-      unsigned bf[9][2];
-      beta_direct<S, false, false>(bf, rband, br, g, lc, sc44, oh, ow0, g.H, g.W, g.Wo, gq);
+      if (!zero_rot) beta_direct<S, false, false>(bf, rband, br, g, lc, sc44, oh, ow0, g.H, g.W, g.Wo, gq);
       float acc[NS][4];
 #pragma unroll
       for (int sidx = 0; sidx < NS; ++sidx) acc[sidx][0] = acc[sidx][1] = acc[sidx][2] = acc[sidx][3] = 0.f;
@@ -268,7 +301,7 @@ __global__ void __launch_bounds__(512, 1) mma_deform_fwd_kernel(const __half* __
 // Bank gradient.  dK = dy * xs is the A operand (rows = channels, k = 8 pixels x 2 taps), beta the B operand;
 // the accumulators live in registers over all units of the block, are reduced across its warps at the end and
 // written as one partial [16 * NS channels][16 cells] per block.
-template <int S, int NS>
+template <int S, int NS, bool ZR>
 __global__ void __launch_bounds__(512, 1) mma_deform_filter_kernel(const __half* __restrict__ dy, const __half* __restrict__ x,
                                                                   const __half* __restrict__ off, const __half* __restrict__ rot,
                                                                   float* __restrict__ partial, const Geom g, const DcnPlan pl) {
@@ -297,6 +330,19 @@ __global__ void __launch_bounds__(512, 1) mma_deform_filter_kernel(const __half*
 #pragma unroll
     for (int k = 0; k < 4; ++k) acc[sidx][0][k] = acc[sidx][1][k] = 0.f;
 
+  constexpr bool zero_rot = ZR;  // rot == nullptr
+  unsigned bw[9][2];  // beta as B fragments: [tap][cells 0-7 | cells 8-15]
+  if (zero_rot) {
+    const unsigned z[9] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    unsigned bf[9][2];
+    beta_from_regs(bf, z, g, lc, sc44, true);
+#pragma unroll
+    for (int t = 0; t < 9; ++t) {
+      bw[t][0] = movmatrix_trans(bf[t][0]);
+      bw[t][1] = movmatrix_trans(bf[t][1]);
+    }
+  }
+
   const int total_units = g.N * pl.bands;
   const int u_begin = blockIdx.x * pl.units_per_block;
   const int u_end = min(u_begin + pl.units_per_block, total_units);
@@ -309,7 +355,7 @@ __global__ void __launch_bounds__(512, 1) mma_deform_filter_kernel(const __half*
     const Band bo = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_off);
     __syncthreads();  // readers of the previous unit are done
     load_band(yband, by, dy, n, g.C, c0, CG, g.Ho, g.Wo);
-    load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
+    if (!zero_rot) load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
     load_band(oband, bo, off, n, 18, 0, 18, g.Ho, g.Wo);
     if (n != cur_n) {
 #pragma unroll
@@ -324,8 +370,7 @@ __global__ void __launch_bounds__(512, 1) mma_deform_filter_kernel(const __half*
       const int oh = oh0 + dr;
       if (oh >= g.Ho) break;
       const int ow0 = (item - dr * NB) << 3;
-      unsigned bw[9][2];  // beta as B fragments: [tap][cells 0-7 | cells 8-15]
-      {
+      if (!zero_rot) {
         unsigned bf[9][2];
         beta_direct<S, false, false>(bf, rband, br, g, lc, sc44, oh, ow0, g.H, g.W, g.Wo, gq);
 #pragma unroll
@@ -492,7 +537,7 @@ __device__ __forceinline__ void fetch_item(ItemRegs& r, const __half* __restrict
 #pragma unroll
     for (int t = 0; t < 9; ++t) {
       r.rp[t] = 0u;
-      if (pc < g.Wo)
+      if (rot != nullptr && pc < g.Wo)
         r.rp[t] = (unsigned)__half_as_ushort(__ldg(rp + (size_t)(2 * t) * g.P)) |
                   ((unsigned)__half_as_ushort(__ldg(rp + (size_t)(2 * t + 1) * g.P)) << 16);
     }
@@ -529,34 +574,7 @@ __device__ __forceinline__ void fetch_item(ItemRegs& r, const __half* __restrict
   }
 }
 
-// hat-product fragments (as beta_direct without the image mask) from offsets held in registers
-__device__ __forceinline__ void beta_from_regs(unsigned (&bf)[9][2], const unsigned (&rp)[9], const Geom& g, const LaneCells& lc,
-                                               bool sc44, bool valid) {
-  const float uh0 = (float)(g.scH - 3) * 0.5f, uw0 = (float)(g.scW - 3) * 0.5f;
-#pragma unroll
-  for (int fh = 0; fh < 3; ++fh) {
-#pragma unroll
-    for (int fw = 0; fw < 3; ++fw) {
-      const int t = fh * 3 + fw;
-      const float u = ((float)fh + lo2f(rp[t])) + uh0;
-      const float v = valid ? ((float)fw + hi2f(rp[t])) + uw0 : 1e30f;
-      if (sc44) {
-        const float hh0 = hat(u - lc.ca[0]), hh1 = hat(u - lc.ca[2]);
-        const float hw0 = hat(v - lc.cb[0]), hw1 = hat(v - lc.cb[1]);
-        bf[t][0] = pack2(hh0 * hw0, hh0 * hw1);
-        bf[t][1] = pack2(hh1 * hw0, hh1 * hw1);
-      } else {
-        float b4[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) b4[k] = lc.ok[k] ? hat(u - lc.ca[k]) * hat(v - lc.cb[k]) : 0.f;
-        bf[t][0] = pack2(b4[0], b4[1]);
-        bf[t][1] = pack2(b4[2], b4[3]);
-      }
-    }
-  }
-}
-
-template <int S>
+template <int S, bool ZR>
 __global__ void __launch_bounds__(512, 1) mma_deform_data_kernel(const __half* __restrict__ dy, const __half* __restrict__ off,
                                                                 const __half* __restrict__ rot, const __half* __restrict__ w,
                                                                 const int* __restrict__ hits, __half* __restrict__ dx,
@@ -594,6 +612,13 @@ __global__ void __launch_bounds__(512, 1) mma_deform_data_kernel(const __half* _
     wa[3] = cell2(w1, 2 * q + 8);
   }
   const unsigned lane_off = gq * 4;
+  constexpr bool zero_rot = ZR;  // rot == nullptr
+  unsigned bf[9][2];
+  if (zero_rot) {
+    const unsigned z[9] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    beta_from_regs(bf, z, g, lc, sc44, true);
+  }
+
   const int n_begin = blockIdx.x * pl.samples_per_block;
   const int n_end = min(n_begin + pl.samples_per_block, g.N);
   for (int n = n_begin; n < n_end; ++n) {
@@ -648,8 +673,7 @@ __global__ void __launch_bounds__(512, 1) mma_deform_data_kernel(const __half* _
         const int oh2 = item2 / NB;
         fetch_item(nxt, dy, off, rot, g, n, c0, oh2, (item2 - oh2 * NB) << 3, lane, pl.pair_dy);
       }
-      unsigned bf[9][2];
-      beta_from_regs(bf, cur.rp, g, lc, sc44, ow0 + gq < g.Wo);
+      if (!zero_rot) beta_from_regs(bf, cur.rp, g, lc, sc44, ow0 + gq < g.Wo);
 #pragma unroll
       for (int fh = 0; fh < 3; ++fh) {
         __syncwarp();
@@ -757,7 +781,7 @@ __device__ __forceinline__ void sample_pair3(unsigned& v, unsigned& dh, unsigned
   dw = hfma2u(x3, cw.w, hfma2u(x2, cw.z, hfma2u(x1, cw.y, hmul2u(x0, cw.x))));
 }
 
-template <int S, int NS, bool DO_OFF, bool DO_ROT>
+template <int S, int NS, bool DO_OFF, bool DO_ROT, bool ZR>
 __global__ void __launch_bounds__(512, 1)
     mma_deform_coords_kernel(const __half* __restrict__ dy, const __half* __restrict__ x, const __half* __restrict__ off,
                              const __half* __restrict__ rot, const __half* __restrict__ w, __half* __restrict__ doff,
@@ -793,6 +817,13 @@ __global__ void __launch_bounds__(512, 1)
     bank[c * kBankPitch + cell] = v;
   }
 
+  constexpr bool zero_rot = ZR;  // rot == nullptr; then DO_ROT is false: there is nothing to differentiate
+  unsigned bf[9][2];
+  if (zero_rot) {
+    const unsigned z[9] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    beta_from_regs(bf, z, g, lc, sc44, true);
+  }
+
   const int total_units = g.N * pl.bands;
   const int u_begin = blockIdx.x * pl.units_per_block;
   const int u_end = min(u_begin + pl.units_per_block, total_units);
@@ -805,7 +836,7 @@ __global__ void __launch_bounds__(512, 1)
     const Band bo = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_off);
     __syncthreads();  // readers of the previous unit are done
     load_band(yband, by, dy, n, g.C, c0, CG, g.Ho, g.Wo);
-    load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
+    if (!zero_rot) load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
     load_band(oband, bo, off, n, 18, 0, 18, g.Ho, g.Wo);
     if (n != cur_n) {
 #pragma unroll
@@ -824,10 +855,9 @@ __global__ void __launch_bounds__(512, 1)
       const int oh = oh0 + dr;
       if (oh >= g.Ho) break;
       const int ow0 = (item - dr * NB) << 3;
-      unsigned bf[9][2];
-      beta_direct<S, false, false>(bf, rband, br, g, lc, sc44, oh, ow0, g.H, g.W, g.Wo, gq);
+      if (!zero_rot) beta_direct<S, false, false>(bf, rband, br, g, lc, sc44, oh, ow0, g.H, g.W, g.Wo, gq);
       __syncwarp();
-      item_uv<S, false>(uv, rband, br, g, oh, ow0, lane);
+      if (DO_ROT) item_uv<S, false>(uv, rband, br, g, oh, ow0, lane);
       const int yoff = kSlack + oh * by.Wp + ow0 + 2 * q - by.org;
       unsigned dy0[NS], dy1[NS];
 #pragma unroll
@@ -1142,12 +1172,12 @@ int deform_filter_mma(const __half* dy, const __half* x, const __half* off, cons
     return check_launch();
   };
   int rc;
-  if (g.sH == 1)
-    rc = pl.NS == 4 ? launch(mma_deform_filter_kernel<1, 4>) : pl.NS == 2 ? launch(mma_deform_filter_kernel<1, 2>)
-                                                                        : launch(mma_deform_filter_kernel<1, 1>);
+#define DK_PICK(K, SS, ZZ) \
+  (pl.NS == 4 ? launch(K<SS, 4, ZZ>) : pl.NS == 2 ? launch(K<SS, 2, ZZ>) : launch(K<SS, 1, ZZ>))
+  if (rot)
+    rc = g.sH == 1 ? DK_PICK(mma_deform_filter_kernel, 1, false) : DK_PICK(mma_deform_filter_kernel, 2, false);
   else
-    rc = pl.NS == 4 ? launch(mma_deform_filter_kernel<2, 4>) : pl.NS == 2 ? launch(mma_deform_filter_kernel<2, 2>)
-                                                                        : launch(mma_deform_filter_kernel<2, 1>);
+    rc = g.sH == 1 ? DK_PICK(mma_deform_filter_kernel, 1, true) : DK_PICK(mma_deform_filter_kernel, 2, true);
   if (rc) return rc;
   const int n_out = g.C * g.cells;
   reduce_dcn_bank_partials_kernel<<<(n_out + 7) / 8, 256, 0, s>>>(partial, dw, g.C, g.cells, pl.blocks_x);
@@ -1168,11 +1198,8 @@ int deform_forward_mma(const __half* x, const __half* off, const __half* rot, co
     kern<<<grid, pl.warps * 32, pl.smem, s>>>(x, off, rot, w, y, g, pl);
     return check_launch();
   };
-  if (g.sH == 1)
-    return pl.NS == 4 ? launch(mma_deform_fwd_kernel<1, 4>) : pl.NS == 2 ? launch(mma_deform_fwd_kernel<1, 2>)
-                                                                        : launch(mma_deform_fwd_kernel<1, 1>);
-  return pl.NS == 4 ? launch(mma_deform_fwd_kernel<2, 4>) : pl.NS == 2 ? launch(mma_deform_fwd_kernel<2, 2>)
-                                                                      : launch(mma_deform_fwd_kernel<2, 1>);
+  if (rot) return g.sH == 1 ? DK_PICK(mma_deform_fwd_kernel, 1, false) : DK_PICK(mma_deform_fwd_kernel, 2, false);
+  return g.sH == 1 ? DK_PICK(mma_deform_fwd_kernel, 1, true) : DK_PICK(mma_deform_fwd_kernel, 2, true);
 }
 
 size_t deform_data_mma_workspace(const Geom& g) { return ddata_plan(g).warps ? (size_t)g.N * sizeof(int) : 0; }
@@ -1194,7 +1221,8 @@ int deform_data_mma(const __half* dy, const __half* off, const __half* rot, cons
     kern<<<grid, pl.warps * 32, pl.smem, s>>>(dy, off, rot, w, hits, dx, g, pl);
     return check_launch();
   };
-  return g.sH == 1 ? launch(mma_deform_data_kernel<1>) : launch(mma_deform_data_kernel<2>);
+  if (rot) return g.sH == 1 ? launch(mma_deform_data_kernel<1, false>) : launch(mma_deform_data_kernel<2, false>);
+  return g.sH == 1 ? launch(mma_deform_data_kernel<1, true>) : launch(mma_deform_data_kernel<2, true>);
 }
 
 size_t deform_coords_mma_workspace(const Geom& g) {
@@ -1209,6 +1237,7 @@ size_t deform_coords_mma_workspace(const Geom& g) {
 int deform_coords_mma(const __half* dy, const __half* x, const __half* off, const __half* rot, const __half* w, __half* doff,
                       __half* drot, const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s) {
   if (!doff && !drot) return DK_OK;
+  if (!rot && drot) return DK_ERR_BAD_ARGUMENT;
   DCoordPlan pl = dcoord_plan(g, slab_cap());
   if (!pl.BH || pl.smem > (size_t)device_smem_optin() || g.C / (16 * pl.NS) > 65535) return DK_ERR_UNSUPPORTED;
   if (pl.ws_bytes && (ws == nullptr || ws_bytes < pl.ws_bytes)) return DK_ERR_UNSUPPORTED;  // no scratch: the SIMT kernel
@@ -1231,10 +1260,11 @@ int deform_coords_mma(const __half* dy, const __half* x, const __half* off, cons
     return check_launch();
   };
   int rc;
-#define DK_COORDS(SS, NN)                                                              \
-  (doff && drot ? launch(mma_deform_coords_kernel<SS, NN, true, true>)                \
-                : doff ? launch(mma_deform_coords_kernel<SS, NN, true, false>)        \
-                       : launch(mma_deform_coords_kernel<SS, NN, false, true>))
+#define DK_COORDS(SS, NN)                                                                     \
+  (!rot ? launch(mma_deform_coords_kernel<SS, NN, true, false, true>)                         \
+        : doff && drot ? launch(mma_deform_coords_kernel<SS, NN, true, true, false>)         \
+                       : doff ? launch(mma_deform_coords_kernel<SS, NN, true, false, false>) \
+                              : launch(mma_deform_coords_kernel<SS, NN, false, true, false>))
   if (g.sH == 1)
     rc = pl.NS == 2 ? DK_COORDS(1, 2) : DK_COORDS(1, 1);
   else

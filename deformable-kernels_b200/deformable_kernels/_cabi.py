@@ -78,6 +78,9 @@ for _name, (_res, _args) in _PROTOS.items():
 EXPORTS = tuple(_PROTOS)
 
 
+UNSUPPORTED = 2  # DK_ERR_UNSUPPORTED
+
+
 class DkError(RuntimeError):
     pass
 

@@ -37,7 +37,7 @@ def _check_shapes(input, rotation, weight, out_size, kernel_size, groups, offset
         raise ValueError("channels must be divisible by rotation_groups")
     taps2 = kernel_size[0] * kernel_size[1] * 2
     want = (input.size(0), groups * taps2, out_size[2], out_size[3])
-    if tuple(rotation.shape) != want:
+    if rotation is not None and tuple(rotation.shape) != want:
         raise ValueError("rotation must have shape {}, got {}".format(want, tuple(rotation.shape)))
     if offset is not None:
         want = (input.size(0), taps2, out_size[2], out_size[3])
@@ -94,12 +94,28 @@ class DeformableSampleDepthwiseFunction(Function):
         C.same_dtype(input, offset, rotation, weight)
         kernel_size, stride, padding, dilation = _pair(kernel_size), _pair(stride), _pair(padding), _pair(dilation)
         out_size = _output_size(input, kernel_size, stride, padding, dilation)
+        taps2 = kernel_size[0] * kernel_size[1] * 2
+        rot_shape = (input.size(0), rotation_groups * taps2, out_size[2], out_size[3])
+        output = input.new_empty(out_size)
+        ctx.geom = C.geom(input.shape, kernel_size, stride, padding, dilation, weight.shape[2:], rotation_groups)
+        if rotation is None:
+            # zero kernel-space offsets: the library builds the (pixel-independent) kernel once where it can
+            _check_shapes(input, None, weight, out_size, kernel_size, rotation_groups, offset)
+            input, offset, weight = input.contiguous(), offset.contiguous(), weight.contiguous()
+            with C.device_of(input):
+                status = C.lib.dk_deform_sample_depthwise_forward(
+                    C.ptr(input), C.ptr(offset), None, C.ptr(weight), C.ptr(output), ctx.geom, C.dtype_code(input),
+                    C.stream_ptr(input.device))
+            if status == 0:
+                ctx.save_for_backward(input, offset, None, weight)
+                return output
+            if status != C.UNSUPPORTED:
+                C.check(status, "deform_sample_depthwise forward")
+            rotation = input.new_zeros(rot_shape)
         _check_shapes(input, rotation, weight, out_size, kernel_size, rotation_groups, offset)
         input, offset, rotation, weight = (input.contiguous(), offset.contiguous(), rotation.contiguous(),
                                            weight.contiguous())
-        ctx.geom = C.geom(input.shape, kernel_size, stride, padding, dilation, weight.shape[2:], rotation_groups)
         ctx.save_for_backward(input, offset, rotation, weight)
-        output = input.new_empty(out_size)
         with C.device_of(input):
             C.check(C.lib.dk_deform_sample_depthwise_forward(
                 C.ptr(input), C.ptr(offset), C.ptr(rotation), C.ptr(weight), C.ptr(output), ctx.geom,
@@ -116,9 +132,24 @@ class DeformableSampleDepthwiseFunction(Function):
         need = ctx.needs_input_grad
         grad_input = torch.empty_like(input) if need[0] else None
         grad_offset = torch.empty_like(offset) if need[1] else None
-        grad_rotation = torch.empty_like(rotation) if need[2] else None
         grad_weight = torch.empty_like(weight) if need[3] else None
         code = C.dtype_code(input)
+        if rotation is None:
+            with C.device_of(input):
+                nbytes = C.lib.dk_deform_sample_depthwise_backward_workspace_bytes(ctx.geom, code)
+                ws = C.workspace(nbytes, input.device)
+                status = C.lib.dk_deform_sample_depthwise_backward(
+                    C.ptr(grad_output), C.ptr(input), C.ptr(offset), None, C.ptr(weight), C.ptr(grad_input),
+                    C.ptr(grad_offset), None, C.ptr(grad_weight), ctx.geom, code, C.ptr(ws), nbytes,
+                    C.stream_ptr(input.device))
+            if status == 0:
+                return (grad_input, grad_offset, None, grad_weight) + (None,) * 5
+            if status != C.UNSUPPORTED:
+                C.check(status, "deform_sample_depthwise backward")
+            g = ctx.geom
+            rotation = input.new_zeros((input.size(0), g.rotation_groups * g.kernel_h * g.kernel_w * 2) +
+                                       tuple(grad_output.shape[2:]))
+        grad_rotation = torch.empty_like(rotation) if need[2] else None
         with C.device_of(input):
             nbytes = C.lib.dk_deform_sample_depthwise_backward_workspace_bytes(ctx.geom, code)
             ws = C.workspace(nbytes, input.device)
@@ -144,6 +175,9 @@ def sample_depthwise(input, rotation, weight, kernel_size=(3, 3), stride=(1, 1),
 
 def deform_sample_depthwise(input, offset, rotation, weight, kernel_size=(3, 3), stride=(1, 1), padding=(1, 1),
                             dilation=(1, 1), rotation_groups=1):
-    offset, rotation, weight = _common_dtype(input, offset, rotation, weight)
+    if rotation is None:
+        offset, weight = _common_dtype(input, offset, weight)
+    else:
+        offset, rotation, weight = _common_dtype(input, offset, rotation, weight)
     return DeformableSampleDepthwiseFunction.apply(input, offset, rotation, weight, kernel_size, stride, padding,
                                                    dilation, rotation_groups)

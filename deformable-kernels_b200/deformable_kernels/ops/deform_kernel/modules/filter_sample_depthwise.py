@@ -89,8 +89,6 @@ class DeformableSampleDepthwise(_BankConv):
     def forward(self, input, offset=None, rotation=None):
         if offset is None:
             offset = self._zero_offsets(input, 1)
-        if rotation is None:
-            rotation = self._zero_offsets(input, self.rotation_groups)
         out = deform_sample_depthwise(input, offset, rotation, self.weight, self.kernel_size, self.stride,
                                       self.padding, self.dilation, self.rotation_groups)
         return self._add_bias(out)

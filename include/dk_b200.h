@@ -125,7 +125,11 @@ int dk_sample_depthwise_backward(const void *grad_output, const void *input, con
  * as above, with x read by zero-extended bilinear sampling at
  * (oh*s-p+fh*d + off_h, ow*s-p+fw*d + off_w); a tap is used only if -1 < pos < size. */
 
-/* replaces deformable_sample_depthwise_forward_cuda, csrc/filter_sample_depthwise_cuda.cpp:237-294 */
+/* replaces deformable_sample_depthwise_forward_cuda, csrc/filter_sample_depthwise_cuda.cpp:237-294.
+ * `rotation` may be NULL here and in dk_deform_sample_depthwise_backward, meaning zero kernel-space offsets (what
+ * DeformKernelConv2d / DeformConv2d pass, modules/deform_kernel.py:276): the sampled kernel is then the same for every
+ * pixel and is built once.  Only the fp16 tensor-core path takes NULL; otherwise DK_ERR_UNSUPPORTED is returned and
+ * the caller passes a tensor of zeros, as the reference does. */
 int dk_deform_sample_depthwise_forward(const void *input, const void *offset, const void *rotation,
                                        const void *filter, void *output, const dk_geom *g, int dtype, void *stream);
 

@@ -193,6 +193,24 @@ def test_deform_dk_fp16_batched_shapes_match_oracle(ops, oracle, cfg):
     compare(mine_deform(ops, case, torch.float16), oracle_deform(oracle, case, torch.float16), torch.float16, "deform-batched")
 
 
+@pytest.mark.parametrize("cfg", [DCN_BATCHED[0], DCN_BATCHED[2], FAST[3]])
+def test_deform_dk_without_kernel_offsets_matches_zero_offsets(ops, oracle, cfg):
+    """rotation=None (what DeformKernelConv2d and DeformConv2d pass) against the oracle with a tensor of zeros: fp16
+    takes the path that builds the pixel-independent kernel once, fp32 falls back to zeros inside the binding."""
+    case = make_case(seed=42, off_std=2.0, **cfg)
+    case["rotation"] = torch.zeros_like(case["rotation"])
+    for dtype in (torch.float16, torch.float32):
+        x, o, w, dy = (case[k].to(dtype).to(DEV) for k in ("input", "offset", "weight", "grad_output"))
+        for t in (x, o, w):
+            t.requires_grad_(True)
+        y = ops.deform_sample_depthwise(x, o, None, w, **case["args"])
+        dx, do, dw = torch.autograd.grad(y, [x, o, w], dy)
+        want = oracle_deform(oracle, case, dtype)
+        got = dict(output=y.detach(), grad_input=dx, grad_offset=do, grad_weight=dw)
+        want.pop("grad_rotation")
+        compare(got, want, dtype, "deform-no-rotation")
+
+
 def test_deform_grad_input_fixed_point_accumulation(ops, oracle):
     """The fp16 grad-input kernel sums in fixed point.  Bit-reproducible; an outlier in dy coarsens only its own
     (sample, channel) plane and the result still holds the tolerance on every plane taken by itself; offsets that
