@@ -437,7 +437,9 @@ RotPlan rot_plan(const Geom& g) {
     const size_t budget = attempt == 0 ? kTwoPerSm : kOnePerSm;
     const int maxw = attempt == 0 ? 8 : 16;
     int best = 0;
-    for (int bh = 1; bh <= g.Ho; ++bh) {
+    int cap = g.Ho;
+    if (const char* e = std::getenv("DK_B200_ROT_BH")) cap = atoi(e) > 0 ? atoi(e) : cap;  // tuning knob
+    for (int bh = 1; bh <= g.Ho && bh <= cap; ++bh) {
       if (rot_smem(g, g.C, bh, pick_warps(bh * NB, maxw)) > budget) break;
       best = bh;
       if (bh * NB >= 2 * maxw) break;
