@@ -211,6 +211,35 @@ def test_deform_dk_without_kernel_offsets_matches_zero_offsets(ops, oracle, cfg)
         compare(got, want, dtype, "deform-no-rotation")
 
 
+def _random_fast_shapes(count, seed):
+    """Seeded random geometries inside the fp16 tensor-core fast path (3x3, pad 1, C % 16 == 0, <= 16 cells)."""
+    import random
+    rng = random.Random(seed)
+    out = []
+    for _ in range(count):
+        scope = rng.choice([(4, 4), (4, 4), (3, 3), (2, 2), (3, 5), (4, 2), (1, 4)])
+        out.append(dict(n=rng.randint(1, 5), c=rng.choice([16, 32, 48, 64, 80, 96, 144]), h=rng.randint(3, 36),
+                        w=rng.randint(3, 36), scope=scope, k=3, stride=rng.choice([1, 1, 2]), pad=1,
+                        rot_std=rng.choice([0.5, 1.0, 2.5])))
+    return out
+
+
+@pytest.mark.parametrize("cfg", _random_fast_shapes(16, 101))
+def test_local_dk_fp16_random_shapes_match_oracle(ops, oracle, cfg):
+    case = make_case(seed=43, **cfg)
+    case["rotation"] = snap(case["rotation"])
+    compare(mine_local(ops, case, torch.float16), oracle_local(oracle, case, torch.float16), torch.float16, "random-local")
+
+
+@pytest.mark.parametrize("cfg", _random_fast_shapes(12, 202))
+def test_deform_dk_fp16_random_shapes_match_oracle(ops, oracle, cfg):
+    cfg = dict(cfg, n=cfg["n"] * 6)   # enough (sample, channel group) pairs for the whole-sample grad-input kernel on most
+    case = make_case(seed=44, off_std=2.0, **cfg)
+    case["rotation"] = snap(case["rotation"])
+    case["offset"] = snap(case["offset"], seed=5)
+    compare(mine_deform(ops, case, torch.float16), oracle_deform(oracle, case, torch.float16), torch.float16, "random-deform")
+
+
 def test_deform_grad_input_fixed_point_accumulation(ops, oracle):
     """The fp16 grad-input kernel sums in fixed point.  Bit-reproducible; an outlier in dy coarsens only its own
     (sample, channel) plane and the result still holds the tolerance on every plane taken by itself; offsets that
