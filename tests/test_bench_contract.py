@@ -22,10 +22,10 @@ def test_reference_arm_prints_one_contract_line():
     assert "workload" in d["config"] and d["vs_baseline"] is None
 
 
-def test_layer_byte_formulas_match_the_survey_totals():
+def test_layer_byte_formulas_match_the_tabulated_totals():
     sys.path.insert(0, ROOT)
     import bench
-    # fwd+bwd algorithmic MB at batch 128, fp16
+    # fwd+bwd algorithmic MB at batch 128, fp16: every tensor read or written once per pass
     want = {(96, 112, 1): 1714.8, (96, 112, 2): 1122.3, (144, 56, 1): 621.4, (144, 56, 2): 415.5, (192, 28, 1): 203.5,
             (192, 28, 2): 137.6, (384, 14, 1): 99.1, (384, 14, 2): 68.2, (960, 7, 1): 61.0, (960, 7, 2): 44.3}
     for (c, hw, s), mb in want.items():
