@@ -158,6 +158,10 @@ FAST = [   # shapes inside the fp16 tensor-core fast path (3x3, pad 1, dil 1, on
     dict(n=1, c=32, h=9, w=16, scope=(2, 2), k=3, stride=1, pad=1, rot_std=0.6),       # 4 cells, zero-padded to 16
     dict(n=1, c=16, h=10, w=12, scope=(3, 5), k=3, stride=1, pad=1, rot_std=1.2),      # 15 cells, non-square scope
     dict(n=2, c=16, h=5, w=6, scope=(4, 4), k=3, stride=2, pad=1, rot_std=3.0),        # most samples outside the bank
+    dict(n=1, c=16, h=1, w=1, scope=(4, 4), k=3, stride=1, pad=1, rot_std=1.0),        # a single pixel
+    dict(n=3, c=32, h=2, w=9, scope=(1, 1), k=3, stride=2, pad=1, rot_std=0.8),        # one bank cell, 1 x 5 output
+    dict(n=2, c=16, h=1, w=17, scope=(2, 8), k=3, stride=1, pad=1, rot_std=1.5),       # 16 cells in a flat scope, one row
+    dict(n=1, c=16, h=33, w=2, scope=(4, 4), k=3, stride=2, pad=1, rot_std=1.0),       # one output column
 ]
 
 
