@@ -1,4 +1,5 @@
-// fp16 tensor-core paths of the DK + DCN operator: forward and bank gradient.
+// fp16 tensor-core paths of the DK + DCN operator: forward, bank gradient, gradients of both offset fields, and
+// grad-input.
 //
 // y[c, p]      = sum over taps of K[c, p, tap] * xs[c, p, tap],          K = W * beta^T
 // dW[c, cell]  = sum over (sample, pixel, tap) of dy[c, p] * xs[c, p, tap] * beta[(p, tap), cell]
@@ -6,7 +7,8 @@
 // sample at the tap's deformed position: four data-dependent reads per (pixel, tap, channel).  A block keeps the
 // WHOLE input plane of its channels in shared memory, so those reads never leave the SM, and builds, three taps
 // at a time, a table of (byte offset, coefficient) x 4 corners per (pixel, tap) that all its channels reuse.
-// The two products with beta are mma.sync.m16n8k16 as for the local operator.
+// The products with beta are mma.sync.m16n8k16 as for the local operator.  The offset gradients and grad-input
+// (a scatter into on-chip planes) are described at their kernels further down.
 //
 // Covers fp16, 3x3, pad 1, dilation 1, stride 1 or 2, one rotation group, <= 16 bank cells, C % 16 == 0 and
 // planes small enough for 16 of them to fit on chip (56 x 56 and below); other shapes use the SIMT kernels.
@@ -23,7 +25,7 @@ namespace {
 constexpr size_t kOnePerSm = 226 * 1024;
 
 // ------------------------------------------------------------------ channel-pair planes
-// The forward keeps its input planes as 32-bit words (channel j | channel j + 8 << 16), eight words per pixel
+// The kernels that sample the image keep its planes as 32-bit words (channel j | channel j + 8 << 16), eight words per pixel
 // ("chunk"), so that one shared-memory read serves both channel rows of a lane's mma fragments and the eight
 // lanes of a pixel read 32 contiguous bytes.  Chunks are permuted inside groups of 8 (stride 1) or 16 (stride 2)
 // pixels so that the four pixel pairs of a warp, 2 (or 4) source pixels apart when the offsets are smooth, start

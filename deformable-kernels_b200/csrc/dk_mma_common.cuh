@@ -320,7 +320,7 @@ __device__ __forceinline__ LaneCells lane_cells(const Geom& g, int q) {
   }
   return lc;
 }
-__device__ __forceinline__ float hat(float t) { return fmaxf(0.f, 1.f - fabsf(t)); }
+__device__ __forceinline__ float hat(float t) { return __saturatef(1.f - fabsf(t)); }  // max(0, 1 - |t|) in one add
 __device__ __forceinline__ unsigned pack2(float a, float b) {
   const __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<const unsigned*>(&h);
