@@ -211,10 +211,16 @@ def run_training_step(args, rank, world, local, dev):
     labels = torch.randint(0, 1000, (per_gpu,), device=dev, generator=gen)
     loss_fn = torch.nn.CrossEntropyLoss()
     scaler = torch.amp.GradScaler("cuda", init_scale=1024.0)
+    graphed = bool(args.cuda_graph) and world == 1
+    if graphed:
+        # forward and backward of the whole network as two CUDA graphs (the operators capture: they enqueue on the
+        # current stream, never synchronise and take their scratch from the caller); loss, scaler and optimizer stay eager
+        with torch.autocast("cuda", dtype=torch.float16, cache_enabled=False):
+            model = torch.cuda.make_graphed_callables(model, (x.clone(),))
 
     def step():
-        opt.zero_grad(set_to_none=True)
-        with torch.autocast("cuda", dtype=torch.float16):
+        opt.zero_grad(set_to_none=not graphed)
+        with torch.autocast("cuda", dtype=torch.float16, cache_enabled=not graphed):
             loss = loss_fn(model(x), labels)
         scaler.scale(loss).backward()
         scaler.step(opt)
@@ -249,7 +255,8 @@ def run_training_step(args, rank, world, local, dev):
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16 autocast, f32 master weights", "data": "synthetic",
             "config": {"workload": "cfg5: MobileNetV2-1.0 with %d DeformKernel2d layers (scope 4x4), 224x224, SGD step, "
-                                   "DDP/NCCL gradient all-reduce" % replaced, "per_gpu_batch": per_gpu},
+                                   "DDP/NCCL gradient all-reduce" % replaced, "per_gpu_batch": per_gpu,
+                       "cuda_graph": graphed},
             "loss": float(loss.item()), "clocks": clocks, "peak_mem_GB": round(torch.cuda.max_memory_allocated() / 1e9, 1)}))
 
 
@@ -375,6 +382,8 @@ def main():
                     help="sweep: the DK layer sweep (headline); train: MobileNetV2-DK training step, global batch 1024; "
                          "dcn: one DK + DCN layer (BASELINE config 4)")
     ap.add_argument("--global-batch", type=int, default=1024)
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="train workload, one GPU: run the network's forward and backward as captured CUDA graphs")
     ap.add_argument("--dcn-batch", type=int, default=64, help="images per GPU of the dcn workload")
     ap.add_argument("--layers", default="", help="comma-separated indices into the ten-layer sweep (default: all)")
     ap.add_argument("--ref-gpu", action="store_true",
