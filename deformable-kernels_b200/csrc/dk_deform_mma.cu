@@ -1008,6 +1008,12 @@ bool dcn_fast_shape(const Geom& g) {
   return true;
 }
 
+int min_items() {  // DK_B200_DCN_MIN_ITEMS: fewest items per band for which more than one slab per block is taken (tuning knob)
+  const char* e = getenv("DK_B200_DCN_MIN_ITEMS");
+  const int v = e ? atoi(e) : 0;
+  return v > 0 ? v : 14;  // measured at 56 x 56: forward 0.75 -> 0.69 ms with two slabs and 21 items; 7 items lose
+}
+
 // Shape of the grid.  NS slabs of 16 channels per block share the hat products and the sampling tables, so more
 // is better while every SM still gets a block; the band of output rows is as tall as shared memory allows beside
 // the planes (its loads are paid once per unit), cut finer when there are too few units to fill the GPU.
@@ -1037,7 +1043,7 @@ DcnPlan dcn_plan(const Geom& g, int ns_cap, int dy_rows) {
       if (need(bh, wv) > kOnePerSm) break;
       bh_max = bh;
     }
-    if (!bh_max || (ns > 1 && bh_max * NB < 32 && bh_max < g.Ho)) continue;  // short bands: the per-unit cost eats the gain
+    if (!bh_max || (ns > 1 && bh_max * NB < min_items() && bh_max < g.Ho)) continue;  // short bands: the per-unit cost eats the gain
     const int groups = slabs / ns;
     int bands = (g.Ho + bh_max - 1) / bh_max;
     const long long base_units = (long long)g.N * groups;
