@@ -509,6 +509,12 @@ def main():
                 "traffic": (NCU_TRAFFIC_BATCH64[dom] * n / 64.0) if (bt["c"], bt["hw"], bt["s"]) == (96, 112, 1) else None,
                 "algorithmic_bytes": kb, "kernel_ms": round(bkt[dom], 4),
                 "sweep_fwd_bwd_GBps": round(sweep_gbs, 1), "sweep_frac": round(sweep_gbs / peak, 4)}
+    # the same figures for all four kernels of that layer
+    roofline["all_kernels_largest_layer"] = {
+        k: {"kernel_ms": round(v, 4), "algorithmic_bytes": kernel_bytes(k, n, bt["c"], bt["hw"], bt["s"]),
+            "achieved": round(kernel_bytes(k, n, bt["c"], bt["hw"], bt["s"]) / (v * 1e-3) / 1e9, 1),
+            "frac": round(kernel_bytes(k, n, bt["c"], bt["hw"], bt["s"]) / (v * 1e-3) / 1e9 / peak, 4)}
+        for k, v in bkt.items()}
 
     # end to end: pinned host inputs -> device, forward + backward, all results -> pinned host
     host = []
