@@ -267,6 +267,7 @@ __device__ __forceinline__ void dk_products(unsigned (&dk0)[9], unsigned (&dk1)[
 }
 
 struct RotPlan {
+  bool dy_direct;  // dy straight from global memory into registers (see FiltPlan)
   int BH, warps, bands;
   int CG, groups;  // channels per block; with more than one group the blocks write fp32 partial sums
   bool big;        // one block of up to 16 warps per SM instead of two of up to 8
@@ -275,7 +276,7 @@ struct RotPlan {
 };
 constexpr int kRotScratch = 3 * 16 * 8 * 4 + 72 * 8;  // G of three taps (aliases the beta table) + (u, v)
 
-template <int S, int MAXT, int MINB>
+template <int S, int MAXT, int MINB, bool DYD>
 __global__ void __launch_bounds__(MAXT, MINB) mma_rot_kernel(const __half* __restrict__ dy, const __half* __restrict__ x,
                                                          const __half* __restrict__ rot, const __half* __restrict__ w,
                                                          __half* __restrict__ drot, float* __restrict__ partial,
@@ -292,7 +293,7 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_rot_kernel(const __half* __res
 
   __half* xband = reinterpret_cast<__half*>(smem_raw);
   __half* yband = xband + (size_t)pl.CG * bx.pitch_c;
-  __half* rband = yband + (size_t)pl.CG * by.pitch_c;                      // [18][br.pitch_c]
+  __half* rband = yband + (DYD ? (size_t)0 : (size_t)pl.CG * by.pitch_c);  // [18][br.pitch_c]
   __half* bankT = rband + (size_t)18 * br.pitch_c;                         // [16 cells][CG + 8]
   unsigned char* scratch = reinterpret_cast<unsigned char*>(bankT + 16 * pitchT);
 
@@ -301,7 +302,7 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_rot_kernel(const __half* __res
     bankT[cell * pitchT + c] = cell < g.cells ? __ldg(w + (size_t)(c0 + c) * g.cells + cell) : __float2half(0.f);
   }
   load_band(xband, bx, x, n, g.C, c0, cnt, g.H, g.W);
-  load_band(yband, by, dy, n, g.C, c0, cnt, g.Ho, g.Wo);
+  if (!DYD) load_band(yband, by, dy, n, g.C, c0, cnt, g.Ho, g.Wo);
   load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
   cp_async_wait_all();
   __syncthreads();
@@ -330,9 +331,28 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_rot_kernel(const __half* __res
 #pragma unroll
     for (int t = 0; t < 9; ++t) G[t][0] = G[t][1] = G[t][2] = G[t][3] = 0.f;
 
+    // DYD: the slab's two dy words come from global memory, fetched one slab ahead
+    const bool dy_in = ow < g.Wo;
+    const unsigned* dp = reinterpret_cast<const unsigned*>(dy + ((size_t)n * g.C + c0 + gq) * g.P + (size_t)oh * g.Wo + ow);
+    const size_t dstep8 = (size_t)8 * g.P / 2;  // words between channel rows gq and gq + 8
+    unsigned ndy0 = 0u, ndy1 = 0u;
+    if (DYD && dy_in) {
+      ndy0 = __ldg(dp);
+      ndy1 = __ldg(dp + dstep8);
+    }
     for (int cb16 = 0; cb16 < cnt; cb16 += 16) {
-      const unsigned dy0 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq) * by.pitch_c + yoff);
-      const unsigned dy1 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq + 8) * by.pitch_c + yoff);
+      unsigned dy0, dy1;
+      if (DYD) {
+        dy0 = ndy0;
+        dy1 = ndy1;
+        if (dy_in && cb16 + 16 < cnt) {
+          ndy0 = __ldg(dp + (size_t)(cb16 + 16) / 8 * dstep8);
+          ndy1 = __ldg(dp + (size_t)(cb16 + 24) / 8 * dstep8);
+        }
+      } else {
+        dy0 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq) * by.pitch_c + yoff);
+        dy1 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq + 8) * by.pitch_c + yoff);
+      }
       unsigned dk0[9], dk1[9];
       dk_products<S>(dk0, dk1, xband + (size_t)(cb16 + gq) * bx.pitch_c + xoff, 8 * bx.pitch_c, bx.Wp, dy0, dy1);
       // A = W^T slab: rows = cells (gq, gq+8), k = channels (2q,2q+1) and (2q+8,2q+9)
@@ -410,10 +430,18 @@ __global__ void reduce_rot_partials_kernel(const float* __restrict__ partial, __
 //   3. else (small planes, many channels) split the channels into groups that each write an
 //      fp32 partial sum, reduced by a second pass: cheap there because the offset tensor is
 //      small next to the activations.
+static bool rot_dy_direct(const Geom& g) {
+  // even rows (the pixel pairs of dy are aligned words) and small planes: measured faster up to 28 x 28 outputs
+  // (0.095 -> 0.080, 0.083 -> 0.056 ms), slower on the wide layers, whose blocks walk over many slabs per item
+  bool on = (g.Wo & 1) == 0 && g.P <= 784;
+  if (const char* e = std::getenv("DK_B200_ROT_DY_DIRECT")) on = on && atoi(e) != 0;  // comparison runs
+  return on;
+}
 static size_t rot_smem(const Geom& g, int cg, int bh, int warps) {
   const int S = g.sH;
   const int Wp = g.W + (g.W & 1), Wpo = g.Wo + (g.Wo & 1);
-  return (size_t)cg * (band_pitch((bh - 1) * S + 3, Wp) + band_pitch(bh, Wpo)) * 2 + (size_t)18 * band_pitch(bh, Wpo) * 2 +
+  return (size_t)cg * (band_pitch((bh - 1) * S + 3, Wp) + (rot_dy_direct(g) ? 0 : band_pitch(bh, Wpo))) * 2 +
+         (size_t)18 * band_pitch(bh, Wpo) * 2 +
          (size_t)16 * (cg + 8) * 2 + (size_t)warps * kRotScratch;
 }
 
@@ -425,6 +453,7 @@ RotPlan rot_plan(const Geom& g) {
   pl.big = false;
   pl.groups = 1;
   pl.CG = g.C;
+  pl.dy_direct = rot_dy_direct(g);
   // One block of up to 16 warps per SM with a taller band first: the halo rows of x weigh less and a block's load is
   // spread over more items (measured: C = 144 at 56 x 56 0.38 -> 0.22 ms, never slower on the sweep's layers).
   // DK_B200_ROT_BIG=0 tries two blocks per SM first (tuning knob).
@@ -484,13 +513,14 @@ RotPlan rot_plan(const Geom& g) {
 
 // ------------------------------------------------------------------ grad-bank
 struct FiltPlan {
+  bool dy_direct;  // dy goes from global memory straight into registers (each word is used once) instead of through a band
   bool big;  // six channel slabs per block, one block of up to 14 warps per SM
   int BH, CG, groups, warps, bands, units_per_block, blocks_x;
   int mode_x, mode_dy, mode_rot;
   size_t smem, ws_bytes;
 };
 
-template <int S, int NS, int MAXT, int MINB>
+template <int S, int NS, int MAXT, int MINB, bool DYD>
 __global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __restrict__ dy, const __half* __restrict__ x,
                                                             const __half* __restrict__ rot, float* __restrict__ partial,
                                                             const Geom g, const FiltPlan pl) {
@@ -507,7 +537,7 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __
 
   __half* xband = reinterpret_cast<__half*>(smem_raw);
   __half* yband = xband + (size_t)pl.CG * xpitch;
-  __half* rband = yband + (size_t)pl.CG * ypitch;  // [18][ypitch]
+  __half* rband = yband + (DYD ? (size_t)0 : (size_t)pl.CG * ypitch);  // [18][ypitch]
   const LaneCells lc = lane_cells(g, q);
   const bool sc44 = g.scH == 4 && g.scW == 4;
 
@@ -528,7 +558,7 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __
     const Band br = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_rot);
     __syncthreads();  // previous unit's readers are done
     load_band(xband, bx, x, n, g.C, c0, cnt, g.H, g.W);
-    load_band(yband, by, dy, n, g.C, c0, cnt, g.Ho, g.Wo);
+    if (!DYD) load_band(yband, by, dy, n, g.C, c0, cnt, g.Ho, g.Wo);
     load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
     cp_async_wait_all();
     __syncthreads();
@@ -537,6 +567,20 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __
       const int oh = oh0 + dr;
       if (oh >= g.Ho) break;
       const int ow0 = (item - dr * NB) << 3;
+      // dy of the item for every slab, fetched before the hat products so that its latency hides behind them
+      unsigned dyw[NS][2];
+      if (DYD) {
+        const int owl = ow0 + 2 * q;
+        const __half* dp = dy + ((size_t)n * g.C + c0 + gq) * g.P + (size_t)oh * g.Wo + owl;
+#pragma unroll
+        for (int sidx = 0; sidx < NS; ++sidx) {
+          dyw[sidx][0] = dyw[sidx][1] = 0u;
+          if (sidx < nslab && owl < g.Wo) {
+            dyw[sidx][0] = __ldg(reinterpret_cast<const unsigned*>(dp + (size_t)(sidx << 4) * g.P));
+            dyw[sidx][1] = __ldg(reinterpret_cast<const unsigned*>(dp + (size_t)((sidx << 4) + 8) * g.P));
+          }
+        }
+      }
       unsigned bw[10][2];  // beta as B fragments of the grad-bank product: [tap][cells 0-7 | cells 8-15]
       {
         unsigned bf[9][2];
@@ -555,8 +599,14 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __
       for (int sidx = 0; sidx < NS; ++sidx) {
         if (sidx < nslab) {
           const int cb16 = sidx << 4;
-          const unsigned dy0 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq) * by.pitch_c + yoff);
-          const unsigned dy1 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq + 8) * by.pitch_c + yoff);
+          unsigned dy0, dy1;
+          if (DYD) {
+            dy0 = dyw[sidx][0];
+            dy1 = dyw[sidx][1];
+          } else {
+            dy0 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq) * by.pitch_c + yoff);
+            dy1 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq + 8) * by.pitch_c + yoff);
+          }
           unsigned dk0[10], dk1[10];
           {
             unsigned a9[9], b9[9];
@@ -628,9 +678,16 @@ FiltPlan filt_plan(const Geom& g) {
   const int Wp = g.W + (g.W & 1), Wpo = g.Wo + (g.Wo & 1);
   const size_t budget = pl.big ? kOnePerSm : kTwoPerSm;
   pl.BH = 0;
+  // Every dy word is used exactly once, so staging it in shared memory only adds traffic on the path the kernel is bound
+  // by; with even output rows it is read straight into registers and the room goes to a taller band (fewer halo rows
+  // of x per output row).  DK_B200_FILT_DY_DIRECT=0 keeps the band (comparison runs).
+  pl.dy_direct = (g.Wo & 1) == 0 && !pl.big;  // six slabs of dy words do not fit the registers of the big block
+  if (const char* e = std::getenv("DK_B200_FILT_DY_DIRECT")) pl.dy_direct = pl.dy_direct && atoi(e) != 0;
+  int max_items = (pl.dy_direct && S == 1) ? 56 : 24;  // measured: taller bands pay at stride 1 once dy is out of shared memory
+  if (const char* e = std::getenv("DK_B200_FILT_ITEMS")) max_items = atoi(e) > 0 ? atoi(e) : max_items;  // tuning knob
   for (int bh = 1; bh <= g.Ho; ++bh) {
     const int warps = pick_warps(bh * NB, pl.big ? 14 : 8);
-    size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + band_pitch(bh, Wpo)) * 2 +
+    size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + (pl.dy_direct ? 0 : band_pitch(bh, Wpo))) * 2 +
                   (size_t)18 * band_pitch(bh, Wpo) * 2;
     const size_t red = (size_t)warps * pl.CG * 16 * 4;
     if (smem < red) smem = red;
@@ -638,7 +695,7 @@ FiltPlan filt_plan(const Geom& g) {
     pl.BH = bh;
     pl.warps = warps;
     pl.smem = smem;
-    if (bh * NB >= 24) break;
+    if (bh * NB >= max_items) break;
   }
   if (!pl.BH) return pl;
   pl.bands = (g.Ho + pl.BH - 1) / pl.BH;
@@ -680,12 +737,15 @@ int local_rot_mma(const __half* dy, const __half* x, const __half* rot, const __
   pl.mode_x = ptr_mode(x);
   pl.mode_dy = ptr_mode(dy);
   pl.mode_rot = ptr_mode(rot);
+  if (pl.dy_direct && pl.mode_dy == 0) return DK_ERR_UNSUPPORTED;  // a dy pointer that is not 4-byte aligned: SIMT kernels
   int rc;
   const dim3 grid(pl.bands, g.N, pl.groups);
   float* partial = reinterpret_cast<float*>(ws);
 #define DK_LAUNCH_ROT(SS, MAXT, MINB)                                                     \
+  if (pl.dy_direct) DK_LAUNCH_ROT2(SS, MAXT, MINB, true) else DK_LAUNCH_ROT2(SS, MAXT, MINB, false)
+#define DK_LAUNCH_ROT2(SS, MAXT, MINB, DD)                                                \
   {                                                                                       \
-    auto kern = mma_rot_kernel<SS, MAXT, MINB>;                                           \
+    auto kern = mma_rot_kernel<SS, MAXT, MINB, DD>;                                       \
     if ((rc = enable_smem(kern, pl.smem))) return rc;                                     \
     kern<<<grid, pl.warps * 32, pl.smem, s>>>(dy, x, rot, w, drot, partial, g, pl);       \
   }
@@ -695,6 +755,7 @@ int local_rot_mma(const __half* dy, const __half* x, const __half* rot, const __
     if (pl.big) DK_LAUNCH_ROT(2, 512, 1) else DK_LAUNCH_ROT(2, 256, 2)
   }
 #undef DK_LAUNCH_ROT
+#undef DK_LAUNCH_ROT2
   if ((rc = check_launch())) return rc;
   if (pl.groups > 1) {
     const size_t n_out = (size_t)g.N * 18 * g.P;
@@ -721,18 +782,23 @@ int local_filter_mma(const __half* dy, const __half* x, const __half* rot, __hal
   pl.mode_x = ptr_mode(x);
   pl.mode_dy = ptr_mode(dy);
   pl.mode_rot = ptr_mode(rot);
+  if (pl.dy_direct && pl.mode_dy == 0) return DK_ERR_UNSUPPORTED;  // a dy pointer that is not 4-byte aligned: SIMT kernels
   int rc;
   float* partial = reinterpret_cast<float*>(ws);
-#define DK_LAUNCH_FILT(SS, NS, MAXT, MINB)                                                            \
+#define DK_LAUNCH_FILT(SS, NS, MAXT, MINB, DD)                                                        \
   {                                                                                                 \
-    auto kern = mma_filter_kernel<SS, NS, MAXT, MINB>;                                              \
+    auto kern = mma_filter_kernel<SS, NS, MAXT, MINB, DD>;                                          \
     if ((rc = enable_smem(kern, pl.smem))) return rc;                                               \
     kern<<<dim3(pl.blocks_x, pl.groups), pl.warps * 32, pl.smem, s>>>(dy, x, rot, partial, g, pl);  \
   }
   if (g.sH == 1) {
-    if (pl.big) DK_LAUNCH_FILT(1, 6, 448, 1) else DK_LAUNCH_FILT(1, 4, 256, 2)
+    if (pl.big) DK_LAUNCH_FILT(1, 6, 448, 1, false)
+    else if (pl.dy_direct) DK_LAUNCH_FILT(1, 4, 256, 2, true)
+    else DK_LAUNCH_FILT(1, 4, 256, 2, false)
   } else {
-    if (pl.big) DK_LAUNCH_FILT(2, 6, 448, 1) else DK_LAUNCH_FILT(2, 4, 256, 2)
+    if (pl.big) DK_LAUNCH_FILT(2, 6, 448, 1, false)
+    else if (pl.dy_direct) DK_LAUNCH_FILT(2, 4, 256, 2, true)
+    else DK_LAUNCH_FILT(2, 4, 256, 2, false)
   }
 #undef DK_LAUNCH_FILT
   if ((rc = check_launch())) return rc;
