@@ -567,19 +567,22 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __
       const int oh = oh0 + dr;
       if (oh >= g.Ho) break;
       const int ow0 = (item - dr * NB) << 3;
-      // dy of the item for every slab, fetched before the hat products so that its latency hides behind them
+      // dy of the item, fetched ahead of its use: every slab before the hat products (their latency hides behind those), or,
+      // with more than four slabs, the first two now and each further one two slabs ahead (fewer registers held)
+      constexpr int PRE = NS > 4 ? 2 : NS;
       unsigned dyw[NS][2];
-      if (DYD) {
-        const int owl = ow0 + 2 * q;
-        const __half* dp = dy + ((size_t)n * g.C + c0 + gq) * g.P + (size_t)oh * g.Wo + owl;
-#pragma unroll
-        for (int sidx = 0; sidx < NS; ++sidx) {
-          dyw[sidx][0] = dyw[sidx][1] = 0u;
-          if (sidx < nslab && owl < g.Wo) {
-            dyw[sidx][0] = __ldg(reinterpret_cast<const unsigned*>(dp + (size_t)(sidx << 4) * g.P));
-            dyw[sidx][1] = __ldg(reinterpret_cast<const unsigned*>(dp + (size_t)((sidx << 4) + 8) * g.P));
-          }
+      const int owl = ow0 + 2 * q;
+      const __half* dp = dy + ((size_t)n * g.C + c0 + gq) * g.P + (size_t)oh * g.Wo + owl;
+      auto fetch_dy = [&](int sidx) {
+        dyw[sidx][0] = dyw[sidx][1] = 0u;
+        if (sidx < nslab && owl < g.Wo) {
+          dyw[sidx][0] = __ldg(reinterpret_cast<const unsigned*>(dp + (size_t)(sidx << 4) * g.P));
+          dyw[sidx][1] = __ldg(reinterpret_cast<const unsigned*>(dp + (size_t)((sidx << 4) + 8) * g.P));
         }
+      };
+      if (DYD) {
+#pragma unroll
+        for (int sidx = 0; sidx < PRE; ++sidx) fetch_dy(sidx);
       }
       unsigned bw[10][2];  // beta as B fragments of the grad-bank product: [tap][cells 0-7 | cells 8-15]
       {
@@ -603,6 +606,7 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __
           if (DYD) {
             dy0 = dyw[sidx][0];
             dy1 = dyw[sidx][1];
+            if (sidx + PRE < NS) fetch_dy(sidx + PRE);
           } else {
             dy0 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq) * by.pitch_c + yoff);
             dy1 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq + 8) * by.pitch_c + yoff);
@@ -681,7 +685,7 @@ FiltPlan filt_plan(const Geom& g) {
   // Every dy word is used exactly once, so staging it in shared memory only adds traffic on the path the kernel is bound
   // by; with even output rows it is read straight into registers and the room goes to a taller band (fewer halo rows
   // of x per output row).  DK_B200_FILT_DY_DIRECT=0 keeps the band (comparison runs).
-  pl.dy_direct = (g.Wo & 1) == 0 && !pl.big;  // six slabs of dy words do not fit the registers of the big block
+  pl.dy_direct = (g.Wo & 1) == 0;
   if (const char* e = std::getenv("DK_B200_FILT_DY_DIRECT")) pl.dy_direct = pl.dy_direct && atoi(e) != 0;
   int max_items = (pl.dy_direct && S == 1) ? 56 : 24;  // measured: taller bands pay at stride 1 once dy is out of shared memory
   if (const char* e = std::getenv("DK_B200_FILT_ITEMS")) max_items = atoi(e) > 0 ? atoi(e) : max_items;  // tuning knob
@@ -792,11 +796,13 @@ int local_filter_mma(const __half* dy, const __half* x, const __half* rot, __hal
     kern<<<dim3(pl.blocks_x, pl.groups), pl.warps * 32, pl.smem, s>>>(dy, x, rot, partial, g, pl);  \
   }
   if (g.sH == 1) {
-    if (pl.big) DK_LAUNCH_FILT(1, 6, 448, 1, false)
+    if (pl.big && pl.dy_direct) DK_LAUNCH_FILT(1, 6, 448, 1, true)
+    else if (pl.big) DK_LAUNCH_FILT(1, 6, 448, 1, false)
     else if (pl.dy_direct) DK_LAUNCH_FILT(1, 4, 256, 2, true)
     else DK_LAUNCH_FILT(1, 4, 256, 2, false)
   } else {
-    if (pl.big) DK_LAUNCH_FILT(2, 6, 448, 1, false)
+    if (pl.big && pl.dy_direct) DK_LAUNCH_FILT(2, 6, 448, 1, true)
+    else if (pl.big) DK_LAUNCH_FILT(2, 6, 448, 1, false)
     else if (pl.dy_direct) DK_LAUNCH_FILT(2, 4, 256, 2, true)
     else DK_LAUNCH_FILT(2, 4, 256, 2, false)
   }
