@@ -197,44 +197,100 @@ int pick_warps(int items, int maxw) {
   return bw;
 }
 
+// Share of the GPU's block slots that a grid of ctas blocks keeps busy, bpsm blocks resident per SM.  Up to three waves the
+// last, partly filled one costs a whole wave; with more, blocks of later waves start as earlier ones finish and it costs
+// about half its gap.
+double wave_fill(long long ctas, int bpsm) {
+  const long long slots = 148LL * bpsm;
+  const double exact = (double)ctas / (double)slots;
+  const double whole = (double)((ctas + slots - 1) / slots);
+  return exact / (exact + (whole - exact) * (whole <= 3.0 ? 1.0 : 0.5));
+}
+
+// Shared memory of a forward / grad-input block.
+size_t conv_smem(const Geom& g, bool transposed, int cg, int bh) {
+  const int S = g.sH;
+  const int Ws = transposed ? g.Wo : g.W;
+  const int Wp = Ws + (Ws & 1), Wpo = g.Wo + (g.Wo & 1);
+  const int rb = conv_band_rows(bh, S, transposed);
+  return (size_t)cg * band_pitch(rb, Wp) * 2 + (size_t)18 * band_pitch(transposed ? rb : bh, Wpo) * 2 +
+         (size_t)cg * kBankPitch * 2;
+}
+
+// Channel group, band height and warps per block are chosen together by an estimate of the time per output row.
 ConvPlan conv_plan(const Geom& g, bool transposed) {
   ConvPlan pl;
   const int S = g.sH;
   const int Hd = transposed ? g.H : g.Ho, Wd = transposed ? g.W : g.Wo;
-  const int Ws = transposed ? g.Wo : g.W;
-  const int Wp = Ws + (Ws & 1), Wpo = g.Wo + (g.Wo & 1);
-  int cgmax = 128;
-  if (const char* e = std::getenv("DK_B200_CONV_CG")) cgmax = atoi(e) > 0 ? atoi(e) : cgmax;  // tuning knob
-  const int ngrp = (g.C + cgmax - 1) / cgmax;
-  pl.CG = (((g.C + ngrp - 1) / ngrp) + 15) & ~15;
-  pl.groups = (g.C + pl.CG - 1) / pl.CG;
   const int NB = (Wd + 7) / 8;
+  int cg_only = 0, cap = Hd;
   size_t budget = kTwoPerSm;
-  if (const char* e = std::getenv("DK_B200_CONV_SMEM_KB")) budget = (size_t)atoi(e) * 1024;  // tuning knob
-  int best = 1;
-  for (int bh = 1; bh <= Hd; ++bh) {
-    const int rb = conv_band_rows(bh, S, transposed);
-    const size_t smem = (size_t)pl.CG * band_pitch(rb, Wp) * 2 + (size_t)18 * band_pitch(transposed ? rb : bh, Wpo) * 2 +
-                        (size_t)pl.CG * kBankPitch * 2;
-    if (smem > budget) break;
-    const long long ctas = (long long)((Hd + bh - 1) / bh) * pl.groups * g.N;
-    if (bh > 1 && ctas < 2 * 148) break;
-    best = bh;
-    if (bh * NB >= 32) break;
+  if (const char* e = std::getenv("DK_B200_CONV_CG")) cg_only = atoi(e) > 0 ? atoi(e) : 0;        // tuning knobs
+  if (const char* e = std::getenv("DK_B200_CONV_BH")) cap = atoi(e) > 0 ? atoi(e) : cap;
+  if (const char* e = std::getenv("DK_B200_CONV_SMEM_KB")) budget = (size_t)atoi(e) * 1024;
+  static const int kCgMax[] = {64, 96, 128, 192, 256, 320, 480};
+  double best_cost = 1e30;
+  pl.BH = 0;
+  for (int ci = 0; ci < 7; ++ci) {
+    const int cgmax = cg_only ? cg_only : kCgMax[ci];
+    const int ngrp = (g.C + cgmax - 1) / cgmax;
+    const int cg = (((g.C + ngrp - 1) / ngrp) + 15) & ~15;
+    const int groups = (g.C + cg - 1) / cg;
+    // Estimated time per output, in instructions per item and channel slab; only ratios matter:
+    //   (hat products / slabs + work per slab) / (share of warp slots with an item x occupancy)   -- issue-bound part
+    //   + halves staged per output (rows of the group's channels, the 18 offset planes)            -- not overlapped
+    // over the share of block slots kept busy and the share of the last band's rows that exist.
+    // Constants from timing block shapes on 112 x 112 ... 7 x 7 planes with 96 ... 960 channels: blocks whose item count
+    // is a multiple of their warps at 28 resident warps per SM beat blocks with no idle warp slot but 14 resident warps
+    // by 10 %.
+    const double per_item = 250.0 / (cg / 16) + 220.0;
+    const int Ws = transposed ? g.Wo : g.W;
+    for (int bh = 1; bh <= Hd && bh <= cap; ++bh) {
+      const size_t smem = conv_smem(g, transposed, cg, bh);
+      if (smem > budget) break;
+      const int items = bh * NB;
+      if (items < 14 && bh < Hd && bh < cap) continue;  // a block's fixed costs (launch, bank copy, first load) want 14 items or more
+      const int bands = (Hd + bh - 1) / bh;
+      const long long ctas = (long long)bands * groups * g.N;
+      const int rb = conv_band_rows(bh, S, transposed);
+      const double staged = ((double)cg * rb * Ws + 18.0 * (transposed ? rb : bh) * g.Wo) / ((double)cg * bh * Wd);
+      const double band_fill = (double)Hd / (bands * bh);
+      const int wmax = items < 2 ? 2 : (items < 14 ? items : 14);
+      for (int w = wmax; w >= 2 && w >= wmax / 2; --w) {
+        int bpsm = (int)((228 * 1024) / (smem + 1024));
+        if (bpsm > 28 / w) bpsm = 28 / w;  // 72 registers per thread: 28 warps per SM
+        if (bpsm > 16) bpsm = 16;
+        if (bpsm < 1) continue;
+        const int rounds = (items + w - 1) / w;
+        const double util = (double)items / (rounds * w);
+        const int resident = bpsm * w;
+        const double occ = resident >= 20 ? 1.0 : 0.6 + 0.02 * resident;
+        const double cost = (per_item / (util * occ) + 46.0 * staged) / (wave_fill(ctas, bpsm) * band_fill);
+        if (cost < best_cost) {
+          best_cost = cost;
+          pl.BH = bh;
+          pl.CG = cg;
+          pl.groups = groups;
+          pl.warps = w;
+        }
+      }
+    }
+    if (cg_only) break;
   }
-  pl.BH = best;
+  if (!pl.BH) {  // no block shape fits the budget: the caller falls back to the SIMT kernels
+    pl.CG = pl.groups = pl.warps = pl.bands = 0;
+    pl.smem = 0;
+    return pl;
+  }
   pl.bands = (Hd + pl.BH - 1) / pl.BH;
-  pl.warps = pick_warps(pl.BH * NB, 14);
-  const int rb = conv_band_rows(pl.BH, S, transposed);
-  pl.smem = (size_t)pl.CG * band_pitch(rb, Wp) * 2 + (size_t)18 * band_pitch(transposed ? rb : pl.BH, Wpo) * 2 +
-            (size_t)pl.CG * kBankPitch * 2;
+  pl.smem = conv_smem(g, transposed, pl.CG, pl.BH);
   return pl;
 }
 
 template <int S, bool TRANSPOSED>
 int launch_conv(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, cudaStream_t s) {
   ConvPlan pl = conv_plan(g, TRANSPOSED);
-  if (pl.smem > (size_t)device_smem_optin() || pl.groups > 65535) return DK_ERR_UNSUPPORTED;
+  if (!pl.BH || pl.smem > (size_t)device_smem_optin() || pl.groups > 65535) return DK_ERR_UNSUPPORTED;
   pl.mode_src = ptr_mode(src);
   pl.mode_rot = ptr_mode(rot);
   pl.pair_store = (((TRANSPOSED ? g.W : g.Wo) & 1) == 0) && ptr_mode(dst) >= 1;
@@ -465,22 +521,43 @@ RotPlan rot_plan(const Geom& g) {
     const int attempt = first_attempt ? 1 - k : k;
     const size_t budget = attempt == 0 ? kTwoPerSm : kOnePerSm;
     const int maxw = attempt == 0 ? 8 : 16;
-    int best = 0;
+    int tallest = 0;
     int cap = g.Ho;
     if (const char* e = std::getenv("DK_B200_ROT_BH")) cap = atoi(e) > 0 ? atoi(e) : cap;  // tuning knob
     for (int bh = 1; bh <= g.Ho && bh <= cap; ++bh) {
       if (rot_smem(g, g.C, bh, pick_warps(bh * NB, maxw)) > budget) break;
-      best = bh;
+      tallest = bh;
       if (bh * NB >= 2 * maxw) break;
     }
-    if (!best) continue;
-    const int items = best * NB;
-    const long long ctas = (long long)((g.Ho + best - 1) / best) * g.N;
-    if (items >= 7 && ctas >= min_ctas) {
-      pl.BH = best;
-      pl.warps = pick_warps(items, maxw);
-      pl.big = attempt == 1;
+    if (!tallest) continue;
+    if (tallest * NB < 7 || (long long)((g.Ho + tallest - 1) / tallest) * g.N < min_ctas) continue;
+    // Among the bands up to that height: time of a band = fixed part (latency of its loads, barriers) + rows staged
+    // + rounds of items over the warps; nothing overlaps in a block that has the SM to itself.  Constants fitted to
+    // 28 x 28 ... 112 x 112 planes (band heights 1-14), in instructions per warp.
+    const double t_item = 250.0 + 220.0 * (g.C / 16);
+    const double per_half = 0.0645;
+    double best_cost = 1e30;
+    for (int bh = 1; bh <= tallest; ++bh) {
+      const int items = bh * NB;
+      if (items < 7 && bh < tallest) continue;
+      const int wfull = items < maxw ? items : maxw;
+      const int rounds = (items + wfull - 1) / wfull;
+      int w = (items + rounds - 1) / rounds;  // fewest warps that finish in as many rounds
+      if (w < 2) w = 2;
+      if (rot_smem(g, g.C, bh, w) > budget) continue;
+      const int bands = (g.Ho + bh - 1) / bh;
+      auto band_time = [&](int rows) {
+        const double staged = per_half * ((double)g.C * ((rows - 1) * g.sH + 3) * g.W + (pl.dy_direct ? 18.0 : g.C + 18.0) * rows * g.Wo);
+        return 1000.0 + staged + ((rows * NB + w - 1) / w) * t_item;
+      };
+      const double cost = ((bands - 1) * band_time(bh) + band_time(g.Ho - (bands - 1) * bh)) / g.Ho;
+      if (cost < best_cost) {
+        best_cost = cost;
+        pl.BH = bh;
+        pl.warps = w;
+      }
     }
+    pl.big = attempt == 1;
   }
   if (!pl.BH) {
     const int slabs = g.C / 16;
@@ -672,7 +749,11 @@ FiltPlan filt_plan(const Geom& g) {
   // Two shapes of block: up to four channel slabs and two blocks per SM, or six slabs in one block of up to
   // 14 warps per SM.  The second halves the hat-product work per slab; it pays on wide rows where the first
   // would be stuck with three slabs (measured: C = 96 at 112 x 112).
-  const int cg_small = (g.C % 64 == 0) ? 64 : (g.C % 48 == 0) ? 48 : (g.C % 32 == 0) ? 32 : 16;
+  int cg_small = (g.C % 64 == 0) ? 64 : (g.C % 48 == 0) ? 48 : (g.C % 32 == 0) ? 32 : 16;
+  if (const char* e = std::getenv("DK_B200_FILT_CG")) {  // tuning knob: 16, 32, 48 or 64 channels per block
+    const int v = atoi(e);
+    if ((v == 16 || v == 32 || v == 48 || v == 64) && g.C % v == 0) cg_small = v;
+  }
   const int cg_big = (g.C % 96 == 0) ? 96 : (g.C % 80 == 0) ? 80 : cg_small;
   pl.big = cg_big >= 2 * cg_small && (g.Wo + 7) / 8 >= 14;
   if (const char* e = std::getenv("DK_B200_FILT_BIG")) pl.big = atoi(e) != 0;  // tuning knob
@@ -689,22 +770,31 @@ FiltPlan filt_plan(const Geom& g) {
   if (const char* e = std::getenv("DK_B200_FILT_DY_DIRECT")) pl.dy_direct = pl.dy_direct && atoi(e) != 0;
   int max_items = (pl.dy_direct && S == 1) ? 56 : 24;  // measured: taller bands pay at stride 1 once dy is out of shared memory
   if (const char* e = std::getenv("DK_B200_FILT_ITEMS")) max_items = atoi(e) > 0 ? atoi(e) : max_items;  // tuning knob
+  auto shape = [&](int bh, int* warps) {
+    *warps = pick_warps(bh * NB, pl.big ? 14 : 8);
+    const size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + (pl.dy_direct ? 0 : band_pitch(bh, Wpo))) * 2 +
+                        (size_t)18 * band_pitch(bh, Wpo) * 2;
+    const size_t red = (size_t)*warps * pl.CG * 16 * 4;
+    return smem < red ? red : smem;
+  };
   for (int bh = 1; bh <= g.Ho; ++bh) {
-    const int warps = pick_warps(bh * NB, pl.big ? 14 : 8);
-    size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + (pl.dy_direct ? 0 : band_pitch(bh, Wpo))) * 2 +
-                  (size_t)18 * band_pitch(bh, Wpo) * 2;
-    const size_t red = (size_t)warps * pl.CG * 16 * 4;
-    if (smem < red) smem = red;
-    if (smem > budget) break;
+    int warps;
+    if (shape(bh, &warps) > budget) break;
     pl.BH = bh;
-    pl.warps = warps;
-    pl.smem = smem;
     if (bh * NB >= max_items) break;
   }
   if (!pl.BH) return pl;
   pl.bands = (g.Ho + pl.BH - 1) / pl.BH;
+  pl.BH = (g.Ho + pl.bands - 1) / pl.bands;  // as many bands, all of (nearly) one height
+  pl.smem = shape(pl.BH, &pl.warps);
   const long long units = (long long)g.N * pl.bands;
-  long long want = ((pl.big ? 2LL : 4LL) * 148 + pl.groups - 1) / pl.groups;  // a few blocks per SM over the grid
+  // As many blocks as are resident at once (one wave): the kernel holds 128 registers per thread, so 16 warps per SM.
+  // Measured 8-23 % faster than twice as many blocks on planes of 28 x 28 and smaller.
+  long long per_sm = 16 / pl.warps;
+  if (per_sm > (long long)((228 * 1024) / (pl.smem + 1024))) per_sm = (long long)((228 * 1024) / (pl.smem + 1024));
+  if (per_sm < 1) per_sm = 1;
+  if (const char* e = std::getenv("DK_B200_FILT_BLOCKS_PER_SM")) per_sm = atoi(e) > 0 ? atoi(e) : per_sm;  // tuning knob
+  long long want = per_sm * 148 / pl.groups;
   if (want > units) want = units;
   if (want < 1) want = 1;
   pl.units_per_block = (int)((units + want - 1) / want);
