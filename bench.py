@@ -367,6 +367,29 @@ def run_reference(args, rank):
     print(json.dumps(line))
 
 
+def bind_host_to_gpu(index):
+    """Run this process on the CPUs NVML lists as local to GPU `index`, so that its pinned buffers (placed by first touch)
+    and its copies stay on the GPU's side of the host.  Returns the number of CPUs kept, or None when NVML has no answer."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(index).uuid)
+            h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        except Exception:
+            h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = ((os.cpu_count() or 64) + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * i + b for i, w in enumerate(mask) for b in range(64) if (int(w) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -404,6 +427,8 @@ def main():
 
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    all_cpus = os.sched_getaffinity(0)
+    host_cpus = None if os.environ.get("DK_BENCH_NO_BIND") else bind_host_to_gpu(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -619,6 +644,7 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import dk_oracle as O
+        os.sched_setaffinity(0, all_cpus)  # the CPU baseline gets every host core again
         O.set_threads(os.cpu_count() or 1)
         n_img = 16
         cpu_sweep(1)
@@ -639,7 +665,7 @@ def main():
                              "are evicted between steps" % (tot_bytes / 1e9)},
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "rel_err_vs_resident_step": e2e_check},
+                    "rel_err_vs_resident_step": e2e_check, "host_cpus_local_to_gpu": host_cpus},
             "gpu_launches": args.steps * len(layers) * 5, "clocks": clocks, "per_layer": per_layer,
             "reference_cuda_on_this_gpu": ref_gpu, "other_configs": others,
             "kernel_ms_sum_over_layers": {k: round(v, 4) for k, v in kern_tot.items()},
