@@ -591,13 +591,16 @@ RotPlan rot_plan(const Geom& g) {
 // ------------------------------------------------------------------ grad-bank
 struct FiltPlan {
   bool dy_direct;  // dy goes from global memory straight into registers (each word is used once) instead of through a band
+  bool dy_ring;    // ... or, rows of 8 n pixels: each warp copies its next item's dy (16 bytes per channel row) with cp.async
+                   // into a two-slot ring of its own while it works on the current item
   bool big;  // six channel slabs per block, one block of up to 14 warps per SM
   int BH, CG, groups, warps, bands, units_per_block, blocks_x;
   int mode_x, mode_dy, mode_rot;
   size_t smem, ws_bytes;
 };
 
-template <int S, int NS, int MAXT, int MINB, bool DYD>
+// DYM: 0 = dy band in shared memory, 1 = dy words from global memory into registers, 2 = per-warp ring (see FiltPlan)
+template <int S, int NS, int MAXT, int MINB, int DYM>
 __global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __restrict__ dy, const __half* __restrict__ x,
                                                             const __half* __restrict__ rot, float* __restrict__ partial,
                                                             const Geom g, const FiltPlan pl) {
@@ -614,7 +617,8 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __
 
   __half* xband = reinterpret_cast<__half*>(smem_raw);
   __half* yband = xband + (size_t)pl.CG * xpitch;
-  __half* rband = yband + (DYD ? (size_t)0 : (size_t)pl.CG * ypitch);  // [18][ypitch]
+  __half* rband = yband + (DYM ? (size_t)0 : (size_t)pl.CG * ypitch);  // [18][ypitch]
+  __half* ring = rband + (size_t)18 * ypitch + (size_t)warp * (2 * pl.CG * 8);  // DYM == 2: [2 slots][CG rows][8 pixels]
   const LaneCells lc = lane_cells(g, q);
   const bool sc44 = g.scH == 4 && g.scW == 4;
 
@@ -635,15 +639,31 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __
     const Band br = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_rot);
     __syncthreads();  // previous unit's readers are done
     load_band(xband, bx, x, n, g.C, c0, cnt, g.H, g.W);
-    if (!DYD) load_band(yband, by, dy, n, g.C, c0, cnt, g.Ho, g.Wo);
+    if (!DYM) load_band(yband, by, dy, n, g.C, c0, cnt, g.Ho, g.Wo);
     load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
+    // DYM == 2: 16 bytes of every channel row of item it_ go to ring slot slot_, one row per lane and step
+    auto ring_fill = [&](int it_, int slot_) {
+      const int r_ = it_ / NB;
+      if (it_ < items && oh0 + r_ < g.Ho) {
+        const __half* sp = dy + ((size_t)n * g.C + c0) * g.P + (size_t)(oh0 + r_) * g.Wo + ((it_ - r_ * NB) << 3);
+        __half* dp = ring + slot_ * (pl.CG * 8);
+        for (int c = lane; c < cnt; c += 32) cp_async16(dp + c * 8, sp + (size_t)c * g.P);
+      }
+      cp_async_commit();
+    };
+    if (DYM == 2) ring_fill(warp, 0);
     cp_async_wait_all();
     __syncthreads();
-    for (int item = warp; item < items; item += nwarps) {
+    int slot = 0;
+    for (int item = warp; item < items; item += nwarps, slot ^= 1) {
       const int dr = item / NB;
       const int oh = oh0 + dr;
       if (oh >= g.Ho) break;
       const int ow0 = (item - dr * NB) << 3;
+      if (DYM == 2) {
+        __syncwarp();                        // the item before last has been read out of the other slot
+        ring_fill(item + nwarps, slot ^ 1);  // next item (an empty group when there is none)
+      }
       // dy of the item, fetched ahead of its use: every slab before the hat products (their latency hides behind those), or,
       // with more than four slabs, the first two now and each further one two slabs ahead (fewer registers held)
       constexpr int PRE = NS > 4 ? 2 : NS;
@@ -657,7 +677,7 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __
           dyw[sidx][1] = __ldg(reinterpret_cast<const unsigned*>(dp + (size_t)((sidx << 4) + 8) * g.P));
         }
       };
-      if (DYD) {
+      if (DYM == 1) {
 #pragma unroll
         for (int sidx = 0; sidx < PRE; ++sidx) fetch_dy(sidx);
       }
@@ -675,15 +695,23 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_filter_kernel(const __half* __
       const int ow = ow0 + 2 * q;
       const int xoff = window_offset(bx, oh * S - 1, ow, S);
       const int yoff = kSlack + oh * by.Wp + ow - by.org;
+      const unsigned* rw = reinterpret_cast<const unsigned*>(ring + slot * (pl.CG * 8)) + gq * 4 + q;
+      if (DYM == 2) {
+        cp_async_wait_group<1>();  // everything but the copy of the next item has landed
+        __syncwarp();
+      }
 #pragma unroll
       for (int sidx = 0; sidx < NS; ++sidx) {
         if (sidx < nslab) {
           const int cb16 = sidx << 4;
           unsigned dy0, dy1;
-          if (DYD) {
+          if (DYM == 1) {
             dy0 = dyw[sidx][0];
             dy1 = dyw[sidx][1];
             if (sidx + PRE < NS) fetch_dy(sidx + PRE);
+          } else if (DYM == 2) {
+            dy0 = rw[sidx * 64];       // rows cb16 + gq and cb16 + gq + 8, four words per row
+            dy1 = rw[sidx * 64 + 32];
           } else {
             dy0 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq) * by.pitch_c + yoff);
             dy1 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq + 8) * by.pitch_c + yoff);
@@ -768,12 +796,20 @@ FiltPlan filt_plan(const Geom& g) {
   // of x per output row).  DK_B200_FILT_DY_DIRECT=0 keeps the band (comparison runs).
   pl.dy_direct = (g.Wo & 1) == 0;
   if (const char* e = std::getenv("DK_B200_FILT_DY_DIRECT")) pl.dy_direct = pl.dy_direct && atoi(e) != 0;
-  int max_items = (pl.dy_direct && S == 1) ? 56 : 24;  // measured: taller bands pay at stride 1 once dy is out of shared memory
+  // Six-slab blocks on rows of 8 n pixels (16-byte pieces per item and channel row): their warps waited 2.5 issue slots
+  // per instruction on the register loads of dy (two slabs of lookahead is all the registers allow), so each warp copies
+  // the whole next item into a ring of its own instead: 0.58 -> 0.47 ms on C = 96 at 112 x 112.  The four-slab blocks
+  // fetch all of an item's dy before its hat products and gain nothing (measured 0-7 % slower with the ring).
+  // DK_B200_FILT_DY_RING=0 keeps the register path (comparison runs).
+  pl.dy_ring = pl.big && pl.dy_direct && (g.Wo & 7) == 0 && (g.P & 7) == 0;
+  if (const char* e = std::getenv("DK_B200_FILT_DY_RING")) pl.dy_ring = pl.dy_ring && atoi(e) != 0;
+  // measured: taller bands pay at stride 1 once dy is out of shared memory (five rows of 112 with the ring: 0.468 -> 0.452 ms)
+  int max_items = (pl.dy_direct && S == 1) ? (pl.dy_ring ? 70 : 56) : 24;
   if (const char* e = std::getenv("DK_B200_FILT_ITEMS")) max_items = atoi(e) > 0 ? atoi(e) : max_items;  // tuning knob
   auto shape = [&](int bh, int* warps) {
     *warps = pick_warps(bh * NB, pl.big ? 14 : 8);
     const size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + (pl.dy_direct ? 0 : band_pitch(bh, Wpo))) * 2 +
-                        (size_t)18 * band_pitch(bh, Wpo) * 2;
+                        (size_t)18 * band_pitch(bh, Wpo) * 2 + (pl.dy_ring ? (size_t)*warps * 2 * pl.CG * 16 : 0);
     const size_t red = (size_t)*warps * pl.CG * 16 * 4;
     return smem < red ? red : smem;
   };
@@ -885,17 +921,17 @@ int local_filter_mma(const __half* dy, const __half* x, const __half* rot, __hal
     if ((rc = enable_smem(kern, pl.smem))) return rc;                                               \
     kern<<<dim3(pl.blocks_x, pl.groups), pl.warps * 32, pl.smem, s>>>(dy, x, rot, partial, g, pl);  \
   }
+  const int dym = !pl.dy_direct ? 0 : (pl.dy_ring && pl.mode_dy == 2) ? 2 : 1;
+#define DK_LAUNCH_FILT3(SS, NS, MAXT, MINB)                                \
+  if (dym == 2) DK_LAUNCH_FILT(SS, NS, MAXT, MINB, 2)                      \
+  else if (dym == 1) DK_LAUNCH_FILT(SS, NS, MAXT, MINB, 1)                 \
+  else DK_LAUNCH_FILT(SS, NS, MAXT, MINB, 0)
   if (g.sH == 1) {
-    if (pl.big && pl.dy_direct) DK_LAUNCH_FILT(1, 6, 448, 1, true)
-    else if (pl.big) DK_LAUNCH_FILT(1, 6, 448, 1, false)
-    else if (pl.dy_direct) DK_LAUNCH_FILT(1, 4, 256, 2, true)
-    else DK_LAUNCH_FILT(1, 4, 256, 2, false)
+    if (pl.big) DK_LAUNCH_FILT3(1, 6, 448, 1) else DK_LAUNCH_FILT3(1, 4, 256, 2)
   } else {
-    if (pl.big && pl.dy_direct) DK_LAUNCH_FILT(2, 6, 448, 1, true)
-    else if (pl.big) DK_LAUNCH_FILT(2, 6, 448, 1, false)
-    else if (pl.dy_direct) DK_LAUNCH_FILT(2, 4, 256, 2, true)
-    else DK_LAUNCH_FILT(2, 4, 256, 2, false)
+    if (pl.big) DK_LAUNCH_FILT3(2, 6, 448, 1) else DK_LAUNCH_FILT3(2, 4, 256, 2)
   }
+#undef DK_LAUNCH_FILT3
 #undef DK_LAUNCH_FILT
   if ((rc = check_launch())) return rc;
   const int n_out = g.C * g.cells;
