@@ -106,6 +106,13 @@ const char* dk_status_string(int status) {
 int dk_last_cuda_error(void) { return g_last_cuda_error; }
 const char* dk_version(void) { return "dk_b200 0.1 (sm_100a)"; }
 
+int dk_local_plan_query(const dk_geom* g, int dtype, int pass, long long* out8) {
+  Geom gg;
+  if (!out8 || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+  if (dtype != DK_F16 || !mma_path_enabled()) return DK_ERR_UNSUPPORTED;
+  return local_mma_plan_query(gg, pass, out8);
+}
+
 int dk_output_size(const dk_geom* g, int* out_h, int* out_w) {
   Geom gg;
   if (!make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;

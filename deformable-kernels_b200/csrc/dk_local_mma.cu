@@ -844,6 +844,34 @@ FiltPlan filt_plan(const Geom& g) {
 // ------------------------------------------------------------------ entry points used by dk_local.cu
 // Each returns DK_ERR_UNSUPPORTED when the shape is outside the fast path.
 
+// Block shape the fp16 fast path would launch for `pass` (0 forward, 1 grad-input, 2 grad-offsets, 3 grad-bank), for
+// tools and tests; no GPU is touched.  out = {band height, channels per block, channel groups, warps per block, bands,
+// dynamic shared memory (bytes), blocks in the grid, workspace (bytes)}.
+int local_mma_plan_query(const Geom& g, int pass, long long out[8]) {
+  if (!fast_shape(g)) return DK_ERR_UNSUPPORTED;
+  if (pass == 0 || pass == 1) {
+    const ConvPlan pl = conv_plan(g, pass == 1);
+    if (!pl.BH) return DK_ERR_UNSUPPORTED;
+    const long long v[8] = {pl.BH, pl.CG, pl.groups, pl.warps, pl.bands, (long long)pl.smem, (long long)pl.bands * pl.groups * g.N, 0};
+    for (int i = 0; i < 8; ++i) out[i] = v[i];
+  } else if (pass == 2) {
+    const RotPlan pl = rot_plan(g);
+    if (!pl.BH) return DK_ERR_UNSUPPORTED;
+    const long long v[8] = {pl.BH, pl.CG, pl.groups, pl.warps, pl.bands, (long long)pl.smem, (long long)pl.bands * pl.groups * g.N,
+                            (long long)pl.ws_bytes};
+    for (int i = 0; i < 8; ++i) out[i] = v[i];
+  } else if (pass == 3) {
+    const FiltPlan pl = filt_plan(g);
+    if (!pl.BH) return DK_ERR_UNSUPPORTED;
+    const long long v[8] = {pl.BH, pl.CG, pl.groups, pl.warps, pl.bands, (long long)pl.smem, (long long)pl.blocks_x * pl.groups,
+                            (long long)pl.ws_bytes};
+    for (int i = 0; i < 8; ++i) out[i] = v[i];
+  } else {
+    return DK_ERR_BAD_ARGUMENT;
+  }
+  return DK_OK;
+}
+
 int local_conv_mma(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, bool transposed,
                    cudaStream_t s) {
   if (!fast_shape(g)) return DK_ERR_UNSUPPORTED;

@@ -69,6 +69,7 @@ _PROTOS = {
     "dk_status_string": (ctypes.c_char_p, [_int]),
     "dk_last_cuda_error": (_int, []),
     "dk_version": (ctypes.c_char_p, []),
+    "dk_local_plan_query": (_int, [_gp, _int, _int, ctypes.POINTER(ctypes.c_longlong)]),
 }
 for _name, (_res, _args) in _PROTOS.items():
     _fn = getattr(lib, _name)

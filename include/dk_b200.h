@@ -67,6 +67,12 @@ const char *dk_status_string(int status);
 /* cudaError_t of the most recent DK_ERR_CUDA on the calling thread (0 if none). */
 int dk_last_cuda_error(void);
 const char *dk_version(void);
+
+/* Block shape the fp16 tensor-core kernels of the local deformable kernel would launch for this geometry (no counterpart
+ * in the reference; for tuning tools and tests, touches no GPU).  pass: 0 forward, 1 grad-input, 2 grad-offsets,
+ * 3 grad-bank.  out8 = {band height, channels per block, channel groups, warps per block, bands, dynamic shared memory in
+ * bytes, blocks in the grid, workspace bytes}.  DK_ERR_UNSUPPORTED when the geometry or dtype takes the general kernels. */
+int dk_local_plan_query(const dk_geom *g, int dtype, int pass, long long *out8);
 /* Output extent for a geometry; returns DK_ERR_BAD_ARGUMENT if it is not positive. */
 int dk_output_size(const dk_geom *g, int *out_h, int *out_w);
 

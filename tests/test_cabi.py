@@ -66,6 +66,53 @@ def test_workspace_queries(cabi):
     assert cabi.lib.dk_deform_sample_depthwise_backward_data_workspace_bytes(g, cabi.DK_F16) >= 4 * 64 * 28 * 28 * 4
 
 
+def test_block_shapes_of_the_fp16_fast_path_are_launchable(cabi):
+    """Planner invariants over many geometries (host only): every block shape the tensor-core kernels would launch covers
+    the plane and all channels, fits shared memory and the kernels' launch bounds, and the workspace query covers the
+    partial sums the plan needs."""
+    import random
+    rng = random.Random(7)
+    layers = [(96, 112), (144, 56), (192, 28), (384, 14), (960, 7)]
+    cases = [(128, c, hw, hw, s, (4, 4)) for c, hw in layers for s in (1, 2)]
+    for _ in range(300):
+        cases.append((rng.choice([1, 2, 3, 8, 33, 128, 257]), 16 * rng.randint(1, 64), rng.randint(1, 130), rng.randint(1, 130),
+                      rng.choice([1, 2]), rng.choice([(4, 4), (3, 3), (2, 2), (4, 3), (1, 1), (3, 5)])))
+    out = (ctypes.c_longlong * 8)()
+    max_warps = {0: 14, 1: 14, 2: 16, 3: 14}
+    seen = 0
+    for n, c, h, w, s, scope in cases:
+        g = cabi.geom((n, c, h, w), (3, 3), (s, s), (1, 1), (1, 1), scope, 1)
+        ho, wo = (h + 2 - 3) // s + 1, (w + 2 - 3) // s + 1
+        for p in range(4):
+            rc = cabi.lib.dk_local_plan_query(g, cabi.DK_F16, p, out)
+            assert rc in (0, 2), (n, c, h, w, s, scope, p, rc)
+            if rc:
+                continue
+            seen += 1
+            bh, cg, groups, warps, bands, smem, blocks, ws = list(out)
+            rows = h if p == 1 else ho
+            tag = (n, c, h, w, s, scope, p, list(out))
+            assert 1 <= bh <= rows and bands * bh >= rows and (bands - 1) * bh < rows, tag
+            assert cg % 16 == 0 and cg * groups >= c and cg * (groups - 1) < c, tag
+            assert 1 <= warps <= max_warps[p], tag
+            assert 0 < smem <= 227 * 1024, tag
+            assert 0 < blocks < 2 ** 31 and groups <= 65535, tag
+            if p == 2:
+                assert ws == (groups * n * 18 * ho * wo * 4 if groups > 1 else 0), tag
+                assert cabi.lib.dk_sample_depthwise_backward_rotation_workspace_bytes(g, cabi.DK_F16) >= ws, tag
+            if p == 3:
+                assert ws == blocks // groups * c * 16 * 4, tag
+                assert cabi.lib.dk_sample_depthwise_backward_filter_workspace_bytes(g, cabi.DK_F16) >= ws, tag
+    assert seen > 600
+    # outside the fast path: other dtypes, kernels other than 3x3
+    g = cabi.geom((4, 64, 28, 28), (3, 3), (1, 1), (1, 1), (1, 1), (4, 4), 1)
+    assert cabi.lib.dk_local_plan_query(g, cabi.DK_F32, 0, out) == 2
+    g5 = cabi.geom((4, 64, 28, 28), (5, 5), (1, 1), (2, 2), (1, 1), (4, 4), 1)
+    assert cabi.lib.dk_local_plan_query(g5, cabi.DK_F16, 0, out) == 2
+    assert cabi.lib.dk_local_plan_query(g, cabi.DK_F16, 9, out) == 1
+    assert cabi.lib.dk_local_plan_query(g, cabi.DK_F16, 0, None) == 1
+
+
 def test_cpu_tensors_raise_like_the_reference():
     import torch
     from deformable_kernels.ops.deform_kernel.functions import sample_depthwise, nd_linear_sample
