@@ -3,6 +3,7 @@ concatenate to the full-batch result, and the all-reduced partial bank gradients
 full-batch bank gradient.  The operator itself is played by the CPU oracle (the product has no
 CPU path); what is under test is the host-side sharding and reduction logic."""
 import os
+import socket
 
 import torch
 import torch.distributed as dist
@@ -47,11 +48,13 @@ def test_two_rank_sharding_reproduces_the_full_batch():
     from oracle import dk_oracle as O
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29600 + os.getpid() % 300
+    with socket.socket() as sock:  # a port that is free now, rather than one derived from the pid
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    y, dx, do, dr, dw = q.get(timeout=120)
+    y, dx, do, dr, dw = q.get(timeout=600)  # the children's first `import torch` can take a minute on a cold page cache
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
