@@ -214,34 +214,52 @@ __device__ __forceinline__ void load_band_group(__half* __restrict__ band, const
     for (int v = lane + 32; v < tail; v += 32) zt[v] = 0u;
   }
 }
-// The same copy in 16-byte mode with the (channel, 16-byte piece) pairs spread evenly over the nt threads and advanced
+// The same copy (16- or 4-byte pieces) with the (channel, piece) pairs spread evenly over the nt threads and advanced
 // incrementally: a handful of instructions per piece and every lane busy, where the one-warp-per-channel loops above leave
 // lanes idle on the last pass over a row and pay their set-up per channel.  The loader's instructions are what the "load
 // phase" of the kernels costs (they are bound by instruction issue), so this matters more than the copy's latency.
-// Other modes, and bands without a row inside the image, go through load_band_group.
+// Odd row widths, and bands without a row inside the image, go through load_band_group.
 __device__ __forceinline__ void load_band_flat(__half* __restrict__ band, const Band& b, const __half* __restrict__ src, int n,
                                                int C, int c0, int cnt, int Hs, int Ws, int tid, int nt, int bar_id) {
   const int r_s = max(b.row_lo, 0), r_e = min(b.row_lo + b.RB, Hs);
-  if (b.mode != 2 || r_e <= r_s) {
+  if (b.mode == 0 || r_e <= r_s) {
     load_band_group(band, b, src, n, C, c0, cnt, Hs, Ws, tid, nt, bar_id);
     return;
   }
   const size_t plane = (size_t)Hs * Ws;
-  const int gs = (r_s * Ws) & ~7;
-  const int ge = min((r_e * Ws + 7) & ~7, (int)plane);
-  const int lo = kSlack + (gs - b.org), hi = lo + (ge - gs);
-  const int npiece = (hi - lo) >> 3;
+  // contiguous span [lo, hi) of each channel band that receives data, as in load_band_group
+  int gs, lo, hi;
+  if (b.mode == 2) {
+    gs = (r_s * Ws) & ~7;
+    const int ge = min((r_e * Ws + 7) & ~7, (int)plane);
+    lo = kSlack + (gs - b.org);
+    hi = lo + (ge - gs);
+  } else {
+    gs = r_s * Ws;
+    lo = kSlack + (r_s * b.Wp - b.org);
+    hi = lo + (r_e - r_s) * Ws;
+  }
+  const int esz = b.mode == 2 ? 8 : 2;  // halves per copy
+  const int npiece = (hi - lo) / esz;
   {
     const int dc = nt / npiece, dv = nt - dc * npiece;
     int c = tid / npiece, v = tid - c * npiece;
-    const __half* sp = src + ((size_t)n * C + c0 + c) * plane + gs + v * 8;
-    __half* dp = band + (size_t)c * b.pitch_c + lo + v * 8;
-    const size_t s_step = (size_t)dc * plane + dv * 8, s_wrap = plane - (size_t)npiece * 8;
-    const int d_step = dc * b.pitch_c + dv * 8, d_wrap = b.pitch_c - npiece * 8;
-    while (c < cnt) {
-      cp_async16(dp, sp);
-      c += dc; v += dv; sp += s_step; dp += d_step;
-      if (v >= npiece) { v -= npiece; ++c; sp += s_wrap; dp += d_wrap; }
+    const __half* sp = src + ((size_t)n * C + c0 + c) * plane + gs + v * esz;
+    __half* dp = band + (size_t)c * b.pitch_c + lo + v * esz;
+    const size_t s_step = (size_t)dc * plane + dv * esz, s_wrap = plane - (size_t)npiece * esz;
+    const int d_step = dc * b.pitch_c + dv * esz, d_wrap = b.pitch_c - npiece * esz;
+    if (b.mode == 2) {
+      while (c < cnt) {
+        cp_async16(dp, sp);
+        c += dc; v += dv; sp += s_step; dp += d_step;
+        if (v >= npiece) { v -= npiece; ++c; sp += s_wrap; dp += d_wrap; }
+      }
+    } else {
+      while (c < cnt) {
+        cp_async4(dp, sp);
+        c += dc; v += dv; sp += s_step; dp += d_step;
+        if (v >= npiece) { v -= npiece; ++c; sp += s_wrap; dp += d_wrap; }
+      }
     }
   }
   // zero what the copies leave out: the words in front of lo and behind hi of every channel
