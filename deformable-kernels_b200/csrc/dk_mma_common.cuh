@@ -214,6 +214,25 @@ __device__ __forceinline__ void load_band_group(__half* __restrict__ band, const
     for (int v = lane + 32; v < tail; v += 32) zt[v] = 0u;
   }
 }
+// Copies of ESZ halves each (8: cp.async 16 bytes, 2: 4 bytes) for the span [lo, hi) of cnt channel bands: thread tid of nt takes
+// the (channel, piece) pairs tid, tid + nt, ... in channel-major order and steps both pointers incrementally.
+template <int ESZ>
+__device__ __forceinline__ void flat_copies(__half* __restrict__ band, int pitch_c, int lo, int hi, const __half* __restrict__ s0,
+                                            size_t plane, int cnt, int tid, int nt) {
+  const int npiece = (hi - lo) / ESZ;
+  const int dc = nt / npiece, dv = nt - dc * npiece;
+  int c = tid / npiece, v = tid - c * npiece;
+  const __half* sp = s0 + (size_t)c * plane + v * ESZ;
+  __half* dp = band + (size_t)c * pitch_c + lo + v * ESZ;
+  const size_t s_step = (size_t)dc * plane + dv * ESZ, s_wrap = plane - (size_t)npiece * ESZ;
+  const int d_step = dc * pitch_c + dv * ESZ, d_wrap = pitch_c - npiece * ESZ;
+  while (c < cnt) {
+    if (ESZ == 8) cp_async16(dp, sp);
+    else cp_async4(dp, sp);
+    c += dc; v += dv; sp += s_step; dp += d_step;
+    if (v >= npiece) { v -= npiece; ++c; sp += s_wrap; dp += d_wrap; }
+  }
+}
 // The same copy (16- or 4-byte pieces) with the (channel, piece) pairs spread evenly over the nt threads and advanced
 // incrementally: a handful of instructions per piece and every lane busy, where the one-warp-per-channel loops above leave
 // lanes idle on the last pass over a row and pay their set-up per channel.  The loader's instructions are what the "load
@@ -239,29 +258,8 @@ __device__ __forceinline__ void load_band_flat(__half* __restrict__ band, const 
     lo = kSlack + (r_s * b.Wp - b.org);
     hi = lo + (r_e - r_s) * Ws;
   }
-  const int esz = b.mode == 2 ? 8 : 2;  // halves per copy
-  const int npiece = (hi - lo) / esz;
-  {
-    const int dc = nt / npiece, dv = nt - dc * npiece;
-    int c = tid / npiece, v = tid - c * npiece;
-    const __half* sp = src + ((size_t)n * C + c0 + c) * plane + gs + v * esz;
-    __half* dp = band + (size_t)c * b.pitch_c + lo + v * esz;
-    const size_t s_step = (size_t)dc * plane + dv * esz, s_wrap = plane - (size_t)npiece * esz;
-    const int d_step = dc * b.pitch_c + dv * esz, d_wrap = b.pitch_c - npiece * esz;
-    if (b.mode == 2) {
-      while (c < cnt) {
-        cp_async16(dp, sp);
-        c += dc; v += dv; sp += s_step; dp += d_step;
-        if (v >= npiece) { v -= npiece; ++c; sp += s_wrap; dp += d_wrap; }
-      }
-    } else {
-      while (c < cnt) {
-        cp_async4(dp, sp);
-        c += dc; v += dv; sp += s_step; dp += d_step;
-        if (v >= npiece) { v -= npiece; ++c; sp += s_wrap; dp += d_wrap; }
-      }
-    }
-  }
+  if (b.mode == 2) flat_copies<8>(band, b.pitch_c, lo, hi, src + ((size_t)n * C + c0) * plane + gs, plane, cnt, tid, nt);
+  else flat_copies<2>(band, b.pitch_c, lo, hi, src + ((size_t)n * C + c0) * plane + gs, plane, cnt, tid, nt);
   // zero what the copies leave out: the words in front of lo and behind hi of every channel
   const int head = lo >> 1, tail = (b.pitch_c - hi) >> 1, nz = head + tail;
   if (nz > 0) {
