@@ -61,7 +61,7 @@ def kernel_bytes(name, n, c, hw, s, e=2):
 # DRAM bytes (read + write) per launch of each fast-path kernel on the largest layer, from one ncu capture at batch 64
 # (dram__bytes_read.sum + dram__bytes_write.sum, profiles/local_dk_mma_kernels_C96_112x112_batch64.md); traffic grows in
 # proportion to the batch, so it is scaled by batch / 64.
-NCU_TRAFFIC_BATCH64 = {"forward": 298.2e6, "backward_data": 296.5e6, "backward_rotation": 363.9e6, "backward_filter": 349.1e6}
+NCU_TRAFFIC_BATCH64 = {"forward": 293.5e6, "backward_data": 293.8e6, "backward_rotation": 363.0e6, "backward_filter": 352.0e6}
 
 
 def measured_peak():
