@@ -15,7 +15,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libdk_b200.so")
-SOURCES = ["dk_api.cu", "dk_local.cu", "dk_local_mma.cu", "dk_deform.cu", "dk_deform_mma.cu", "dk_nd.cu", "dk_scale.cu", "dk_global.cu", "dk_static_scratch.cu"]
+SOURCES = ["dk_api.cu", "dk_local.cu", "dk_local_mma.cu", "dk_local_ring.cu", "dk_deform.cu", "dk_deform_mma.cu", "dk_nd.cu", "dk_scale.cu", "dk_global.cu", "dk_static_scratch.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
@@ -36,7 +36,7 @@ def _deps():
     return out
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, defines=()):
     os.makedirs(LIB_DIR, exist_ok=True)
     obj_dir = os.path.join(HERE, "build")
     os.makedirs(obj_dir, exist_ok=True)
@@ -47,7 +47,7 @@ def build(force=False, verbose=False):
     for src in SOURCES:
         obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
         objs.append(obj)
-        cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [_nvcc()] + NVCC_FLAGS + list(defines) + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
         procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for cmd, p in procs:
         out, _ = p.communicate()
@@ -60,4 +60,5 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    # -DNAME arguments are passed to nvcc (e.g. -DDK_TUNING enables the experiment knobs read from the environment)
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, defines=[a for a in sys.argv[1:] if a.startswith("-D")]))

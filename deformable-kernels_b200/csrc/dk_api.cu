@@ -113,6 +113,8 @@ int dk_local_plan_query(const dk_geom* g, int dtype, int pass, long long* out8) 
   return local_mma_plan_query(gg, pass, out8);
 }
 
+int dk_ring_error_status(void) { return ring_error_status(); }
+
 int dk_output_size(const dk_geom* g, int* out_h, int* out_w) {
   Geom gg;
   if (!make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
@@ -176,7 +178,13 @@ int dk_sample_depthwise_backward_rotation(const void* grad_output, const void* i
 size_t dk_sample_depthwise_backward_workspace_bytes(const dk_geom* g, int dtype) {
   const size_t a = dk_sample_depthwise_backward_filter_workspace_bytes(g, dtype);
   const size_t b = dk_sample_depthwise_backward_rotation_workspace_bytes(g, dtype);
-  return a > b ? a : b;  // the two passes run one after the other on the stream and share the buffer
+  size_t need = a > b ? a : b;  // the passes run one after the other on the stream and share the buffer
+  Geom gg;
+  if (dtype == DK_F16 && make_geom(g, &gg)) {
+    const size_t c = align256(local_gw_ring_workspace(gg));
+    if (c > need) need = c;
+  }
+  return need;
 }
 
 int dk_sample_depthwise_backward(const void* grad_output, const void* input, const void* rotation, const void* filter,
@@ -187,6 +195,14 @@ int dk_sample_depthwise_backward(const void* grad_output, const void* input, con
   if (grad_input) {
     rc = dk_sample_depthwise_backward_data(grad_output, rotation, filter, grad_input, g, dtype, stream);
     if (rc) return rc;
+  }
+  if (grad_rotation && grad_filter && dtype == DK_F16 && mma_path_enabled()) {
+    // both remaining gradients consume the products dy * x: one pass over dy, x and the offsets where the shape allows
+    Geom gg;
+    if (!grad_output || !input || !rotation || !filter || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+    rc = local_gw_ring(P_(__half, grad_output), P_(__half, input), P_(__half, rotation), P_(__half, filter),
+                       M_(__half, grad_rotation), M_(__half, grad_filter), gg, workspace, workspace_bytes, (cudaStream_t)stream);
+    if (rc != DK_ERR_UNSUPPORTED) return rc;
   }
   if (grad_rotation) {
     rc = dk_sample_depthwise_backward_rotation(grad_output, input, rotation, filter, grad_rotation, g, dtype, workspace,

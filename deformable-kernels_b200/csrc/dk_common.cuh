@@ -173,6 +173,13 @@ int deform_backward_filter(const T* dy, const T* x, const T* off, const T* rot, 
 bool mma_path_enabled();
 int local_conv_mma(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, bool transposed,
                    cudaStream_t s);
+// row-ring kernels (dk_local_ring.cu): TMA-fed producer / consumer blocks; DK_ERR_UNSUPPORTED = shape outside them
+int local_conv_ring(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, bool transposed,
+                    cudaStream_t s);
+size_t local_gw_ring_workspace(const Geom& g);
+int local_gw_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
+                  void* ws, size_t ws_bytes, cudaStream_t s);  // grad-offsets and grad-bank in one pass (either may be null)
+int ring_error_status();
 size_t local_rot_mma_workspace(const Geom& g);
 int local_rot_mma(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, const Geom& g,
                   void* ws, size_t ws_bytes, cudaStream_t s);

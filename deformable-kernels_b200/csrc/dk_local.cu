@@ -118,7 +118,9 @@ static int launch_local_conv(const T* src, const T* rot, const T* w, T* dst, con
   using A = typename Compute<T>::type;
   if constexpr (std::is_same<T, __half>::value) {
     if (mma_path_enabled()) {
-      const int rc = local_conv_mma(src, rot, w, dst, g, TRANSPOSED, s);
+      int rc = local_conv_ring(src, rot, w, dst, g, TRANSPOSED, s);
+      if (rc != DK_ERR_UNSUPPORTED) return rc;
+      rc = local_conv_mma(src, rot, w, dst, g, TRANSPOSED, s);
       if (rc != DK_ERR_UNSUPPORTED) return rc;
     }
   }

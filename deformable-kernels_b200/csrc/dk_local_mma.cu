@@ -841,6 +841,13 @@ FiltPlan filt_plan(const Geom& g) {
 
 }  // namespace
 
+// out[c][cell] = sum over blocks of partial[block][c][16]: the second stage of every tensor-core bank gradient
+int launch_reduce_bank_partials(const float* partial, __half* out, int C, int cells, int nblocks, cudaStream_t s) {
+  const int n_out = C * cells;
+  reduce_bank_partials_kernel<<<(n_out + 7) / 8, 256, 0, s>>>(partial, out, C, cells, nblocks);
+  return check_launch();
+}
+
 // ------------------------------------------------------------------ entry points used by dk_local.cu
 // Each returns DK_ERR_UNSUPPORTED when the shape is outside the fast path.
 

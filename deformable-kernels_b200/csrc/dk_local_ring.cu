@@ -1,0 +1,935 @@
+// Row-ring kernels of the local deformable kernel (fp16 storage, fp32 accumulation) for sm_100a.
+//
+// Same mathematics as dk_local_mma.cu -- the bilinear resampling of the bank is the contraction
+//   K[c, p, tap] = sum_cell W[c, cell] * beta[p, tap, cell],   beta = hat(u - a) * hat(v - b)
+// on mma.sync.m16n8k16, followed by y[c, p] += x[c, p + tap] * K[c, p, tap] on the CUDA cores --
+// but a different way of moving the data.  A block walks down a contiguous range of output rows
+// of ALL its channels.  A producer warp streams the source rows through rings of shared-memory
+// slots, one tiled TMA copy (cp.async.bulk.tensor) per row whose out-of-range elements the
+// hardware fills with zeros: that supplies the convolution padding, so no tap needs a mask.  The
+// consumer warps wait on a slot's mbarrier, never on each other: filling and computing overlap,
+// each source row crosses HBM once and shared memory once, and all pitches are compile-time
+// constants.  K comes out of the tensor cores in fp32 and x is widened to fp32 before the FMA, so
+// every product and every sum of the forward and grad-input passes is fp32.
+//
+// Kernels:
+//   ring_conv_kernel   forward, and grad-input at stride 1 (the same stencil with the taps flipped)
+//   ring_gw_kernel     grad-offsets and grad-bank in ONE pass: both consume dK = dy * x,
+//                        G^T[16 cells x 8 px] += W^T * dK   -> four-corner derivative contraction -> d(offsets)
+//                        dW[16 ch x 16 cells] += dK * beta  -> per-block partial sums, reduced in a fixed order
+//
+// Covers what dk_local_mma.cu covers (fp16, 3x3, pad 1, dilation 1, stride 1 or 2, one offset
+// group, <= 16 bank cells, channels a multiple of 16) on input rows of 112 or 56 elements (TMA
+// needs 16-byte row pitches); other shapes stay on dk_local_mma.cu.
+#include <cstdlib>
+
+#include "dk_ring.cuh"
+
+namespace dk {
+
+using namespace mma;
+using namespace ring;
+
+// out[c][cell] = sum over blocks of partial[block][c][16] (dk_local_mma.cu)
+int launch_reduce_bank_partials(const float* partial, __half* out, int C, int cells, int nblocks, cudaStream_t s);
+
+namespace {
+
+constexpr int kErrTimeout = 1;
+
+// Zero-initialised by the loader; set when a bounded wait ran out (see dk_ring.cuh).
+__device__ int g_ring_error;
+
+struct RingParams {
+  int N, C;
+  int Hs, Hd;      // rows of the source and of the destination plane
+  int CG;          // channels per block (multiple of 16)
+  int lgR, lgRR;   // log2 of the slots in the source ring and in the per-destination-row rings
+  int L;           // padded source rows per sample in the block's stream
+  int rows_total;  // N * Hd
+  int rows_per_block;
+  int scH, scW, cells;
+};
+
+__device__ __forceinline__ LaneCells lane_cells_of(int scW, int cells, int q) {
+  LaneCells lc;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int cell = 2 * q + (k & 1) + (k >> 1) * 8;
+    lc.ok[k] = cell < cells;
+    const int a = cell / scW;
+    lc.ca[k] = (float)a;
+    lc.cb[k] = (float)(cell - a * scW);
+  }
+  return lc;
+}
+
+__device__ __forceinline__ float h_lo(unsigned w) { return __low2float(*reinterpret_cast<const __half2*>(&w)); }
+__device__ __forceinline__ float h_hi(unsigned w) { return __high2float(*reinterpret_cast<const __half2*>(&w)); }
+
+// Hat products of pixel column gq of an item for one tap, as the B fragment of K = W * beta^T:
+// b0 = cells (2q, 2q+1), b1 = cells (2q+8, 2q+9).  rp points at the tap's vertical offset of the
+// pixel in a ring slot; the horizontal one lies WOP halves further.  (u, v) are returned.
+template <int WOP>
+__device__ __forceinline__ void beta_tap(unsigned (&b)[2], const __half* __restrict__ rp, float fh, float fw, const LaneCells& lc,
+                                         bool sc44, float uh0, float uw0, float& u, float& v) {
+  // same association as the reference: (tap index + offset) + (scope - kernel) / 2
+  u = (fh + __half2float(rp[0])) + uh0;
+  v = (fw + __half2float(rp[WOP])) + uw0;
+  if (sc44) {
+    const float hh0 = hat(u - lc.ca[0]), hh1 = hat(u - lc.ca[2]);
+    const float hw0 = hat(v - lc.cb[0]), hw1 = hat(v - lc.cb[1]);
+    b[0] = pack2(hh0 * hw0, hh0 * hw1);
+    b[1] = pack2(hh1 * hw0, hh1 * hw1);
+  } else {
+    float b4[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) b4[k] = lc.ok[k] ? hat(u - lc.ca[k]) * hat(v - lc.cb[k]) : 0.f;
+    b[0] = pack2(b4[0], b4[1]);
+    b[1] = pack2(b4[2], b4[3]);
+  }
+}
+
+// Offset rows in a slot: 18 planes of WOP halves, 8 zero halves in front of each.
+template <int Wr>
+struct RotLayout {
+  static constexpr int kWop = 8 + ((Wr + 7) / 8) * 8 + 8;
+  static constexpr int kSlot = 18 * kWop;  // halves
+  static constexpr int kPiece = (Wr % 8 == 0) ? 16 : ((Wr % 4 == 0) ? 8 : 4);
+  static constexpr int kPieces = Wr * 2 / kPiece;
+  static_assert(Wr % 2 == 0, "offset rows are copied in pieces of 4 bytes or more");
+};
+
+template <int PIECE>
+__device__ __forceinline__ void cp_piece(void* d, const void* s) {
+  if (PIECE == 16) cp_async16(d, s);
+  else if (PIECE == 8) cp_async8(d, s);
+  else cp_async4(d, s);
+}
+
+// producer warp: row `row` of the 18 offset planes of sample n -> ring slot; the slot's "full" barrier (count 32)
+// gets one arrival per lane when that lane's copies have landed
+template <int Wr>
+__device__ __forceinline__ void fill_rot_row(__half* slot, const __half* __restrict__ rot, int n, int rows, int row, int lane,
+                                             unsigned full_bar) {
+  using RL = RotLayout<Wr>;
+  const size_t plane = (size_t)rows * Wr;
+  const __half* sp = rot + (size_t)n * 18 * plane + (size_t)row * Wr;
+  for (int i = lane; i < 18 * RL::kPieces; i += 32) {
+    const int pl = i / RL::kPieces, pc = i - pl * RL::kPieces;
+    cp_piece<RL::kPiece>(slot + pl * RL::kWop + 8 + pc * (RL::kPiece / 2), sp + pl * plane + pc * (RL::kPiece / 2));
+  }
+  cp_async_arrive_noinc(full_bar);
+}
+
+// producer warp: row `row` of channels c0 .. c0+cg-1 of sample n of a [N][C][rows][Wd] tensor -> ring slot with cp.async
+// (for rows TMA cannot fetch); full barrier count 32 as above
+template <int Wd>
+__device__ __forceinline__ void fill_plane_row(__half* slot, const __half* __restrict__ src, int n, int C, int c0, int cg, int rows,
+                                               int row, int lane, unsigned full_bar) {
+  using L = RowLayout<Wd>;
+  constexpr int PB = L::kPiece ? L::kPiece : 4;
+  constexpr int PIECES = Wd * 2 / PB;
+  const size_t plane = (size_t)rows * Wd;
+  const __half* sp = src + ((size_t)n * C + c0) * plane + (size_t)row * Wd;
+  for (int i = lane; i < cg * PIECES; i += 32) {
+    const int ch = i / PIECES, pc = i - ch * PIECES;
+    cp_piece<PB>(slot + ch * L::kInner + 8 + pc * (PB / 2), sp + ch * plane + pc * (PB / 2));
+  }
+  cp_async_arrive_noinc(full_bar);
+}
+
+// d = a * b, fp32 result, without `volatile` so that the compiler may schedule it freely
+__device__ __forceinline__ void mma_new(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ void ring_fail(int lane) {
+  if (lane == 0) atomicExch(&g_ring_error, kErrTimeout);
+}
+
+// Arrivals of one finished item on the three source-row fills k0 .. k0+2 it read.  A stream row is read by
+// U = 3 (stride 1) or 2 (stride 2) destination rows; where a neighbour that would read it lies outside the
+// sample or outside this block's range, the first / last row of the range arrives in its place, so that every
+// fill of a slot collects exactly U * (items per row) arrivals and is only then overwritten.
+template <int S>
+__device__ __forceinline__ int release_count(int j, bool first, bool last) {
+  if (S == 1) return 1 + (first ? 2 - j : 0) + (last ? j : 0);
+  return (j == 1) ? 2 : 1 + (((j == 0 && first) || (j == 2 && last)) ? 1 : 0);
+}
+
+// ================================================================== forward (TR = false) and grad-input at stride 1 (TR = true)
+//
+// Destination pixel (d, ow) of channel c:  sum over taps of src[c, d*S - 1 + fh, ow*S - 1 + fw] * K[c, (d, ow), tap]   (forward)
+//                                          sum over taps of src[c, d + 1 - fh, ow + 1 - fw] * K[c, (d+1-fh, ow+1-fw), tap]  (TR)
+// The block's source rows form one stream: sample after sample, per sample the L rows
+// -1 .. (Hd-1)*S + 1 (rows outside the plane arrive as zeros).  Stream row T is fill T - T0 of the source ring.
+template <int S, int W, bool TR>
+struct ConvShape {
+  static constexpr int kWd = TR ? W : (W - 1) / S + 1;  // destination width
+  static constexpr int kWr = TR ? W : kWd;              // width of the offset planes
+  static constexpr int kNB = (kWd + 7) / 8;             // items (8 destination pixels) per row
+  static constexpr int kInner = RowLayout<W>::kInner;
+  static_assert(RowLayout<W>::kTma, "source rows of this kernel come by TMA");
+};
+
+__host__ __device__ inline size_t conv_ring_smem(int cg, int inner, int rot_slot, int R, int RR) {
+  return (size_t)R * cg * inner * 2 + 32 + (size_t)RR * rot_slot * 2 + (size_t)cg * kBankPitch * 2 + (size_t)(2 * R + 2 * RR) * 8 +
+         16 + 128;
+}
+
+template <int S, int W, bool TR, int MAXT>
+__global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constant__ CUtensorMap tm_src, const __half* __restrict__ rot,
+                                                            const __half* __restrict__ bankw, __half* __restrict__ dst,
+                                                            const RingParams p) {
+  using Sh = ConvShape<S, W, TR>;
+  using RL = RotLayout<Sh::kWr>;
+  constexpr int INNER = Sh::kInner, WOP = RL::kWop, NB = Sh::kNB, Wd = Sh::kWd;
+  static_assert(!TR || S == 1, "the transposed form of this kernel is the stride-1 one");
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int R = 1 << p.lgR, RR = 1 << p.lgRR;
+  const int CG = p.CG;
+  const int c0 = blockIdx.y * CG;
+  const int slot_halves = CG * INNER;
+
+  __half* xring = reinterpret_cast<__half*>(smem_raw);
+  __half* rring = xring + (size_t)R * slot_halves + 16;
+  __half* bank = rring + (size_t)RR * RL::kSlot;
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(
+      (reinterpret_cast<uintptr_t>(bank + (size_t)CG * kBankPitch) + 7) & ~(uintptr_t)7);
+  Ring rx, rr;
+  rx.full = smem_u32(bars); rx.empty = rx.full + 8 * R; rx.lg = p.lgR;
+  rr.full = rx.empty + 8 * R; rr.empty = rr.full + 8 * RR; rr.lg = p.lgRR;
+  rx.issued = rr.empty + 8 * RR; rr.issued = rx.issued + 4;
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ncw = (blockDim.x >> 5) - 1;
+
+  // ---- set-up: barriers, zeroed rings (pads and the tail must read as zero from the start), bank copy
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < R; ++i) {
+      mbar_init(rx.full + 8 * i, 1);
+      mbar_init(rx.empty + 8 * i, (S == 1 ? 3 : 2) * NB);
+    }
+    for (int i = 0; i < RR; ++i) {
+      mbar_init(rr.full + 8 * i, 32);
+      mbar_init(rr.empty + 8 * i, (TR ? 3 : 1) * NB);
+    }
+    int* cnt = reinterpret_cast<int*>(bars + 2 * R + 2 * RR);
+    cnt[0] = cnt[1] = 0;
+    fence_barrier_init();
+  }
+  {
+    uint4* z = reinterpret_cast<uint4*>(smem_raw);
+    const int nz = (int)((reinterpret_cast<unsigned char*>(bank) - smem_raw) >> 4);
+    for (int i = threadIdx.x; i < nz; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
+  }
+  for (int i = threadIdx.x; i < CG * 16; i += blockDim.x) {
+    const int j = i >> 4, cell = i & 15;
+    bank[j * kBankPitch + cell] = cell < p.cells ? __ldg(bankw + (size_t)(c0 + j) * p.cells + cell) : __float2half(0.f);
+  }
+  fence_proxy_async();
+  __syncthreads();
+
+  const int g0 = blockIdx.x * p.rows_per_block;
+  const int g1 = min(g0 + p.rows_per_block, p.rows_total);
+  if (g0 >= g1) return;
+  const int Hd = p.Hd, L = p.L;
+  const int n_first = g0 / Hd;
+  const int T0 = n_first * L + (g0 - n_first * Hd) * S;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) prefetch_tensormap(&tm_src);
+    const unsigned slot_bytes = (unsigned)slot_halves * 2;
+    const unsigned xring_u32 = smem_u32(xring);
+    int T = T0;
+    bool ok = true;
+    for (int g = g0; g < g1 && ok; ++g) {
+      const int n = g / Hd, d = g - n * Hd;
+      if (!TR) {
+        const int kr = g - g0;
+        ok = rr.reclaim(kr, lane);
+        if (ok) fill_rot_row<Sh::kWr>(rring + (size_t)rr.slot(kr) * RL::kSlot, rot, n, Hd, d, lane, rr.full + 8 * rr.slot(kr));
+      }
+      const int Tend = n * L + d * S + 2;
+      for (; T <= Tend && ok; ++T) {
+        const int k = T - T0;
+        const int r = T - n * L - 1;  // source row; -1 and >= Hs arrive as zero rows
+        if (TR) {
+          ok = rr.reclaim(k, lane);
+          if (ok)
+            fill_rot_row<Sh::kWr>(rring + (size_t)rr.slot(k) * RL::kSlot, rot, n, p.Hs, min(max(r, 0), p.Hs - 1), lane,
+                                  rr.full + 8 * rr.slot(k));
+        }
+        ok = ok && rx.reclaim(k, lane);
+        if (lane == 0 && ok) {
+          mbar_arrive_expect_tx(rx.full + 8 * rx.slot(k), slot_bytes);
+          tma_load_3d(xring_u32 + rx.slot(k) * slot_bytes, &tm_src, -8, r, n * p.C + c0, rx.full + 8 * rx.slot(k));
+        }
+        __syncwarp();
+      }
+    }
+    cp_async_wait_all();
+    if (!ok) ring_fail(lane);
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int cw = warp - 1;
+  const int gq = lane >> 2, q = lane & 3;
+  const LaneCells lc = lane_cells_of(p.scW, p.cells, q);
+  const bool sc44 = p.scH == 4 && p.scW == 4;
+  const float uh0 = (float)(p.scH - 3) * 0.5f, uw0 = (float)(p.scW - 3) * 0.5f;
+  const int nslab = CG >> 4;
+  const size_t dplane = (size_t)Hd * Wd;
+  const int items = (g1 - g0) * NB;
+
+  for (int it = cw; it < items; it += ncw) {
+    const int grow = it / NB, cb = it - grow * NB;
+    const int g = g0 + grow;
+    const int n = g / Hd, d = g - n * Hd;
+    const int k0 = n * L + d * S - T0;
+    const int ow0 = cb << 3;
+    const int pg = ow0 + gq;
+    bool ok = true;
+    float u, v;
+
+    // hat products of the item's 72 (pixel, tap) pairs
+    unsigned bf[9][2];
+    if (!TR) {
+      ok = rr.wait_full(grow);
+      const __half* rp = rring + (size_t)rr.slot(grow) * RL::kSlot + 8 + pg;
+#pragma unroll
+      for (int t = 0; t < 9; ++t) beta_tap<WOP>(bf[t], rp + 2 * t * WOP, (float)(t / 3), (float)(t % 3), lc, sc44, uh0, uw0, u, v);
+    } else {
+      ok = rr.wait_full(k0 + 2);
+#pragma unroll
+      for (int fh = 0; fh < 3; ++fh) {
+        const int k = k0 + 2 - fh;  // offsets of destination row d + 1 - fh
+        if (fh) ok = rr.wait_full(k) && ok;
+        const __half* rp = rring + (size_t)rr.slot(k) * RL::kSlot + 8 + pg + 1;
+#pragma unroll
+        for (int fw = 0; fw < 3; ++fw)
+          beta_tap<WOP>(bf[fh * 3 + fw], rp + 2 * (fh * 3 + fw) * WOP - fw, (float)fh, (float)fw, lc, sc44, uh0, uw0, u, v);
+      }
+    }
+    const __half* xr[3];
+    ok = rx.wait_full(k0 + 2) && ok;
+#pragma unroll
+    for (int fh = 0; fh < 3; ++fh) {
+      const int k = k0 + (TR ? 2 - fh : fh);
+      if (k != k0 + 2) ok = rx.wait_full(k) && ok;
+      xr[fh] = xring + (size_t)rx.slot(k) * slot_halves + gq * INNER + (8 + (ow0 + 2 * q) * S - 2);
+    }
+    if (!ok) {
+      ring_fail(lane);
+      return;
+    }
+
+    const int ow = ow0 + 2 * q;
+    const unsigned* bkp = reinterpret_cast<const unsigned*>(bank + gq * kBankPitch) + q;
+    __half* y0 = dst + ((size_t)n * p.C + c0 + gq) * dplane + (size_t)d * Wd + ow;
+#pragma unroll 3
+    for (int sb = 0; sb < nslab; ++sb) {
+      unsigned a[4];
+      a[0] = bkp[sb * (16 * kBankPitch / 2)];
+      a[1] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2];
+      a[2] = bkp[sb * (16 * kBankPitch / 2) + 4];
+      a[3] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2 + 4];
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int fh = 0; fh < 3; ++fh) {
+        const unsigned* p0 = reinterpret_cast<const unsigned*>(xr[fh] + sb * 16 * INNER);
+        const unsigned* p1 = p0 + 8 * INNER / 2;
+        const unsigned w0 = p0[0], w1 = p0[1], w2 = p0[2];
+        const unsigned v0 = p1[0], v1 = p1[1], v2 = p1[2];
+        // source columns ow*S - 1 .. of the two channel rows, widened to fp32
+        float fa[5], fb[5];
+        fa[0] = h_hi(w0); fa[1] = h_lo(w1); fa[2] = h_hi(w1); fa[3] = h_lo(w2);
+        fb[0] = h_hi(v0); fb[1] = h_lo(v1); fb[2] = h_hi(v1); fb[3] = h_lo(v2);
+        if (S == 2) {
+          fa[4] = h_hi(w2);
+          fb[4] = h_hi(v2);
+        }
+#pragma unroll
+        for (int fw = 0; fw < 3; ++fw) {
+          float kd[4];
+          mma_new(kd, a, bf[fh * 3 + fw][0], bf[fh * 3 + fw][1]);
+          const int i0 = TR ? 2 - fw : fw;      // pixel 0 reads this element of the window
+          const int i1 = TR ? 3 - fw : fw + S;  // pixel 1
+          acc[0] = fmaf(kd[0], fa[i0], acc[0]);
+          acc[1] = fmaf(kd[1], fa[i1], acc[1]);
+          acc[2] = fmaf(kd[2], fb[i0], acc[2]);
+          acc[3] = fmaf(kd[3], fb[i1], acc[3]);
+        }
+      }
+      if (ow < Wd) {
+        __half* ya = y0 + (size_t)sb * 16 * dplane;
+        *reinterpret_cast<__half2*>(ya) = __floats2half2_rn(acc[0], acc[1]);
+        *reinterpret_cast<__half2*>(ya + 8 * dplane) = __floats2half2_rn(acc[2], acc[3]);
+      }
+    }
+
+    // done with the three source rows (and the offset rows)
+    __syncwarp();
+    if (lane == 0) {
+      const bool first = (d == 0) || (g == g0), last = (d == Hd - 1) || (g == g1 - 1);
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        const int m = release_count<S>(j, first, last);
+        rx.release(k0 + j, m);
+        if (TR) rr.release(k0 + j, m);
+      }
+      if (!TR) rr.release(grow, 1);
+    }
+  }
+}
+
+// ================================================================== grad-offsets + grad-bank in one pass
+//
+// Item = 8 output pixels (oh, ow0 .. ow0+7).  The warp that owns it runs over all channel slabs of the
+// block: dK = dy * x (fp16 pairs), G += W^T * dK (all channels, complete inside the item), dW[slab] += dK * beta
+// (kept in registers across the warp's items).  x rows stream as in the forward kernel; the rows of dy and of
+// the offsets have their own rings, one fill per output row.
+template <int S, int W>
+struct GwShape {
+  static constexpr int kWo = (W - 1) / S + 1;
+  static constexpr int kNB = (kWo + 7) / 8;
+  static constexpr int kInnerX = RowLayout<W>::kInner;
+  static constexpr int kInnerD = RowLayout<kWo>::kInner;
+  static constexpr bool kDyTma = RowLayout<kWo>::kTma;
+};
+constexpr int kGwScratch = 3 * 16 * 8 * 4 + 24 * 8;  // per warp: G and the bank coordinates (u, v) of three taps x eight pixels
+
+__host__ __device__ inline size_t gw_ring_smem(int cg, int inner_x, int inner_d, int rot_slot, int R, int RR, int warps) {
+  const size_t rings = (size_t)R * cg * inner_x * 2 + 128 + (size_t)RR * cg * inner_d * 2 + 128 + (size_t)RR * rot_slot * 2;
+  const size_t red = (size_t)warps * cg * 16 * 4;  // the bank-gradient reduction at the end reuses the rings
+  return (rings > red ? rings : red) + 16 + (size_t)16 * (cg + 8) * 2 + (size_t)warps * kGwScratch + (size_t)(2 * R + 4 * RR) * 8 +
+         16 + 128;
+}
+
+template <int S, int W, int NS, int MAXT>
+__global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
+                                                          const __half* __restrict__ dy, const __half* __restrict__ rot,
+                                                          const __half* __restrict__ bankw, __half* __restrict__ drot,
+                                                          float* __restrict__ partial, const RingParams p) {
+  using Sh = GwShape<S, W>;
+  using RL = RotLayout<Sh::kWo>;
+  constexpr int IX = Sh::kInnerX, ID = Sh::kInnerD, WOP = RL::kWop, NB = Sh::kNB, Wo = Sh::kWo;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int R = 1 << p.lgR, RR = 1 << p.lgRR;
+  const int CG = p.CG;  // = 16 * (slabs <= NS); the block covers every channel
+  const int xslot = CG * IX, dslot = CG * ID;
+  const int ncw = (blockDim.x >> 5) - 1;
+  const int pitchT = CG + 8;
+
+  __half* xring = reinterpret_cast<__half*>(smem_raw);
+  __half* dring = xring + (size_t)R * xslot + 64;  // 128 bytes of zeros behind each ring; TMA destinations stay 128-byte aligned
+  __half* rring = dring + (size_t)RR * dslot + 64;
+  unsigned char* rings_end = reinterpret_cast<unsigned char*>(rring + (size_t)RR * RL::kSlot);
+  unsigned char* after = rings_end;
+  {
+    unsigned char* red_end = smem_raw + (size_t)ncw * CG * 16 * 4;
+    if (red_end > after) after = red_end;
+    after = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(after) + 15) & ~(uintptr_t)15);
+  }
+  __half* bankT = reinterpret_cast<__half*>(after);  // [16 cells][CG + 8]
+  unsigned char* scratch = reinterpret_cast<unsigned char*>(bankT + 16 * pitchT);
+  unsigned long long* bars =
+      reinterpret_cast<unsigned long long*>((reinterpret_cast<uintptr_t>(scratch + (size_t)ncw * kGwScratch) + 7) & ~(uintptr_t)7);
+  Ring rx, rd, rr;
+  rx.full = smem_u32(bars); rx.empty = rx.full + 8 * R; rx.lg = p.lgR;
+  rd.full = rx.empty + 8 * R; rd.empty = rd.full + 8 * RR; rd.lg = p.lgRR;
+  rr.full = rd.empty + 8 * RR; rr.empty = rr.full + 8 * RR; rr.lg = p.lgRR;
+  rx.issued = rr.empty + 8 * RR; rd.issued = rx.issued + 4; rr.issued = rx.issued + 8;
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < R; ++i) {
+      mbar_init(rx.full + 8 * i, 1);
+      mbar_init(rx.empty + 8 * i, (S == 1 ? 3 : 2) * NB);
+    }
+    for (int i = 0; i < RR; ++i) {
+      mbar_init(rd.full + 8 * i, Sh::kDyTma ? 1 : 32);
+      mbar_init(rd.empty + 8 * i, NB);
+      mbar_init(rr.full + 8 * i, 32);
+      mbar_init(rr.empty + 8 * i, NB);
+    }
+    int* cnt = reinterpret_cast<int*>(bars + 2 * R + 4 * RR);
+    cnt[0] = cnt[1] = cnt[2] = 0;
+    fence_barrier_init();
+  }
+  {
+    uint4* z = reinterpret_cast<uint4*>(smem_raw);
+    const int nz = (int)((rings_end - smem_raw) >> 4);
+    for (int i = threadIdx.x; i < nz; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
+  }
+  for (int i = threadIdx.x; i < 16 * CG; i += blockDim.x) {
+    const int cell = i / CG, c = i - cell * CG;
+    bankT[cell * pitchT + c] = cell < p.cells ? __ldg(bankw + (size_t)c * p.cells + cell) : __float2half(0.f);
+  }
+  fence_proxy_async();
+  __syncthreads();
+
+  const int g0 = blockIdx.x * p.rows_per_block;
+  const int g1 = min(g0 + p.rows_per_block, p.rows_total);
+  const int Ho = p.Hd, L = p.L;
+  const int n_first = g0 < g1 ? g0 / Ho : 0;
+  const int T0 = n_first * L + (g0 - n_first * Ho) * S;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (g0 >= g1) return;
+    if (lane == 0) {
+      prefetch_tensormap(&tm_x);
+      if (Sh::kDyTma) prefetch_tensormap(&tm_dy);
+    }
+    const unsigned xbytes = (unsigned)xslot * 2, dbytes = (unsigned)dslot * 2;
+    const unsigned xring_u32 = smem_u32(xring), dring_u32 = smem_u32(dring);
+    int T = T0;
+    bool ok = true;
+    for (int g = g0; g < g1 && ok; ++g) {
+      const int n = g / Ho, oh = g - n * Ho;
+      const int kr = g - g0;
+      ok = rr.reclaim(kr, lane);
+      if (ok) fill_rot_row<Wo>(rring + (size_t)rr.slot(kr) * RL::kSlot, rot, n, Ho, oh, lane, rr.full + 8 * rr.slot(kr));
+      ok = ok && rd.reclaim(kr, lane);
+      if (ok) {
+        if (Sh::kDyTma) {
+          if (lane == 0) {
+            mbar_arrive_expect_tx(rd.full + 8 * rd.slot(kr), dbytes);
+            tma_load_3d(dring_u32 + rd.slot(kr) * dbytes, &tm_dy, -8, oh, n * p.C, rd.full + 8 * rd.slot(kr));
+          }
+        } else {
+          fill_plane_row<Wo>(dring + (size_t)rd.slot(kr) * dslot, dy, n, p.C, 0, CG, Ho, oh, lane, rd.full + 8 * rd.slot(kr));
+        }
+      }
+      const int Tend = n * L + oh * S + 2;
+      for (; T <= Tend && ok; ++T) {
+        const int k = T - T0;
+        ok = rx.reclaim(k, lane);
+        if (lane == 0 && ok) {
+          mbar_arrive_expect_tx(rx.full + 8 * rx.slot(k), xbytes);
+          tma_load_3d(xring_u32 + rx.slot(k) * xbytes, &tm_x, -8, T - n * L - 1, n * p.C, rx.full + 8 * rx.slot(k));
+        }
+        __syncwarp();
+      }
+    }
+    cp_async_wait_all();
+    if (!ok) ring_fail(lane);
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int cw = warp - 1;
+  const int gq = lane >> 2, q = lane & 3;
+  const LaneCells lc = lane_cells_of(p.scW, p.cells, q);
+  const bool sc44 = p.scH == 4 && p.scW == 4;
+  const float uh0 = (float)(p.scH - 3) * 0.5f, uw0 = (float)(p.scW - 3) * 0.5f;
+  const int nslab = CG >> 4;
+  const int items = g0 < g1 ? (g1 - g0) * NB : 0;
+  const int P = Ho * Wo;
+  float* Gs = reinterpret_cast<float*>(scratch + (size_t)cw * kGwScratch);  // [3 taps][16 cells][8 px]
+  float2* uv = reinterpret_cast<float2*>(Gs + 3 * 16 * 8);                    // [3 taps][8 px]
+
+  float acc[NS][2][4];  // bank gradient of up to NS slabs of 16 channels x (cells 0-7 | cells 8-15)
+#pragma unroll
+  for (int sidx = 0; sidx < NS; ++sidx)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[sidx][0][k] = acc[sidx][1][k] = 0.f;
+
+  for (int it = cw; it < items; it += ncw) {
+    const int grow = it / NB, cb = it - grow * NB;
+    const int g = g0 + grow;
+    const int n = g / Ho, oh = g - n * Ho;
+    const int k0 = n * L + oh * S - T0;
+    const int ow0 = cb << 3;
+    const int pg = ow0 + gq;
+    bool ok = rr.wait_full(grow);
+    ok = rd.wait_full(grow) && ok;
+    const int ow = ow0 + 2 * q;
+    const __half* rp = rring + (size_t)rr.slot(grow) * RL::kSlot + 8 + pg;
+    const __half* dyr = dring + (size_t)rd.slot(grow) * dslot + gq * ID + 8 + ow;
+    __half* drot_n = drot + (size_t)n * 18 * P;
+
+    // One pass per kernel row fh (three taps): keeps 12 instead of 36 accumulators of G live, and its source row is
+    // waited for only when the pass starts.
+#pragma unroll
+    for (int fh = 0; fh < 3; ++fh) {
+      // hat products of the three taps, transposed into B fragments of dW += dK * beta:
+      // bw[fw][0] = (pixels 2q, 2q+1; cell gq), bw[fw][1] = cell gq + 8
+      unsigned bw[3][2];
+#pragma unroll
+      for (int fw = 0; fw < 3; ++fw) {
+        unsigned bb[2];
+        float u, v;
+        beta_tap<WOP>(bb, rp + 2 * (fh * 3 + fw) * WOP, (float)fh, (float)fw, lc, sc44, uh0, uw0, u, v);
+        bw[fw][0] = movmatrix_trans(bb[0]);
+        bw[fw][1] = movmatrix_trans(bb[1]);
+        if (q == 0) {
+          const bool valid = u > -1.f && v > -1.f && u < (float)p.scH && v < (float)p.scW;
+          uv[fw * 8 + gq] = make_float2(valid ? u : 1e30f, v);
+        }
+      }
+      ok = rx.wait_full(k0 + fh) && ok;
+      if (!ok) break;
+      const __half* xr = xring + (size_t)rx.slot(k0 + fh) * xslot + gq * IX + (8 + ow * S - 2);
+
+      float G[3][4];
+#pragma unroll
+      for (int t = 0; t < 3; ++t) G[t][0] = G[t][1] = G[t][2] = G[t][3] = 0.f;
+
+#pragma unroll
+      for (int sidx = 0; sidx < NS; ++sidx) {
+        if (sidx < nslab) {
+          const unsigned dy0 = *reinterpret_cast<const unsigned*>(dyr + sidx * 16 * ID);
+          const unsigned dy1 = *reinterpret_cast<const unsigned*>(dyr + sidx * 16 * ID + 8 * ID);
+          const unsigned* p0 = reinterpret_cast<const unsigned*>(xr + sidx * 16 * IX);
+          const unsigned* p1 = p0 + 8 * IX / 2;
+          const unsigned w0 = p0[0], w1 = p0[1], w2 = p0[2];
+          const unsigned v0 = p1[0], v1 = p1[1], v2 = p1[2];
+          unsigned d0[3], d1[3];  // dK of channel rows gq and gq + 8 for the three taps
+#pragma unroll
+          for (int fw = 0; fw < 3; ++fw) {
+            d0[fw] = hmul2u(dy0, tap_pair<S>(w0, w1, w2, fw));
+            d1[fw] = hmul2u(dy1, tap_pair<S>(v0, v1, v2, fw));
+          }
+          if (drot != nullptr) {
+            // A = W^T slab: rows = cells (gq, gq+8), k = channels (2q, 2q+1) and (2q+8, 2q+9)
+            const unsigned* wt0 = reinterpret_cast<const unsigned*>(bankT + gq * pitchT + sidx * 16);
+            const unsigned* wt1 = reinterpret_cast<const unsigned*>(bankT + (gq + 8) * pitchT + sidx * 16);
+            const unsigned a0 = wt0[q], a1 = wt1[q], a2 = wt0[q + 4], a3 = wt1[q + 4];
+#pragma unroll
+            for (int fw = 0; fw < 3; ++fw) mma16816_acc(G[fw], a0, a1, a2, a3, movmatrix_trans(d0[fw]), movmatrix_trans(d1[fw]));
+          }
+          if (partial != nullptr) {
+            // k = 16 = 8 pixels x (tap 0 | tap 1), then 8 pixels x (tap 2 | nothing)
+            mma16816_acc(acc[sidx][0], d0[0], d1[0], d0[1], d1[1], bw[0][0], bw[1][0]);
+            mma16816_acc(acc[sidx][1], d0[0], d1[0], d0[1], d1[1], bw[0][1], bw[1][1]);
+            mma16816_acc(acc[sidx][0], d0[2], d1[2], 0u, 0u, bw[2][0], 0u);
+            mma16816_acc(acc[sidx][1], d0[2], d1[2], 0u, 0u, bw[2][1], 0u);
+          }
+        }
+      }
+      if (fh == 2) {
+        // all rows of the item have been read: hand them back before the last epilogue
+        __syncwarp();
+        if (lane == 0) {
+          const bool first = (oh == 0) || (g == g0), last = (oh == Ho - 1) || (g == g1 - 1);
+#pragma unroll
+          for (int j = 0; j < 3; ++j) rx.release(k0 + j, release_count<S>(j, first, last));
+          rd.release(grow, 1);
+          rr.release(grow, 1);
+        }
+      }
+
+      // d(offset)[pixel, tap, dir] = sum over the four corner cells of G * d(coefficient)/d(u or v)  (floor-based:
+      // at an integer coordinate the right-hand derivative, as csrc/filter_sample_depthwise_cuda_kernel.cu:137-158)
+      if (drot != nullptr) {
+        __syncwarp();
+#pragma unroll
+        for (int tt = 0; tt < 3; ++tt) {
+          *reinterpret_cast<float2*>(Gs + (tt * 16 + gq) * 8 + 2 * q) = make_float2(G[tt][0], G[tt][1]);
+          *reinterpret_cast<float2*>(Gs + (tt * 16 + gq + 8) * 8 + 2 * q) = make_float2(G[tt][2], G[tt][3]);
+        }
+        __syncwarp();
+        if (lane < 24) {
+          const int px = lane & 7, tt = lane >> 3;
+          const int t = fh * 3 + tt;
+          const float2 c = uv[tt * 8 + px];
+          float gu = 0.f, gv = 0.f;
+          if (c.x < 1e29f) {
+            const float fu = floorf(c.x), fv = floorf(c.y);
+            const int h0 = (int)fu, w0 = (int)fv;
+            const float lh = c.x - fu, lw = c.y - fv;
+            const float hh = 1.f - lh, hw = 1.f - lw;
+            const float* Gp = Gs + tt * 128 + px;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int a = h0 + (k >> 1), b = w0 + (k & 1);
+              if (a >= 0 && a < p.scH && b >= 0 && b < p.scW) {
+                const float gval = Gp[(a * p.scW + b) * 8];
+                const float du = (k >> 1) ? ((k & 1) ? lw : hw) : ((k & 1) ? -lw : -hw);
+                const float dv = (k & 1) ? ((k >> 1) ? lh : hh) : ((k >> 1) ? -lh : -hh);
+                gu += du * gval;
+                gv += dv * gval;
+              }
+            }
+          }
+          if (ow0 + px < Wo) {
+            const size_t o = (size_t)(2 * t) * P + oh * Wo + ow0 + px;
+            drot_n[o] = __float2half_rn(gu);
+            drot_n[o + P] = __float2half_rn(gv);
+          }
+        }
+        __syncwarp();
+      }
+    }
+    if (!ok) {
+      ring_fail(lane);
+      break;
+    }
+  }
+
+  // ---- bank gradient: sum the consumer warps' accumulators (the rings are free now) and write this block's partial
+  asm volatile("bar.sync 1, %0;\n" ::"r"(ncw * 32) : "memory");
+  if (partial != nullptr) {
+    float* red = reinterpret_cast<float*>(smem_raw);  // [ncw][CG][16]
+#pragma unroll
+    for (int sidx = 0; sidx < NS; ++sidx) {
+      if (sidx < nslab) {
+        float* r0 = red + ((size_t)cw * CG + (sidx << 4) + gq) * 16;
+        float* r1 = r0 + 8 * 16;
+        r0[2 * q] = acc[sidx][0][0]; r0[2 * q + 1] = acc[sidx][0][1];
+        r1[2 * q] = acc[sidx][0][2]; r1[2 * q + 1] = acc[sidx][0][3];
+        r0[8 + 2 * q] = acc[sidx][1][0]; r0[8 + 2 * q + 1] = acc[sidx][1][1];
+        r1[8 + 2 * q] = acc[sidx][1][2]; r1[8 + 2 * q + 1] = acc[sidx][1][3];
+      }
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"r"(ncw * 32) : "memory");
+    for (int i = threadIdx.x - 32; i < CG * 16; i += ncw * 32) {
+      float sum = 0.f;
+      for (int wv = 0; wv < ncw; ++wv) sum += red[(size_t)wv * CG * 16 + i];
+      partial[(size_t)blockIdx.x * CG * 16 + i] = sum;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up through the runtime (the library links no driver library).
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    (void)cudaGetLastError();
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// fp16 planes [planes][rows][width] viewed as a rank-3 tensor; one box = `box_w` halves of one row of
+// `box_planes` consecutive planes.  Elements outside the tensor are delivered as zeros.
+bool make_row_map(CUtensorMap* tm, const __half* base, int width, int rows, long long planes, int box_w, int box_planes) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (width & 7) || box_w > 256 || box_planes > 256 || (box_w & 7)) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)width, (cuuint64_t)rows, (cuuint64_t)planes};
+  const cuuint64_t strides[2] = {(cuuint64_t)width * 2, (cuuint64_t)width * rows * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)box_w, 1u, (cuuint32_t)box_planes};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  return enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool ring_shape(const Geom& g) {
+  if (g.kH != 3 || g.kW != 3 || g.dH != 1 || g.dW != 1 || g.pH != 1 || g.pW != 1) return false;
+  if (g.sH != g.sW || (g.sH != 1 && g.sH != 2)) return false;
+  if (g.G != 1 || g.cells > 16 || (g.C & 15)) return false;
+  if ((long long)g.N * (g.H + 2) > 0x3fffffff) return false;  // stream row indices are 32-bit
+  return g.W == 112 || g.W == 56;                              // the widths the kernels are instantiated for
+}
+
+void spread_rows(long long rows, int groups, int* blocks_x, int* rows_per_block) {
+  long long bx = device_sm_count() / groups;
+  if (bx < 1) bx = 1;
+  if (bx > rows) bx = rows;
+  *rows_per_block = (int)((rows + bx - 1) / bx);
+  *blocks_x = (int)((rows + *rows_per_block - 1) / *rows_per_block);
+}
+
+struct ConvRingPlan {
+  bool ok;
+  int CG, groups, lgR, lgRR, warps, blocks_x, rows_per_block;
+  size_t smem;
+};
+
+// Channels per block, ring depths and grid of the forward / stride-1 grad-input kernel.
+template <int S, int W, bool TR>
+ConvRingPlan conv_ring_plan(const Geom& g) {
+  using Sh = ConvShape<S, W, TR>;
+  using RL = RotLayout<Sh::kWr>;
+  ConvRingPlan pl;
+  pl.ok = false;
+  const size_t budget = (size_t)device_smem_optin();
+  // all channels in one block when their rows fit eight (or four) deep, else the fewest equal groups that do
+  for (int groups = 1; groups <= g.C / 16 && !pl.ok; ++groups) {
+    if (g.C % (16 * groups)) continue;
+    const int cg = g.C / groups;
+    if (cg > 256) continue;
+    for (int lgR = 3; lgR >= 2 && !pl.ok; --lgR) {
+      const int lgRR = TR ? lgR : 2;
+      const size_t smem = conv_ring_smem(cg, Sh::kInner, RL::kSlot, 1 << lgR, 1 << lgRR);
+      if (smem > budget) continue;
+      pl.ok = true;
+      pl.CG = cg;
+      pl.groups = groups;
+      pl.lgR = lgR;
+      pl.lgRR = lgRR;
+      pl.smem = smem;
+    }
+  }
+  if (!pl.ok || pl.groups > 65535) {
+    pl.ok = false;
+    return pl;
+  }
+  spread_rows((long long)g.N * (TR ? g.H : g.Ho), pl.groups, &pl.blocks_x, &pl.rows_per_block);
+  pl.warps = 21;  // one producer + twenty consumers
+  return pl;
+}
+
+template <int S, int W, bool TR>
+int launch_conv_ring(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, cudaStream_t s) {
+  using Sh = ConvShape<S, W, TR>;
+  const ConvRingPlan pl = conv_ring_plan<S, W, TR>(g);
+  if (!pl.ok) return DK_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(dst) & 3)) return DK_ERR_UNSUPPORTED;
+  const int Hs = TR ? g.Ho : g.H, Hd = TR ? g.H : g.Ho;
+  CUtensorMap tm;
+  if (!make_row_map(&tm, src, W, Hs, (long long)g.N * g.C, Sh::kInner, pl.CG)) return DK_ERR_UNSUPPORTED;
+  RingParams p;
+  p.N = g.N; p.C = g.C; p.Hs = Hs; p.Hd = Hd;
+  p.CG = pl.CG; p.lgR = pl.lgR; p.lgRR = pl.lgRR;
+  p.L = (Hd - 1) * S + 3;
+  p.rows_total = g.N * Hd;
+  p.rows_per_block = pl.rows_per_block;
+  p.scH = g.scH; p.scW = g.scW; p.cells = g.cells;
+  int warps = pl.warps;
+#ifdef DK_TUNING
+  if (const char* e = std::getenv("DK_B200_RING_WARPS")) warps = atoi(e) > 1 ? atoi(e) : warps;
+#endif
+  int rc;
+  if (warps <= 21) {
+    auto kern = ring_conv_kernel<S, W, TR, 672>;
+    if ((rc = enable_smem(kern, pl.smem))) return rc;
+    kern<<<dim3(pl.blocks_x, pl.groups), warps * 32, pl.smem, s>>>(tm, rot, w, dst, p);
+  } else {
+    auto kern = ring_conv_kernel<S, W, TR, 800>;
+    if ((rc = enable_smem(kern, pl.smem))) return rc;
+    kern<<<dim3(pl.blocks_x, pl.groups), (warps > 25 ? 25 : warps) * 32, pl.smem, s>>>(tm, rot, w, dst, p);
+  }
+  return check_launch();
+}
+
+struct GwRingPlan {
+  bool ok;
+  int lgR, lgRR, warps, blocks_x, rows_per_block, ns;
+  size_t smem, ws_bytes;
+};
+
+template <int S, int W>
+GwRingPlan gw_ring_plan(const Geom& g) {
+  using Sh = GwShape<S, W>;
+  using RL = RotLayout<Sh::kWo>;
+  GwRingPlan pl;
+  pl.ok = false;
+  pl.ns = g.C <= 96 ? 6 : 9;
+  if (g.C > 144) return pl;  // the bank-gradient accumulators of all channels live in registers
+  pl.warps = pl.ns == 6 ? 16 : 12;
+  const size_t budget = (size_t)device_smem_optin();
+  for (int lgR = 3; lgR >= 2 && !pl.ok; --lgR)
+    for (int lgRR = 2; lgRR >= 1 && !pl.ok; --lgRR) {
+      const size_t smem = gw_ring_smem(g.C, Sh::kInnerX, Sh::kInnerD, RL::kSlot, 1 << lgR, 1 << lgRR, pl.warps - 1);
+      if (smem > budget) continue;
+      pl.ok = true;
+      pl.lgR = lgR;
+      pl.lgRR = lgRR;
+      pl.smem = smem;
+    }
+  if (!pl.ok) return pl;
+  spread_rows((long long)g.N * g.Ho, 1, &pl.blocks_x, &pl.rows_per_block);
+  pl.ws_bytes = (size_t)pl.blocks_x * g.C * 16 * sizeof(float);
+  return pl;
+}
+
+template <int S, int W>
+int launch_gw_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
+                   void* ws, size_t ws_bytes, cudaStream_t s) {
+  using Sh = GwShape<S, W>;
+  const GwRingPlan pl = gw_ring_plan<S, W>(g);
+  if (!pl.ok) return DK_ERR_UNSUPPORTED;
+  if (dw != nullptr && (ws == nullptr || ws_bytes < pl.ws_bytes)) return DK_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(dy) & 15)) return DK_ERR_UNSUPPORTED;
+  CUtensorMap tmx, tmd;
+  if (!make_row_map(&tmx, x, W, g.H, (long long)g.N * g.C, Sh::kInnerX, g.C)) return DK_ERR_UNSUPPORTED;
+  if (Sh::kDyTma) {
+    if (!make_row_map(&tmd, dy, Sh::kWo, g.Ho, (long long)g.N * g.C, Sh::kInnerD, g.C)) return DK_ERR_UNSUPPORTED;
+  } else {
+    tmd = tmx;
+  }
+  RingParams p;
+  p.N = g.N; p.C = g.C; p.Hs = g.H; p.Hd = g.Ho;
+  p.CG = g.C; p.lgR = pl.lgR; p.lgRR = pl.lgRR;
+  p.L = (g.Ho - 1) * S + 3;
+  p.rows_total = g.N * g.Ho;
+  p.rows_per_block = pl.rows_per_block;
+  p.scH = g.scH; p.scW = g.scW; p.cells = g.cells;
+  float* partial = dw != nullptr ? reinterpret_cast<float*>(ws) : nullptr;
+  int rc;
+  if (pl.ns == 6) {
+    auto kern = ring_gw_kernel<S, W, 6, 512>;
+    if ((rc = enable_smem(kern, pl.smem))) return rc;
+    kern<<<pl.blocks_x, pl.warps * 32, pl.smem, s>>>(tmx, tmd, dy, rot, w, drot, partial, p);
+  } else {
+    auto kern = ring_gw_kernel<S, W, 9, 384>;
+    if ((rc = enable_smem(kern, pl.smem))) return rc;
+    kern<<<pl.blocks_x, pl.warps * 32, pl.smem, s>>>(tmx, tmd, dy, rot, w, drot, partial, p);
+  }
+  if ((rc = check_launch())) return rc;
+  if (dw != nullptr) return launch_reduce_bank_partials(partial, dw, g.C, g.cells, pl.blocks_x, s);
+  return DK_OK;
+}
+
+}  // namespace
+
+// Code of the last bounded wait that ran out in a ring kernel on the current device (0 = none);
+// synchronises with the device.  For tests and diagnosis.
+int ring_error_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_ring_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+// forward (transposed = false) or grad-input (transposed = true); DK_ERR_UNSUPPORTED = not a ring shape
+int local_conv_ring(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, bool transposed,
+                    cudaStream_t s) {
+  if (!ring_shape(g)) return DK_ERR_UNSUPPORTED;
+  if (!transposed) {
+    if (g.W == 112) return g.sH == 1 ? launch_conv_ring<1, 112, false>(src, rot, w, dst, g, s) : launch_conv_ring<2, 112, false>(src, rot, w, dst, g, s);
+    return g.sH == 1 ? launch_conv_ring<1, 56, false>(src, rot, w, dst, g, s) : launch_conv_ring<2, 56, false>(src, rot, w, dst, g, s);
+  }
+  if (g.sH != 1) return DK_ERR_UNSUPPORTED;
+  return g.W == 112 ? launch_conv_ring<1, 112, true>(src, rot, w, dst, g, s) : launch_conv_ring<1, 56, true>(src, rot, w, dst, g, s);
+}
+
+// Workspace of local_gw_ring (the per-block partial bank gradients); 0 = the shape is not covered.
+size_t local_gw_ring_workspace(const Geom& g) {
+  if (!ring_shape(g)) return 0;
+  GwRingPlan pl;
+  if (g.W == 112) pl = g.sH == 1 ? gw_ring_plan<1, 112>(g) : gw_ring_plan<2, 112>(g);
+  else pl = g.sH == 1 ? gw_ring_plan<1, 56>(g) : gw_ring_plan<2, 56>(g);
+  return pl.ok ? pl.ws_bytes : 0;
+}
+
+// grad-offsets (drot, may be null) and grad-bank (dw, may be null) in one pass
+int local_gw_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
+                  void* ws, size_t ws_bytes, cudaStream_t s) {
+  if (!ring_shape(g)) return DK_ERR_UNSUPPORTED;
+  if (g.W == 112)
+    return g.sH == 1 ? launch_gw_ring<1, 112>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s)
+                     : launch_gw_ring<2, 112>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s);
+  return g.sH == 1 ? launch_gw_ring<1, 56>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s)
+                   : launch_gw_ring<2, 56>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s);
+}
+
+}  // namespace dk

@@ -70,6 +70,7 @@ _PROTOS = {
     "dk_last_cuda_error": (_int, []),
     "dk_version": (ctypes.c_char_p, []),
     "dk_local_plan_query": (_int, [_gp, _int, _int, ctypes.POINTER(ctypes.c_longlong)]),
+    "dk_ring_error_status": (_int, []),
 }
 for _name, (_res, _args) in _PROTOS.items():
     _fn = getattr(lib, _name)

@@ -73,6 +73,11 @@ const char *dk_version(void);
  * 3 grad-bank.  out8 = {band height, channels per block, channel groups, warps per block, bands, dynamic shared memory in
  * bytes, blocks in the grid, workspace bytes}.  DK_ERR_UNSUPPORTED when the geometry or dtype takes the general kernels. */
 int dk_local_plan_query(const dk_geom *g, int dtype, int pass, long long *out8);
+/* The producer / consumer kernels of the fp16 path bound every wait on a shared-memory barrier; a wait that
+ * runs out records a non-zero code on the device and the kernel returns early instead of hanging.  This reads
+ * that code for the current device (0 = no wait ever ran out, -1 = the query itself failed).  It synchronises with
+ * the device, so it is for tests and diagnosis, not for the hot path.  No counterpart in the reference. */
+int dk_ring_error_status(void);
 /* Output extent for a geometry; returns DK_ERR_BAD_ARGUMENT if it is not positive. */
 int dk_output_size(const dk_geom *g, int *out_h, int *out_w);
 
