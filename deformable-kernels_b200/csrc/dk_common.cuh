@@ -178,7 +178,7 @@ int local_conv_ring(const __half* src, const __half* rot, const __half* w, __hal
                     cudaStream_t s);
 size_t local_gw_ring_workspace(const Geom& g);
 int local_gw_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
-                  void* ws, size_t ws_bytes, cudaStream_t s);  // grad-offsets and grad-bank in one pass (either may be null)
+                  void* ws, size_t ws_bytes, cudaStream_t s);  // grad-offsets and grad-bank in one pass
 int ring_error_status();
 size_t local_rot_mma_workspace(const Geom& g);
 int local_rot_mma(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, const Geom& g,

@@ -22,6 +22,7 @@
 // group, <= 16 bank cells, channels a multiple of 16) on input rows of 112 or 56 elements (TMA
 // needs 16-byte row pitches); other shapes stay on dk_local_mma.cu.
 #include <cstdlib>
+#include <cstring>
 
 #include "dk_ring.cuh"
 
@@ -70,13 +71,13 @@ __device__ __forceinline__ float h_hi(unsigned w) { return __high2float(*reinter
 // Hat products of pixel column gq of an item for one tap, as the B fragment of K = W * beta^T:
 // b0 = cells (2q, 2q+1), b1 = cells (2q+8, 2q+9).  rp points at the tap's vertical offset of the
 // pixel in a ring slot; the horizontal one lies WOP halves further.  (u, v) are returned.
-template <int WOP>
+template <int WOP, bool SC44>
 __device__ __forceinline__ void beta_tap(unsigned (&b)[2], const __half* __restrict__ rp, float fh, float fw, const LaneCells& lc,
-                                         bool sc44, float uh0, float uw0, float& u, float& v) {
+                                         float uh0, float uw0, float& u, float& v) {
   // same association as the reference: (tap index + offset) + (scope - kernel) / 2
   u = (fh + __half2float(rp[0])) + uh0;
   v = (fw + __half2float(rp[WOP])) + uw0;
-  if (sc44) {
+  if (SC44) {  // 4 x 4 scope: the lane's four cells share two rows and two columns
     const float hh0 = hat(u - lc.ca[0]), hh1 = hat(u - lc.ca[2]);
     const float hw0 = hat(v - lc.cb[0]), hw1 = hat(v - lc.cb[1]);
     b[0] = pack2(hh0 * hw0, hh0 * hw1);
@@ -179,7 +180,7 @@ __host__ __device__ inline size_t conv_ring_smem(int cg, int inner, int rot_slot
          16 + 128;
 }
 
-template <int S, int W, bool TR, int MAXT>
+template <int S, int W, bool TR, bool SC44, int MAXT>
 __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constant__ CUtensorMap tm_src, const __half* __restrict__ rot,
                                                             const __half* __restrict__ bankw, __half* __restrict__ dst,
                                                             const RingParams p) {
@@ -280,7 +281,6 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
   const int cw = warp - 1;
   const int gq = lane >> 2, q = lane & 3;
   const LaneCells lc = lane_cells_of(p.scW, p.cells, q);
-  const bool sc44 = p.scH == 4 && p.scW == 4;
   const float uh0 = (float)(p.scH - 3) * 0.5f, uw0 = (float)(p.scW - 3) * 0.5f;
   const int nslab = CG >> 4;
   const size_t dplane = (size_t)Hd * Wd;
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
       ok = rr.wait_full(grow);
       const __half* rp = rring + (size_t)rr.slot(grow) * RL::kSlot + 8 + pg;
 #pragma unroll
-      for (int t = 0; t < 9; ++t) beta_tap<WOP>(bf[t], rp + 2 * t * WOP, (float)(t / 3), (float)(t % 3), lc, sc44, uh0, uw0, u, v);
+      for (int t = 0; t < 9; ++t) beta_tap<WOP, SC44>(bf[t], rp + 2 * t * WOP, (float)(t / 3), (float)(t % 3), lc, uh0, uw0, u, v);
     } else {
       ok = rr.wait_full(k0 + 2);
 #pragma unroll
@@ -312,7 +312,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
         const __half* rp = rring + (size_t)rr.slot(k) * RL::kSlot + 8 + pg + 1;
 #pragma unroll
         for (int fw = 0; fw < 3; ++fw)
-          beta_tap<WOP>(bf[fh * 3 + fw], rp + 2 * (fh * 3 + fw) * WOP - fw, (float)fh, (float)fw, lc, sc44, uh0, uw0, u, v);
+          beta_tap<WOP, SC44>(bf[fh * 3 + fw], rp + 2 * (fh * 3 + fw) * WOP - fw, (float)fh, (float)fw, lc, uh0, uw0, u, v);
       }
     }
     const __half* xr[3];
@@ -387,6 +387,223 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
   }
 }
 
+// ================================================================== grad-input at stride 2
+//
+// dx[2a + rr, 2b + cc] collects, from the output pixels (a + da, b + db) with da, db in {0, 1}, the taps
+//   rows: rr = 0 <- (da 0, fh 1);  rr = 1 <- (da 0, fh 2) and (da 1, fh 0)        (columns alike with db, fw, cc)
+// so an item of 8 output pixels (a, b0 .. b0+7) yields the 2 x 16 patch dx[2a .. 2a+1, 2 b0 .. 2 b0 + 15] from nine
+// (pixel shift, tap) pairs, all of them useful: one mma and 4 FMAs per lane each, as in the forward pass.  The
+// rows a and a + 1 of dy and of the offsets stream through two rings (row Ho of a sample is a zero row).
+template <int W>  // W = width of dx
+struct ConvT2Shape {
+  static constexpr int kWo = (W - 1) / 2 + 1;
+  static constexpr int kNB = (kWo + 7) / 8;
+  static constexpr int kInner = RowLayout<kWo>::kInner;
+  static constexpr bool kTma = RowLayout<kWo>::kTma;
+};
+
+template <int W, bool SC44, int MAXT>
+__global__ void __launch_bounds__(MAXT, 1) ring_convT2_kernel(const __grid_constant__ CUtensorMap tm_dy, const __half* __restrict__ dy,
+                                                              const __half* __restrict__ rot, const __half* __restrict__ bankw,
+                                                              __half* __restrict__ dx, const RingParams p) {
+  using Sh = ConvT2Shape<W>;
+  using RL = RotLayout<Sh::kWo>;
+  constexpr int INNER = Sh::kInner, WOP = RL::kWop, NB = Sh::kNB, Wo = Sh::kWo;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int R = 1 << p.lgR;  // both rings have R slots and share their fill numbers
+  const int CG = p.CG;
+  const int c0 = blockIdx.y * CG;
+  const int slot_halves = CG * INNER;
+
+  __half* dring = reinterpret_cast<__half*>(smem_raw);
+  __half* rring = dring + (size_t)R * slot_halves + 64;
+  __half* bank = rring + (size_t)R * RL::kSlot;
+  const unsigned bars_off = (unsigned)((((size_t)R * slot_halves + 64 + (size_t)R * RL::kSlot + (size_t)CG * kBankPitch) * 2 + 7) & ~(size_t)7);
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + bars_off);
+  Ring rd, rr;
+  rd.full = smem_u32(bars); rd.empty = rd.full + 8 * R; rd.lg = p.lgR;
+  rr.full = rd.empty + 8 * R; rr.empty = rr.full + 8 * R; rr.lg = p.lgR;
+  rd.issued = rr.empty + 8 * R; rr.issued = rd.issued + 4;
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ncw = (blockDim.x >> 5) - 1;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < R; ++i) {
+      mbar_init(rd.full + 8 * i, Sh::kTma ? 1 : 32);
+      mbar_init(rd.empty + 8 * i, 2 * NB);
+      mbar_init(rr.full + 8 * i, 32);
+      mbar_init(rr.empty + 8 * i, 2 * NB);
+    }
+    int* cnt = reinterpret_cast<int*>(bars + 4 * R);
+    cnt[0] = cnt[1] = 0;
+    fence_barrier_init();
+  }
+  {
+    uint4* z = reinterpret_cast<uint4*>(smem_raw);
+    const int nz = (int)((reinterpret_cast<unsigned char*>(bank) - smem_raw) >> 4);
+    for (int i = threadIdx.x; i < nz; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
+  }
+  for (int i = threadIdx.x; i < CG * 16; i += blockDim.x) {
+    const int j = i >> 4, cell = i & 15;
+    bank[j * kBankPitch + cell] = cell < p.cells ? __ldg(bankw + (size_t)(c0 + j) * p.cells + cell) : __float2half(0.f);
+  }
+  fence_proxy_async();
+  __syncthreads();
+
+  const int Ho = p.Hs, H = p.Hd, L = p.L;  // L = Ho + 1 stream rows per sample
+  const int g0 = blockIdx.x * p.rows_per_block;  // rows of the OUTPUT plane (a) that this block expands
+  const int g1 = min(g0 + p.rows_per_block, p.rows_total);
+  if (g0 >= g1) return;
+  const int n_first = g0 / Ho;
+  const int T0 = n_first * L + (g0 - n_first * Ho);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0 && Sh::kTma) prefetch_tensormap(&tm_dy);
+    const unsigned slot_bytes = (unsigned)slot_halves * 2;
+    const unsigned dring_u32 = smem_u32(dring);
+    int T = T0;
+    bool ok = true;
+    for (int g = g0; g < g1 && ok; ++g) {
+      const int n = g / Ho, a = g - n * Ho;
+      const int Tend = n * L + a + 1;
+      for (; T <= Tend && ok; ++T) {
+        const int k = T - T0;
+        const int r = T - n * L;  // row of dy and of the offsets; r = Ho is the zero row below the plane
+        ok = rr.reclaim(k, lane);
+        if (ok) fill_rot_row<Wo>(rring + (size_t)rr.slot(k) * RL::kSlot, rot, n, Ho, min(r, Ho - 1), lane, rr.full + 8 * rr.slot(k));
+        ok = ok && rd.reclaim(k, lane);
+        if (ok) {
+          if (Sh::kTma) {
+            if (lane == 0) {
+              mbar_arrive_expect_tx(rd.full + 8 * rd.slot(k), slot_bytes);
+              tma_load_3d(dring_u32 + rd.slot(k) * slot_bytes, &tm_dy, -8, r, n * p.C + c0, rd.full + 8 * rd.slot(k));
+            }
+          } else {
+            __half* slot = dring + (size_t)rd.slot(k) * slot_halves;
+            if (r < Ho) {
+              fill_plane_row<Wo>(slot, dy, n, p.C, c0, CG, Ho, r, lane, rd.full + 8 * rd.slot(k));
+            } else {  // the zero row: plain stores, then the same 32 arrivals
+              for (int i = lane; i < slot_halves / 8; i += 32) reinterpret_cast<uint4*>(slot)[i] = make_uint4(0, 0, 0, 0);
+              mbar_arrive(rd.full + 8 * rd.slot(k));
+            }
+          }
+        }
+        __syncwarp();
+      }
+    }
+    cp_async_wait_all();
+    if (!ok) ring_fail(lane);
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int cw = warp - 1;
+  const int gq = lane >> 2, q = lane & 3;
+  const LaneCells lc = lane_cells_of(p.scW, p.cells, q);
+  const float uh0 = (float)(p.scH - 3) * 0.5f, uw0 = (float)(p.scW - 3) * 0.5f;
+  const int nslab = CG >> 4;
+  const size_t dplane = (size_t)H * W;
+  const int items = (g1 - g0) * NB;
+
+  for (int it = cw; it < items; it += ncw) {
+    const int grow = it / NB, cb = it - grow * NB;
+    const int g = g0 + grow;
+    const int n = g / Ho, a = g - n * Ho;
+    const int k0 = n * L + a - T0;
+    const int b0 = cb << 3;
+    const int pg = b0 + gq;
+    bool ok = rr.wait_full(k0 + 1);
+    ok = rr.wait_full(k0) && ok;
+    float u, v;
+
+    // hat products of the nine (pixel shift, tap) pairs: index vt = 3 * vr + vc, with (da, fh) = (0,1), (0,2), (1,0) for
+    // vr = 0, 1, 2 and (db, fw) alike for vc
+    unsigned bf[9][2];
+#pragma unroll
+    for (int vr = 0; vr < 3; ++vr) {
+      const int da = vr == 2 ? 1 : 0, fh = vr == 2 ? 0 : vr + 1;
+      const __half* rp = rring + (size_t)rr.slot(k0 + da) * RL::kSlot + 8 + pg;
+#pragma unroll
+      for (int vc = 0; vc < 3; ++vc) {
+        const int db = vc == 2 ? 1 : 0, fw = vc == 2 ? 0 : vc + 1;
+        beta_tap<WOP, SC44>(bf[vr * 3 + vc], rp + 2 * (fh * 3 + fw) * WOP + db, (float)fh, (float)fw, lc, uh0, uw0, u, v);
+      }
+    }
+    ok = rd.wait_full(k0 + 1) && ok;
+    ok = rd.wait_full(k0) && ok;
+    if (!ok) {
+      ring_fail(lane);
+      return;
+    }
+    const int b = b0 + 2 * q;
+    const __half* dr[2];
+#pragma unroll
+    for (int da = 0; da < 2; ++da) dr[da] = dring + (size_t)rd.slot(k0 + da) * slot_halves + gq * INNER + 8 + b;
+
+    const unsigned* bkp = reinterpret_cast<const unsigned*>(bank + gq * kBankPitch) + q;
+    __half* x0 = dx + ((size_t)n * p.C + c0 + gq) * dplane + (size_t)(2 * a) * W + 2 * b;
+    const bool row1 = 2 * a + 1 < H, col_ok = 2 * b < W;
+#pragma unroll 3
+    for (int sb = 0; sb < nslab; ++sb) {
+      unsigned af[4];
+      af[0] = bkp[sb * (16 * kBankPitch / 2)];
+      af[1] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2];
+      af[2] = bkp[sb * (16 * kBankPitch / 2) + 4];
+      af[3] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2 + 4];
+      // dy of channel rows gq (fa) and gq + 8 (fb): [da][column b, b+1, b+2], widened to fp32
+      float fa[2][3], fb[2][3];
+#pragma unroll
+      for (int da = 0; da < 2; ++da) {
+        const unsigned* p0 = reinterpret_cast<const unsigned*>(dr[da] + sb * 16 * INNER);
+        const unsigned* p1 = p0 + 8 * INNER / 2;
+        const unsigned w0 = p0[0], w1 = p0[1], v0 = p1[0], v1 = p1[1];
+        fa[da][0] = h_lo(w0); fa[da][1] = h_hi(w0); fa[da][2] = h_lo(w1);
+        fb[da][0] = h_lo(v0); fb[da][1] = h_hi(v0); fb[da][2] = h_lo(v1);
+      }
+      float acc[2][2][4];  // [channel row][rr][dx columns 2b .. 2b+3]
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[0][0][i] = acc[0][1][i] = acc[1][0][i] = acc[1][1][i] = 0.f;
+#pragma unroll
+      for (int vr = 0; vr < 3; ++vr) {
+        const int da = vr == 2 ? 1 : 0, rr_ = vr == 0 ? 0 : 1;
+#pragma unroll
+        for (int vc = 0; vc < 3; ++vc) {
+          const int db = vc == 2 ? 1 : 0, cc = vc == 0 ? 0 : 1;
+          float kd[4];
+          mma_new(kd, af, bf[vr * 3 + vc][0], bf[vr * 3 + vc][1]);
+          acc[0][rr_][cc] = fmaf(kd[0], fa[da][db], acc[0][rr_][cc]);
+          acc[0][rr_][2 + cc] = fmaf(kd[1], fa[da][1 + db], acc[0][rr_][2 + cc]);
+          acc[1][rr_][cc] = fmaf(kd[2], fb[da][db], acc[1][rr_][cc]);
+          acc[1][rr_][2 + cc] = fmaf(kd[3], fb[da][1 + db], acc[1][rr_][2 + cc]);
+        }
+      }
+      if (col_ok) {
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          __half* xa = x0 + ((size_t)sb * 16 + ch * 8) * dplane;
+          const __half2 lo = __floats2half2_rn(acc[ch][0][0], acc[ch][0][1]), hi = __floats2half2_rn(acc[ch][0][2], acc[ch][0][3]);
+          *reinterpret_cast<uint2*>(xa) = make_uint2(*reinterpret_cast<const unsigned*>(&lo), *reinterpret_cast<const unsigned*>(&hi));
+          if (row1) {
+            const __half2 lo1 = __floats2half2_rn(acc[ch][1][0], acc[ch][1][1]), hi1 = __floats2half2_rn(acc[ch][1][2], acc[ch][1][3]);
+            *reinterpret_cast<uint2*>(xa + W) = make_uint2(*reinterpret_cast<const unsigned*>(&lo1), *reinterpret_cast<const unsigned*>(&hi1));
+          }
+        }
+      }
+    }
+    // every stream row is read by the output rows a - 1 and a; the first / last row of the range stands in for a missing neighbour
+    __syncwarp();
+    if (lane == 0) {
+      const bool first = (a == 0) || (g == g0), last = (a == Ho - 1) || (g == g1 - 1);
+      rd.release(k0, first ? 2 : 1);
+      rr.release(k0, first ? 2 : 1);
+      rd.release(k0 + 1, last ? 2 : 1);
+      rr.release(k0 + 1, last ? 2 : 1);
+    }
+  }
+}
+
 // ================================================================== grad-offsets + grad-bank in one pass
 //
 // Item = 8 output pixels (oh, ow0 .. ow0+7).  The warp that owns it runs over all channel slabs of the
@@ -410,7 +627,7 @@ __host__ __device__ inline size_t gw_ring_smem(int cg, int inner_x, int inner_d,
          16 + 128;
 }
 
-template <int S, int W, int NS, int MAXT>
+template <int S, int W, int NS, bool SC44, int MAXT>
 __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
                                                           const __half* __restrict__ dy, const __half* __restrict__ rot,
                                                           const __half* __restrict__ bankw, __half* __restrict__ drot,
@@ -428,17 +645,14 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
   __half* xring = reinterpret_cast<__half*>(smem_raw);
   __half* dring = xring + (size_t)R * xslot + 64;  // 128 bytes of zeros behind each ring; TMA destinations stay 128-byte aligned
   __half* rring = dring + (size_t)RR * dslot + 64;
-  unsigned char* rings_end = reinterpret_cast<unsigned char*>(rring + (size_t)RR * RL::kSlot);
-  unsigned char* after = rings_end;
-  {
-    unsigned char* red_end = smem_raw + (size_t)ncw * CG * 16 * 4;
-    if (red_end > after) after = red_end;
-    after = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(after) + 15) & ~(uintptr_t)15);
-  }
-  __half* bankT = reinterpret_cast<__half*>(after);  // [16 cells][CG + 8]
-  unsigned char* scratch = reinterpret_cast<unsigned char*>(bankT + 16 * pitchT);
-  unsigned long long* bars =
-      reinterpret_cast<unsigned long long*>((reinterpret_cast<uintptr_t>(scratch + (size_t)ncw * kGwScratch) + 7) & ~(uintptr_t)7);
+  // everything is addressed as smem_raw + offset, so that the compiler keeps using shared-memory loads and stores
+  const unsigned rings_bytes = (unsigned)(((size_t)R * xslot + 64 + (size_t)RR * dslot + 64 + (size_t)RR * RL::kSlot) * 2);
+  const unsigned red_bytes = (unsigned)ncw * CG * 16 * 4;
+  const unsigned after = ((rings_bytes > red_bytes ? rings_bytes : red_bytes) + 15u) & ~15u;
+  __half* bankT = reinterpret_cast<__half*>(smem_raw + after);  // [16 cells][CG + 8]
+  const unsigned scratch_off = after + 16 * pitchT * 2;
+  unsigned char* scratch = smem_raw + scratch_off;
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + ((scratch_off + (unsigned)ncw * kGwScratch + 7u) & ~7u));
   Ring rx, rd, rr;
   rx.full = smem_u32(bars); rx.empty = rx.full + 8 * R; rx.lg = p.lgR;
   rd.full = rx.empty + 8 * R; rd.empty = rd.full + 8 * RR; rd.lg = p.lgRR;
@@ -464,7 +678,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
   }
   {
     uint4* z = reinterpret_cast<uint4*>(smem_raw);
-    const int nz = (int)((rings_end - smem_raw) >> 4);
+    const int nz = (int)(rings_bytes >> 4);
     for (int i = threadIdx.x; i < nz; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
   }
   for (int i = threadIdx.x; i < 16 * CG; i += blockDim.x) {
@@ -527,7 +741,6 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
   const int cw = warp - 1;
   const int gq = lane >> 2, q = lane & 3;
   const LaneCells lc = lane_cells_of(p.scW, p.cells, q);
-  const bool sc44 = p.scH == 4 && p.scW == 4;
   const float uh0 = (float)(p.scH - 3) * 0.5f, uw0 = (float)(p.scW - 3) * 0.5f;
   const int nslab = CG >> 4;
   const int items = g0 < g1 ? (g1 - g0) * NB : 0;
@@ -553,7 +766,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
     const int ow = ow0 + 2 * q;
     const __half* rp = rring + (size_t)rr.slot(grow) * RL::kSlot + 8 + pg;
     const __half* dyr = dring + (size_t)rd.slot(grow) * dslot + gq * ID + 8 + ow;
-    __half* drot_n = drot + (size_t)n * 18 * P;
+    __half* drot_item = drot + (size_t)n * 18 * P + oh * Wo + ow0;
 
     // One pass per kernel row fh (three taps): keeps 12 instead of 36 accumulators of G live, and its source row is
     // waited for only when the pass starts.
@@ -566,13 +779,10 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
       for (int fw = 0; fw < 3; ++fw) {
         unsigned bb[2];
         float u, v;
-        beta_tap<WOP>(bb, rp + 2 * (fh * 3 + fw) * WOP, (float)fh, (float)fw, lc, sc44, uh0, uw0, u, v);
+        beta_tap<WOP, SC44>(bb, rp + 2 * (fh * 3 + fw) * WOP, (float)fh, (float)fw, lc, uh0, uw0, u, v);
         bw[fw][0] = movmatrix_trans(bb[0]);
         bw[fw][1] = movmatrix_trans(bb[1]);
-        if (q == 0) {
-          const bool valid = u > -1.f && v > -1.f && u < (float)p.scH && v < (float)p.scW;
-          uv[fw * 8 + gq] = make_float2(valid ? u : 1e30f, v);
-        }
+        if (q == 0) uv[fw * 8 + gq] = make_float2(u, v);
       }
       ok = rx.wait_full(k0 + fh) && ok;
       if (!ok) break;
@@ -597,21 +807,17 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
             d0[fw] = hmul2u(dy0, tap_pair<S>(w0, w1, w2, fw));
             d1[fw] = hmul2u(dy1, tap_pair<S>(v0, v1, v2, fw));
           }
-          if (drot != nullptr) {
-            // A = W^T slab: rows = cells (gq, gq+8), k = channels (2q, 2q+1) and (2q+8, 2q+9)
-            const unsigned* wt0 = reinterpret_cast<const unsigned*>(bankT + gq * pitchT + sidx * 16);
-            const unsigned* wt1 = reinterpret_cast<const unsigned*>(bankT + (gq + 8) * pitchT + sidx * 16);
-            const unsigned a0 = wt0[q], a1 = wt1[q], a2 = wt0[q + 4], a3 = wt1[q + 4];
+          // A = W^T slab: rows = cells (gq, gq+8), k = channels (2q, 2q+1) and (2q+8, 2q+9)
+          const unsigned* wt0 = reinterpret_cast<const unsigned*>(bankT + gq * pitchT + sidx * 16);
+          const unsigned* wt1 = reinterpret_cast<const unsigned*>(bankT + (gq + 8) * pitchT + sidx * 16);
+          const unsigned a0 = wt0[q], a1 = wt1[q], a2 = wt0[q + 4], a3 = wt1[q + 4];
 #pragma unroll
-            for (int fw = 0; fw < 3; ++fw) mma16816_acc(G[fw], a0, a1, a2, a3, movmatrix_trans(d0[fw]), movmatrix_trans(d1[fw]));
-          }
-          if (partial != nullptr) {
-            // k = 16 = 8 pixels x (tap 0 | tap 1), then 8 pixels x (tap 2 | nothing)
-            mma16816_acc(acc[sidx][0], d0[0], d1[0], d0[1], d1[1], bw[0][0], bw[1][0]);
-            mma16816_acc(acc[sidx][1], d0[0], d1[0], d0[1], d1[1], bw[0][1], bw[1][1]);
-            mma16816_acc(acc[sidx][0], d0[2], d1[2], 0u, 0u, bw[2][0], 0u);
-            mma16816_acc(acc[sidx][1], d0[2], d1[2], 0u, 0u, bw[2][1], 0u);
-          }
+          for (int fw = 0; fw < 3; ++fw) mma16816_acc(G[fw], a0, a1, a2, a3, movmatrix_trans(d0[fw]), movmatrix_trans(d1[fw]));
+          // k = 16 = 8 pixels x (tap 0 | tap 1), then 8 pixels x (tap 2 | nothing)
+          mma16816_acc(acc[sidx][0], d0[0], d1[0], d0[1], d1[1], bw[0][0], bw[1][0]);
+          mma16816_acc(acc[sidx][1], d0[0], d1[0], d0[1], d1[1], bw[0][1], bw[1][1]);
+          mma16816_acc(acc[sidx][0], d0[2], d1[2], 0u, 0u, bw[2][0], 0u);
+          mma16816_acc(acc[sidx][1], d0[2], d1[2], 0u, 0u, bw[2][1], 0u);
         }
       }
       if (fh == 2) {
@@ -626,47 +832,43 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
         }
       }
 
-      // d(offset)[pixel, tap, dir] = sum over the four corner cells of G * d(coefficient)/d(u or v)  (floor-based:
-      // at an integer coordinate the right-hand derivative, as csrc/filter_sample_depthwise_cuda_kernel.cu:137-158)
-      if (drot != nullptr) {
-        __syncwarp();
+      // d(offset)[pixel, tap, dir] = sum over the four corner cells of G * d(coefficient)/d(u or v).  Floor-based, so at an
+      // integer coordinate it is the right-hand derivative and at the upper edge the derivative into the zero extension
+      // (csrc/filter_sample_depthwise_cuda_kernel.cu:137-158); zero when the tap samples outside the bank (:131-135).
+      __syncwarp();
 #pragma unroll
-        for (int tt = 0; tt < 3; ++tt) {
-          *reinterpret_cast<float2*>(Gs + (tt * 16 + gq) * 8 + 2 * q) = make_float2(G[tt][0], G[tt][1]);
-          *reinterpret_cast<float2*>(Gs + (tt * 16 + gq + 8) * 8 + 2 * q) = make_float2(G[tt][2], G[tt][3]);
-        }
-        __syncwarp();
-        if (lane < 24) {
-          const int px = lane & 7, tt = lane >> 3;
-          const int t = fh * 3 + tt;
-          const float2 c = uv[tt * 8 + px];
-          float gu = 0.f, gv = 0.f;
-          if (c.x < 1e29f) {
-            const float fu = floorf(c.x), fv = floorf(c.y);
-            const int h0 = (int)fu, w0 = (int)fv;
-            const float lh = c.x - fu, lw = c.y - fv;
-            const float hh = 1.f - lh, hw = 1.f - lw;
-            const float* Gp = Gs + tt * 128 + px;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const int a = h0 + (k >> 1), b = w0 + (k & 1);
-              if (a >= 0 && a < p.scH && b >= 0 && b < p.scW) {
-                const float gval = Gp[(a * p.scW + b) * 8];
-                const float du = (k >> 1) ? ((k & 1) ? lw : hw) : ((k & 1) ? -lw : -hw);
-                const float dv = (k & 1) ? ((k >> 1) ? lh : hh) : ((k >> 1) ? -lh : -hh);
-                gu += du * gval;
-                gv += dv * gval;
-              }
-            }
-          }
-          if (ow0 + px < Wo) {
-            const size_t o = (size_t)(2 * t) * P + oh * Wo + ow0 + px;
-            drot_n[o] = __float2half_rn(gu);
-            drot_n[o + P] = __float2half_rn(gv);
-          }
-        }
-        __syncwarp();
+      for (int tt = 0; tt < 3; ++tt) {
+        *reinterpret_cast<float2*>(Gs + (tt * 16 + gq) * 8 + 2 * q) = make_float2(G[tt][0], G[tt][1]);
+        *reinterpret_cast<float2*>(Gs + (tt * 16 + gq + 8) * 8 + 2 * q) = make_float2(G[tt][2], G[tt][3]);
       }
+      __syncwarp();
+      if (lane < 24) {
+        const int px = lane & 7, tt = lane >> 3;
+        const float2 c = uv[tt * 8 + px];
+        const int scH = SC44 ? 4 : p.scH, scW = SC44 ? 4 : p.scW;
+        const bool valid = c.x > -1.f && c.y > -1.f && c.x < (float)scH && c.y < (float)scW;
+        const float fu = floorf(c.x), fv = floorf(c.y);
+        const float lh = c.x - fu, lw = c.y - fv;
+        const float hh = 1.f - lh, hw = 1.f - lw;
+        // corner rows h0, h0+1 and columns w0, w0+1, clamped into the bank for the loads; a corner outside counts as 0
+        const int h0 = (int)fmaxf(fminf(fu, (float)scH), -2.f), w0 = (int)fmaxf(fminf(fv, (float)scW), -2.f);
+        const bool r0 = h0 >= 0 && h0 < scH, r1 = h0 + 1 >= 0 && h0 + 1 < scH;
+        const bool c0 = w0 >= 0 && w0 < scW, c1 = w0 + 1 >= 0 && w0 + 1 < scW;
+        const int ra = min(max(h0, 0), scH - 1) * scW, rb = min(max(h0 + 1, 0), scH - 1) * scW;
+        const int ca = min(max(w0, 0), scW - 1), cb2 = min(max(w0 + 1, 0), scW - 1);
+        const float* Gp = Gs + tt * 128 + px;
+        const float g00 = (r0 && c0) ? Gp[(ra + ca) * 8] : 0.f, g01 = (r0 && c1) ? Gp[(ra + cb2) * 8] : 0.f;
+        const float g10 = (r1 && c0) ? Gp[(rb + ca) * 8] : 0.f, g11 = (r1 && c1) ? Gp[(rb + cb2) * 8] : 0.f;
+        float gu = hw * (g10 - g00) + lw * (g11 - g01);
+        float gv = hh * (g01 - g00) + lh * (g11 - g10);
+        if (!valid) gu = gv = 0.f;
+        if (ow0 + px < Wo) {
+          __half* o = drot_item + (2 * (fh * 3 + tt)) * P + px;
+          o[0] = __float2half_rn(gu);
+          o[P] = __float2half_rn(gv);
+        }
+      }
+      __syncwarp();
     }
     if (!ok) {
       ring_fail(lane);
@@ -676,7 +878,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
 
   // ---- bank gradient: sum the consumer warps' accumulators (the rings are free now) and write this block's partial
   asm volatile("bar.sync 1, %0;\n" ::"r"(ncw * 32) : "memory");
-  if (partial != nullptr) {
+  {
     float* red = reinterpret_cast<float*>(smem_raw);  // [ncw][CG][16]
 #pragma unroll
     for (int sidx = 0; sidx < NS; ++sidx) {
@@ -788,8 +990,8 @@ ConvRingPlan conv_ring_plan(const Geom& g) {
   return pl;
 }
 
-template <int S, int W, bool TR>
-int launch_conv_ring(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, cudaStream_t s) {
+template <int S, int W, bool TR, bool SC44>
+int launch_conv_ring_sc(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, cudaStream_t s) {
   using Sh = ConvShape<S, W, TR>;
   const ConvRingPlan pl = conv_ring_plan<S, W, TR>(g);
   if (!pl.ok) return DK_ERR_UNSUPPORTED;
@@ -810,15 +1012,69 @@ int launch_conv_ring(const __half* src, const __half* rot, const __half* w, __ha
 #endif
   int rc;
   if (warps <= 21) {
-    auto kern = ring_conv_kernel<S, W, TR, 672>;
+    auto kern = ring_conv_kernel<S, W, TR, SC44, 672>;
     if ((rc = enable_smem(kern, pl.smem))) return rc;
     kern<<<dim3(pl.blocks_x, pl.groups), warps * 32, pl.smem, s>>>(tm, rot, w, dst, p);
   } else {
-    auto kern = ring_conv_kernel<S, W, TR, 800>;
+    auto kern = ring_conv_kernel<S, W, TR, SC44, 800>;
     if ((rc = enable_smem(kern, pl.smem))) return rc;
     kern<<<dim3(pl.blocks_x, pl.groups), (warps > 25 ? 25 : warps) * 32, pl.smem, s>>>(tm, rot, w, dst, p);
   }
   return check_launch();
+}
+
+template <int S, int W, bool TR>
+int launch_conv_ring(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, cudaStream_t s) {
+  if (g.scH == 4 && g.scW == 4) return launch_conv_ring_sc<S, W, TR, true>(src, rot, w, dst, g, s);
+  return launch_conv_ring_sc<S, W, TR, false>(src, rot, w, dst, g, s);
+}
+
+__host__ __device__ inline size_t convT2_ring_smem(int cg, int inner, int rot_slot, int R) {
+  return ((size_t)R * cg * inner + 64 + (size_t)R * rot_slot + (size_t)cg * kBankPitch) * 2 + 8 + (size_t)4 * R * 8 + 16 + 128;
+}
+
+template <int W, bool SC44>
+int launch_convT2_ring_sc(const __half* dy, const __half* rot, const __half* w, __half* dx, const Geom& g, cudaStream_t s) {
+  using Sh = ConvT2Shape<W>;
+  using RL = RotLayout<Sh::kWo>;
+  if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(dx) & 7) || (reinterpret_cast<uintptr_t>(dy) & 15) || (W & 3))
+    return DK_ERR_UNSUPPORTED;
+  const size_t budget = (size_t)device_smem_optin();
+  int cg = 0, groups = 0, lgR = 0;
+  size_t smem = 0;
+  for (int gr = 1; gr <= g.C / 16 && !cg; ++gr) {
+    if (g.C % (16 * gr) || g.C / gr > 256) continue;
+    for (int lg = 3; lg >= 2 && !cg; --lg) {
+      const size_t need = convT2_ring_smem(g.C / gr, Sh::kInner, RL::kSlot, 1 << lg);
+      if (need > budget) continue;
+      cg = g.C / gr; groups = gr; lgR = lg; smem = need;
+    }
+  }
+  if (!cg || groups > 65535) return DK_ERR_UNSUPPORTED;
+  CUtensorMap tm;
+  if (Sh::kTma) {
+    if (!make_row_map(&tm, dy, Sh::kWo, g.Ho, (long long)g.N * g.C, Sh::kInner, cg)) return DK_ERR_UNSUPPORTED;
+  } else {
+    memset(&tm, 0, sizeof(tm));
+  }
+  RingParams p;
+  p.N = g.N; p.C = g.C; p.Hs = g.Ho; p.Hd = g.H;
+  p.CG = cg; p.lgR = lgR; p.lgRR = lgR;
+  p.L = g.Ho + 1;
+  p.rows_total = g.N * g.Ho;
+  int blocks_x;
+  spread_rows((long long)g.N * g.Ho, groups, &blocks_x, &p.rows_per_block);
+  p.scH = g.scH; p.scW = g.scW; p.cells = g.cells;
+  auto kern = ring_convT2_kernel<W, SC44, 640>;
+  int rc = enable_smem(kern, smem);
+  if (rc) return rc;
+  kern<<<dim3(blocks_x, groups), 20 * 32, smem, s>>>(tm, dy, rot, w, dx, p);
+  return check_launch();
+}
+template <int W>
+int launch_convT2_ring(const __half* dy, const __half* rot, const __half* w, __half* dx, const Geom& g, cudaStream_t s) {
+  if (g.scH == 4 && g.scW == 4) return launch_convT2_ring_sc<W, true>(dy, rot, w, dx, g, s);
+  return launch_convT2_ring_sc<W, false>(dy, rot, w, dx, g, s);
 }
 
 struct GwRingPlan {
@@ -852,13 +1108,13 @@ GwRingPlan gw_ring_plan(const Geom& g) {
   return pl;
 }
 
-template <int S, int W>
-int launch_gw_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
+template <int S, int W, bool SC44>
+int launch_gw_ring_sc(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
                    void* ws, size_t ws_bytes, cudaStream_t s) {
   using Sh = GwShape<S, W>;
   const GwRingPlan pl = gw_ring_plan<S, W>(g);
   if (!pl.ok) return DK_ERR_UNSUPPORTED;
-  if (dw != nullptr && (ws == nullptr || ws_bytes < pl.ws_bytes)) return DK_ERR_WORKSPACE;
+  if (ws == nullptr || ws_bytes < pl.ws_bytes) return DK_ERR_WORKSPACE;
   if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(dy) & 15)) return DK_ERR_UNSUPPORTED;
   CUtensorMap tmx, tmd;
   if (!make_row_map(&tmx, x, W, g.H, (long long)g.N * g.C, Sh::kInnerX, g.C)) return DK_ERR_UNSUPPORTED;
@@ -874,20 +1130,26 @@ int launch_gw_ring(const __half* dy, const __half* x, const __half* rot, const _
   p.rows_total = g.N * g.Ho;
   p.rows_per_block = pl.rows_per_block;
   p.scH = g.scH; p.scW = g.scW; p.cells = g.cells;
-  float* partial = dw != nullptr ? reinterpret_cast<float*>(ws) : nullptr;
+  float* partial = reinterpret_cast<float*>(ws);
   int rc;
   if (pl.ns == 6) {
-    auto kern = ring_gw_kernel<S, W, 6, 512>;
+    auto kern = ring_gw_kernel<S, W, 6, SC44, 512>;
     if ((rc = enable_smem(kern, pl.smem))) return rc;
     kern<<<pl.blocks_x, pl.warps * 32, pl.smem, s>>>(tmx, tmd, dy, rot, w, drot, partial, p);
   } else {
-    auto kern = ring_gw_kernel<S, W, 9, 384>;
+    auto kern = ring_gw_kernel<S, W, 9, SC44, 384>;
     if ((rc = enable_smem(kern, pl.smem))) return rc;
     kern<<<pl.blocks_x, pl.warps * 32, pl.smem, s>>>(tmx, tmd, dy, rot, w, drot, partial, p);
   }
   if ((rc = check_launch())) return rc;
-  if (dw != nullptr) return launch_reduce_bank_partials(partial, dw, g.C, g.cells, pl.blocks_x, s);
-  return DK_OK;
+  return launch_reduce_bank_partials(partial, dw, g.C, g.cells, pl.blocks_x, s);
+}
+
+template <int S, int W>
+int launch_gw_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
+                   void* ws, size_t ws_bytes, cudaStream_t s) {
+  if (g.scH == 4 && g.scW == 4) return launch_gw_ring_sc<S, W, true>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s);
+  return launch_gw_ring_sc<S, W, false>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s);
 }
 
 }  // namespace
@@ -908,7 +1170,7 @@ int local_conv_ring(const __half* src, const __half* rot, const __half* w, __hal
     if (g.W == 112) return g.sH == 1 ? launch_conv_ring<1, 112, false>(src, rot, w, dst, g, s) : launch_conv_ring<2, 112, false>(src, rot, w, dst, g, s);
     return g.sH == 1 ? launch_conv_ring<1, 56, false>(src, rot, w, dst, g, s) : launch_conv_ring<2, 56, false>(src, rot, w, dst, g, s);
   }
-  if (g.sH != 1) return DK_ERR_UNSUPPORTED;
+  if (g.sH != 1) return g.W == 112 ? launch_convT2_ring<112>(src, rot, w, dst, g, s) : launch_convT2_ring<56>(src, rot, w, dst, g, s);
   return g.W == 112 ? launch_conv_ring<1, 112, true>(src, rot, w, dst, g, s) : launch_conv_ring<1, 56, true>(src, rot, w, dst, g, s);
 }
 
@@ -921,10 +1183,10 @@ size_t local_gw_ring_workspace(const Geom& g) {
   return pl.ok ? pl.ws_bytes : 0;
 }
 
-// grad-offsets (drot, may be null) and grad-bank (dw, may be null) in one pass
+// grad-offsets and grad-bank in one pass
 int local_gw_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
                   void* ws, size_t ws_bytes, cudaStream_t s) {
-  if (!ring_shape(g)) return DK_ERR_UNSUPPORTED;
+  if (!ring_shape(g) || drot == nullptr || dw == nullptr) return DK_ERR_UNSUPPORTED;
   if (g.W == 112)
     return g.sH == 1 ? launch_gw_ring<1, 112>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s)
                      : launch_gw_ring<2, 112>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s);
