@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+
 #include "dk_b200.h"
 
 namespace dk {
@@ -127,6 +129,17 @@ template <typename A> __device__ __forceinline__ A dot4(const A (&c)[4], const A
 
 // ---------------------------------------------------------------- host side
 
+// Experiment knobs read from the environment exist only in builds made with -DDK_TUNING; the product build ignores them
+// (the one switch it keeps is DK_B200_DISABLE_MMA, which forces the general kernels for A/B runs).
+inline const char* tuning_env(const char* name) {
+#ifdef DK_TUNING
+  return std::getenv(name);
+#else
+  (void)name;
+  return nullptr;
+#endif
+}
+
 struct LaunchError {
   int status;
   cudaError_t cuda;
@@ -157,6 +170,10 @@ template <typename T>
 int local_backward_rotation(const T*, const T*, const T*, const T*, T*, const Geom&, void* ws, size_t ws_bytes, cudaStream_t);
 template <typename T>
 int local_backward_filter(const T* dy, const T* x, const T* rot, T* dw, const Geom&, void* ws, size_t ws_bytes, cudaStream_t);
+
+template <typename T>
+int local_backward_filter_fit(const T* dy, const T* x, const T* rot, T* dw, const Geom&, void* ws, size_t ws_bytes, cudaStream_t,
+                              bool launch, size_t* need_out);  // fixed-size workspace: the plan shrinks to fit
 
 template <typename T> int deform_forward(const T*, const T*, const T*, const T*, T*, const Geom&, cudaStream_t);
 template <typename T>
@@ -197,6 +214,7 @@ struct FilterPlan {
   size_t ws_bytes;   // pix_blocks * C * cells * sizeof(acc)
 };
 FilterPlan filter_plan(const Geom& g, size_t acc_bytes);
+FilterPlan filter_plan_fit(const Geom& g, size_t acc_bytes, size_t max_bytes);
 size_t deform_filter_mma_workspace(const Geom& g);
 size_t deform_coords_mma_workspace(const Geom& g);
 int deform_coords_mma(const __half* dy, const __half* x, const __half* off, const __half* rot, const __half* w, __half* doff,

@@ -1009,7 +1009,7 @@ bool dcn_fast_shape(const Geom& g) {
 }
 
 int min_items() {  // DK_B200_DCN_MIN_ITEMS: fewest items per band for which more than one slab per block is taken (tuning knob)
-  const char* e = getenv("DK_B200_DCN_MIN_ITEMS");
+  const char* e = tuning_env("DK_B200_DCN_MIN_ITEMS");
   const int v = e ? atoi(e) : 0;
   return v > 0 ? v : 14;  // measured at 56 x 56: forward 0.75 -> 0.69 ms with two slabs and 21 items; 7 items lose
 }
@@ -1144,7 +1144,7 @@ DCoordPlan dcoord_plan(const Geom& g, int ns_cap) {
 
 int slab_cap() {  // DK_B200_DCN_SLABS = 1, 2 or 4 caps the channel slabs per block (tuning knob)
   static const int cap = [] {
-    const char* e = getenv("DK_B200_DCN_SLABS");
+    const char* e = tuning_env("DK_B200_DCN_SLABS");
     const int v = e ? atoi(e) : 0;
     return (v == 1 || v == 2 || v == 4) ? v : 4;
   }();

@@ -565,9 +565,28 @@ FilterPlan filter_plan(const Geom& g, size_t acc_bytes) {
   return pl;
 }
 
+// The same plan with fewer, larger pixel blocks where its partial sums would not fit into max_bytes (pix_blocks = 0
+// when not even one block's partial sums fit).
+FilterPlan filter_plan_fit(const Geom& g, size_t acc_bytes, size_t max_bytes) {
+  FilterPlan pl = filter_plan(g, acc_bytes);
+  if (pl.ws_bytes <= max_bytes) return pl;
+  const size_t per_block = (size_t)g.C * g.cells * acc_bytes;
+  const long long fit = (long long)(max_bytes / per_block);
+  if (fit < 1) {
+    pl.pix_blocks = 0;
+    pl.ws_bytes = 0;
+    return pl;
+  }
+  const long long total = (long long)g.N * g.P;
+  pl.pix_per_block = (total + fit - 1) / fit;
+  pl.pix_blocks = (int)((total + pl.pix_per_block - 1) / pl.pix_per_block);
+  pl.ws_bytes = (size_t)pl.pix_blocks * per_block;
+  return pl;
+}
+
 template <typename T, bool DEFORM>
 static int filter_backward(const T* dy, const T* x, const T* off, const T* rot, T* dw, const Geom& g, void* ws,
-                           size_t ws_bytes, cudaStream_t s) {
+                           size_t ws_bytes, cudaStream_t s, bool fit = false) {
   using A = typename Compute<T>::type;
   if (DEFORM) {
     const PlanePlan pp = plane_plan<T, DEFORM>(g);
@@ -585,8 +604,8 @@ static int filter_backward(const T* dy, const T* x, const T* off, const T* rot, 
       return check_launch();
     }
   }
-  const FilterPlan pl = filter_plan(g, sizeof(A));
-  if (ws == nullptr || ws_bytes < pl.ws_bytes) return DK_ERR_WORKSPACE;
+  const FilterPlan pl = fit ? filter_plan_fit(g, sizeof(A), ws_bytes) : filter_plan(g, sizeof(A));
+  if (ws == nullptr || ws_bytes < pl.ws_bytes || pl.pix_blocks < 1) return DK_ERR_WORKSPACE;
   if (pl.chan_blocks > 65535 || g.G > 65535) return DK_ERR_UNSUPPORTED;
   const size_t smem =
       (size_t)pl.warps * g.cells * 32 * sizeof(A) + (size_t)kFilterPixBatch * g.taps * sizeof(TapEntry<A, DEFORM>);
@@ -614,6 +633,29 @@ int local_backward_filter(const T* dy, const T* x, const T* rot, T* dw, const Ge
   }
   return filter_backward<T, false>(dy, x, nullptr, rot, dw, g, ws, ws_bytes, s);
 }
+// The same for a caller whose workspace has a fixed size: the tensor-core kernel when its own partial sums fit, else the
+// general kernel with as many pixel blocks as fit.  need_out (optional) receives the bytes the call uses.
+template <typename T>
+int local_backward_filter_fit(const T* dy, const T* x, const T* rot, T* dw, const Geom& g, void* ws, size_t ws_bytes,
+                              cudaStream_t s, bool launch, size_t* need_out) {
+  if constexpr (std::is_same<T, __half>::value) {
+    if (mma_path_enabled()) {
+      const size_t fast = local_filter_mma_workspace(g);
+      if (fast > 0 && fast <= ws_bytes) {
+        if (need_out) *need_out = fast;
+        if (!launch) return DK_OK;
+        const int rc = local_filter_mma(dy, x, rot, dw, g, ws, ws_bytes, s);
+        if (rc != DK_ERR_UNSUPPORTED) return rc;
+      }
+    }
+  }
+  using A = typename Compute<T>::type;
+  const FilterPlan pl = filter_plan_fit(g, sizeof(A), ws_bytes);
+  if (pl.pix_blocks < 1) return DK_ERR_WORKSPACE;
+  if (need_out) *need_out = pl.ws_bytes;
+  if (!launch) return DK_OK;
+  return filter_backward<T, false>(dy, x, nullptr, rot, dw, g, ws, ws_bytes, s, true);
+}
 template <typename T>
 int deform_backward_filter(const T* dy, const T* x, const T* off, const T* rot, T* dw, const Geom& g, void* ws,
                            size_t ws_bytes, cudaStream_t s) {
@@ -632,6 +674,8 @@ int deform_backward_filter(const T* dy, const T* x, const T* off, const T* rot, 
   template int local_backward_rotation<T>(const T*, const T*, const T*, const T*, T*, const Geom&, void*, size_t, \
                                           cudaStream_t);                                                           \
   template int local_backward_filter<T>(const T*, const T*, const T*, T*, const Geom&, void*, size_t, cudaStream_t); \
+  template int local_backward_filter_fit<T>(const T*, const T*, const T*, T*, const Geom&, void*, size_t, cudaStream_t, bool,  \
+                                            size_t*);                                                                          \
   template int deform_backward_filter<T>(const T*, const T*, const T*, const T*, T*, const Geom&, void*, size_t,      \
                                          cudaStream_t);
 DK_INSTANTIATE_LOCAL(float)

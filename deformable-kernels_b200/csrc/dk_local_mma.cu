@@ -19,6 +19,9 @@
 // group, at most 16 bank cells, channels a multiple of 16.
 // Everything else stays on the SIMT kernels of dk_local.cu.
 #include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <vector>
 
 #include "dk_mma_common.cuh"
 
@@ -27,6 +30,33 @@ namespace dk {
 using namespace mma;
 
 namespace {
+
+// Block shapes are searched once per (geometry, pass) and remembered: the latency-bound small calls would otherwise pay
+// the search on every launch.  (Builds with -DDK_TUNING, whose knobs can change between calls, search every time.)
+template <typename Plan, typename F>
+Plan cached_plan(const Geom& g, int tag, F compute) {
+#ifdef DK_TUNING
+  (void)tag;
+  return compute();
+#else
+  struct Entry {
+    Geom g;
+    int tag;
+    Plan pl;
+  };
+  static std::mutex mu;
+  static std::vector<Entry> cache;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Entry& e : cache)
+      if (e.tag == tag && std::memcmp(&e.g, &g, sizeof(Geom)) == 0) return e.pl;
+  }
+  const Plan pl = compute();
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() < 256) cache.push_back(Entry{g, tag, pl});
+  return pl;
+#endif
+}
 
 // ================================================================== forward / grad-input
 struct ConvPlan {
@@ -218,16 +248,16 @@ size_t conv_smem(const Geom& g, bool transposed, int cg, int bh) {
 }
 
 // Channel group, band height and warps per block are chosen together by an estimate of the time per output row.
-ConvPlan conv_plan(const Geom& g, bool transposed) {
+ConvPlan conv_plan_search(const Geom& g, bool transposed) {
   ConvPlan pl;
   const int S = g.sH;
   const int Hd = transposed ? g.H : g.Ho, Wd = transposed ? g.W : g.Wo;
   const int NB = (Wd + 7) / 8;
   int cg_only = 0, cap = Hd;
   size_t budget = kTwoPerSm;
-  if (const char* e = std::getenv("DK_B200_CONV_CG")) cg_only = atoi(e) > 0 ? atoi(e) : 0;        // tuning knobs
-  if (const char* e = std::getenv("DK_B200_CONV_BH")) cap = atoi(e) > 0 ? atoi(e) : cap;
-  if (const char* e = std::getenv("DK_B200_CONV_SMEM_KB")) budget = (size_t)atoi(e) * 1024;
+  if (const char* e = tuning_env("DK_B200_CONV_CG")) cg_only = atoi(e) > 0 ? atoi(e) : 0;        // tuning knobs
+  if (const char* e = tuning_env("DK_B200_CONV_BH")) cap = atoi(e) > 0 ? atoi(e) : cap;
+  if (const char* e = tuning_env("DK_B200_CONV_SMEM_KB")) budget = (size_t)atoi(e) * 1024;
   static const int kCgMax[] = {64, 96, 128, 192, 256, 320, 480};
   double best_cost = 1e30;
   pl.BH = 0;
@@ -285,6 +315,10 @@ ConvPlan conv_plan(const Geom& g, bool transposed) {
   pl.bands = (Hd + pl.BH - 1) / pl.BH;
   pl.smem = conv_smem(g, transposed, pl.CG, pl.BH);
   return pl;
+}
+
+ConvPlan conv_plan(const Geom& g, bool transposed) {
+  return cached_plan<ConvPlan>(g, transposed ? 1 : 0, [&] { return conv_plan_search(g, transposed); });
 }
 
 template <int S, bool TRANSPOSED>
@@ -490,7 +524,7 @@ static bool rot_dy_direct(const Geom& g) {
   // even rows (the pixel pairs of dy are aligned words) and small planes: measured faster up to 28 x 28 outputs
   // (0.095 -> 0.080, 0.083 -> 0.056 ms), slower on the wide layers, whose blocks walk over many slabs per item
   bool on = (g.Wo & 1) == 0 && g.P <= 784;
-  if (const char* e = std::getenv("DK_B200_ROT_DY_DIRECT")) on = on && atoi(e) != 0;  // comparison runs
+  if (const char* e = tuning_env("DK_B200_ROT_DY_DIRECT")) on = on && atoi(e) != 0;  // comparison runs
   return on;
 }
 static size_t rot_smem(const Geom& g, int cg, int bh, int warps) {
@@ -501,7 +535,7 @@ static size_t rot_smem(const Geom& g, int cg, int bh, int warps) {
          (size_t)16 * (cg + 8) * 2 + (size_t)warps * kRotScratch;
 }
 
-RotPlan rot_plan(const Geom& g) {
+RotPlan rot_plan_search(const Geom& g) {
   RotPlan pl;
   const int NB = (g.Wo + 7) / 8;
   const long long min_ctas = 2 * 148;
@@ -514,7 +548,7 @@ RotPlan rot_plan(const Geom& g) {
   // spread over more items (measured: C = 144 at 56 x 56 0.38 -> 0.22 ms, never slower on the sweep's layers).
   // DK_B200_ROT_BIG=0 tries two blocks per SM first (tuning knob).
   static const int first_attempt = [] {
-    const char* e = std::getenv("DK_B200_ROT_BIG");
+    const char* e = tuning_env("DK_B200_ROT_BIG");
     return (e && atoi(e) == 0) ? 0 : 1;
   }();
   for (int k = 0; k < 2 && !pl.BH; ++k) {
@@ -523,7 +557,7 @@ RotPlan rot_plan(const Geom& g) {
     const int maxw = attempt == 0 ? 8 : 16;
     int tallest = 0;
     int cap = g.Ho;
-    if (const char* e = std::getenv("DK_B200_ROT_BH")) cap = atoi(e) > 0 ? atoi(e) : cap;  // tuning knob
+    if (const char* e = tuning_env("DK_B200_ROT_BH")) cap = atoi(e) > 0 ? atoi(e) : cap;  // tuning knob
     for (int bh = 1; bh <= g.Ho && bh <= cap; ++bh) {
       if (rot_smem(g, g.C, bh, pick_warps(bh * NB, maxw)) > budget) break;
       tallest = bh;
@@ -586,6 +620,10 @@ RotPlan rot_plan(const Geom& g) {
     pl.ws_bytes = pl.groups > 1 ? (size_t)pl.groups * g.N * 18 * g.P * sizeof(float) : 0;
   }
   return pl;
+}
+
+RotPlan rot_plan(const Geom& g) {
+  return cached_plan<RotPlan>(g, 2, [&] { return rot_plan_search(g); });
 }
 
 // ------------------------------------------------------------------ grad-bank
@@ -771,20 +809,20 @@ __global__ void reduce_bank_partials_kernel(const float* __restrict__ partial, _
   if (lane == 0) out[i] = __float2half_rn(s);
 }
 
-FiltPlan filt_plan(const Geom& g) {
+FiltPlan filt_plan_search(const Geom& g) {
   FiltPlan pl;
   const int S = g.sH;
   // Two shapes of block: up to four channel slabs and two blocks per SM, or six slabs in one block of up to
   // 14 warps per SM.  The second halves the hat-product work per slab; it pays on wide rows where the first
   // would be stuck with three slabs (measured: C = 96 at 112 x 112).
   int cg_small = (g.C % 64 == 0) ? 64 : (g.C % 48 == 0) ? 48 : (g.C % 32 == 0) ? 32 : 16;
-  if (const char* e = std::getenv("DK_B200_FILT_CG")) {  // tuning knob: 16, 32, 48 or 64 channels per block
+  if (const char* e = tuning_env("DK_B200_FILT_CG")) {  // tuning knob: 16, 32, 48 or 64 channels per block
     const int v = atoi(e);
     if ((v == 16 || v == 32 || v == 48 || v == 64) && g.C % v == 0) cg_small = v;
   }
   const int cg_big = (g.C % 96 == 0) ? 96 : (g.C % 80 == 0) ? 80 : cg_small;
   pl.big = cg_big >= 2 * cg_small && (g.Wo + 7) / 8 >= 14;
-  if (const char* e = std::getenv("DK_B200_FILT_BIG")) pl.big = atoi(e) != 0;  // tuning knob
+  if (const char* e = tuning_env("DK_B200_FILT_BIG")) pl.big = atoi(e) != 0;  // tuning knob
   pl.CG = pl.big ? cg_big : cg_small;
   pl.groups = g.C / pl.CG;
   const int NB = (g.Wo + 7) / 8;
@@ -795,17 +833,17 @@ FiltPlan filt_plan(const Geom& g) {
   // by; with even output rows it is read straight into registers and the room goes to a taller band (fewer halo rows
   // of x per output row).  DK_B200_FILT_DY_DIRECT=0 keeps the band (comparison runs).
   pl.dy_direct = (g.Wo & 1) == 0;
-  if (const char* e = std::getenv("DK_B200_FILT_DY_DIRECT")) pl.dy_direct = pl.dy_direct && atoi(e) != 0;
+  if (const char* e = tuning_env("DK_B200_FILT_DY_DIRECT")) pl.dy_direct = pl.dy_direct && atoi(e) != 0;
   // Six-slab blocks on rows of 8 n pixels (16-byte pieces per item and channel row): their warps waited 2.5 issue slots
   // per instruction on the register loads of dy (two slabs of lookahead is all the registers allow), so each warp copies
   // the whole next item into a ring of its own instead: 0.58 -> 0.47 ms on C = 96 at 112 x 112.  The four-slab blocks
   // fetch all of an item's dy before its hat products and gain nothing (measured 0-7 % slower with the ring).
   // DK_B200_FILT_DY_RING=0 keeps the register path (comparison runs).
   pl.dy_ring = pl.big && pl.dy_direct && (g.Wo & 7) == 0 && (g.P & 7) == 0;
-  if (const char* e = std::getenv("DK_B200_FILT_DY_RING")) pl.dy_ring = pl.dy_ring && atoi(e) != 0;
+  if (const char* e = tuning_env("DK_B200_FILT_DY_RING")) pl.dy_ring = pl.dy_ring && atoi(e) != 0;
   // measured: taller bands pay at stride 1 once dy is out of shared memory (five rows of 112 with the ring: 0.468 -> 0.452 ms)
   int max_items = (pl.dy_direct && S == 1) ? (pl.dy_ring ? 70 : 56) : 24;
-  if (const char* e = std::getenv("DK_B200_FILT_ITEMS")) max_items = atoi(e) > 0 ? atoi(e) : max_items;  // tuning knob
+  if (const char* e = tuning_env("DK_B200_FILT_ITEMS")) max_items = atoi(e) > 0 ? atoi(e) : max_items;  // tuning knob
   auto shape = [&](int bh, int* warps) {
     *warps = pick_warps(bh * NB, pl.big ? 14 : 8);
     const size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + (pl.dy_direct ? 0 : band_pitch(bh, Wpo))) * 2 +
@@ -829,7 +867,7 @@ FiltPlan filt_plan(const Geom& g) {
   long long per_sm = 16 / pl.warps;
   if (per_sm > (long long)((228 * 1024) / (pl.smem + 1024))) per_sm = (long long)((228 * 1024) / (pl.smem + 1024));
   if (per_sm < 1) per_sm = 1;
-  if (const char* e = std::getenv("DK_B200_FILT_BLOCKS_PER_SM")) per_sm = atoi(e) > 0 ? atoi(e) : per_sm;  // tuning knob
+  if (const char* e = tuning_env("DK_B200_FILT_BLOCKS_PER_SM")) per_sm = atoi(e) > 0 ? atoi(e) : per_sm;  // tuning knob
   long long want = per_sm * 148 / pl.groups;
   if (want > units) want = units;
   if (want < 1) want = 1;
@@ -837,6 +875,10 @@ FiltPlan filt_plan(const Geom& g) {
   pl.blocks_x = (int)((units + pl.units_per_block - 1) / pl.units_per_block);
   pl.ws_bytes = (size_t)pl.blocks_x * g.C * 16 * sizeof(float);
   return pl;
+}
+
+FiltPlan filt_plan(const Geom& g) {
+  return cached_plan<FiltPlan>(g, 3, [&] { return filt_plan_search(g); });
 }
 
 }  // namespace

@@ -1007,9 +1007,7 @@ int launch_conv_ring_sc(const __half* src, const __half* rot, const __half* w, _
   p.rows_per_block = pl.rows_per_block;
   p.scH = g.scH; p.scW = g.scW; p.cells = g.cells;
   int warps = pl.warps;
-#ifdef DK_TUNING
-  if (const char* e = std::getenv("DK_B200_RING_WARPS")) warps = atoi(e) > 1 ? atoi(e) : warps;
-#endif
+  if (const char* e = tuning_env("DK_B200_RING_WARPS")) warps = atoi(e) > 1 ? atoi(e) : warps;
   int rc;
   if (warps <= 21) {
     auto kern = ring_conv_kernel<S, W, TR, SC44, 672>;

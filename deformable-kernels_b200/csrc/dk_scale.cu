@@ -59,10 +59,11 @@ int scale_backward(const T* dy, const T* x, const T* k, T* dx, T* dk, long long 
 
 // Offset clipping of the layers that produce the offsets (reference modules/deform_kernel.py:185-218, 273-276), one
 // pass instead of five elementwise ones:  v = r * dilate + bias[channel];  y = (clamp(v, lo, hi) - bias) / dilate * post.
-// The backward passes the gradient where lo <= v <= hi (both ends included, as torch.clamp does).
+// The backward passes the gradient where lo <= v <= hi (both ends included, as torch.clamp does).  The four scalars come as
+// doubles and are narrowed to the arithmetic type of the tensors in the kernel, so that fp64 tensors see fp64 bounds.
 template <typename T>
 __global__ void clip_fwd_kernel(const T* __restrict__ r, const float* __restrict__ bias, T* __restrict__ y, long long total,
-                                int channels, int hw, float lo, float hi, float dilate, float post) {
+                                int channels, int hw, double lo, double hi, double dilate, double post) {
   using A = typename Compute<T>::type;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
@@ -73,8 +74,8 @@ __global__ void clip_fwd_kernel(const T* __restrict__ r, const float* __restrict
 }
 template <typename T>
 __global__ void clip_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ r, const float* __restrict__ bias,
-                                T* __restrict__ dr, long long total, int channels, int hw, float lo, float hi, float dilate,
-                                float post) {
+                                T* __restrict__ dr, long long total, int channels, int hw, double lo, double hi, double dilate,
+                                double post) {
   using A = typename Compute<T>::type;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
@@ -85,16 +86,16 @@ __global__ void clip_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
 }
 
 template <typename T>
-int clip_forward(const T* r, const float* bias, T* y, long long total, int channels, int hw, float lo, float hi, float dilate,
-                 float post, cudaStream_t s) {
+int clip_forward(const T* r, const float* bias, T* y, long long total, int channels, int hw, double lo, double hi, double dilate,
+                 double post, cudaStream_t s) {
   const long long blocks = (total + 255) / 256;
   if (blocks > 0x7fffffffLL) return DK_ERR_UNSUPPORTED;
   clip_fwd_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(r, bias, y, total, channels, hw, lo, hi, dilate, post);
   return check_launch();
 }
 template <typename T>
-int clip_backward(const T* dy, const T* r, const float* bias, T* dr, long long total, int channels, int hw, float lo, float hi,
-                  float dilate, float post, cudaStream_t s) {
+int clip_backward(const T* dy, const T* r, const float* bias, T* dr, long long total, int channels, int hw, double lo, double hi,
+                  double dilate, double post, cudaStream_t s) {
   const long long blocks = (total + 255) / 256;
   if (blocks > 0x7fffffffLL) return DK_ERR_UNSUPPORTED;
   clip_bwd_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(dy, r, bias, dr, total, channels, hw, lo, hi, dilate, post);
@@ -138,8 +139,8 @@ int dk_plane_scale_backward(const void* grad_output, const void* input, const vo
 }
 
 int dk_offset_clip_forward(const void* offsets, const void* bias, void* output, int batch, int channels, int plane_size,
-                           float lo, float hi, float dilate, float post_scale, int dtype, void* stream) {
-  if (!offsets || !output || batch <= 0 || channels <= 0 || plane_size <= 0 || dilate == 0.f) return DK_ERR_BAD_ARGUMENT;
+                           double lo, double hi, double dilate, double post_scale, int dtype, void* stream) {
+  if (!offsets || !output || batch <= 0 || channels <= 0 || plane_size <= 0 || dilate == 0.0) return DK_ERR_BAD_ARGUMENT;
   cudaStream_t s = (cudaStream_t)stream;
   const long long total = (long long)batch * channels * plane_size;
   const float* b = (const float*)bias;
@@ -152,9 +153,9 @@ int dk_offset_clip_forward(const void* offsets, const void* bias, void* output, 
 }
 
 int dk_offset_clip_backward(const void* grad_output, const void* offsets, const void* bias, void* grad_offsets, int batch,
-                            int channels, int plane_size, float lo, float hi, float dilate, float post_scale, int dtype,
+                            int channels, int plane_size, double lo, double hi, double dilate, double post_scale, int dtype,
                             void* stream) {
-  if (!grad_output || !offsets || !grad_offsets || batch <= 0 || channels <= 0 || plane_size <= 0 || dilate == 0.f)
+  if (!grad_output || !offsets || !grad_offsets || batch <= 0 || channels <= 0 || plane_size <= 0 || dilate == 0.0)
     return DK_ERR_BAD_ARGUMENT;
   cudaStream_t s = (cudaStream_t)stream;
   const long long total = (long long)batch * channels * plane_size;

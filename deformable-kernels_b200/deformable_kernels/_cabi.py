@@ -40,6 +40,7 @@ _PROTOS = {
     "dk_sample_depthwise_backward_filter_workspace_bytes": (_sz, [_gp, _int]),
     "dk_sample_depthwise_backward_filter": (_int, [_vp, _vp, _vp, _vp, _gp, _int, _vp, _sz, _vp]),
     "dk_sample_depthwise_backward_filter_noalloc_max_bytes": (_sz, []),
+    "dk_sample_depthwise_backward_filter_noalloc_bytes": (_sz, [_gp, _int]),
     "dk_sample_depthwise_backward_filter_noalloc": (_int, [_vp, _vp, _vp, _vp, _gp, _int, _vp]),
     "dk_sample_depthwise_backward_rotation_workspace_bytes": (_sz, [_gp, _int]),
     "dk_sample_depthwise_backward_rotation": (_int, [_vp, _vp, _vp, _vp, _vp, _gp, _int, _vp, _sz, _vp]),
@@ -63,8 +64,8 @@ _PROTOS = {
     "dk_global_dk_forward": (_int, [_vp] * 10 + [_int, _int, _int, _int, _ip, _int, _vp]),
     "dk_global_dk_backward_workspace_bytes": (ctypes.c_size_t, [_int, _int, _int]),
     "dk_global_dk_backward": (_int, [_vp] * 12 + [_int, _int, _int, _int, _ip, _int, _vp, ctypes.c_size_t, _vp]),
-    "dk_offset_clip_forward": (_int, [_vp, _vp, _vp, _int, _int, _int] + [ctypes.c_float] * 4 + [_int, _vp]),
-    "dk_offset_clip_backward": (_int, [_vp, _vp, _vp, _vp, _int, _int, _int] + [ctypes.c_float] * 4 + [_int, _vp]),
+    "dk_offset_clip_forward": (_int, [_vp, _vp, _vp, _int, _int, _int] + [ctypes.c_double] * 4 + [_int, _vp]),
+    "dk_offset_clip_backward": (_int, [_vp, _vp, _vp, _vp, _int, _int, _int] + [ctypes.c_double] * 4 + [_int, _vp]),
     "dk_output_size": (_int, [_gp, _ip, _ip]),
     "dk_status_string": (ctypes.c_char_p, [_int]),
     "dk_last_cuda_error": (_int, []),
@@ -154,6 +155,13 @@ def same_dtype(first, *rest):
     for t in rest:
         if t is not None and t.dtype != first.dtype:
             raise TypeError("all tensors of one call must share a dtype (%s vs %s)" % (first.dtype, t.dtype))
+
+
+def same_device(first, *rest):
+    """The library launches on the first tensor's device with raw pointers: every tensor of a call must live there."""
+    for t in rest:
+        if t is not None and t.device != first.device:
+            raise RuntimeError("all tensors of one call must be on the same device (%s vs %s)" % (first.device, t.device))
 
 
 def workspace(nbytes, device):

@@ -51,6 +51,7 @@ class SampleDepthwiseFunction(Function):
                 rotation_groups=1):
         C.require_cuda(input, rotation, weight)
         C.same_dtype(input, rotation, weight)
+        C.same_device(input, rotation, weight)
         kernel_size, stride, padding, dilation = _pair(kernel_size), _pair(stride), _pair(padding), _pair(dilation)
         out_size = _output_size(input, kernel_size, stride, padding, dilation)
         _check_shapes(input, rotation, weight, out_size, kernel_size, rotation_groups)
@@ -92,6 +93,7 @@ class DeformableSampleDepthwiseFunction(Function):
                 dilation=(1, 1), rotation_groups=1):
         C.require_cuda(input, offset, rotation, weight)
         C.same_dtype(input, offset, rotation, weight)
+        C.same_device(input, offset, rotation, weight)
         kernel_size, stride, padding, dilation = _pair(kernel_size), _pair(stride), _pair(padding), _pair(dilation)
         out_size = _output_size(input, kernel_size, stride, padding, dilation)
         taps2 = kernel_size[0] * kernel_size[1] * 2

@@ -20,6 +20,7 @@ class NdLinearSampleFunction(Function):
     def forward(ctx, input, coord):
         C.require_cuda(input, coord)
         C.same_dtype(input, coord)
+        C.same_device(input, coord)
         if input.dim() < 2 or coord.dim() != 2 or coord.size(1) != input.dim() - 1:
             raise ValueError("expected input [C, s1..sD] and coord [B, D]")
         input, coord = input.contiguous(), coord.contiguous()

@@ -14,6 +14,7 @@ class PlaneScaleFunction(Function):
     def forward(ctx, input, scale):
         C.require_cuda(input, scale)
         C.same_dtype(input, scale)
+        C.same_device(input, scale)
         if input.dim() != 4 or tuple(scale.shape) != tuple(input.shape[:2]):
             raise ValueError("expected input [N,C,H,W] and scale [N,C]")
         input, scale = input.contiguous(), scale.contiguous()

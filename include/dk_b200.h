@@ -43,6 +43,12 @@ typedef enum dk_status {
 
 typedef enum dk_dtype { DK_F32 = 0, DK_F16 = 1, DK_F64 = 2 } dk_dtype;
 
+/* Devices and numeric limits.  Every pointer of a call must belong to the CURRENT device (cudaGetDevice()): the library
+ * launches there, on the given stream, and never checks ownership.  fp16 calls: forward and grad-input multiply and sum
+ * in fp32; grad-offsets and grad-bank feed the products grad_output * input to the tensor cores as fp16, so
+ * |grad_output * input| must stay below 65504 (an overflow gives Inf / NaN gradients, which a loss scaler's
+ * overflow check catches and answers by lowering its scale); all sums are fp32. */
+
 /* Geometry of one depthwise call.  Same fields as the reference's
  * SampleDepthwiseArgs (csrc/filter_sample_depthwise_cuda.h:1-28) minus the output
  * extent, which is derived as in csrc/filter_sample_depthwise_cuda.cpp:42-43:
@@ -105,13 +111,18 @@ int dk_sample_depthwise_backward_filter(const void *grad_output, const void *inp
 /* No counterpart in the reference.  Same result as dk_sample_depthwise_backward_filter, for callers
  * that cannot supply a workspace because they may not allocate device memory at call time (plugins
  * inside a memory-planned runtime, fixed-memory control loops, FFI hosts without a CUDA allocator):
- * the partial sums go to a fixed array built into the library, at most
- * dk_sample_depthwise_backward_filter_noalloc_max_bytes() (8 MiB, held by every GPU that loads the
- * library until the process exits).  Nothing is allocated or freed on this path.  Shapes that need
- * more return DK_ERR_WORKSPACE.  All calls on one device share that array, so calls that overlap
- * on the GPU race: serialise them.  The first call on a device queries the array's address; make
- * it before any stream capture begins. */
+ * the partial sums go to a fixed array built into the library, of
+ * dk_sample_depthwise_backward_filter_noalloc_max_bytes() bytes (8 MiB, held by every GPU that loads the
+ * library until the process exits).  Nothing is allocated or freed on this path.  The call sizes itself for the
+ * kernel it launches: the fp16 tensor-core kernel when its partial sums fit, otherwise the general kernel with as
+ * many pixel blocks as fit (slower, same result up to summation order); DK_ERR_WORKSPACE only when one block's
+ * partial sums (channels x bank cells x 4 bytes; x 8 for fp64) exceed the array.
+ * dk_sample_depthwise_backward_filter_noalloc_bytes() returns, without touching a GPU, the bytes of the array a
+ * call would use (0 = refused).  All calls on one device share that array, so calls that overlap on the GPU race:
+ * serialise them.  The first call on a device queries the array's address; make it before any stream capture
+ * begins.  The tensors must live on the current device. */
 size_t dk_sample_depthwise_backward_filter_noalloc_max_bytes(void);
+size_t dk_sample_depthwise_backward_filter_noalloc_bytes(const dk_geom *g, int dtype);
 int dk_sample_depthwise_backward_filter_noalloc(const void *grad_output, const void *input, const void *rotation,
                                                 void *grad_filter, const dk_geom *g, int dtype, void *stream);
 
@@ -237,9 +248,9 @@ int dk_global_dk_backward(const void *grad_output, const void *input, const void
  * offsets [batch, channels, plane_size]; bias [channels] float or NULL (zero).  The backward passes
  * grad_output * post_scale where lo <= v <= hi.  No counterpart among the reference's compiled functions. */
 int dk_offset_clip_forward(const void *offsets, const void *bias, void *output, int batch, int channels, int plane_size,
-                           float lo, float hi, float dilate, float post_scale, int dtype, void *stream);
+                           double lo, double hi, double dilate, double post_scale, int dtype, void *stream);
 int dk_offset_clip_backward(const void *grad_output, const void *offsets, const void *bias, void *grad_offsets, int batch,
-                            int channels, int plane_size, float lo, float hi, float dilate, float post_scale, int dtype,
+                            int channels, int plane_size, double lo, double hi, double dilate, double post_scale, int dtype,
                             void *stream);
 
 #ifdef __cplusplus

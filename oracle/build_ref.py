@@ -79,6 +79,73 @@ def build(root=None, verbose=False):
     return outs
 
 
+LAYER_FILES = ("deform_kernel.py", "deform_conv.py")
+
+
+def stage_layers(root=None):
+    """Install the reference's two layer files (deformable_kernels/modules/deform_kernel.py and deform_conv.py) unmodified
+    under oracle/_ref/ref_layers/, the way `pip install --target` would, so that the GPU tests can run the reference's own
+    layers on top of this package's operators on a machine without the reference tree.  oracle/_ref/ is git-ignored."""
+    import shutil
+    src = os.path.join(reference_root(root), "deformable_kernels", "modules")
+    if not os.path.isdir(src):
+        raise FileNotFoundError("reference tree not found at %s" % reference_root(root))
+    dst = os.path.join(OUT, "ref_layers")
+    os.makedirs(dst, exist_ok=True)
+    for f in LAYER_FILES:
+        shutil.copyfile(os.path.join(src, f), os.path.join(dst, f))
+    return dst
+
+
+def layers_dir():
+    """Directory holding the reference's layer files: the reference tree when present, else the staged copy, else None."""
+    live = os.path.join(reference_root(), "deformable_kernels", "modules")
+    if all(os.path.exists(os.path.join(live, f)) for f in LAYER_FILES):
+        return live
+    staged = os.path.join(OUT, "ref_layers")
+    if all(os.path.exists(os.path.join(staged, f)) for f in LAYER_FILES):
+        return staged
+    return None
+
+
+def load_layers():
+    """The reference's layer modules, imported unchanged on top of this package's operators ({'deform_kernel': module,
+    'deform_conv': module}), or None when neither the tree nor the staged copy is present.  `apex` is not installed here:
+    a stand-in for apex.amp.float_function (the identity, which is what it is while amp is uninitialised) is put in
+    sys.modules for the duration of the import."""
+    import importlib.util
+    import types
+    mod_dir = layers_dir()
+    if mod_dir is None:
+        return None
+    import deformable_kernels  # noqa: F401  (this package: the ops the layers import)
+    amp = types.ModuleType("apex.amp")
+    amp.float_function = lambda f: f
+    apex = types.ModuleType("apex")
+    apex.amp = amp
+    saved = {k: sys.modules.get(k) for k in ("apex", "apex.amp")}
+    sys.modules["apex"], sys.modules["apex.amp"] = apex, amp
+    try:
+        pkg = types.ModuleType("deformable_kernels._ref_layers")
+        pkg.__path__ = [mod_dir]
+        sys.modules["deformable_kernels._ref_layers"] = pkg
+        mods = {}
+        for name in ("deform_kernel", "deform_conv"):
+            full = "deformable_kernels._ref_layers." + name
+            spec = importlib.util.spec_from_file_location(full, os.path.join(mod_dir, name + ".py"))
+            mod = importlib.util.module_from_spec(spec)
+            sys.modules[full] = mod
+            spec.loader.exec_module(mod)
+            mods[name] = mod
+        return mods
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
+
+
 def load_module(name):
     """Import one of the built pybind modules from oracle/_ref/ (torch must be
     imported first so that its shared libraries are resolvable)."""
@@ -97,3 +164,4 @@ def load_module(name):
 if __name__ == "__main__":
     for p in build(sys.argv[1] if len(sys.argv) > 1 else None, verbose=True):
         print("built", p)
+    print("staged", stage_layers(sys.argv[1] if len(sys.argv) > 1 else None))

@@ -66,6 +66,29 @@ def test_workspace_queries(cabi):
     assert cabi.lib.dk_deform_sample_depthwise_backward_data_workspace_bytes(g, cabi.DK_F16) >= 4 * 64 * 28 * 28 * 4
 
 
+def test_noalloc_entry_point_fits_every_sweep_layer(cabi):
+    """Host-only sizing of dk_sample_depthwise_backward_filter_noalloc: each of the ten MobileNetV2 sweep layers at
+    batch 128, in fp16 and fp32, is accepted and uses at most the 8 MiB array; the two 7 x 7 layers, whose usual
+    general-kernel partial sums (8.97 / 9.03 MB) exceed it, run with fewer pixel blocks in fp32 and with the tensor-core
+    kernel's smaller partial sums in fp16.  fp64 is accepted too (its partial sums are twice as large, the block count shrinks)."""
+    cap = cabi.lib.dk_sample_depthwise_backward_filter_noalloc_max_bytes()
+    assert cap == 8 << 20
+    for c, hw in [(96, 112), (144, 56), (192, 28), (384, 14), (960, 7)]:
+        for s in (1, 2):
+            g = cabi.geom((128, c, hw, hw), (3, 3), (s, s), (1, 1), (1, 1), (4, 4), 1)
+            for dt in (cabi.DK_F16, cabi.DK_F32, cabi.DK_F64):
+                used = cabi.lib.dk_sample_depthwise_backward_filter_noalloc_bytes(g, dt)
+                assert 0 < used <= cap, (c, hw, s, dt, used)
+                assert used % (c * 16 * 4) == 0, (c, hw, s, dt, used)
+            usual = cabi.lib.dk_sample_depthwise_backward_filter_workspace_bytes(g, cabi.DK_F32)
+            if (c, hw) == (960, 7):
+                assert usual > cap   # the case the shrinking plan exists for
+                assert cabi.lib.dk_sample_depthwise_backward_filter_noalloc_bytes(g, cabi.DK_F16) < (2 << 20)
+    # one block's partial sums beyond the array: refused
+    g = cabi.geom((64, 64, 600, 600), (3, 3), (1, 1), (1, 1), (1, 1), (200, 200), 1)
+    assert cabi.lib.dk_sample_depthwise_backward_filter_noalloc_bytes(g, cabi.DK_F32) == 0
+
+
 def test_block_shapes_of_the_fp16_fast_path_are_launchable(cabi):
     """Planner invariants over many geometries (host only): every block shape the tensor-core kernels would launch covers
     the plane and all channels, fits shared memory and the kernels' launch bounds, and the workspace query covers the
@@ -145,33 +168,13 @@ def test_modules_keep_reference_names_and_shapes():
 
 def test_reference_layers_import_unchanged_on_top_of_this_package():
     """The reference's own modules/deform_kernel.py and modules/deform_conv.py, loaded from
-    the reference tree as they are, resolve their imports against this package's ops."""
-    import importlib.util
-    import sys
-    import types
-    ref_root = os.environ.get("DK_REFERENCE_ROOT", "/root/reference")
-    mod_dir = os.path.join(ref_root, "deformable_kernels", "modules")
-    if not os.path.isdir(mod_dir):
-        pytest.skip("reference tree not present")
-    import deformable_kernels  # noqa: F401
-    amp = types.ModuleType("apex.amp")
-    amp.float_function = lambda f: f      # identity while amp is not initialised
-    apex = types.ModuleType("apex")
-    apex.amp = amp
-    saved = {k: sys.modules.get(k) for k in ("apex", "apex.amp")}
-    sys.modules["apex"], sys.modules["apex.amp"] = apex, amp
+    the reference tree (or its staged copy) as they are, resolve their imports against this package's ops.
+    tests/test_reference_layers_gpu.py runs their forward and backward on a GPU."""
+    from oracle import build_ref
+    mods = build_ref.load_layers()
+    if mods is None:
+        pytest.skip("neither the reference tree nor its staged layer files (oracle/_ref/ref_layers) are present")
     try:
-        pkg = types.ModuleType("deformable_kernels._ref_layers")
-        pkg.__path__ = [mod_dir]
-        sys.modules["deformable_kernels._ref_layers"] = pkg
-        mods = {}
-        for name in ("deform_kernel", "deform_conv"):
-            full = "deformable_kernels._ref_layers." + name
-            spec = importlib.util.spec_from_file_location(full, os.path.join(mod_dir, name + ".py"))
-            mod = importlib.util.module_from_spec(spec)
-            sys.modules[full] = mod
-            spec.loader.exec_module(mod)
-            mods[name] = mod
         from deformable_kernels.ops.deform_kernel.modules import SampleDepthwise
         layer = mods["deform_kernel"].DeformKernel2d((4, 4), 8, 8, 3, 1, 1, groups=8)
         assert isinstance(layer.inner_conv, SampleDepthwise)
@@ -181,10 +184,6 @@ def test_reference_layers_import_unchanged_on_top_of_this_package():
             layer(torch.randn(1, 8, 6, 6))
         assert mods["deform_conv"].DeformConv2d(8, 8, 3, 1, 1, groups=8).inner_conv.weight.shape == (8, 1, 3, 3)
     finally:
-        for k, v in saved.items():
-            if v is None:
-                sys.modules.pop(k, None)
-            else:
-                sys.modules[k] = v
+        import sys
         for k in [k for k in sys.modules if k.startswith("deformable_kernels._ref_layers")]:
             sys.modules.pop(k, None)

@@ -51,13 +51,29 @@ def test_two_rank_sharding_reproduces_the_full_batch():
     with socket.socket() as sock:  # a port that is free now, rather than one derived from the pid
         sock.bind(("127.0.0.1", 0))
         port = sock.getsockname()[1]
+    import queue
+    import time
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    y, dx, do, dr, dw = q.get(timeout=600)  # the children's first `import torch` can take a minute on a cold page cache
-    for p in procs:
-        p.join(timeout=60)
-        assert p.exitcode == 0
+    try:
+        result, deadline = None, time.time() + 600   # the children's first `import torch` can take a minute on a cold page cache
+        while result is None:
+            try:
+                result = q.get(timeout=2)
+            except queue.Empty:
+                dead = [p.exitcode for p in procs if p.exitcode not in (None, 0)]
+                assert not dead, "a rank died with exit code %r before the result arrived" % dead
+                assert time.time() < deadline, "no result from the ranks within 600 s"
+        y, dx, do, dr, dw = result
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+            p.join(timeout=10)
     case = dk_cases.make_case(5, 6, 9, 8, rot_std=1.0, off_std=1.5, seed=50)
     full = {k: case[k].double() for k in ("input", "offset", "rotation", "weight", "grad_output")}
     y0 = O.deform_sample_depthwise_forward(full["input"], full["offset"], full["rotation"], full["weight"], **case["args"])
