@@ -181,8 +181,9 @@ size_t dk_sample_depthwise_backward_workspace_bytes(const dk_geom* g, int dtype)
   size_t need = a > b ? a : b;  // the passes run one after the other on the stream and share the buffer
   Geom gg;
   if (dtype == DK_F16 && make_geom(g, &gg)) {
-    const size_t c = align256(local_gw_ring_workspace(gg));
+    const size_t c = align256(local_gw_ring_workspace(gg)), d = align256(local_bwd_ring_workspace(gg));
     if (c > need) need = c;
+    if (d > need) need = d;
   }
   return need;
 }
@@ -192,6 +193,17 @@ int dk_sample_depthwise_backward(const void* grad_output, const void* input, con
                                  void* workspace, size_t workspace_bytes, void* stream) {
   if (!dtype_ok(dtype)) return DK_ERR_BAD_ARGUMENT;
   int rc = DK_OK;
+  if (grad_input && grad_rotation && grad_filter && dtype == DK_F16 && mma_path_enabled()) {
+    // the whole backward in one pass over grad_output, input and the offsets, where that is the faster way
+    Geom gg;
+    if (!grad_output || !input || !rotation || !filter || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
+    if (local_bwd_ring_preferred(gg)) {
+      rc = local_bwd_ring(P_(__half, grad_output), P_(__half, input), P_(__half, rotation), P_(__half, filter),
+                          M_(__half, grad_input), M_(__half, grad_rotation), M_(__half, grad_filter), gg, workspace,
+                          workspace_bytes, (cudaStream_t)stream);
+      if (rc != DK_ERR_UNSUPPORTED) return rc;
+    }
+  }
   if (grad_input) {
     rc = dk_sample_depthwise_backward_data(grad_output, rotation, filter, grad_input, g, dtype, stream);
     if (rc) return rc;
@@ -214,6 +226,18 @@ int dk_sample_depthwise_backward(const void* grad_output, const void* input, con
                                              workspace_bytes, stream);
   }
   return rc;
+}
+
+int dk_sample_depthwise_backward_one_pass(const void* grad_output, const void* input, const void* rotation, const void* filter,
+                                          void* grad_input, void* grad_rotation, void* grad_filter, const dk_geom* g, int dtype,
+                                          void* workspace, size_t workspace_bytes, void* stream) {
+  Geom gg;
+  if (!grad_output || !input || !rotation || !filter || !grad_input || !grad_rotation || !grad_filter || !make_geom(g, &gg))
+    return DK_ERR_BAD_ARGUMENT;
+  if (dtype != DK_F16 || !mma_path_enabled()) return DK_ERR_UNSUPPORTED;
+  return local_bwd_ring(P_(__half, grad_output), P_(__half, input), P_(__half, rotation), P_(__half, filter),
+                        M_(__half, grad_input), M_(__half, grad_rotation), M_(__half, grad_filter), gg, workspace, workspace_bytes,
+                        (cudaStream_t)stream);
 }
 
 /* ---------------------------------------------------------------- DK + DCN */

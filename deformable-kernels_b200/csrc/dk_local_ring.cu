@@ -160,6 +160,54 @@ __device__ __forceinline__ int release_count(int j, bool first, bool last) {
   return (j == 1) ? 2 : 1 + (((j == 0 && first) || (j == 2 && last)) ? 1 : 0);
 }
 
+// The channel-slab loop of the forward / stride-1 grad-input stencil for one item: xr[fh] points at the lane's window
+// (channel row gq, source column ow*S - 2) in the slot of source row fh, bkp at the lane's words of the bank copy, y0 at
+// destination (channel gq, pixel ow); bf holds the hat products of the nine taps.
+template <int S, int INNER, bool TR>
+__device__ __forceinline__ void conv_slabs(const __half* const (&xr)[3], const unsigned* __restrict__ bkp, __half* __restrict__ y0,
+                                           int nslab, size_t dplane, bool store, const unsigned (&bf)[9][2]) {
+#pragma unroll 3
+  for (int sb = 0; sb < nslab; ++sb) {
+    unsigned a[4];
+    a[0] = bkp[sb * (16 * kBankPitch / 2)];
+    a[1] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2];
+    a[2] = bkp[sb * (16 * kBankPitch / 2) + 4];
+    a[3] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2 + 4];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int fh = 0; fh < 3; ++fh) {
+      const unsigned* p0 = reinterpret_cast<const unsigned*>(xr[fh] + sb * 16 * INNER);
+      const unsigned* p1 = p0 + 8 * INNER / 2;
+      const unsigned w0 = p0[0], w1 = p0[1], w2 = p0[2];
+      const unsigned v0 = p1[0], v1 = p1[1], v2 = p1[2];
+      // source columns ow*S - 1 .. of the two channel rows, widened to fp32
+      float fa[5], fb[5];
+      fa[0] = h_hi(w0); fa[1] = h_lo(w1); fa[2] = h_hi(w1); fa[3] = h_lo(w2);
+      fb[0] = h_hi(v0); fb[1] = h_lo(v1); fb[2] = h_hi(v1); fb[3] = h_lo(v2);
+      if (S == 2) {
+        fa[4] = h_hi(w2);
+        fb[4] = h_hi(v2);
+      }
+#pragma unroll
+      for (int fw = 0; fw < 3; ++fw) {
+        float kd[4];
+        mma_new(kd, a, bf[fh * 3 + fw][0], bf[fh * 3 + fw][1]);
+        const int i0 = TR ? 2 - fw : fw;      // pixel 0 reads this element of the window
+        const int i1 = TR ? 3 - fw : fw + S;  // pixel 1
+        acc[0] = fmaf(kd[0], fa[i0], acc[0]);
+        acc[1] = fmaf(kd[1], fa[i1], acc[1]);
+        acc[2] = fmaf(kd[2], fb[i0], acc[2]);
+        acc[3] = fmaf(kd[3], fb[i1], acc[3]);
+      }
+    }
+    if (store) {
+      __half* ya = y0 + (size_t)sb * 16 * dplane;
+      *reinterpret_cast<__half2*>(ya) = __floats2half2_rn(acc[0], acc[1]);
+      *reinterpret_cast<__half2*>(ya + 8 * dplane) = __floats2half2_rn(acc[2], acc[3]);
+    }
+  }
+}
+
 // ================================================================== forward (TR = false) and grad-input at stride 1 (TR = true)
 //
 // Destination pixel (d, ow) of channel c:  sum over taps of src[c, d*S - 1 + fh, ow*S - 1 + fw] * K[c, (d, ow), tap]   (forward)
@@ -331,46 +379,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
     const int ow = ow0 + 2 * q;
     const unsigned* bkp = reinterpret_cast<const unsigned*>(bank + gq * kBankPitch) + q;
     __half* y0 = dst + ((size_t)n * p.C + c0 + gq) * dplane + (size_t)d * Wd + ow;
-#pragma unroll 3
-    for (int sb = 0; sb < nslab; ++sb) {
-      unsigned a[4];
-      a[0] = bkp[sb * (16 * kBankPitch / 2)];
-      a[1] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2];
-      a[2] = bkp[sb * (16 * kBankPitch / 2) + 4];
-      a[3] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2 + 4];
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int fh = 0; fh < 3; ++fh) {
-        const unsigned* p0 = reinterpret_cast<const unsigned*>(xr[fh] + sb * 16 * INNER);
-        const unsigned* p1 = p0 + 8 * INNER / 2;
-        const unsigned w0 = p0[0], w1 = p0[1], w2 = p0[2];
-        const unsigned v0 = p1[0], v1 = p1[1], v2 = p1[2];
-        // source columns ow*S - 1 .. of the two channel rows, widened to fp32
-        float fa[5], fb[5];
-        fa[0] = h_hi(w0); fa[1] = h_lo(w1); fa[2] = h_hi(w1); fa[3] = h_lo(w2);
-        fb[0] = h_hi(v0); fb[1] = h_lo(v1); fb[2] = h_hi(v1); fb[3] = h_lo(v2);
-        if (S == 2) {
-          fa[4] = h_hi(w2);
-          fb[4] = h_hi(v2);
-        }
-#pragma unroll
-        for (int fw = 0; fw < 3; ++fw) {
-          float kd[4];
-          mma_new(kd, a, bf[fh * 3 + fw][0], bf[fh * 3 + fw][1]);
-          const int i0 = TR ? 2 - fw : fw;      // pixel 0 reads this element of the window
-          const int i1 = TR ? 3 - fw : fw + S;  // pixel 1
-          acc[0] = fmaf(kd[0], fa[i0], acc[0]);
-          acc[1] = fmaf(kd[1], fa[i1], acc[1]);
-          acc[2] = fmaf(kd[2], fb[i0], acc[2]);
-          acc[3] = fmaf(kd[3], fb[i1], acc[3]);
-        }
-      }
-      if (ow < Wd) {
-        __half* ya = y0 + (size_t)sb * 16 * dplane;
-        *reinterpret_cast<__half2*>(ya) = __floats2half2_rn(acc[0], acc[1]);
-        *reinterpret_cast<__half2*>(ya + 8 * dplane) = __floats2half2_rn(acc[2], acc[3]);
-      }
-    }
+    conv_slabs<S, INNER, TR>(xr, bkp, y0, nslab, dplane, ow < Wd, bf);
 
     // done with the three source rows (and the offset rows)
     __syncwarp();
@@ -383,6 +392,61 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
         if (TR) rr.release(k0 + j, m);
       }
       if (!TR) rr.release(grow, 1);
+    }
+  }
+}
+
+// The channel-slab loop of the stride-2 grad-input for one item: dr[da] points at the lane's dy pair (channel row gq,
+// column b) in the slot of output row a + da, x0 at dx (channel gq, row 2a, column 2b); bf holds the hat products of
+// the nine (pixel shift, tap) pairs, index 3 * vr + vc with (da, fh) = (0,1), (0,2), (1,0) for vr = 0, 1, 2 and (db, fw) alike.
+template <int INNER, int W>
+__device__ __forceinline__ void convT2_slabs(const __half* const (&dr)[2], const unsigned* __restrict__ bkp, __half* __restrict__ x0,
+                                             int nslab, size_t dplane, bool row1, bool col_ok, const unsigned (&bf)[9][2]) {
+#pragma unroll 3
+  for (int sb = 0; sb < nslab; ++sb) {
+    unsigned af[4];
+    af[0] = bkp[sb * (16 * kBankPitch / 2)];
+    af[1] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2];
+    af[2] = bkp[sb * (16 * kBankPitch / 2) + 4];
+    af[3] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2 + 4];
+    // dy of channel rows gq (fa) and gq + 8 (fb): [da][column b, b+1, b+2], widened to fp32
+    float fa[2][3], fb[2][3];
+#pragma unroll
+    for (int da = 0; da < 2; ++da) {
+      const unsigned* p0 = reinterpret_cast<const unsigned*>(dr[da] + sb * 16 * INNER);
+      const unsigned* p1 = p0 + 8 * INNER / 2;
+      const unsigned w0 = p0[0], w1 = p0[1], v0 = p1[0], v1 = p1[1];
+      fa[da][0] = h_lo(w0); fa[da][1] = h_hi(w0); fa[da][2] = h_lo(w1);
+      fb[da][0] = h_lo(v0); fb[da][1] = h_hi(v0); fb[da][2] = h_lo(v1);
+    }
+    float acc[2][2][4];  // [channel row][rr][dx columns 2b .. 2b+3]
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[0][0][i] = acc[0][1][i] = acc[1][0][i] = acc[1][1][i] = 0.f;
+#pragma unroll
+    for (int vr = 0; vr < 3; ++vr) {
+      const int da = vr == 2 ? 1 : 0, rr_ = vr == 0 ? 0 : 1;
+#pragma unroll
+      for (int vc = 0; vc < 3; ++vc) {
+        const int db = vc == 2 ? 1 : 0, cc = vc == 0 ? 0 : 1;
+        float kd[4];
+        mma_new(kd, af, bf[vr * 3 + vc][0], bf[vr * 3 + vc][1]);
+        acc[0][rr_][cc] = fmaf(kd[0], fa[da][db], acc[0][rr_][cc]);
+        acc[0][rr_][2 + cc] = fmaf(kd[1], fa[da][1 + db], acc[0][rr_][2 + cc]);
+        acc[1][rr_][cc] = fmaf(kd[2], fb[da][db], acc[1][rr_][cc]);
+        acc[1][rr_][2 + cc] = fmaf(kd[3], fb[da][1 + db], acc[1][rr_][2 + cc]);
+      }
+    }
+    if (col_ok) {
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        __half* xa = x0 + ((size_t)sb * 16 + ch * 8) * dplane;
+        const __half2 lo = __floats2half2_rn(acc[ch][0][0], acc[ch][0][1]), hi = __floats2half2_rn(acc[ch][0][2], acc[ch][0][3]);
+        *reinterpret_cast<uint2*>(xa) = make_uint2(*reinterpret_cast<const unsigned*>(&lo), *reinterpret_cast<const unsigned*>(&hi));
+        if (row1) {
+          const __half2 lo1 = __floats2half2_rn(acc[ch][1][0], acc[ch][1][1]), hi1 = __floats2half2_rn(acc[ch][1][2], acc[ch][1][3]);
+          *reinterpret_cast<uint2*>(xa + W) = make_uint2(*reinterpret_cast<const unsigned*>(&lo1), *reinterpret_cast<const unsigned*>(&hi1));
+        }
+      }
     }
   }
 }
@@ -545,53 +609,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_convT2_kernel(const __grid_const
     const unsigned* bkp = reinterpret_cast<const unsigned*>(bank + gq * kBankPitch) + q;
     __half* x0 = dx + ((size_t)n * p.C + c0 + gq) * dplane + (size_t)(2 * a) * W + 2 * b;
     const bool row1 = 2 * a + 1 < H, col_ok = 2 * b < W;
-#pragma unroll 3
-    for (int sb = 0; sb < nslab; ++sb) {
-      unsigned af[4];
-      af[0] = bkp[sb * (16 * kBankPitch / 2)];
-      af[1] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2];
-      af[2] = bkp[sb * (16 * kBankPitch / 2) + 4];
-      af[3] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2 + 4];
-      // dy of channel rows gq (fa) and gq + 8 (fb): [da][column b, b+1, b+2], widened to fp32
-      float fa[2][3], fb[2][3];
-#pragma unroll
-      for (int da = 0; da < 2; ++da) {
-        const unsigned* p0 = reinterpret_cast<const unsigned*>(dr[da] + sb * 16 * INNER);
-        const unsigned* p1 = p0 + 8 * INNER / 2;
-        const unsigned w0 = p0[0], w1 = p0[1], v0 = p1[0], v1 = p1[1];
-        fa[da][0] = h_lo(w0); fa[da][1] = h_hi(w0); fa[da][2] = h_lo(w1);
-        fb[da][0] = h_lo(v0); fb[da][1] = h_hi(v0); fb[da][2] = h_lo(v1);
-      }
-      float acc[2][2][4];  // [channel row][rr][dx columns 2b .. 2b+3]
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[0][0][i] = acc[0][1][i] = acc[1][0][i] = acc[1][1][i] = 0.f;
-#pragma unroll
-      for (int vr = 0; vr < 3; ++vr) {
-        const int da = vr == 2 ? 1 : 0, rr_ = vr == 0 ? 0 : 1;
-#pragma unroll
-        for (int vc = 0; vc < 3; ++vc) {
-          const int db = vc == 2 ? 1 : 0, cc = vc == 0 ? 0 : 1;
-          float kd[4];
-          mma_new(kd, af, bf[vr * 3 + vc][0], bf[vr * 3 + vc][1]);
-          acc[0][rr_][cc] = fmaf(kd[0], fa[da][db], acc[0][rr_][cc]);
-          acc[0][rr_][2 + cc] = fmaf(kd[1], fa[da][1 + db], acc[0][rr_][2 + cc]);
-          acc[1][rr_][cc] = fmaf(kd[2], fb[da][db], acc[1][rr_][cc]);
-          acc[1][rr_][2 + cc] = fmaf(kd[3], fb[da][1 + db], acc[1][rr_][2 + cc]);
-        }
-      }
-      if (col_ok) {
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          __half* xa = x0 + ((size_t)sb * 16 + ch * 8) * dplane;
-          const __half2 lo = __floats2half2_rn(acc[ch][0][0], acc[ch][0][1]), hi = __floats2half2_rn(acc[ch][0][2], acc[ch][0][3]);
-          *reinterpret_cast<uint2*>(xa) = make_uint2(*reinterpret_cast<const unsigned*>(&lo), *reinterpret_cast<const unsigned*>(&hi));
-          if (row1) {
-            const __half2 lo1 = __floats2half2_rn(acc[ch][1][0], acc[ch][1][1]), hi1 = __floats2half2_rn(acc[ch][1][2], acc[ch][1][3]);
-            *reinterpret_cast<uint2*>(xa + W) = make_uint2(*reinterpret_cast<const unsigned*>(&lo1), *reinterpret_cast<const unsigned*>(&hi1));
-          }
-        }
-      }
-    }
+    convT2_slabs<INNER, W>(dr, bkp, x0, nslab, dplane, row1, col_ok, bf);
     // every stream row is read by the output rows a - 1 and a; the first / last row of the range stands in for a missing neighbour
     __syncwarp();
     if (lane == 0) {
@@ -601,6 +619,141 @@ __global__ void __launch_bounds__(MAXT, 1) ring_convT2_kernel(const __grid_const
       rd.release(k0 + 1, last ? 2 : 1);
       rr.release(k0 + 1, last ? 2 : 1);
     }
+  }
+}
+
+// grad-offsets and grad-bank of one item (8 output pixels ow0 .. ow0+7 of one row): three passes, one per kernel row fh
+// (three taps), which keeps 12 instead of 36 accumulators of G live and waits for a source row only when its pass starts.
+//   rp    the item's offsets in the ring slot of its row (plane 0, pixel ow0 + gq)
+//   dyr   the lane's dy pair (channel row gq, pixels ow0 + 2q, + 1) in the slot of that row
+//   x rows: fills kx0 .. kx0 + 2 of ring rx (slots of xslot halves in xring)
+//   acc   the warp's bank-gradient accumulators; Gs / uv the warp's scratch; drot_item -> d(offsets)[n, 0, oh, ow0]
+// Returns false when a wait ran out.  The caller releases the rows afterwards.
+template <int S, int W, int NS, bool SC44>
+__device__ __forceinline__ bool gw_item(float (&acc)[NS][2][4], const Ring& rx, int kx0, const __half* __restrict__ xring, int xslot,
+                                        const __half* __restrict__ rp, const __half* __restrict__ dyr,
+                                        const __half* __restrict__ bankT, int pitchT, float* __restrict__ Gs,
+                                        float2* __restrict__ uv, __half* __restrict__ drot_item, int P, int nslab, int ow0,
+                                        const LaneCells& lc, float uh0, float uw0, int scH_rt, int scW_rt, int lane) {
+  constexpr int Wo = (W - 1) / S + 1;
+  constexpr int IX = RowLayout<W>::kInner, ID = RowLayout<Wo>::kInner, WOP = RotLayout<Wo>::kWop;
+  const int gq = lane >> 2, q = lane & 3;
+  const int ow = ow0 + 2 * q;
+#pragma unroll
+  for (int fh = 0; fh < 3; ++fh) {
+    // hat products of the three taps, transposed into B fragments of dW += dK * beta:
+    // bw[fw][0] = (pixels 2q, 2q+1; cell gq), bw[fw][1] = cell gq + 8
+    unsigned bw[3][2];
+#pragma unroll
+    for (int fw = 0; fw < 3; ++fw) {
+      unsigned bb[2];
+      float u, v;
+      beta_tap<WOP, SC44>(bb, rp + 2 * (fh * 3 + fw) * WOP, (float)fh, (float)fw, lc, uh0, uw0, u, v);
+      bw[fw][0] = movmatrix_trans(bb[0]);
+      bw[fw][1] = movmatrix_trans(bb[1]);
+      if (q == 0) uv[fw * 8 + gq] = make_float2(u, v);
+    }
+    if (!rx.wait_full(kx0 + fh)) return false;
+    const __half* xr = xring + (size_t)rx.slot(kx0 + fh) * xslot + gq * IX + (8 + ow * S - 2);
+
+    float G[3][4];
+#pragma unroll
+    for (int t = 0; t < 3; ++t) G[t][0] = G[t][1] = G[t][2] = G[t][3] = 0.f;
+
+#pragma unroll
+    for (int sidx = 0; sidx < NS; ++sidx) {
+      if (sidx < nslab) {
+        const unsigned dy0 = *reinterpret_cast<const unsigned*>(dyr + sidx * 16 * ID);
+        const unsigned dy1 = *reinterpret_cast<const unsigned*>(dyr + sidx * 16 * ID + 8 * ID);
+        const unsigned* p0 = reinterpret_cast<const unsigned*>(xr + sidx * 16 * IX);
+        const unsigned* p1 = p0 + 8 * IX / 2;
+        const unsigned w0 = p0[0], w1 = p0[1], w2 = p0[2];
+        const unsigned v0 = p1[0], v1 = p1[1], v2 = p1[2];
+        unsigned d0[3], d1[3];  // dK of channel rows gq and gq + 8 for the three taps
+#pragma unroll
+        for (int fw = 0; fw < 3; ++fw) {
+          d0[fw] = hmul2u(dy0, tap_pair<S>(w0, w1, w2, fw));
+          d1[fw] = hmul2u(dy1, tap_pair<S>(v0, v1, v2, fw));
+        }
+        // A = W^T slab: rows = cells (gq, gq+8), k = channels (2q, 2q+1) and (2q+8, 2q+9)
+        const unsigned* wt0 = reinterpret_cast<const unsigned*>(bankT + gq * pitchT + sidx * 16);
+        const unsigned* wt1 = reinterpret_cast<const unsigned*>(bankT + (gq + 8) * pitchT + sidx * 16);
+        const unsigned a0 = wt0[q], a1 = wt1[q], a2 = wt0[q + 4], a3 = wt1[q + 4];
+#pragma unroll
+        for (int fw = 0; fw < 3; ++fw) mma16816_acc(G[fw], a0, a1, a2, a3, movmatrix_trans(d0[fw]), movmatrix_trans(d1[fw]));
+        // k = 16 = 8 pixels x (tap 0 | tap 1), then 8 pixels x (tap 2 | nothing)
+        mma16816_acc(acc[sidx][0], d0[0], d1[0], d0[1], d1[1], bw[0][0], bw[1][0]);
+        mma16816_acc(acc[sidx][1], d0[0], d1[0], d0[1], d1[1], bw[0][1], bw[1][1]);
+        mma16816_acc(acc[sidx][0], d0[2], d1[2], 0u, 0u, bw[2][0], 0u);
+        mma16816_acc(acc[sidx][1], d0[2], d1[2], 0u, 0u, bw[2][1], 0u);
+      }
+    }
+
+    // d(offset)[pixel, tap, dir] = sum over the four corner cells of G * d(coefficient)/d(u or v).  Floor-based, so at an
+    // integer coordinate it is the right-hand derivative and at the upper edge the derivative into the zero extension
+    // (csrc/filter_sample_depthwise_cuda_kernel.cu:137-158); zero when the tap samples outside the bank (:131-135).
+    __syncwarp();
+#pragma unroll
+    for (int tt = 0; tt < 3; ++tt) {
+      *reinterpret_cast<float2*>(Gs + (tt * 16 + gq) * 8 + 2 * q) = make_float2(G[tt][0], G[tt][1]);
+      *reinterpret_cast<float2*>(Gs + (tt * 16 + gq + 8) * 8 + 2 * q) = make_float2(G[tt][2], G[tt][3]);
+    }
+    __syncwarp();
+    if (lane < 24) {
+      const int px = lane & 7, tt = lane >> 3;
+      const float2 c = uv[tt * 8 + px];
+      const int scH = SC44 ? 4 : scH_rt, scW = SC44 ? 4 : scW_rt;
+      const bool valid = c.x > -1.f && c.y > -1.f && c.x < (float)scH && c.y < (float)scW;
+      const float fu = floorf(c.x), fv = floorf(c.y);
+      const float lh = c.x - fu, lw = c.y - fv;
+      const float hh = 1.f - lh, hw = 1.f - lw;
+      // corner rows h0, h0+1 and columns w0, w0+1, clamped into the bank for the loads; a corner outside counts as 0
+      const int h0 = (int)fmaxf(fminf(fu, (float)scH), -2.f), w0 = (int)fmaxf(fminf(fv, (float)scW), -2.f);
+      const bool r0 = h0 >= 0 && h0 < scH, r1 = h0 + 1 >= 0 && h0 + 1 < scH;
+      const bool c0 = w0 >= 0 && w0 < scW, c1 = w0 + 1 >= 0 && w0 + 1 < scW;
+      const int ra = min(max(h0, 0), scH - 1) * scW, rb = min(max(h0 + 1, 0), scH - 1) * scW;
+      const int ca = min(max(w0, 0), scW - 1), cb2 = min(max(w0 + 1, 0), scW - 1);
+      const float* Gp = Gs + tt * 128 + px;
+      const float g00 = (r0 && c0) ? Gp[(ra + ca) * 8] : 0.f, g01 = (r0 && c1) ? Gp[(ra + cb2) * 8] : 0.f;
+      const float g10 = (r1 && c0) ? Gp[(rb + ca) * 8] : 0.f, g11 = (r1 && c1) ? Gp[(rb + cb2) * 8] : 0.f;
+      float gu = hw * (g10 - g00) + lw * (g11 - g01);
+      float gv = hh * (g01 - g00) + lh * (g11 - g10);
+      if (!valid) gu = gv = 0.f;
+      if (ow0 + px < Wo) {
+        __half* o = drot_item + (2 * (fh * 3 + tt)) * P + px;
+        o[0] = __float2half_rn(gu);
+        o[P] = __float2half_rn(gv);
+      }
+    }
+    __syncwarp();
+  }
+  return true;
+}
+
+// End of a block of the bank-gradient kernels: the consumer warps (cw = 0 .. ncw-1; all of them must call this) sum their
+// accumulators through shared memory (red: [ncw][CG][16] floats, reusing the rings, which are idle by now) and write the
+// block's partial sums out[CG][16].
+template <int NS>
+__device__ __forceinline__ void reduce_bank_accumulators(const float (&acc)[NS][2][4], float* __restrict__ red, float* __restrict__ out,
+                                                         int CG, int nslab, int cw, int ncw, int lane) {
+  const int gq = lane >> 2, q = lane & 3;
+  asm volatile("bar.sync 1, %0;\n" ::"r"(ncw * 32) : "memory");
+#pragma unroll
+  for (int sidx = 0; sidx < NS; ++sidx) {
+    if (sidx < nslab) {
+      float* r0 = red + ((size_t)cw * CG + (sidx << 4) + gq) * 16;
+      float* r1 = r0 + 8 * 16;
+      r0[2 * q] = acc[sidx][0][0]; r0[2 * q + 1] = acc[sidx][0][1];
+      r1[2 * q] = acc[sidx][0][2]; r1[2 * q + 1] = acc[sidx][0][3];
+      r0[8 + 2 * q] = acc[sidx][1][0]; r0[8 + 2 * q + 1] = acc[sidx][1][1];
+      r1[8 + 2 * q] = acc[sidx][1][2]; r1[8 + 2 * q + 1] = acc[sidx][1][3];
+    }
+  }
+  asm volatile("bar.sync 1, %0;\n" ::"r"(ncw * 32) : "memory");
+  for (int i = cw * 32 + lane; i < CG * 16; i += ncw * 32) {
+    float sum = 0.f;
+    for (int wv = 0; wv < ncw; ++wv) sum += red[(size_t)wv * CG * 16 + i];
+    out[i] = sum;
   }
 }
 
@@ -768,107 +921,16 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
     const __half* dyr = dring + (size_t)rd.slot(grow) * dslot + gq * ID + 8 + ow;
     __half* drot_item = drot + (size_t)n * 18 * P + oh * Wo + ow0;
 
-    // One pass per kernel row fh (three taps): keeps 12 instead of 36 accumulators of G live, and its source row is
-    // waited for only when the pass starts.
+    ok = gw_item<S, W, NS, SC44>(acc, rx, k0, xring, xslot, rp, dyr, bankT, pitchT, Gs, uv, drot_item, P, nslab, ow0, lc, uh0, uw0,
+                                 p.scH, p.scW, lane) && ok;
+    // the rows are no longer needed
+    __syncwarp();
+    if (lane == 0 && ok) {
+      const bool first = (oh == 0) || (g == g0), last = (oh == Ho - 1) || (g == g1 - 1);
 #pragma unroll
-    for (int fh = 0; fh < 3; ++fh) {
-      // hat products of the three taps, transposed into B fragments of dW += dK * beta:
-      // bw[fw][0] = (pixels 2q, 2q+1; cell gq), bw[fw][1] = cell gq + 8
-      unsigned bw[3][2];
-#pragma unroll
-      for (int fw = 0; fw < 3; ++fw) {
-        unsigned bb[2];
-        float u, v;
-        beta_tap<WOP, SC44>(bb, rp + 2 * (fh * 3 + fw) * WOP, (float)fh, (float)fw, lc, uh0, uw0, u, v);
-        bw[fw][0] = movmatrix_trans(bb[0]);
-        bw[fw][1] = movmatrix_trans(bb[1]);
-        if (q == 0) uv[fw * 8 + gq] = make_float2(u, v);
-      }
-      ok = rx.wait_full(k0 + fh) && ok;
-      if (!ok) break;
-      const __half* xr = xring + (size_t)rx.slot(k0 + fh) * xslot + gq * IX + (8 + ow * S - 2);
-
-      float G[3][4];
-#pragma unroll
-      for (int t = 0; t < 3; ++t) G[t][0] = G[t][1] = G[t][2] = G[t][3] = 0.f;
-
-#pragma unroll
-      for (int sidx = 0; sidx < NS; ++sidx) {
-        if (sidx < nslab) {
-          const unsigned dy0 = *reinterpret_cast<const unsigned*>(dyr + sidx * 16 * ID);
-          const unsigned dy1 = *reinterpret_cast<const unsigned*>(dyr + sidx * 16 * ID + 8 * ID);
-          const unsigned* p0 = reinterpret_cast<const unsigned*>(xr + sidx * 16 * IX);
-          const unsigned* p1 = p0 + 8 * IX / 2;
-          const unsigned w0 = p0[0], w1 = p0[1], w2 = p0[2];
-          const unsigned v0 = p1[0], v1 = p1[1], v2 = p1[2];
-          unsigned d0[3], d1[3];  // dK of channel rows gq and gq + 8 for the three taps
-#pragma unroll
-          for (int fw = 0; fw < 3; ++fw) {
-            d0[fw] = hmul2u(dy0, tap_pair<S>(w0, w1, w2, fw));
-            d1[fw] = hmul2u(dy1, tap_pair<S>(v0, v1, v2, fw));
-          }
-          // A = W^T slab: rows = cells (gq, gq+8), k = channels (2q, 2q+1) and (2q+8, 2q+9)
-          const unsigned* wt0 = reinterpret_cast<const unsigned*>(bankT + gq * pitchT + sidx * 16);
-          const unsigned* wt1 = reinterpret_cast<const unsigned*>(bankT + (gq + 8) * pitchT + sidx * 16);
-          const unsigned a0 = wt0[q], a1 = wt1[q], a2 = wt0[q + 4], a3 = wt1[q + 4];
-#pragma unroll
-          for (int fw = 0; fw < 3; ++fw) mma16816_acc(G[fw], a0, a1, a2, a3, movmatrix_trans(d0[fw]), movmatrix_trans(d1[fw]));
-          // k = 16 = 8 pixels x (tap 0 | tap 1), then 8 pixels x (tap 2 | nothing)
-          mma16816_acc(acc[sidx][0], d0[0], d1[0], d0[1], d1[1], bw[0][0], bw[1][0]);
-          mma16816_acc(acc[sidx][1], d0[0], d1[0], d0[1], d1[1], bw[0][1], bw[1][1]);
-          mma16816_acc(acc[sidx][0], d0[2], d1[2], 0u, 0u, bw[2][0], 0u);
-          mma16816_acc(acc[sidx][1], d0[2], d1[2], 0u, 0u, bw[2][1], 0u);
-        }
-      }
-      if (fh == 2) {
-        // all rows of the item have been read: hand them back before the last epilogue
-        __syncwarp();
-        if (lane == 0) {
-          const bool first = (oh == 0) || (g == g0), last = (oh == Ho - 1) || (g == g1 - 1);
-#pragma unroll
-          for (int j = 0; j < 3; ++j) rx.release(k0 + j, release_count<S>(j, first, last));
-          rd.release(grow, 1);
-          rr.release(grow, 1);
-        }
-      }
-
-      // d(offset)[pixel, tap, dir] = sum over the four corner cells of G * d(coefficient)/d(u or v).  Floor-based, so at an
-      // integer coordinate it is the right-hand derivative and at the upper edge the derivative into the zero extension
-      // (csrc/filter_sample_depthwise_cuda_kernel.cu:137-158); zero when the tap samples outside the bank (:131-135).
-      __syncwarp();
-#pragma unroll
-      for (int tt = 0; tt < 3; ++tt) {
-        *reinterpret_cast<float2*>(Gs + (tt * 16 + gq) * 8 + 2 * q) = make_float2(G[tt][0], G[tt][1]);
-        *reinterpret_cast<float2*>(Gs + (tt * 16 + gq + 8) * 8 + 2 * q) = make_float2(G[tt][2], G[tt][3]);
-      }
-      __syncwarp();
-      if (lane < 24) {
-        const int px = lane & 7, tt = lane >> 3;
-        const float2 c = uv[tt * 8 + px];
-        const int scH = SC44 ? 4 : p.scH, scW = SC44 ? 4 : p.scW;
-        const bool valid = c.x > -1.f && c.y > -1.f && c.x < (float)scH && c.y < (float)scW;
-        const float fu = floorf(c.x), fv = floorf(c.y);
-        const float lh = c.x - fu, lw = c.y - fv;
-        const float hh = 1.f - lh, hw = 1.f - lw;
-        // corner rows h0, h0+1 and columns w0, w0+1, clamped into the bank for the loads; a corner outside counts as 0
-        const int h0 = (int)fmaxf(fminf(fu, (float)scH), -2.f), w0 = (int)fmaxf(fminf(fv, (float)scW), -2.f);
-        const bool r0 = h0 >= 0 && h0 < scH, r1 = h0 + 1 >= 0 && h0 + 1 < scH;
-        const bool c0 = w0 >= 0 && w0 < scW, c1 = w0 + 1 >= 0 && w0 + 1 < scW;
-        const int ra = min(max(h0, 0), scH - 1) * scW, rb = min(max(h0 + 1, 0), scH - 1) * scW;
-        const int ca = min(max(w0, 0), scW - 1), cb2 = min(max(w0 + 1, 0), scW - 1);
-        const float* Gp = Gs + tt * 128 + px;
-        const float g00 = (r0 && c0) ? Gp[(ra + ca) * 8] : 0.f, g01 = (r0 && c1) ? Gp[(ra + cb2) * 8] : 0.f;
-        const float g10 = (r1 && c0) ? Gp[(rb + ca) * 8] : 0.f, g11 = (r1 && c1) ? Gp[(rb + cb2) * 8] : 0.f;
-        float gu = hw * (g10 - g00) + lw * (g11 - g01);
-        float gv = hh * (g01 - g00) + lh * (g11 - g10);
-        if (!valid) gu = gv = 0.f;
-        if (ow0 + px < Wo) {
-          __half* o = drot_item + (2 * (fh * 3 + tt)) * P + px;
-          o[0] = __float2half_rn(gu);
-          o[P] = __float2half_rn(gv);
-        }
-      }
-      __syncwarp();
+      for (int j = 0; j < 3; ++j) rx.release(k0 + j, release_count<S>(j, first, last));
+      rd.release(grow, 1);
+      rr.release(grow, 1);
     }
     if (!ok) {
       ring_fail(lane);
@@ -877,27 +939,288 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
   }
 
   // ---- bank gradient: sum the consumer warps' accumulators (the rings are free now) and write this block's partial
-  asm volatile("bar.sync 1, %0;\n" ::"r"(ncw * 32) : "memory");
+  reduce_bank_accumulators<NS>(acc, reinterpret_cast<float*>(smem_raw), partial + (size_t)blockIdx.x * CG * 16, CG, nslab, cw, ncw, lane);
+}
+
+// ================================================================== the whole backward in one pass
+//
+// grad-input, grad-offsets and grad-bank of one item by the same warp, back to back, from ONE stream of rows: every
+// row of dy, of the offsets and of x crosses HBM and shared memory once for all three gradients.  Stride 1: the item at
+// row j needs the rows j-1 .. j+1 of dy and of the offsets (grad-input, taps flipped) and of x (the products dy * x),
+// i.e. the same three fills of all three rings.  Stride 2: grad-input expands output row j into dx rows 2j, 2j+1 from
+// the rows j, j+1 of dy / offsets, the other two gradients read row j of those and rows 2j-1 .. 2j+1 of x.
+template <int S, int W>
+struct BwdShape {
+  static constexpr int kWo = (W - 1) / S + 1;
+  static constexpr int kNB = (kWo + 7) / 8;
+  static constexpr int kInnerX = RowLayout<W>::kInner;
+  static constexpr int kInnerD = RowLayout<kWo>::kInner;
+  static constexpr bool kDyTma = RowLayout<kWo>::kTma;
+  static constexpr int kUsersD = S == 1 ? 3 : 2;  // destination rows that read one row of dy / offsets
+};
+
+__host__ __device__ inline size_t bwd_ring_smem(int cg, int inner_x, int inner_d, int rot_slot, int Rx, int Rd, int warps) {
+  const size_t rings = ((size_t)Rx * cg * inner_x + 64 + (size_t)Rd * cg * inner_d + 64 + (size_t)Rd * rot_slot) * 2;
+  const size_t red = (size_t)warps * cg * 16 * 4;  // the bank-gradient reduction at the end reuses the rings
+  return (rings > red ? rings : red) + 16 + (size_t)cg * kBankPitch * 2 + (size_t)16 * (cg + 8) * 2 + (size_t)warps * kGwScratch +
+         (size_t)(2 * Rx + 4 * Rd) * 8 + 16 + 128;
+}
+
+template <int S, int W, int NS, bool SC44, int MAXT>
+__global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
+                                                           const __half* __restrict__ dy, const __half* __restrict__ rot,
+                                                           const __half* __restrict__ bankw, __half* __restrict__ dx,
+                                                           __half* __restrict__ drot, float* __restrict__ partial,
+                                                           const RingParams p) {
+  using Sh = BwdShape<S, W>;
+  using RL = RotLayout<Sh::kWo>;
+  constexpr int IX = Sh::kInnerX, ID = Sh::kInnerD, WOP = RL::kWop, NB = Sh::kNB, Wo = Sh::kWo;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int Rx = 1 << p.lgR, Rd = 1 << p.lgRR;
+  const int CG = p.CG;  // every channel
+  const int xslot = CG * IX, dslot = CG * ID;
+  const int ncw = (blockDim.x >> 5) - 1;
+  const int pitchT = CG + 8;
+
+  __half* xring = reinterpret_cast<__half*>(smem_raw);
+  __half* dring = xring + (size_t)Rx * xslot + 64;
+  __half* rring = dring + (size_t)Rd * dslot + 64;
+  const unsigned rings_bytes = (unsigned)(((size_t)Rx * xslot + 64 + (size_t)Rd * dslot + 64 + (size_t)Rd * RL::kSlot) * 2);
+  const unsigned red_bytes = (unsigned)ncw * CG * 16 * 4;
+  const unsigned after = ((rings_bytes > red_bytes ? rings_bytes : red_bytes) + 15u) & ~15u;
+  __half* bank = reinterpret_cast<__half*>(smem_raw + after);                             // [CG][kBankPitch], for K = W * beta
+  __half* bankT = bank + (size_t)CG * kBankPitch;                                         // [16 cells][CG + 8], for G = W^T * dK
+  const unsigned scratch_off = after + (unsigned)(CG * kBankPitch + 16 * pitchT) * 2;
+  unsigned char* scratch = smem_raw + scratch_off;
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + ((scratch_off + (unsigned)ncw * kGwScratch + 7u) & ~7u));
+  Ring rx, rd, rr;
+  rx.full = smem_u32(bars); rx.empty = rx.full + 8 * Rx; rx.lg = p.lgR;
+  rd.full = rx.empty + 8 * Rx; rd.empty = rd.full + 8 * Rd; rd.lg = p.lgRR;
+  rr.full = rd.empty + 8 * Rd; rr.empty = rr.full + 8 * Rd; rr.lg = p.lgRR;
+  rx.issued = rr.empty + 8 * Rd; rd.issued = rx.issued + 4; rr.issued = rx.issued + 8;
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < Rx; ++i) {
+      mbar_init(rx.full + 8 * i, 1);
+      mbar_init(rx.empty + 8 * i, (S == 1 ? 3 : 2) * NB);
+    }
+    for (int i = 0; i < Rd; ++i) {
+      mbar_init(rd.full + 8 * i, Sh::kDyTma ? 1 : 32);
+      mbar_init(rd.empty + 8 * i, Sh::kUsersD * NB);
+      mbar_init(rr.full + 8 * i, 32);
+      mbar_init(rr.empty + 8 * i, Sh::kUsersD * NB);
+    }
+    int* cnt = reinterpret_cast<int*>(bars + 2 * Rx + 4 * Rd);
+    cnt[0] = cnt[1] = cnt[2] = 0;
+    fence_barrier_init();
+  }
   {
-    float* red = reinterpret_cast<float*>(smem_raw);  // [ncw][CG][16]
-#pragma unroll
-    for (int sidx = 0; sidx < NS; ++sidx) {
-      if (sidx < nslab) {
-        float* r0 = red + ((size_t)cw * CG + (sidx << 4) + gq) * 16;
-        float* r1 = r0 + 8 * 16;
-        r0[2 * q] = acc[sidx][0][0]; r0[2 * q + 1] = acc[sidx][0][1];
-        r1[2 * q] = acc[sidx][0][2]; r1[2 * q + 1] = acc[sidx][0][3];
-        r0[8 + 2 * q] = acc[sidx][1][0]; r0[8 + 2 * q + 1] = acc[sidx][1][1];
-        r1[8 + 2 * q] = acc[sidx][1][2]; r1[8 + 2 * q + 1] = acc[sidx][1][3];
+    uint4* z = reinterpret_cast<uint4*>(smem_raw);
+    const int nz = (int)(rings_bytes >> 4);
+    for (int i = threadIdx.x; i < nz; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
+  }
+  for (int i = threadIdx.x; i < 16 * CG; i += blockDim.x) {
+    const int c = i >> 4, cell = i & 15;
+    const __half v = cell < p.cells ? __ldg(bankw + (size_t)c * p.cells + cell) : __float2half(0.f);
+    bank[c * kBankPitch + cell] = v;
+    bankT[cell * pitchT + c] = v;
+  }
+  fence_proxy_async();
+  __syncthreads();
+
+  const int g0 = blockIdx.x * p.rows_per_block;
+  const int g1 = min(g0 + p.rows_per_block, p.rows_total);
+  const int Ho = p.Hs, H = p.Hd;        // rows of dy / offsets and of x / dx
+  const int Lx = p.L;                   // stream rows of x per sample
+  const int Ld = S == 1 ? Lx : Ho + 1;  // ... of dy and the offsets
+  const int n_first = g0 < g1 ? g0 / Ho : 0;
+  const int d_first = g0 - n_first * Ho;
+  const int Tx0 = n_first * Lx + d_first * S;
+  const int Td0 = n_first * Ld + d_first;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (g0 >= g1) return;
+    if (lane == 0) {
+      prefetch_tensormap(&tm_x);
+      if (Sh::kDyTma) prefetch_tensormap(&tm_dy);
+    }
+    const unsigned xbytes = (unsigned)xslot * 2, dbytes = (unsigned)dslot * 2;
+    const unsigned xring_u32 = smem_u32(xring), dring_u32 = smem_u32(dring);
+    int Tx = Tx0, Td = Td0;
+    bool ok = true;
+    for (int g = g0; g < g1 && ok; ++g) {
+      const int n = g / Ho, j = g - n * Ho;
+      const int Td_end = n * Ld + j + (S == 1 ? 2 : 1);
+      for (; Td <= Td_end && ok; ++Td) {
+        const int k = Td - Td0;
+        const int r = Td - n * Ld - (S == 1 ? 1 : 0);  // row of dy / offsets; -1 and Ho are zero rows
+        ok = rr.reclaim(k, lane);
+        if (ok) fill_rot_row<Wo>(rring + (size_t)rr.slot(k) * RL::kSlot, rot, n, Ho, min(max(r, 0), Ho - 1), lane, rr.full + 8 * rr.slot(k));
+        ok = ok && rd.reclaim(k, lane);
+        if (ok) {
+          if (Sh::kDyTma) {
+            if (lane == 0) {
+              mbar_arrive_expect_tx(rd.full + 8 * rd.slot(k), dbytes);
+              tma_load_3d(dring_u32 + rd.slot(k) * dbytes, &tm_dy, -8, r, n * p.C, rd.full + 8 * rd.slot(k));
+            }
+          } else {
+            __half* slot = dring + (size_t)rd.slot(k) * dslot;
+            if (r >= 0 && r < Ho) {
+              fill_plane_row<Wo>(slot, dy, n, p.C, 0, CG, Ho, r, lane, rd.full + 8 * rd.slot(k));
+            } else {  // a zero row: plain stores, then the same 32 arrivals
+              for (int i = lane; i < dslot / 8; i += 32) reinterpret_cast<uint4*>(slot)[i] = make_uint4(0, 0, 0, 0);
+              mbar_arrive(rd.full + 8 * rd.slot(k));
+            }
+          }
+        }
+        __syncwarp();
+      }
+      const int Tx_end = n * Lx + j * S + 2;
+      for (; Tx <= Tx_end && ok; ++Tx) {
+        const int k = Tx - Tx0;
+        ok = rx.reclaim(k, lane);
+        if (lane == 0 && ok) {
+          mbar_arrive_expect_tx(rx.full + 8 * rx.slot(k), xbytes);
+          tma_load_3d(xring_u32 + rx.slot(k) * xbytes, &tm_x, -8, Tx - n * Lx - 1, n * p.C, rx.full + 8 * rx.slot(k));
+        }
+        __syncwarp();
       }
     }
-    asm volatile("bar.sync 1, %0;\n" ::"r"(ncw * 32) : "memory");
-    for (int i = threadIdx.x - 32; i < CG * 16; i += ncw * 32) {
-      float sum = 0.f;
-      for (int wv = 0; wv < ncw; ++wv) sum += red[(size_t)wv * CG * 16 + i];
-      partial[(size_t)blockIdx.x * CG * 16 + i] = sum;
+    cp_async_wait_all();
+    if (!ok) ring_fail(lane);
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int cw = warp - 1;
+  const int gq = lane >> 2, q = lane & 3;
+  const LaneCells lc = lane_cells_of(p.scW, p.cells, q);
+  const float uh0 = (float)(p.scH - 3) * 0.5f, uw0 = (float)(p.scW - 3) * 0.5f;
+  const int nslab = CG >> 4;
+  const int items = g0 < g1 ? (g1 - g0) * NB : 0;
+  const int P = Ho * Wo;
+  const size_t xplane = (size_t)H * W;
+  float* Gs = reinterpret_cast<float*>(scratch + (size_t)cw * kGwScratch);  // [3 taps][16 cells][8 px]
+  float2* uv = reinterpret_cast<float2*>(Gs + 3 * 16 * 8);                    // [3 taps][8 px]
+  const unsigned* bkp = reinterpret_cast<const unsigned*>(bank + gq * kBankPitch) + q;
+
+  float acc[NS][2][4];  // bank gradient of up to NS slabs of 16 channels x (cells 0-7 | cells 8-15)
+#pragma unroll
+  for (int sidx = 0; sidx < NS; ++sidx)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[sidx][0][k] = acc[sidx][1][k] = 0.f;
+
+  bool failed = false;
+  for (int it = cw; it < items; it += ncw) {
+    const int grow = it / NB, cb = it - grow * NB;
+    const int g = g0 + grow;
+    const int n = g / Ho, j = g - n * Ho;
+    const int kx0 = n * Lx + j * S - Tx0;
+    const int kd0 = n * Ld + j - Td0;
+    const int ow0 = cb << 3;
+    const int pg = ow0 + gq;
+    const int ow = ow0 + 2 * q;
+    bool ok = true;
+    float u, v;
+
+    // ---- grad-input
+    {
+      unsigned bf[9][2];
+      if (S == 1) {
+        // dx[j, ow] = sum over taps of dy[j + 1 - fh, ow + 1 - fw] * K[(j + 1 - fh, ow + 1 - fw), tap]
+        ok = rr.wait_full(kd0 + 2);
+#pragma unroll
+        for (int fh = 0; fh < 3; ++fh) {
+          const int k = kd0 + 2 - fh;
+          if (fh) ok = rr.wait_full(k) && ok;
+          const __half* rq = rring + (size_t)rr.slot(k) * RL::kSlot + 8 + pg + 1;
+#pragma unroll
+          for (int fw = 0; fw < 3; ++fw)
+            beta_tap<WOP, SC44>(bf[fh * 3 + fw], rq + 2 * (fh * 3 + fw) * WOP - fw, (float)fh, (float)fw, lc, uh0, uw0, u, v);
+        }
+        const __half* dr[3];
+        ok = rd.wait_full(kd0 + 2) && ok;
+#pragma unroll
+        for (int fh = 0; fh < 3; ++fh) {
+          const int k = kd0 + 2 - fh;
+          if (fh) ok = rd.wait_full(k) && ok;
+          dr[fh] = dring + (size_t)rd.slot(k) * dslot + gq * ID + (8 + ow - 2);
+        }
+        if (!ok) {
+          failed = true;
+          break;
+        }
+        __half* x0 = dx + ((size_t)n * p.C + gq) * xplane + (size_t)j * W + ow;
+        conv_slabs<1, ID, true>(dr, bkp, x0, nslab, xplane, ow < W, bf);
+      } else {
+        ok = rr.wait_full(kd0 + 1);
+        ok = rr.wait_full(kd0) && ok;
+#pragma unroll
+        for (int vr = 0; vr < 3; ++vr) {
+          const int da = vr == 2 ? 1 : 0, fh = vr == 2 ? 0 : vr + 1;
+          const __half* rq = rring + (size_t)rr.slot(kd0 + da) * RL::kSlot + 8 + pg;
+#pragma unroll
+          for (int vc = 0; vc < 3; ++vc) {
+            const int db = vc == 2 ? 1 : 0, fw = vc == 2 ? 0 : vc + 1;
+            beta_tap<WOP, SC44>(bf[vr * 3 + vc], rq + 2 * (fh * 3 + fw) * WOP + db, (float)fh, (float)fw, lc, uh0, uw0, u, v);
+          }
+        }
+        ok = rd.wait_full(kd0 + 1) && ok;
+        ok = rd.wait_full(kd0) && ok;
+        if (!ok) {
+          failed = true;
+          break;
+        }
+        const __half* dr[2];
+#pragma unroll
+        for (int da = 0; da < 2; ++da) dr[da] = dring + (size_t)rd.slot(kd0 + da) * dslot + gq * ID + 8 + ow;
+        __half* x0 = dx + ((size_t)n * p.C + gq) * xplane + (size_t)(2 * j) * W + 2 * ow;
+        convT2_slabs<ID, W>(dr, bkp, x0, nslab, xplane, 2 * j + 1 < H, 2 * ow < W, bf);
+      }
+    }
+
+    // ---- grad-offsets and grad-bank: row j of dy and of the offsets, rows j*S - 1 .. j*S + 1 of x
+    {
+      const int kr = S == 1 ? kd0 + 1 : kd0;
+      const __half* rp = rring + (size_t)rr.slot(kr) * RL::kSlot + 8 + pg;
+      const __half* dyr = dring + (size_t)rd.slot(kr) * dslot + gq * ID + 8 + ow;
+      __half* drot_item = drot + (size_t)n * 18 * P + j * Wo + ow0;
+      ok = gw_item<S, W, NS, SC44>(acc, rx, kx0, xring, xslot, rp, dyr, bankT, pitchT, Gs, uv, drot_item, P, nslab, ow0, lc, uh0, uw0,
+                                   p.scH, p.scW, lane);
+      if (!ok) {
+        failed = true;
+        break;
+      }
+    }
+
+    // every row the item read goes back to the producer
+    __syncwarp();
+    if (lane == 0) {
+      const bool first = (j == 0) || (g == g0), last = (j == Ho - 1) || (g == g1 - 1);
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int m = release_count<S>(i, first, last);
+        rx.release(kx0 + i, m);
+        if (S == 1) {
+          rd.release(kd0 + i, m);
+          rr.release(kd0 + i, m);
+        }
+      }
+      if (S == 2) {
+        rd.release(kd0, first ? 2 : 1);
+        rr.release(kd0, first ? 2 : 1);
+        rd.release(kd0 + 1, last ? 2 : 1);
+        rr.release(kd0 + 1, last ? 2 : 1);
+      }
     }
   }
+  if (failed) ring_fail(lane);
+
+  // ---- bank gradient: sum the consumer warps' accumulators (the rings are free now) and write this block's partial
+  reduce_bank_accumulators<NS>(acc, reinterpret_cast<float*>(smem_raw), partial + (size_t)blockIdx.x * CG * 16, CG, nslab, cw, ncw, lane);
 }
 
 // ------------------------------------------------------------------ host side
@@ -1150,6 +1473,86 @@ int launch_gw_ring(const __half* dy, const __half* x, const __half* rot, const _
   return launch_gw_ring_sc<S, W, false>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s);
 }
 
+struct BwdRingPlan {
+  bool ok;
+  int lgRx, lgRd, warps, blocks_x, rows_per_block, ns;
+  size_t smem, ws_bytes;
+};
+
+template <int S, int W>
+BwdRingPlan bwd_ring_plan(const Geom& g) {
+  using Sh = BwdShape<S, W>;
+  using RL = RotLayout<Sh::kWo>;
+  BwdRingPlan pl;
+  pl.ok = false;
+  pl.ns = g.C <= 96 ? 6 : 9;
+  if (g.C > 144) return pl;  // the bank-gradient accumulators of all channels live in registers
+  const int max_warps = pl.ns == 6 ? 16 : 12;  // 128 or 168 registers per thread
+  const size_t budget = (size_t)device_smem_optin();
+  // Deeper rings first; four slots is the least that lets the producer run one row ahead.  Each consumer warp owns 1.7 KB
+  // of scratch, so where shared memory is short a few warps fewer are launched rather than falling back to two passes.
+  static const int kDepth[][2] = {{3, 3}, {3, 2}, {2, 2}};
+  for (int i = 0; i < 3 && !pl.ok; ++i)
+    for (int warps = max_warps; warps >= max_warps - (i == 2 ? 4 : 0) && !pl.ok; --warps) {
+      const size_t smem = bwd_ring_smem(g.C, Sh::kInnerX, Sh::kInnerD, RL::kSlot, 1 << kDepth[i][0], 1 << kDepth[i][1], warps - 1);
+      if (smem > budget) continue;
+      pl.ok = true;
+      pl.lgRx = kDepth[i][0];
+      pl.lgRd = kDepth[i][1];
+      pl.warps = warps;
+      pl.smem = smem;
+    }
+  if (!pl.ok) return pl;
+  spread_rows((long long)g.N * g.Ho, 1, &pl.blocks_x, &pl.rows_per_block);
+  pl.ws_bytes = (size_t)pl.blocks_x * g.C * 16 * sizeof(float);
+  return pl;
+}
+
+template <int S, int W, bool SC44>
+int launch_bwd_ring_sc(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* dx, __half* drot, __half* dw,
+                       const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s) {
+  using Sh = BwdShape<S, W>;
+  const BwdRingPlan pl = bwd_ring_plan<S, W>(g);
+  if (!pl.ok) return DK_ERR_UNSUPPORTED;
+  if (ws == nullptr || ws_bytes < pl.ws_bytes) return DK_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(dy) & 15) || (reinterpret_cast<uintptr_t>(dx) & 7))
+    return DK_ERR_UNSUPPORTED;
+  CUtensorMap tmx, tmd;
+  if (!make_row_map(&tmx, x, W, g.H, (long long)g.N * g.C, Sh::kInnerX, g.C)) return DK_ERR_UNSUPPORTED;
+  if (Sh::kDyTma) {
+    if (!make_row_map(&tmd, dy, Sh::kWo, g.Ho, (long long)g.N * g.C, Sh::kInnerD, g.C)) return DK_ERR_UNSUPPORTED;
+  } else {
+    tmd = tmx;
+  }
+  RingParams p;
+  p.N = g.N; p.C = g.C; p.Hs = g.Ho; p.Hd = g.H;
+  p.CG = g.C; p.lgR = pl.lgRx; p.lgRR = pl.lgRd;
+  p.L = (g.Ho - 1) * S + 3;
+  p.rows_total = g.N * g.Ho;
+  p.rows_per_block = pl.rows_per_block;
+  p.scH = g.scH; p.scW = g.scW; p.cells = g.cells;
+  float* partial = reinterpret_cast<float*>(ws);
+  int rc;
+  if (pl.ns == 6) {
+    auto kern = ring_bwd_kernel<S, W, 6, SC44, 512>;
+    if ((rc = enable_smem(kern, pl.smem))) return rc;
+    kern<<<pl.blocks_x, pl.warps * 32, pl.smem, s>>>(tmx, tmd, dy, rot, w, dx, drot, partial, p);
+  } else {
+    auto kern = ring_bwd_kernel<S, W, 9, SC44, 384>;
+    if ((rc = enable_smem(kern, pl.smem))) return rc;
+    kern<<<pl.blocks_x, pl.warps * 32, pl.smem, s>>>(tmx, tmd, dy, rot, w, dx, drot, partial, p);
+  }
+  if ((rc = check_launch())) return rc;
+  return launch_reduce_bank_partials(partial, dw, g.C, g.cells, pl.blocks_x, s);
+}
+
+template <int S, int W>
+int launch_bwd_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* dx, __half* drot, __half* dw,
+                    const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s) {
+  if (g.scH == 4 && g.scW == 4) return launch_bwd_ring_sc<S, W, true>(dy, x, rot, w, dx, drot, dw, g, ws, ws_bytes, s);
+  return launch_bwd_ring_sc<S, W, false>(dy, x, rot, w, dx, drot, dw, g, ws, ws_bytes, s);
+}
+
 }  // namespace
 
 // Code of the last bounded wait that ran out in a ring kernel on the current device (0 = none);
@@ -1179,6 +1582,33 @@ size_t local_gw_ring_workspace(const Geom& g) {
   if (g.W == 112) pl = g.sH == 1 ? gw_ring_plan<1, 112>(g) : gw_ring_plan<2, 112>(g);
   else pl = g.sH == 1 ? gw_ring_plan<1, 56>(g) : gw_ring_plan<2, 56>(g);
   return pl.ok ? pl.ws_bytes : 0;
+}
+
+// Workspace of local_bwd_ring (the per-block partial bank gradients); 0 = the shape is not covered.
+size_t local_bwd_ring_workspace(const Geom& g) {
+  if (!ring_shape(g)) return 0;
+  BwdRingPlan pl;
+  if (g.W == 112) pl = g.sH == 1 ? bwd_ring_plan<1, 112>(g) : bwd_ring_plan<2, 112>(g);
+  else pl = g.sH == 1 ? bwd_ring_plan<1, 56>(g) : bwd_ring_plan<2, 56>(g);
+  return pl.ok ? pl.ws_bytes : 0;
+}
+
+// Measured on B200 (batch 128, ms, one pass against grad-input + offsets / bank pass): C=96 112x112 stride 1 1.03 / 0.84,
+// stride 2 0.29 / 0.26; C=144 56x56 stride 1 0.36 / 0.33, stride 2 0.172 / 0.184.  One pass moves every tensor once, but
+// its grad-input half runs at the register count and warp count the offsets / bank half needs (12-15 warps of 128-168
+// registers instead of 20 of 80), and on the 112-wide layers shared memory allows only 12 warps.  So it is the default
+// only on the narrow stride-2 shape where it won; dk_sample_depthwise_backward_one_pass asks for it explicitly.
+bool local_bwd_ring_preferred(const Geom& g) { return ring_shape(g) && g.W == 56 && g.sH == 2; }
+
+// all three gradients in one pass over dy, x and the offsets
+int local_bwd_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* dx, __half* drot, __half* dw,
+                   const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s) {
+  if (!ring_shape(g) || dx == nullptr || drot == nullptr || dw == nullptr) return DK_ERR_UNSUPPORTED;
+  if (g.W == 112)
+    return g.sH == 1 ? launch_bwd_ring<1, 112>(dy, x, rot, w, dx, drot, dw, g, ws, ws_bytes, s)
+                     : launch_bwd_ring<2, 112>(dy, x, rot, w, dx, drot, dw, g, ws, ws_bytes, s);
+  return g.sH == 1 ? launch_bwd_ring<1, 56>(dy, x, rot, w, dx, drot, dw, g, ws, ws_bytes, s)
+                   : launch_bwd_ring<2, 56>(dy, x, rot, w, dx, drot, dw, g, ws, ws_bytes, s);
 }
 
 // grad-offsets and grad-bank in one pass

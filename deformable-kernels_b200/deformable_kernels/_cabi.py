@@ -46,6 +46,7 @@ _PROTOS = {
     "dk_sample_depthwise_backward_rotation": (_int, [_vp, _vp, _vp, _vp, _vp, _gp, _int, _vp, _sz, _vp]),
     "dk_sample_depthwise_backward_workspace_bytes": (_sz, [_gp, _int]),
     "dk_sample_depthwise_backward": (_int, [_vp] * 7 + [_gp, _int, _vp, _sz, _vp]),
+    "dk_sample_depthwise_backward_one_pass": (_int, [_vp] * 7 + [_gp, _int, _vp, _sz, _vp]),
     "dk_deform_sample_depthwise_forward": (_int, [_vp] * 5 + [_gp, _int, _vp]),
     "dk_deform_sample_depthwise_backward_data_workspace_bytes": (_sz, [_gp, _int]),
     "dk_deform_sample_depthwise_backward_data": (_int, [_vp] * 5 + [_gp, _int, _vp, _sz, _vp]),

@@ -108,6 +108,15 @@ int dk_sample_depthwise_backward_filter(const void *grad_output, const void *inp
                                         void *grad_filter, const dk_geom *g, int dtype, void *workspace,
                                         size_t workspace_bytes, void *stream);
 
+/* No counterpart in the reference (which runs three launches, functions/filter_sample_depthwise.py:53-87): all three
+ * gradients in ONE pass in which every row of grad_output, of the offsets and of input crosses HBM once (fp16, 3x3, pad 1,
+ * stride 1 or 2, rows of 112 or 56 elements, at most 144 channels; DK_ERR_UNSUPPORTED otherwise).  It moves the least
+ * memory but is not the fastest way on most shapes, so dk_sample_depthwise_backward picks it only where it is.
+ * Workspace: dk_sample_depthwise_backward_workspace_bytes(). */
+int dk_sample_depthwise_backward_one_pass(const void *grad_output, const void *input, const void *rotation, const void *filter,
+                                          void *grad_input, void *grad_rotation, void *grad_filter, const dk_geom *g, int dtype,
+                                          void *workspace, size_t workspace_bytes, void *stream);
+
 /* No counterpart in the reference.  Same result as dk_sample_depthwise_backward_filter, for callers
  * that cannot supply a workspace because they may not allocate device memory at call time (plugins
  * inside a memory-planned runtime, fixed-memory control loops, FFI hosts without a CUDA allocator):

@@ -587,6 +587,26 @@ def test_cfg3_full_size_fp16_against_live_reference(ops, c, hw, stride):
     compare(got, want, torch.float16, "cfg3-full")
 
 
+@pytest.mark.parametrize("c,hw,stride,n", [(96, 112, 1, 3), (48, 112, 2, 5), (144, 56, 1, 4), (32, 56, 2, 7)])
+def test_one_pass_backward_matches_oracle(oracle, c, hw, stride, n):
+    """dk_sample_depthwise_backward_one_pass (all three gradients from one stream of rows) through the C ABI; batch sizes
+    that make the blocks' row ranges start and end inside samples."""
+    from deformable_kernels import _cabi as C
+    case = make_case(n, c, hw, hw, stride=stride, rot_std=1.0, seed=90 + n)
+    x, r, w, dy = (case[k].half().to(DEV) for k in ("input", "rotation", "weight", "grad_output"))
+    g = C.geom(x.shape, (3, 3), (stride, stride), (1, 1), (1, 1), (4, 4), 1)
+    nb = C.lib.dk_sample_depthwise_backward_workspace_bytes(g, C.DK_F16)
+    ws = torch.empty(nb, dtype=torch.uint8, device=DEV)
+    gx, gr, gw = torch.empty_like(x), torch.empty_like(r), torch.empty_like(w)
+    C.check(C.lib.dk_sample_depthwise_backward_one_pass(C.ptr(dy), C.ptr(x), C.ptr(r), C.ptr(w), C.ptr(gx), C.ptr(gr), C.ptr(gw), g,
+                                                        C.DK_F16, C.ptr(ws), nb, C.stream_ptr(x.device)), "one-pass backward")
+    torch.cuda.synchronize()
+    assert C.lib.dk_ring_error_status() == 0
+    want = oracle_local(oracle, case, torch.float16)
+    compare(dict(grad_input=gx, grad_rotation=gr, grad_weight=gw),
+            {k: want[k] for k in ("grad_input", "grad_rotation", "grad_weight")}, torch.float16, "one pass")
+
+
 @pytest.mark.parametrize("shift", [10, 11])
 @pytest.mark.parametrize("c,hw,stride", [(96, 56, 1), (32, 112, 2), (64, 28, 1)])
 def test_local_dk_fp16_with_loss_scaled_gradients(ops, oracle, c, hw, stride, shift):
