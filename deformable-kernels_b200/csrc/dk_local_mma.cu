@@ -890,6 +890,14 @@ int launch_reduce_bank_partials(const float* partial, __half* out, int C, int ce
   return check_launch();
 }
 
+// out[i] = sum over channel groups of partial[group][i]: the second stage of the offset gradient when the channels are split
+int launch_reduce_rot_partials(const float* partial, __half* out, size_t n_out, int groups, cudaStream_t s) {
+  const size_t blocks = (n_out + 255) / 256;
+  if (blocks > 0x7fffffffULL) return DK_ERR_UNSUPPORTED;
+  reduce_rot_partials_kernel<<<(unsigned)blocks, 256, 0, s>>>(partial, out, n_out, groups);
+  return check_launch();
+}
+
 // ------------------------------------------------------------------ entry points used by dk_local.cu
 // Each returns DK_ERR_UNSUPPORTED when the shape is outside the fast path.
 

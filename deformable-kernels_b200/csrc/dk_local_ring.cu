@@ -18,9 +18,11 @@
 //                        G^T[16 cells x 8 px] += W^T * dK   -> four-corner derivative contraction -> d(offsets)
 //                        dW[16 ch x 16 cells] += dK * beta  -> per-block partial sums, reduced in a fixed order
 //
-// Covers what dk_local_mma.cu covers (fp16, 3x3, pad 1, dilation 1, stride 1 or 2, one offset
-// group, <= 16 bank cells, channels a multiple of 16) on input rows of 112 or 56 elements (TMA
-// needs 16-byte row pitches); other shapes stay on dk_local_mma.cu.
+//   ring_convT2_kernel grad-input at stride 2: an item of 8 output pixels expands into a 2 x 16 patch of dx
+//   ring_bwd_kernel    all three gradients from one stream of rows (least memory traffic; not the fastest, see below)
+//
+// Covers fp16, 3x3, pad 1, dilation 1, stride 1 or 2, one offset group, scope 4 x 4, channels a multiple
+// of 16, input rows of 112 or 56 elements (TMA needs 16-byte row pitches); other shapes stay on dk_local_mma.cu.
 #include <cstdlib>
 #include <cstring>
 
@@ -31,8 +33,10 @@ namespace dk {
 using namespace mma;
 using namespace ring;
 
-// out[c][cell] = sum over blocks of partial[block][c][16] (dk_local_mma.cu)
+// second stages of the gradient reductions (dk_local_mma.cu):
+// out[c][cell] = sum over blocks of partial[block][c][16];  out[i] = sum over channel groups of partial[group][i]
 int launch_reduce_bank_partials(const float* partial, __half* out, int C, int cells, int nblocks, cudaStream_t s);
+int launch_reduce_rot_partials(const float* partial, __half* out, size_t n_out, int groups, cudaStream_t s);
 
 namespace {
 
@@ -96,9 +100,8 @@ template <int Wr>
 struct RotLayout {
   static constexpr int kWop = 8 + ((Wr + 7) / 8) * 8 + 8;
   static constexpr int kSlot = 18 * kWop;  // halves
-  static constexpr int kPiece = (Wr % 8 == 0) ? 16 : ((Wr % 4 == 0) ? 8 : 4);
-  static constexpr int kPieces = Wr * 2 / kPiece;
-  static_assert(Wr % 2 == 0, "offset rows are copied in pieces of 4 bytes or more");
+  static constexpr int kPiece = (Wr % 8 == 0) ? 16 : ((Wr % 4 == 0) ? 8 : ((Wr % 2 == 0) ? 4 : 0));  // 0: element by element
+  static constexpr int kPieces = kPiece ? Wr * 2 / kPiece : Wr;
 };
 
 template <int PIECE>
@@ -108,36 +111,98 @@ __device__ __forceinline__ void cp_piece(void* d, const void* s) {
   else cp_async4(d, s);
 }
 
-// producer warp: row `row` of the 18 offset planes of sample n -> ring slot; the slot's "full" barrier (count 32)
-// gets one arrival per lane when that lane's copies have landed
+// producer warp: row `row` of the 18 offset planes of sample n -> ring slot.  The slot's "full" barrier (count 32) gets one
+// arrival per lane: when that lane's cp.async copies have landed, or, for odd row widths that only allow element-wise
+// copies, after the lane's plain stores.
 template <int Wr>
 __device__ __forceinline__ void fill_rot_row(__half* slot, const __half* __restrict__ rot, int n, int rows, int row, int lane,
                                              unsigned full_bar) {
   using RL = RotLayout<Wr>;
   const size_t plane = (size_t)rows * Wr;
   const __half* sp = rot + (size_t)n * 18 * plane + (size_t)row * Wr;
-  for (int i = lane; i < 18 * RL::kPieces; i += 32) {
-    const int pl = i / RL::kPieces, pc = i - pl * RL::kPieces;
-    cp_piece<RL::kPiece>(slot + pl * RL::kWop + 8 + pc * (RL::kPiece / 2), sp + pl * plane + pc * (RL::kPiece / 2));
+  if (RL::kPiece) {
+    for (int i = lane; i < 18 * RL::kPieces; i += 32) {
+      const int pl = i / RL::kPieces, pc = i - pl * RL::kPieces;
+      cp_piece<RL::kPiece ? RL::kPiece : 4>(slot + pl * RL::kWop + 8 + pc * (RL::kPiece / 2), sp + pl * plane + pc * (RL::kPiece / 2));
+    }
+    cp_async_arrive_noinc(full_bar);
+  } else {
+    for (int base = 0; base < 18 * Wr; base += 256) {  // eight independent loads per lane in flight
+      __half v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int i = base + k * 32 + lane, pl = i / Wr;
+        if (i < 18 * Wr) v[k] = __ldg(sp + pl * plane + (i - pl * Wr));
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int i = base + k * 32 + lane, pl = i / Wr;
+        if (i < 18 * Wr) slot[pl * RL::kWop + 8 + (i - pl * Wr)] = v[k];
+      }
+    }
+    mbar_arrive(full_bar);
   }
-  cp_async_arrive_noinc(full_bar);
 }
 
-// producer warp: row `row` of channels c0 .. c0+cg-1 of sample n of a [N][C][rows][Wd] tensor -> ring slot with cp.async
-// (for rows TMA cannot fetch); full barrier count 32 as above
+// producer warp: row `row` of channels c0 .. c0+cg-1 of sample n of a [N][C][rows][Wd] tensor -> ring slot, for rows TMA
+// cannot fetch (cp.async pieces of 16, 8 or 4 bytes, element-wise for odd widths); full barrier count 32 as above
 template <int Wd>
 __device__ __forceinline__ void fill_plane_row(__half* slot, const __half* __restrict__ src, int n, int C, int c0, int cg, int rows,
                                                int row, int lane, unsigned full_bar) {
   using L = RowLayout<Wd>;
-  constexpr int PB = L::kPiece ? L::kPiece : 4;
-  constexpr int PIECES = Wd * 2 / PB;
   const size_t plane = (size_t)rows * Wd;
   const __half* sp = src + ((size_t)n * C + c0) * plane + (size_t)row * Wd;
-  for (int i = lane; i < cg * PIECES; i += 32) {
-    const int ch = i / PIECES, pc = i - ch * PIECES;
-    cp_piece<PB>(slot + ch * L::kInner + 8 + pc * (PB / 2), sp + ch * plane + pc * (PB / 2));
+  if (L::kPiece) {
+    constexpr int PB = L::kPiece ? L::kPiece : 4;
+    constexpr int PIECES = Wd * 2 / PB;
+    for (int i = lane; i < cg * PIECES; i += 32) {
+      const int ch = i / PIECES, pc = i - ch * PIECES;
+      cp_piece<PB>(slot + ch * L::kInner + 8 + pc * (PB / 2), sp + ch * plane + pc * (PB / 2));
+    }
+    cp_async_arrive_noinc(full_bar);
+  } else {
+    for (int base = 0; base < cg * Wd; base += 256) {  // eight independent loads per lane in flight
+      __half v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int i = base + k * 32 + lane, ch = i / Wd;
+        if (i < cg * Wd) v[k] = __ldg(sp + ch * plane + (i - ch * Wd));
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int i = base + k * 32 + lane, ch = i / Wd;
+        if (i < cg * Wd) slot[ch * L::kInner + 8 + (i - ch * Wd)] = v[k];
+      }
+    }
+    mbar_arrive(full_bar);
   }
-  cp_async_arrive_noinc(full_bar);
+}
+
+// producer warp: one source row of the block's channels into its ring slot, whatever the row width allows.  Rows outside
+// the plane (row < 0 or >= rows) become zero rows: the TMA unit fills them by itself, the other paths store zeros.
+// The slot's full barrier counts 1 (TMA: the expect_tx arrival) or 32 (one arrival per lane).
+template <int Wd>
+__device__ __forceinline__ void fill_src_row(__half* slot, unsigned slot_u32, unsigned slot_bytes, const CUtensorMap* tm,
+                                             const __half* __restrict__ src, int n, int C, int c0, int cg, int rows, int row, int lane,
+                                             unsigned full_bar) {
+  if (RowLayout<Wd>::kTma) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(full_bar, slot_bytes);
+      tma_load_3d(slot_u32, tm, -8, row, n * C + c0, full_bar);
+    }
+  } else if (row >= 0 && row < rows) {
+    fill_plane_row<Wd>(slot, src, n, C, c0, cg, rows, row, lane, full_bar);
+  } else {
+    for (int i = lane; i < (int)(slot_bytes >> 4); i += 32) reinterpret_cast<uint4*>(slot)[i] = make_uint4(0, 0, 0, 0);
+    mbar_arrive(full_bar);
+  }
+}
+
+// Four 8 x 8 tiles of 16-bit values in one instruction: lane l passes the address of row l % 8 of tile l / 8 (16 bytes, aligned)
+// and receives, per tile, the fragment element pair (row lane / 4, columns 2 (lane % 4), + 1).
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* row) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 
 // d = a * b, fp32 result, without `volatile` so that the compiler may schedule it freely
@@ -163,16 +228,14 @@ __device__ __forceinline__ int release_count(int j, bool first, bool last) {
 // The channel-slab loop of the forward / stride-1 grad-input stencil for one item: xr[fh] points at the lane's window
 // (channel row gq, source column ow*S - 2) in the slot of source row fh, bkp at the lane's words of the bank copy, y0 at
 // destination (channel gq, pixel ow); bf holds the hat products of the nine taps.
-template <int S, int INNER, bool TR>
-__device__ __forceinline__ void conv_slabs(const __half* const (&xr)[3], const unsigned* __restrict__ bkp, __half* __restrict__ y0,
-                                           int nslab, size_t dplane, bool store, const unsigned (&bf)[9][2]) {
+// npx = how many of the lane's two pixels exist (0, 1, 2); PAIRS = destination rows are even, so a pixel pair is one aligned word.
+template <int S, int INNER, bool TR, bool PAIRS>
+__device__ __forceinline__ void conv_slabs(const __half* const (&xr)[3], const __half* __restrict__ bkp, __half* __restrict__ y0,
+                                           int nslab, size_t dplane, int npx, const unsigned (&bf)[9][2]) {
 #pragma unroll 3
   for (int sb = 0; sb < nslab; ++sb) {
-    unsigned a[4];
-    a[0] = bkp[sb * (16 * kBankPitch / 2)];
-    a[1] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2];
-    a[2] = bkp[sb * (16 * kBankPitch / 2) + 4];
-    a[3] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2 + 4];
+    unsigned a[4];  // A = the slab's 16 channels x 16 cells
+    ldmatrix_x4(a, bkp + sb * 16 * kBankPitch);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int fh = 0; fh < 3; ++fh) {
@@ -200,10 +263,21 @@ __device__ __forceinline__ void conv_slabs(const __half* const (&xr)[3], const u
         acc[3] = fmaf(kd[3], fb[i1], acc[3]);
       }
     }
-    if (store) {
-      __half* ya = y0 + (size_t)sb * 16 * dplane;
-      *reinterpret_cast<__half2*>(ya) = __floats2half2_rn(acc[0], acc[1]);
-      *reinterpret_cast<__half2*>(ya + 8 * dplane) = __floats2half2_rn(acc[2], acc[3]);
+    __half* ya = y0 + (size_t)sb * 16 * dplane;
+    if (PAIRS) {
+      if (npx) {
+        *reinterpret_cast<__half2*>(ya) = __floats2half2_rn(acc[0], acc[1]);
+        *reinterpret_cast<__half2*>(ya + 8 * dplane) = __floats2half2_rn(acc[2], acc[3]);
+      }
+    } else {
+      if (npx > 0) {
+        ya[0] = __float2half_rn(acc[0]);
+        ya[8 * dplane] = __float2half_rn(acc[2]);
+      }
+      if (npx > 1) {
+        ya[1] = __float2half_rn(acc[1]);
+        ya[8 * dplane + 1] = __float2half_rn(acc[3]);
+      }
     }
   }
 }
@@ -220,7 +294,7 @@ struct ConvShape {
   static constexpr int kWr = TR ? W : kWd;              // width of the offset planes
   static constexpr int kNB = (kWd + 7) / 8;             // items (8 destination pixels) per row
   static constexpr int kInner = RowLayout<W>::kInner;
-  static_assert(RowLayout<W>::kTma, "source rows of this kernel come by TMA");
+  static constexpr bool kTma = RowLayout<W>::kTma;
 };
 
 __host__ __device__ inline size_t conv_ring_smem(int cg, int inner, int rot_slot, int R, int RR) {
@@ -229,9 +303,9 @@ __host__ __device__ inline size_t conv_ring_smem(int cg, int inner, int rot_slot
 }
 
 template <int S, int W, bool TR, bool SC44, int MAXT>
-__global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constant__ CUtensorMap tm_src, const __half* __restrict__ rot,
-                                                            const __half* __restrict__ bankw, __half* __restrict__ dst,
-                                                            const RingParams p) {
+__global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constant__ CUtensorMap tm_src, const __half* __restrict__ src,
+                                                            const __half* __restrict__ rot, const __half* __restrict__ bankw,
+                                                            __half* __restrict__ dst, const RingParams p) {
   using Sh = ConvShape<S, W, TR>;
   using RL = RotLayout<Sh::kWr>;
   constexpr int INNER = Sh::kInner, WOP = RL::kWop, NB = Sh::kNB, Wd = Sh::kWd;
@@ -258,7 +332,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
   // ---- set-up: barriers, zeroed rings (pads and the tail must read as zero from the start), bank copy
   if (threadIdx.x == 0) {
     for (int i = 0; i < R; ++i) {
-      mbar_init(rx.full + 8 * i, 1);
+      mbar_init(rx.full + 8 * i, Sh::kTma ? 1 : 32);
       mbar_init(rx.empty + 8 * i, (S == 1 ? 3 : 2) * NB);
     }
     for (int i = 0; i < RR; ++i) {
@@ -290,7 +364,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) prefetch_tensormap(&tm_src);
+    if (lane == 0 && Sh::kTma) prefetch_tensormap(&tm_src);
     const unsigned slot_bytes = (unsigned)slot_halves * 2;
     const unsigned xring_u32 = smem_u32(xring);
     int T = T0;
@@ -313,10 +387,9 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
                                   rr.full + 8 * rr.slot(k));
         }
         ok = ok && rx.reclaim(k, lane);
-        if (lane == 0 && ok) {
-          mbar_arrive_expect_tx(rx.full + 8 * rx.slot(k), slot_bytes);
-          tma_load_3d(xring_u32 + rx.slot(k) * slot_bytes, &tm_src, -8, r, n * p.C + c0, rx.full + 8 * rx.slot(k));
-        }
+        if (ok)
+          fill_src_row<W>(xring + (size_t)rx.slot(k) * slot_halves, xring_u32 + rx.slot(k) * slot_bytes, slot_bytes, &tm_src, src, n,
+                          p.C, c0, CG, p.Hs, r, lane, rx.full + 8 * rx.slot(k));
         __syncwarp();
       }
     }
@@ -377,9 +450,9 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
     }
 
     const int ow = ow0 + 2 * q;
-    const unsigned* bkp = reinterpret_cast<const unsigned*>(bank + gq * kBankPitch) + q;
+    const __half* bkp = bank + ((lane & 7) + ((lane >> 3) & 1) * 8) * kBankPitch + (lane >> 4) * 8;  // this lane's ldmatrix row
     __half* y0 = dst + ((size_t)n * p.C + c0 + gq) * dplane + (size_t)d * Wd + ow;
-    conv_slabs<S, INNER, TR>(xr, bkp, y0, nslab, dplane, ow < Wd, bf);
+    conv_slabs<S, INNER, TR, (Wd % 2 == 0)>(xr, bkp, y0, nslab, dplane, ow + 1 < Wd ? 2 : (ow < Wd ? 1 : 0), bf);
 
     // done with the three source rows (and the offset rows)
     __syncwarp();
@@ -399,16 +472,31 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
 // The channel-slab loop of the stride-2 grad-input for one item: dr[da] points at the lane's dy pair (channel row gq,
 // column b) in the slot of output row a + da, x0 at dx (channel gq, row 2a, column 2b); bf holds the hat products of
 // the nine (pixel shift, tap) pairs, index 3 * vr + vc with (da, fh) = (0,1), (0,2), (1,0) for vr = 0, 1, 2 and (db, fw) alike.
+// Four consecutive dx values of one row (the first ncols of them exist), as wide as the row pitch of W halves allows.
+template <int W>
+__device__ __forceinline__ void store4(__half* __restrict__ p, const float (&v)[4], int ncols) {
+  if (W % 4 == 0) {
+    if (ncols > 0) {
+      const __half2 lo = __floats2half2_rn(v[0], v[1]), hi = __floats2half2_rn(v[2], v[3]);
+      *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const unsigned*>(&lo), *reinterpret_cast<const unsigned*>(&hi));
+    }
+  } else if (W % 2 == 0) {
+    if (ncols > 0) *reinterpret_cast<__half2*>(p) = __floats2half2_rn(v[0], v[1]);
+    if (ncols > 2) *reinterpret_cast<__half2*>(p + 2) = __floats2half2_rn(v[2], v[3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (i < ncols) p[i] = __float2half_rn(v[i]);
+  }
+}
+
 template <int INNER, int W>
-__device__ __forceinline__ void convT2_slabs(const __half* const (&dr)[2], const unsigned* __restrict__ bkp, __half* __restrict__ x0,
-                                             int nslab, size_t dplane, bool row1, bool col_ok, const unsigned (&bf)[9][2]) {
+__device__ __forceinline__ void convT2_slabs(const __half* const (&dr)[2], const __half* __restrict__ bkp, __half* __restrict__ x0,
+                                             int nslab, size_t dplane, bool row1, int ncols, const unsigned (&bf)[9][2]) {
 #pragma unroll 3
   for (int sb = 0; sb < nslab; ++sb) {
-    unsigned af[4];
-    af[0] = bkp[sb * (16 * kBankPitch / 2)];
-    af[1] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2];
-    af[2] = bkp[sb * (16 * kBankPitch / 2) + 4];
-    af[3] = bkp[sb * (16 * kBankPitch / 2) + 8 * kBankPitch / 2 + 4];
+    unsigned af[4];  // A = the slab's 16 channels x 16 cells
+    ldmatrix_x4(af, bkp + sb * 16 * kBankPitch);
     // dy of channel rows gq (fa) and gq + 8 (fb): [da][column b, b+1, b+2], widened to fp32
     float fa[2][3], fb[2][3];
 #pragma unroll
@@ -436,17 +524,12 @@ __device__ __forceinline__ void convT2_slabs(const __half* const (&dr)[2], const
         acc[1][rr_][2 + cc] = fmaf(kd[3], fb[da][1 + db], acc[1][rr_][2 + cc]);
       }
     }
-    if (col_ok) {
+    // dx columns 2b .. 2b+3 of rows 2a (and 2a+1 when it exists) for both channel rows
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        __half* xa = x0 + ((size_t)sb * 16 + ch * 8) * dplane;
-        const __half2 lo = __floats2half2_rn(acc[ch][0][0], acc[ch][0][1]), hi = __floats2half2_rn(acc[ch][0][2], acc[ch][0][3]);
-        *reinterpret_cast<uint2*>(xa) = make_uint2(*reinterpret_cast<const unsigned*>(&lo), *reinterpret_cast<const unsigned*>(&hi));
-        if (row1) {
-          const __half2 lo1 = __floats2half2_rn(acc[ch][1][0], acc[ch][1][1]), hi1 = __floats2half2_rn(acc[ch][1][2], acc[ch][1][3]);
-          *reinterpret_cast<uint2*>(xa + W) = make_uint2(*reinterpret_cast<const unsigned*>(&lo1), *reinterpret_cast<const unsigned*>(&hi1));
-        }
-      }
+    for (int ch = 0; ch < 2; ++ch) {
+      __half* xa = x0 + ((size_t)sb * 16 + ch * 8) * dplane;
+      store4<W>(xa, acc[ch][0], ncols);
+      if (row1) store4<W>(xa + W, acc[ch][1], ncols);
     }
   }
 }
@@ -538,22 +621,9 @@ __global__ void __launch_bounds__(MAXT, 1) ring_convT2_kernel(const __grid_const
         ok = rr.reclaim(k, lane);
         if (ok) fill_rot_row<Wo>(rring + (size_t)rr.slot(k) * RL::kSlot, rot, n, Ho, min(r, Ho - 1), lane, rr.full + 8 * rr.slot(k));
         ok = ok && rd.reclaim(k, lane);
-        if (ok) {
-          if (Sh::kTma) {
-            if (lane == 0) {
-              mbar_arrive_expect_tx(rd.full + 8 * rd.slot(k), slot_bytes);
-              tma_load_3d(dring_u32 + rd.slot(k) * slot_bytes, &tm_dy, -8, r, n * p.C + c0, rd.full + 8 * rd.slot(k));
-            }
-          } else {
-            __half* slot = dring + (size_t)rd.slot(k) * slot_halves;
-            if (r < Ho) {
-              fill_plane_row<Wo>(slot, dy, n, p.C, c0, CG, Ho, r, lane, rd.full + 8 * rd.slot(k));
-            } else {  // the zero row: plain stores, then the same 32 arrivals
-              for (int i = lane; i < slot_halves / 8; i += 32) reinterpret_cast<uint4*>(slot)[i] = make_uint4(0, 0, 0, 0);
-              mbar_arrive(rd.full + 8 * rd.slot(k));
-            }
-          }
-        }
+        if (ok)
+          fill_src_row<Wo>(dring + (size_t)rd.slot(k) * slot_halves, dring_u32 + rd.slot(k) * slot_bytes, slot_bytes, &tm_dy, dy, n, p.C,
+                           c0, CG, Ho, r, lane, rd.full + 8 * rd.slot(k));
         __syncwarp();
       }
     }
@@ -606,10 +676,10 @@ __global__ void __launch_bounds__(MAXT, 1) ring_convT2_kernel(const __grid_const
 #pragma unroll
     for (int da = 0; da < 2; ++da) dr[da] = dring + (size_t)rd.slot(k0 + da) * slot_halves + gq * INNER + 8 + b;
 
-    const unsigned* bkp = reinterpret_cast<const unsigned*>(bank + gq * kBankPitch) + q;
+    const __half* bkp = bank + ((lane & 7) + ((lane >> 3) & 1) * 8) * kBankPitch + (lane >> 4) * 8;  // this lane's ldmatrix row
     __half* x0 = dx + ((size_t)n * p.C + c0 + gq) * dplane + (size_t)(2 * a) * W + 2 * b;
-    const bool row1 = 2 * a + 1 < H, col_ok = 2 * b < W;
-    convT2_slabs<INNER, W>(dr, bkp, x0, nslab, dplane, row1, col_ok, bf);
+    const bool row1 = 2 * a + 1 < H;
+    convT2_slabs<INNER, W>(dr, bkp, x0, nslab, dplane, row1, min(max(W - 2 * b, 0), 4), bf);
     // every stream row is read by the output rows a - 1 and a; the first / last row of the range stands in for a missing neighbour
     __syncwarp();
     if (lane == 0) {
@@ -627,18 +697,21 @@ __global__ void __launch_bounds__(MAXT, 1) ring_convT2_kernel(const __grid_const
 //   rp    the item's offsets in the ring slot of its row (plane 0, pixel ow0 + gq)
 //   dyr   the lane's dy pair (channel row gq, pixels ow0 + 2q, + 1) in the slot of that row
 //   x rows: fills kx0 .. kx0 + 2 of ring rx (slots of xslot halves in xring)
-//   acc   the warp's bank-gradient accumulators; Gs / uv the warp's scratch; drot_item -> d(offsets)[n, 0, oh, ow0]
+//   acc   the warp's bank-gradient accumulators; Gs / uv the warp's scratch; drot_item -> d(offsets)[n, 0, oh, ow0], or, when
+//         the block holds only a group of the channels, gpart_item -> the same element of the group's fp32 partial sums
 // Returns false when a wait ran out.  The caller releases the rows afterwards.
 template <int S, int W, int NS, bool SC44>
 __device__ __forceinline__ bool gw_item(float (&acc)[NS][2][4], const Ring& rx, int kx0, const __half* __restrict__ xring, int xslot,
                                         const __half* __restrict__ rp, const __half* __restrict__ dyr,
                                         const __half* __restrict__ bankT, int pitchT, float* __restrict__ Gs,
-                                        float2* __restrict__ uv, __half* __restrict__ drot_item, int P, int nslab, int ow0,
-                                        const LaneCells& lc, float uh0, float uw0, int scH_rt, int scW_rt, int lane) {
+                                        float2* __restrict__ uv, __half* __restrict__ drot_item, float* __restrict__ gpart_item,
+                                        int P, int nslab, int ow0, const LaneCells& lc, float uh0, float uw0, int scH_rt,
+                                        int scW_rt, int lane) {
   constexpr int Wo = (W - 1) / S + 1;
   constexpr int IX = RowLayout<W>::kInner, ID = RowLayout<Wo>::kInner, WOP = RotLayout<Wo>::kWop;
   const int gq = lane >> 2, q = lane & 3;
   const int ow = ow0 + 2 * q;
+  const __half* wtp = bankT + ((lane & 7) + ((lane >> 3) & 1) * 8) * pitchT + (lane >> 4) * 8;  // this lane's ldmatrix row
 #pragma unroll
   for (int fh = 0; fh < 3; ++fh) {
     // hat products of the three taps, transposed into B fragments of dW += dK * beta:
@@ -675,12 +748,11 @@ __device__ __forceinline__ bool gw_item(float (&acc)[NS][2][4], const Ring& rx, 
           d0[fw] = hmul2u(dy0, tap_pair<S>(w0, w1, w2, fw));
           d1[fw] = hmul2u(dy1, tap_pair<S>(v0, v1, v2, fw));
         }
-        // A = W^T slab: rows = cells (gq, gq+8), k = channels (2q, 2q+1) and (2q+8, 2q+9)
-        const unsigned* wt0 = reinterpret_cast<const unsigned*>(bankT + gq * pitchT + sidx * 16);
-        const unsigned* wt1 = reinterpret_cast<const unsigned*>(bankT + (gq + 8) * pitchT + sidx * 16);
-        const unsigned a0 = wt0[q], a1 = wt1[q], a2 = wt0[q + 4], a3 = wt1[q + 4];
+        // A = W^T slab: rows = the 16 cells, k = the slab's 16 channels
+        unsigned a[4];
+        ldmatrix_x4(a, wtp + sidx * 16);
 #pragma unroll
-        for (int fw = 0; fw < 3; ++fw) mma16816_acc(G[fw], a0, a1, a2, a3, movmatrix_trans(d0[fw]), movmatrix_trans(d1[fw]));
+        for (int fw = 0; fw < 3; ++fw) mma16816_acc(G[fw], a[0], a[1], a[2], a[3], movmatrix_trans(d0[fw]), movmatrix_trans(d1[fw]));
         // k = 16 = 8 pixels x (tap 0 | tap 1), then 8 pixels x (tap 2 | nothing)
         mma16816_acc(acc[sidx][0], d0[0], d1[0], d0[1], d1[1], bw[0][0], bw[1][0]);
         mma16816_acc(acc[sidx][1], d0[0], d1[0], d0[1], d1[1], bw[0][1], bw[1][1]);
@@ -720,9 +792,14 @@ __device__ __forceinline__ bool gw_item(float (&acc)[NS][2][4], const Ring& rx, 
       float gv = hh * (g01 - g00) + lh * (g11 - g10);
       if (!valid) gu = gv = 0.f;
       if (ow0 + px < Wo) {
-        __half* o = drot_item + (2 * (fh * 3 + tt)) * P + px;
-        o[0] = __float2half_rn(gu);
-        o[P] = __float2half_rn(gv);
+        const int off = (2 * (fh * 3 + tt)) * P + px;
+        if (gpart_item != nullptr) {
+          gpart_item[off] = gu;
+          gpart_item[off + P] = gv;
+        } else {
+          drot_item[off] = __float2half_rn(gu);
+          drot_item[off + P] = __float2half_rn(gv);
+        }
       }
     }
     __syncwarp();
@@ -782,15 +859,17 @@ __host__ __device__ inline size_t gw_ring_smem(int cg, int inner_x, int inner_d,
 
 template <int S, int W, int NS, bool SC44, int MAXT>
 __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
-                                                          const __half* __restrict__ dy, const __half* __restrict__ rot,
-                                                          const __half* __restrict__ bankw, __half* __restrict__ drot,
+                                                          const __half* __restrict__ x, const __half* __restrict__ dy,
+                                                          const __half* __restrict__ rot, const __half* __restrict__ bankw,
+                                                          __half* __restrict__ drot, float* __restrict__ gpart,
                                                           float* __restrict__ partial, const RingParams p) {
   using Sh = GwShape<S, W>;
   using RL = RotLayout<Sh::kWo>;
-  constexpr int IX = Sh::kInnerX, ID = Sh::kInnerD, WOP = RL::kWop, NB = Sh::kNB, Wo = Sh::kWo;
+  constexpr int IX = Sh::kInnerX, ID = Sh::kInnerD, NB = Sh::kNB, Wo = Sh::kWo;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int R = 1 << p.lgR, RR = 1 << p.lgRR;
-  const int CG = p.CG;  // = 16 * (slabs <= NS); the block covers every channel
+  const int CG = p.CG;  // = 16 * (slabs <= NS): every channel, or (gpart != null) group blockIdx.y of them
+  const int c0 = blockIdx.y * CG;
   const int xslot = CG * IX, dslot = CG * ID;
   const int ncw = (blockDim.x >> 5) - 1;
   const int pitchT = CG + 8;
@@ -816,7 +895,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < R; ++i) {
-      mbar_init(rx.full + 8 * i, 1);
+      mbar_init(rx.full + 8 * i, RowLayout<W>::kTma ? 1 : 32);
       mbar_init(rx.empty + 8 * i, (S == 1 ? 3 : 2) * NB);
     }
     for (int i = 0; i < RR; ++i) {
@@ -836,7 +915,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
   }
   for (int i = threadIdx.x; i < 16 * CG; i += blockDim.x) {
     const int cell = i / CG, c = i - cell * CG;
-    bankT[cell * pitchT + c] = cell < p.cells ? __ldg(bankw + (size_t)c * p.cells + cell) : __float2half(0.f);
+    bankT[cell * pitchT + c] = cell < p.cells ? __ldg(bankw + (size_t)(c0 + c) * p.cells + cell) : __float2half(0.f);
   }
   fence_proxy_async();
   __syncthreads();
@@ -851,7 +930,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
     // ------------------------------------------------------------ producer
     if (g0 >= g1) return;
     if (lane == 0) {
-      prefetch_tensormap(&tm_x);
+      if (RowLayout<W>::kTma) prefetch_tensormap(&tm_x);
       if (Sh::kDyTma) prefetch_tensormap(&tm_dy);
     }
     const unsigned xbytes = (unsigned)xslot * 2, dbytes = (unsigned)dslot * 2;
@@ -864,24 +943,16 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
       ok = rr.reclaim(kr, lane);
       if (ok) fill_rot_row<Wo>(rring + (size_t)rr.slot(kr) * RL::kSlot, rot, n, Ho, oh, lane, rr.full + 8 * rr.slot(kr));
       ok = ok && rd.reclaim(kr, lane);
-      if (ok) {
-        if (Sh::kDyTma) {
-          if (lane == 0) {
-            mbar_arrive_expect_tx(rd.full + 8 * rd.slot(kr), dbytes);
-            tma_load_3d(dring_u32 + rd.slot(kr) * dbytes, &tm_dy, -8, oh, n * p.C, rd.full + 8 * rd.slot(kr));
-          }
-        } else {
-          fill_plane_row<Wo>(dring + (size_t)rd.slot(kr) * dslot, dy, n, p.C, 0, CG, Ho, oh, lane, rd.full + 8 * rd.slot(kr));
-        }
-      }
+      if (ok)
+        fill_src_row<Wo>(dring + (size_t)rd.slot(kr) * dslot, dring_u32 + rd.slot(kr) * dbytes, dbytes, &tm_dy, dy, n, p.C, c0, CG, Ho,
+                         oh, lane, rd.full + 8 * rd.slot(kr));
       const int Tend = n * L + oh * S + 2;
       for (; T <= Tend && ok; ++T) {
         const int k = T - T0;
         ok = rx.reclaim(k, lane);
-        if (lane == 0 && ok) {
-          mbar_arrive_expect_tx(rx.full + 8 * rx.slot(k), xbytes);
-          tma_load_3d(xring_u32 + rx.slot(k) * xbytes, &tm_x, -8, T - n * L - 1, n * p.C, rx.full + 8 * rx.slot(k));
-        }
+        if (ok)
+          fill_src_row<W>(xring + (size_t)rx.slot(k) * xslot, xring_u32 + rx.slot(k) * xbytes, xbytes, &tm_x, x, n, p.C, c0, CG, p.Hs,
+                          T - n * L - 1, lane, rx.full + 8 * rx.slot(k));
         __syncwarp();
       }
     }
@@ -921,8 +992,9 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
     const __half* dyr = dring + (size_t)rd.slot(grow) * dslot + gq * ID + 8 + ow;
     __half* drot_item = drot + (size_t)n * 18 * P + oh * Wo + ow0;
 
-    ok = gw_item<S, W, NS, SC44>(acc, rx, k0, xring, xslot, rp, dyr, bankT, pitchT, Gs, uv, drot_item, P, nslab, ow0, lc, uh0, uw0,
-                                 p.scH, p.scW, lane) && ok;
+    float* gpart_item = gpart != nullptr ? gpart + ((size_t)blockIdx.y * p.N + n) * 18 * P + oh * Wo + ow0 : nullptr;
+    ok = gw_item<S, W, NS, SC44>(acc, rx, k0, xring, xslot, rp, dyr, bankT, pitchT, Gs, uv, drot_item, gpart_item, P, nslab, ow0, lc,
+                                 uh0, uw0, p.scH, p.scW, lane) && ok;
     // the rows are no longer needed
     __syncwarp();
     if (lane == 0 && ok) {
@@ -939,7 +1011,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
   }
 
   // ---- bank gradient: sum the consumer warps' accumulators (the rings are free now) and write this block's partial
-  reduce_bank_accumulators<NS>(acc, reinterpret_cast<float*>(smem_raw), partial + (size_t)blockIdx.x * CG * 16, CG, nslab, cw, ncw, lane);
+  reduce_bank_accumulators<NS>(acc, reinterpret_cast<float*>(smem_raw), partial + ((size_t)blockIdx.x * p.C + c0) * 16, CG, nslab, cw, ncw, lane);
 }
 
 // ================================================================== the whole backward in one pass
@@ -1105,7 +1177,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant
   const size_t xplane = (size_t)H * W;
   float* Gs = reinterpret_cast<float*>(scratch + (size_t)cw * kGwScratch);  // [3 taps][16 cells][8 px]
   float2* uv = reinterpret_cast<float2*>(Gs + 3 * 16 * 8);                    // [3 taps][8 px]
-  const unsigned* bkp = reinterpret_cast<const unsigned*>(bank + gq * kBankPitch) + q;
+  const __half* bkp = bank + ((lane & 7) + ((lane >> 3) & 1) * 8) * kBankPitch + (lane >> 4) * 8;  // this lane's ldmatrix row
 
   float acc[NS][2][4];  // bank gradient of up to NS slabs of 16 channels x (cells 0-7 | cells 8-15)
 #pragma unroll
@@ -1154,7 +1226,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant
           break;
         }
         __half* x0 = dx + ((size_t)n * p.C + gq) * xplane + (size_t)j * W + ow;
-        conv_slabs<1, ID, true>(dr, bkp, x0, nslab, xplane, ow < W, bf);
+        conv_slabs<1, ID, true, true>(dr, bkp, x0, nslab, xplane, ow < W ? 2 : 0, bf);
       } else {
         ok = rr.wait_full(kd0 + 1);
         ok = rr.wait_full(kd0) && ok;
@@ -1178,7 +1250,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant
 #pragma unroll
         for (int da = 0; da < 2; ++da) dr[da] = dring + (size_t)rd.slot(kd0 + da) * dslot + gq * ID + 8 + ow;
         __half* x0 = dx + ((size_t)n * p.C + gq) * xplane + (size_t)(2 * j) * W + 2 * ow;
-        convT2_slabs<ID, W>(dr, bkp, x0, nslab, xplane, 2 * j + 1 < H, 2 * ow < W, bf);
+        convT2_slabs<ID, W>(dr, bkp, x0, nslab, xplane, 2 * j + 1 < H, min(max(W - 2 * ow, 0), 4), bf);
       }
     }
 
@@ -1188,8 +1260,8 @@ __global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant
       const __half* rp = rring + (size_t)rr.slot(kr) * RL::kSlot + 8 + pg;
       const __half* dyr = dring + (size_t)rd.slot(kr) * dslot + gq * ID + 8 + ow;
       __half* drot_item = drot + (size_t)n * 18 * P + j * Wo + ow0;
-      ok = gw_item<S, W, NS, SC44>(acc, rx, kx0, xring, xslot, rp, dyr, bankT, pitchT, Gs, uv, drot_item, P, nslab, ow0, lc, uh0, uw0,
-                                   p.scH, p.scW, lane);
+      ok = gw_item<S, W, NS, SC44>(acc, rx, kx0, xring, xslot, rp, dyr, bankT, pitchT, Gs, uv, drot_item, nullptr, P, nslab, ow0, lc,
+                                   uh0, uw0, p.scH, p.scW, lane);
       if (!ok) {
         failed = true;
         break;
@@ -1257,12 +1329,25 @@ bool make_row_map(CUtensorMap* tm, const __half* base, int width, int rows, long
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Input widths the kernels are instantiated for; scope 4 x 4.  The kernels themselves take any width (rows that are not
+// multiples of 16 bytes come by cp.async, odd ones element by element: the 28-wide dy and offset rows of the 56-wide
+// stride-2 layer do), and were measured on 28 x 28, 14 x 14 and 7 x 7 planes too (batch 128, C = 192 / 384 / 960): parity-green
+// but 1.2-4x slower than the band kernels of dk_local_mma.cu there (forward 0.10 / 0.09 / 0.14 ms against 0.06 / 0.04 / 0.04),
+// because one producer warp feeding narrow rows piece by piece and four, two or one items per row do not keep twenty
+// consumer warps busy.  So only the widths TMA can fetch are routed here.
+#define DK_RING_FOR_WIDTH(WIDTH, CALL)        \
+  switch (WIDTH) {                            \
+    case 112: { constexpr int W = 112; CALL; } \
+    case 56: { constexpr int W = 56; CALL; }   \
+    default: return DK_ERR_UNSUPPORTED;       \
+  }
+
 bool ring_shape(const Geom& g) {
   if (g.kH != 3 || g.kW != 3 || g.dH != 1 || g.dW != 1 || g.pH != 1 || g.pW != 1) return false;
   if (g.sH != g.sW || (g.sH != 1 && g.sH != 2)) return false;
-  if (g.G != 1 || g.cells > 16 || (g.C & 15)) return false;
+  if (g.G != 1 || g.scH != 4 || g.scW != 4 || (g.C & 15)) return false;
   if ((long long)g.N * (g.H + 2) > 0x3fffffff) return false;  // stream row indices are 32-bit
-  return g.W == 112 || g.W == 56;                              // the widths the kernels are instantiated for
+  return g.W == 112 || g.W == 56;
 }
 
 void spread_rows(long long rows, int groups, int* blocks_x, int* rows_per_block) {
@@ -1273,13 +1358,25 @@ void spread_rows(long long rows, int groups, int* blocks_x, int* rows_per_block)
   *blocks_x = (int)((rows + *rows_per_block - 1) / *rows_per_block);
 }
 
+// log2 of the smallest ring (4 .. 32 slots) that holds `rows` rows
+int ring_lg(int rows) {
+  int lg = 2;
+  while (lg < 5 && (1 << lg) < rows) ++lg;
+  return lg;
+}
+
+constexpr int kConvWarps = 21;  // one producer + twenty consumers (80 registers each)
+
 struct ConvRingPlan {
   bool ok;
   int CG, groups, lgR, lgRR, warps, blocks_x, rows_per_block;
   size_t smem;
 };
 
-// Channels per block, ring depths and grid of the forward / stride-1 grad-input kernel.
+// Channels per block, ring depths and grid of the forward / stride-1 grad-input kernel.  The consumers work on
+// ceil(warps / items per row) + 1 destination rows at a time; the rings are made deep enough for those rows plus the
+// producer's lookahead where shared memory allows, and the channels are split into as few groups as give at least eight
+// (or all wanted) slots.
 template <int S, int W, bool TR>
 ConvRingPlan conv_ring_plan(const Geom& g) {
   using Sh = ConvShape<S, W, TR>;
@@ -1287,13 +1384,16 @@ ConvRingPlan conv_ring_plan(const Geom& g) {
   ConvRingPlan pl;
   pl.ok = false;
   const size_t budget = (size_t)device_smem_optin();
-  // all channels in one block when their rows fit eight (or four) deep, else the fewest equal groups that do
+  const int rows_busy = (kConvWarps - 1 + Sh::kNB - 1) / Sh::kNB + 1;
+  const int want = ring_lg(rows_busy * S + 3), want_rr = TR ? want : ring_lg(rows_busy + 1);
+  // the fewest channel groups (the hat products of an item are shared by the block's channels) that give the wanted depth
+  // or at least eight slots
   for (int groups = 1; groups <= g.C / 16 && !pl.ok; ++groups) {
     if (g.C % (16 * groups)) continue;
     const int cg = g.C / groups;
     if (cg > 256) continue;
-    for (int lgR = 3; lgR >= 2 && !pl.ok; --lgR) {
-      const int lgRR = TR ? lgR : 2;
+    for (int lgR = want; lgR >= (want < 3 ? want : 3) && !pl.ok; --lgR) {
+      const int lgRR = TR ? lgR : (want_rr < lgR ? want_rr : lgR);
       const size_t smem = conv_ring_smem(cg, Sh::kInner, RL::kSlot, 1 << lgR, 1 << lgRR);
       if (smem > budget) continue;
       pl.ok = true;
@@ -1309,19 +1409,24 @@ ConvRingPlan conv_ring_plan(const Geom& g) {
     return pl;
   }
   spread_rows((long long)g.N * (TR ? g.H : g.Ho), pl.groups, &pl.blocks_x, &pl.rows_per_block);
-  pl.warps = 21;  // one producer + twenty consumers
+  pl.warps = kConvWarps;
   return pl;
 }
 
-template <int S, int W, bool TR, bool SC44>
-int launch_conv_ring_sc(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, cudaStream_t s) {
+template <int S, int W, bool TR>
+int launch_conv_ring(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, cudaStream_t s) {
   using Sh = ConvShape<S, W, TR>;
   const ConvRingPlan pl = conv_ring_plan<S, W, TR>(g);
   if (!pl.ok) return DK_ERR_UNSUPPORTED;
-  if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(dst) & 3)) return DK_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 3))
+    return DK_ERR_UNSUPPORTED;
   const int Hs = TR ? g.Ho : g.H, Hd = TR ? g.H : g.Ho;
   CUtensorMap tm;
-  if (!make_row_map(&tm, src, W, Hs, (long long)g.N * g.C, Sh::kInner, pl.CG)) return DK_ERR_UNSUPPORTED;
+  if (Sh::kTma) {
+    if (!make_row_map(&tm, src, W, Hs, (long long)g.N * g.C, Sh::kInner, pl.CG)) return DK_ERR_UNSUPPORTED;
+  } else {
+    memset(&tm, 0, sizeof(tm));
+  }
   RingParams p;
   p.N = g.N; p.C = g.C; p.Hs = Hs; p.Hd = Hd;
   p.CG = pl.CG; p.lgR = pl.lgR; p.lgRR = pl.lgRR;
@@ -1330,42 +1435,31 @@ int launch_conv_ring_sc(const __half* src, const __half* rot, const __half* w, _
   p.rows_per_block = pl.rows_per_block;
   p.scH = g.scH; p.scW = g.scW; p.cells = g.cells;
   int warps = pl.warps;
-  if (const char* e = tuning_env("DK_B200_RING_WARPS")) warps = atoi(e) > 1 ? atoi(e) : warps;
-  int rc;
-  if (warps <= 21) {
-    auto kern = ring_conv_kernel<S, W, TR, SC44, 672>;
-    if ((rc = enable_smem(kern, pl.smem))) return rc;
-    kern<<<dim3(pl.blocks_x, pl.groups), warps * 32, pl.smem, s>>>(tm, rot, w, dst, p);
-  } else {
-    auto kern = ring_conv_kernel<S, W, TR, SC44, 800>;
-    if ((rc = enable_smem(kern, pl.smem))) return rc;
-    kern<<<dim3(pl.blocks_x, pl.groups), (warps > 25 ? 25 : warps) * 32, pl.smem, s>>>(tm, rot, w, dst, p);
-  }
+  if (const char* e = tuning_env("DK_B200_RING_WARPS")) warps = atoi(e) > 1 && atoi(e) <= 21 ? atoi(e) : warps;
+  auto kern = ring_conv_kernel<S, W, TR, true, 672>;
+  int rc = enable_smem(kern, pl.smem);
+  if (rc) return rc;
+  kern<<<dim3(pl.blocks_x, pl.groups), warps * 32, pl.smem, s>>>(tm, src, rot, w, dst, p);
   return check_launch();
-}
-
-template <int S, int W, bool TR>
-int launch_conv_ring(const __half* src, const __half* rot, const __half* w, __half* dst, const Geom& g, cudaStream_t s) {
-  if (g.scH == 4 && g.scW == 4) return launch_conv_ring_sc<S, W, TR, true>(src, rot, w, dst, g, s);
-  return launch_conv_ring_sc<S, W, TR, false>(src, rot, w, dst, g, s);
 }
 
 __host__ __device__ inline size_t convT2_ring_smem(int cg, int inner, int rot_slot, int R) {
   return ((size_t)R * cg * inner + 64 + (size_t)R * rot_slot + (size_t)cg * kBankPitch) * 2 + 8 + (size_t)4 * R * 8 + 16 + 128;
 }
 
-template <int W, bool SC44>
-int launch_convT2_ring_sc(const __half* dy, const __half* rot, const __half* w, __half* dx, const Geom& g, cudaStream_t s) {
+template <int W>
+int launch_convT2_ring(const __half* dy, const __half* rot, const __half* w, __half* dx, const Geom& g, cudaStream_t s) {
   using Sh = ConvT2Shape<W>;
   using RL = RotLayout<Sh::kWo>;
-  if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(dx) & 7) || (reinterpret_cast<uintptr_t>(dy) & 15) || (W & 3))
+  if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(dx) & 7) || (reinterpret_cast<uintptr_t>(dy) & 15))
     return DK_ERR_UNSUPPORTED;
   const size_t budget = (size_t)device_smem_optin();
+  const int want = ring_lg((19 + Sh::kNB - 1) / Sh::kNB + 1 + 2);
   int cg = 0, groups = 0, lgR = 0;
   size_t smem = 0;
   for (int gr = 1; gr <= g.C / 16 && !cg; ++gr) {
     if (g.C % (16 * gr) || g.C / gr > 256) continue;
-    for (int lg = 3; lg >= 2 && !cg; --lg) {
+    for (int lg = want; lg >= (want < 3 ? want : 3) && !cg; --lg) {
       const size_t need = convT2_ring_smem(g.C / gr, Sh::kInner, RL::kSlot, 1 << lg);
       if (need > budget) continue;
       cg = g.C / gr; groups = gr; lgR = lg; smem = need;
@@ -1386,91 +1480,98 @@ int launch_convT2_ring_sc(const __half* dy, const __half* rot, const __half* w, 
   int blocks_x;
   spread_rows((long long)g.N * g.Ho, groups, &blocks_x, &p.rows_per_block);
   p.scH = g.scH; p.scW = g.scW; p.cells = g.cells;
-  auto kern = ring_convT2_kernel<W, SC44, 640>;
+  auto kern = ring_convT2_kernel<W, true, 640>;
   int rc = enable_smem(kern, smem);
   if (rc) return rc;
   kern<<<dim3(blocks_x, groups), 20 * 32, smem, s>>>(tm, dy, rot, w, dx, p);
   return check_launch();
 }
-template <int W>
-int launch_convT2_ring(const __half* dy, const __half* rot, const __half* w, __half* dx, const Geom& g, cudaStream_t s) {
-  if (g.scH == 4 && g.scW == 4) return launch_convT2_ring_sc<W, true>(dy, rot, w, dx, g, s);
-  return launch_convT2_ring_sc<W, false>(dy, rot, w, dx, g, s);
-}
 
 struct GwRingPlan {
   bool ok;
-  int lgR, lgRR, warps, blocks_x, rows_per_block, ns;
-  size_t smem, ws_bytes;
+  int CG, groups, lgR, lgRR, warps, blocks_x, rows_per_block, ns;
+  size_t smem, dw_bytes, ws_bytes;
 };
 
+// The fused offsets + bank pass keeps the bank gradient of all its channels in registers: up to 96 channels (128 registers,
+// 16 warps) or, undivided, up to 144 (168 registers, 12 warps).  More channels are split into groups of up to 96 whose
+// blocks write fp32 partial offset gradients [group][N][18][P], summed by a second small kernel.
 template <int S, int W>
 GwRingPlan gw_ring_plan(const Geom& g) {
   using Sh = GwShape<S, W>;
   using RL = RotLayout<Sh::kWo>;
   GwRingPlan pl;
   pl.ok = false;
-  pl.ns = g.C <= 96 ? 6 : 9;
-  if (g.C > 144) return pl;  // the bank-gradient accumulators of all channels live in registers
+  int groups = 1;
+  if (g.C > 144) {
+    groups = (g.C + 95) / 96;
+    while (groups <= g.C / 16 && (g.C % (16 * groups) || g.C / groups > 96)) ++groups;
+    if (groups > g.C / 16) return pl;
+  }
+  pl.groups = groups;
+  pl.CG = g.C / groups;
+  pl.ns = pl.CG <= 96 ? 6 : 9;
   pl.warps = pl.ns == 6 ? 16 : 12;
   const size_t budget = (size_t)device_smem_optin();
-  for (int lgR = 3; lgR >= 2 && !pl.ok; --lgR)
-    for (int lgRR = 2; lgRR >= 1 && !pl.ok; --lgRR) {
-      const size_t smem = gw_ring_smem(g.C, Sh::kInnerX, Sh::kInnerD, RL::kSlot, 1 << lgR, 1 << lgRR, pl.warps - 1);
+  const int rows_busy = (pl.warps - 1 + Sh::kNB - 1) / Sh::kNB + 1;
+  const int want = ring_lg(rows_busy * S + 3), want_rr = ring_lg(rows_busy + 1);
+  for (int lgR = want; lgR >= 2 && !pl.ok; --lgR)
+    for (int lgRR = want_rr; lgRR >= 1 && !pl.ok; --lgRR) {
+      if (lgRR > lgR) continue;
+      const size_t smem = gw_ring_smem(pl.CG, Sh::kInnerX, Sh::kInnerD, RL::kSlot, 1 << lgR, 1 << lgRR, pl.warps - 1);
       if (smem > budget) continue;
       pl.ok = true;
       pl.lgR = lgR;
       pl.lgRR = lgRR;
       pl.smem = smem;
     }
-  if (!pl.ok) return pl;
-  spread_rows((long long)g.N * g.Ho, 1, &pl.blocks_x, &pl.rows_per_block);
-  pl.ws_bytes = (size_t)pl.blocks_x * g.C * 16 * sizeof(float);
+  if (!pl.ok || pl.groups > 65535) {
+    pl.ok = false;
+    return pl;
+  }
+  spread_rows((long long)g.N * g.Ho, pl.groups, &pl.blocks_x, &pl.rows_per_block);
+  pl.dw_bytes = ((size_t)pl.blocks_x * g.C * 16 * sizeof(float) + 255) & ~(size_t)255;
+  pl.ws_bytes = pl.dw_bytes + (pl.groups > 1 ? (size_t)pl.groups * g.N * 18 * g.P * sizeof(float) : 0);
   return pl;
-}
-
-template <int S, int W, bool SC44>
-int launch_gw_ring_sc(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
-                   void* ws, size_t ws_bytes, cudaStream_t s) {
-  using Sh = GwShape<S, W>;
-  const GwRingPlan pl = gw_ring_plan<S, W>(g);
-  if (!pl.ok) return DK_ERR_UNSUPPORTED;
-  if (ws == nullptr || ws_bytes < pl.ws_bytes) return DK_ERR_WORKSPACE;
-  if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(dy) & 15)) return DK_ERR_UNSUPPORTED;
-  CUtensorMap tmx, tmd;
-  if (!make_row_map(&tmx, x, W, g.H, (long long)g.N * g.C, Sh::kInnerX, g.C)) return DK_ERR_UNSUPPORTED;
-  if (Sh::kDyTma) {
-    if (!make_row_map(&tmd, dy, Sh::kWo, g.Ho, (long long)g.N * g.C, Sh::kInnerD, g.C)) return DK_ERR_UNSUPPORTED;
-  } else {
-    tmd = tmx;
-  }
-  RingParams p;
-  p.N = g.N; p.C = g.C; p.Hs = g.H; p.Hd = g.Ho;
-  p.CG = g.C; p.lgR = pl.lgR; p.lgRR = pl.lgRR;
-  p.L = (g.Ho - 1) * S + 3;
-  p.rows_total = g.N * g.Ho;
-  p.rows_per_block = pl.rows_per_block;
-  p.scH = g.scH; p.scW = g.scW; p.cells = g.cells;
-  float* partial = reinterpret_cast<float*>(ws);
-  int rc;
-  if (pl.ns == 6) {
-    auto kern = ring_gw_kernel<S, W, 6, SC44, 512>;
-    if ((rc = enable_smem(kern, pl.smem))) return rc;
-    kern<<<pl.blocks_x, pl.warps * 32, pl.smem, s>>>(tmx, tmd, dy, rot, w, drot, partial, p);
-  } else {
-    auto kern = ring_gw_kernel<S, W, 9, SC44, 384>;
-    if ((rc = enable_smem(kern, pl.smem))) return rc;
-    kern<<<pl.blocks_x, pl.warps * 32, pl.smem, s>>>(tmx, tmd, dy, rot, w, drot, partial, p);
-  }
-  if ((rc = check_launch())) return rc;
-  return launch_reduce_bank_partials(partial, dw, g.C, g.cells, pl.blocks_x, s);
 }
 
 template <int S, int W>
 int launch_gw_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
                    void* ws, size_t ws_bytes, cudaStream_t s) {
-  if (g.scH == 4 && g.scW == 4) return launch_gw_ring_sc<S, W, true>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s);
-  return launch_gw_ring_sc<S, W, false>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s);
+  using Sh = GwShape<S, W>;
+  const GwRingPlan pl = gw_ring_plan<S, W>(g);
+  if (!pl.ok) return DK_ERR_UNSUPPORTED;
+  if (ws == nullptr || ws_bytes < pl.ws_bytes) return DK_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(dy) & 15) || (reinterpret_cast<uintptr_t>(x) & 15))
+    return DK_ERR_UNSUPPORTED;
+  CUtensorMap tmx, tmd;
+  memset(&tmx, 0, sizeof(tmx));
+  memset(&tmd, 0, sizeof(tmd));
+  if (RowLayout<W>::kTma && !make_row_map(&tmx, x, W, g.H, (long long)g.N * g.C, Sh::kInnerX, pl.CG)) return DK_ERR_UNSUPPORTED;
+  if (Sh::kDyTma && !make_row_map(&tmd, dy, Sh::kWo, g.Ho, (long long)g.N * g.C, Sh::kInnerD, pl.CG)) return DK_ERR_UNSUPPORTED;
+  RingParams p;
+  p.N = g.N; p.C = g.C; p.Hs = g.H; p.Hd = g.Ho;
+  p.CG = pl.CG; p.lgR = pl.lgR; p.lgRR = pl.lgRR;
+  p.L = (g.Ho - 1) * S + 3;
+  p.rows_total = g.N * g.Ho;
+  p.rows_per_block = pl.rows_per_block;
+  p.scH = g.scH; p.scW = g.scW; p.cells = g.cells;
+  float* partial = reinterpret_cast<float*>(ws);
+  float* gpart = pl.groups > 1 ? reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + pl.dw_bytes) : nullptr;
+  const dim3 grid(pl.blocks_x, pl.groups);
+  int rc;
+  if (pl.ns == 6) {
+    auto kern = ring_gw_kernel<S, W, 6, true, 512>;
+    if ((rc = enable_smem(kern, pl.smem))) return rc;
+    kern<<<grid, pl.warps * 32, pl.smem, s>>>(tmx, tmd, x, dy, rot, w, drot, gpart, partial, p);
+  } else {
+    auto kern = ring_gw_kernel<S, W, 9, true, 384>;
+    if ((rc = enable_smem(kern, pl.smem))) return rc;
+    kern<<<grid, pl.warps * 32, pl.smem, s>>>(tmx, tmd, x, dy, rot, w, drot, gpart, partial, p);
+  }
+  if ((rc = check_launch())) return rc;
+  if (pl.groups > 1 && (rc = launch_reduce_rot_partials(gpart, drot, (size_t)g.N * 18 * g.P, pl.groups, s))) return rc;
+  return launch_reduce_bank_partials(partial, dw, g.C, g.cells, pl.blocks_x, s);
 }
 
 struct BwdRingPlan {
@@ -1508,9 +1609,9 @@ BwdRingPlan bwd_ring_plan(const Geom& g) {
   return pl;
 }
 
-template <int S, int W, bool SC44>
-int launch_bwd_ring_sc(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* dx, __half* drot, __half* dw,
-                       const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s) {
+template <int S, int W>
+int launch_bwd_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* dx, __half* drot, __half* dw,
+                    const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s) {
   using Sh = BwdShape<S, W>;
   const BwdRingPlan pl = bwd_ring_plan<S, W>(g);
   if (!pl.ok) return DK_ERR_UNSUPPORTED;
@@ -1534,23 +1635,16 @@ int launch_bwd_ring_sc(const __half* dy, const __half* x, const __half* rot, con
   float* partial = reinterpret_cast<float*>(ws);
   int rc;
   if (pl.ns == 6) {
-    auto kern = ring_bwd_kernel<S, W, 6, SC44, 512>;
+    auto kern = ring_bwd_kernel<S, W, 6, true, 512>;
     if ((rc = enable_smem(kern, pl.smem))) return rc;
     kern<<<pl.blocks_x, pl.warps * 32, pl.smem, s>>>(tmx, tmd, dy, rot, w, dx, drot, partial, p);
   } else {
-    auto kern = ring_bwd_kernel<S, W, 9, SC44, 384>;
+    auto kern = ring_bwd_kernel<S, W, 9, true, 384>;
     if ((rc = enable_smem(kern, pl.smem))) return rc;
     kern<<<pl.blocks_x, pl.warps * 32, pl.smem, s>>>(tmx, tmd, dy, rot, w, dx, drot, partial, p);
   }
   if ((rc = check_launch())) return rc;
   return launch_reduce_bank_partials(partial, dw, g.C, g.cells, pl.blocks_x, s);
-}
-
-template <int S, int W>
-int launch_bwd_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* dx, __half* drot, __half* dw,
-                    const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s) {
-  if (g.scH == 4 && g.scW == 4) return launch_bwd_ring_sc<S, W, true>(dy, x, rot, w, dx, drot, dw, g, ws, ws_bytes, s);
-  return launch_bwd_ring_sc<S, W, false>(dy, x, rot, w, dx, drot, dw, g, ws, ws_bytes, s);
 }
 
 }  // namespace
@@ -1568,28 +1662,24 @@ int local_conv_ring(const __half* src, const __half* rot, const __half* w, __hal
                     cudaStream_t s) {
   if (!ring_shape(g)) return DK_ERR_UNSUPPORTED;
   if (!transposed) {
-    if (g.W == 112) return g.sH == 1 ? launch_conv_ring<1, 112, false>(src, rot, w, dst, g, s) : launch_conv_ring<2, 112, false>(src, rot, w, dst, g, s);
-    return g.sH == 1 ? launch_conv_ring<1, 56, false>(src, rot, w, dst, g, s) : launch_conv_ring<2, 56, false>(src, rot, w, dst, g, s);
+    if (g.sH == 1) DK_RING_FOR_WIDTH(g.W, return (launch_conv_ring<1, W, false>(src, rot, w, dst, g, s)))
+    DK_RING_FOR_WIDTH(g.W, return (launch_conv_ring<2, W, false>(src, rot, w, dst, g, s)))
   }
-  if (g.sH != 1) return g.W == 112 ? launch_convT2_ring<112>(src, rot, w, dst, g, s) : launch_convT2_ring<56>(src, rot, w, dst, g, s);
-  return g.W == 112 ? launch_conv_ring<1, 112, true>(src, rot, w, dst, g, s) : launch_conv_ring<1, 56, true>(src, rot, w, dst, g, s);
+  if (g.sH == 1) DK_RING_FOR_WIDTH(g.W, return (launch_conv_ring<1, W, true>(src, rot, w, dst, g, s)))
+  DK_RING_FOR_WIDTH(g.W, return (launch_convT2_ring<W>(src, rot, w, dst, g, s)))
 }
 
-// Workspace of local_gw_ring (the per-block partial bank gradients); 0 = the shape is not covered.
+// Workspace of local_gw_ring (per-block partial bank gradients, and partial offset gradients when the channels are split
+// into groups); 0 = the shape is not covered.
 size_t local_gw_ring_workspace(const Geom& g) {
   if (!ring_shape(g)) return 0;
   GwRingPlan pl;
-  if (g.W == 112) pl = g.sH == 1 ? gw_ring_plan<1, 112>(g) : gw_ring_plan<2, 112>(g);
-  else pl = g.sH == 1 ? gw_ring_plan<1, 56>(g) : gw_ring_plan<2, 56>(g);
-  return pl.ok ? pl.ws_bytes : 0;
-}
-
-// Workspace of local_bwd_ring (the per-block partial bank gradients); 0 = the shape is not covered.
-size_t local_bwd_ring_workspace(const Geom& g) {
-  if (!ring_shape(g)) return 0;
-  BwdRingPlan pl;
-  if (g.W == 112) pl = g.sH == 1 ? bwd_ring_plan<1, 112>(g) : bwd_ring_plan<2, 112>(g);
-  else pl = g.sH == 1 ? bwd_ring_plan<1, 56>(g) : bwd_ring_plan<2, 56>(g);
+  pl.ok = false;
+  auto plan = [&]() -> int {
+    if (g.sH == 1) DK_RING_FOR_WIDTH(g.W, return ((pl = gw_ring_plan<1, W>(g)).ok))
+    DK_RING_FOR_WIDTH(g.W, return ((pl = gw_ring_plan<2, W>(g)).ok))
+  };
+  plan();
   return pl.ok ? pl.ws_bytes : 0;
 }
 
@@ -1598,12 +1688,23 @@ size_t local_bwd_ring_workspace(const Geom& g) {
 // its grad-input half runs at the register count and warp count the offsets / bank half needs (12-15 warps of 128-168
 // registers instead of 20 of 80), and on the 112-wide layers shared memory allows only 12 warps.  So it is the default
 // only on the narrow stride-2 shape where it won; dk_sample_depthwise_backward_one_pass asks for it explicitly.
-bool local_bwd_ring_preferred(const Geom& g) { return ring_shape(g) && g.W == 56 && g.sH == 2; }
+bool local_bwd_ring_preferred(const Geom& g) { return ring_shape(g) && g.W == 56 && g.sH == 2 && g.C <= 144; }
+
+bool bwd_ring_shape(const Geom& g) { return ring_shape(g) && (g.W == 112 || g.W == 56); }
+
+// Workspace of local_bwd_ring (the per-block partial bank gradients); 0 = the shape is not covered.
+size_t local_bwd_ring_workspace(const Geom& g) {
+  if (!bwd_ring_shape(g)) return 0;
+  BwdRingPlan pl;
+  if (g.W == 112) pl = g.sH == 1 ? bwd_ring_plan<1, 112>(g) : bwd_ring_plan<2, 112>(g);
+  else pl = g.sH == 1 ? bwd_ring_plan<1, 56>(g) : bwd_ring_plan<2, 56>(g);
+  return pl.ok ? pl.ws_bytes : 0;
+}
 
 // all three gradients in one pass over dy, x and the offsets
 int local_bwd_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* dx, __half* drot, __half* dw,
                    const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s) {
-  if (!ring_shape(g) || dx == nullptr || drot == nullptr || dw == nullptr) return DK_ERR_UNSUPPORTED;
+  if (!bwd_ring_shape(g) || dx == nullptr || drot == nullptr || dw == nullptr) return DK_ERR_UNSUPPORTED;
   if (g.W == 112)
     return g.sH == 1 ? launch_bwd_ring<1, 112>(dy, x, rot, w, dx, drot, dw, g, ws, ws_bytes, s)
                      : launch_bwd_ring<2, 112>(dy, x, rot, w, dx, drot, dw, g, ws, ws_bytes, s);
@@ -1615,11 +1716,8 @@ int local_bwd_ring(const __half* dy, const __half* x, const __half* rot, const _
 int local_gw_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
                   void* ws, size_t ws_bytes, cudaStream_t s) {
   if (!ring_shape(g) || drot == nullptr || dw == nullptr) return DK_ERR_UNSUPPORTED;
-  if (g.W == 112)
-    return g.sH == 1 ? launch_gw_ring<1, 112>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s)
-                     : launch_gw_ring<2, 112>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s);
-  return g.sH == 1 ? launch_gw_ring<1, 56>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s)
-                   : launch_gw_ring<2, 56>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s);
+  if (g.sH == 1) DK_RING_FOR_WIDTH(g.W, return (launch_gw_ring<1, W>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s)))
+  DK_RING_FOR_WIDTH(g.W, return (launch_gw_ring<2, W>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s)))
 }
 
 }  // namespace dk

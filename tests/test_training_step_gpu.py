@@ -35,19 +35,23 @@ def _model():
 
 def _step(model, x, labels):
     model.zero_grad(set_to_none=True)
+    torch.manual_seed(1234)      # the classifier's dropout draws the same mask in both runs
     loss = torch.nn.functional.cross_entropy(model(x), labels)
     loss.backward()
     grads = {n: p.grad.detach().clone() for n, p in model.named_parameters()
              if ("inner_conv.weight" in n or "rotation_conv.weight" in n) and p.grad is not None}
-    return float(loss), grads
+    return float(loss.detach()), grads
 
 
 def test_mobilenet_dk_step_matches_the_composition(monkeypatch):
-    """fp32, batch 4, 96 x 96 images, batch-norm in training mode: loss and the gradients of all 17 weight banks and
-    offset-producing convolutions agree with the run in which sample_depthwise is oracle/torch_composition.py."""
+    """fp32, batch 4, 96 x 96 images: loss and the gradients of all 17 weight banks and offset-producing convolutions
+    agree with the run in which sample_depthwise is oracle/torch_composition.py.  Batch-norm uses its running statistics:
+    with batch statistics of four images this random-init network amplifies fp32 rounding differences 3-4x per block
+    (measured: 1e-7 after the first deformable layer, order 1 after the twelfth, with either operator), so nothing
+    could be compared."""
     from deformable_kernels.ops.deform_kernel.modules import filter_sample_depthwise as wrapper
     from oracle import torch_composition as TC
-    model = _model().train()
+    model = _model().eval()
     x = torch.randn(4, 3, 96, 96, device=DEV)
     labels = torch.randint(0, 1000, (4,), device=DEV)
     loss_mine, g_mine = _step(model, x, labels)
@@ -61,7 +65,7 @@ def test_mobilenet_dk_step_matches_the_composition(monkeypatch):
     assert abs(loss_mine - loss_ref) < 1e-4 * max(1.0, abs(loss_ref))
     assert len(g_mine) == 34 and set(g_mine) == set(g_ref)
     for name in g_mine:
-        assert rel_err(g_mine[name], g_ref[name]) < 2e-3, name     # 50-layer fp32 network, batch-norm statistics of 4 images
+        assert rel_err(g_mine[name], g_ref[name]) < 1e-4, name
 
 
 def test_bank_gradients_of_batch_halves_add_up_to_the_full_batch():
