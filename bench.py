@@ -17,6 +17,7 @@ samples except the bank gradient, which op-level runs do not all-reduce).
 reference project has no CPU implementation of this path, so its restatement stands in.
 """
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -150,15 +151,37 @@ def other_configs(dev, time_call):
             torch.autograd.grad(y, ins, dy)
         return run
 
+    def graph_us(run):
+        """The same forward + backward captured once into a CUDA graph and replayed: what the launches cost on the device
+        when the host's per-call work (Python, autograd bookkeeping) is out of the way.  None if capture fails."""
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    run()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                run()
+            return round(time_call(graph.replay, 50) * 1e3, 1)
+        except Exception:
+            torch.cuda.synchronize(dev)
+            return None
+
     c1 = dk_cases.cfg1()
     ins = [c1[k].to(dev).requires_grad_(True) for k in ("input", "rotation", "weight")]
-    t = time_call(fb(lambda x, r, w: sample_depthwise(x, r, w, **c1["args"]), ins, c1["grad_output"].to(dev)), 20)
-    out["cfg1 local DK N=2 C=64 28x28 fp32"] = {"fwd_bwd_us": round(t * 1e3, 1), "algorithmic_MB": 2.36}
+    run1 = fb(lambda x, r, w: sample_depthwise(x, r, w, **c1["args"]), ins, c1["grad_output"].to(dev))
+    t = time_call(run1, 20)
+    out["cfg1 local DK N=2 C=64 28x28 fp32"] = {"fwd_bwd_us": round(t * 1e3, 1), "fwd_bwd_cuda_graph_us": graph_us(run1),
+                                                  "algorithmic_MB": 2.36}
 
     c2 = dk_cases.cfg2()
     ins = [c2[k].to(dev).requires_grad_(True) for k in ("data", "coord")]
-    t = time_call(fb(nd_linear_sample, ins, c2["grad_output"].to(dev)), 20)
-    out["cfg2 nd_linear_sample C=256 2x2, 32 samples fp32"] = {"fwd_bwd_us": round(t * 1e3, 1), "algorithmic_MB": 0.079}
+    run2 = fb(nd_linear_sample, ins, c2["grad_output"].to(dev))
+    t = time_call(run2, 20)
+    out["cfg2 nd_linear_sample C=256 2x2, 32 samples fp32"] = {"fwd_bwd_us": round(t * 1e3, 1),
+                                                                 "fwd_bwd_cuda_graph_us": graph_us(run2), "algorithmic_MB": 0.079}
     m = GlobalDeformKernel2d((2, 2), 256, 256, kernel_size=1, groups=256).to(dev)
     x2 = c2["input"].to(dev).requires_grad_(True)
 
@@ -166,7 +189,8 @@ def other_configs(dev, time_call):
         y = m(x2)
         torch.autograd.grad(y.sum(), [x2, m.weight, m.fc.weight])
     t = time_call(mod, 10)
-    out["cfg2 GlobalDeformKernel2d module N=32 C=256 14x14 fp32"] = {"fwd_bwd_us": round(t * 1e3, 1), "algorithmic_MB": 32.3}
+    out["cfg2 GlobalDeformKernel2d module N=32 C=256 14x14 fp32"] = {"fwd_bwd_us": round(t * 1e3, 1),
+                                                                       "fwd_bwd_cuda_graph_us": graph_us(mod), "algorithmic_MB": 32.3}
 
     n4 = 64
     g = torch.Generator(device=dev).manual_seed(4)
@@ -253,8 +277,50 @@ def run_training_step(args, rank, world, local, dev):
     if world > 1:
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
     ms_step = float(tms.item()) / args.steps
+    share = None
+    if not graphed:
+        # one more step with CUDA-event ranges around the 17 deformable-kernel operators (the SampleDepthwise modules
+        # inside DeformKernel2d): forward range by forward hooks, backward range by the full-backward hooks.  EVERY rank
+        # runs this step (its gradient all-reduce is a collective); only rank 0 reports.
+        from deformable_kernels.ops.deform_kernel.modules import SampleDepthwise
+        ranges, handles = {"fwd": [], "bwd": []}, []
+
+        def opener(kind):
+            def hook(*_a):
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                ranges[kind].append([ev, None])
+            return hook
+
+        def closer(kind):
+            def hook(*_a):
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                for r in reversed(ranges[kind]):
+                    if r[1] is None:
+                        r[1] = ev
+                        break
+            return hook
+        for mod in model.modules():
+            if isinstance(mod, SampleDepthwise):
+                handles += [mod.register_forward_pre_hook(opener("fwd")), mod.register_forward_hook(closer("fwd")),
+                            mod.register_full_backward_pre_hook(opener("bwd")), mod.register_full_backward_hook(closer("bwd"))]
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        step()
+        s1.record()
+        torch.cuda.synchronize()
+        for h in handles:
+            h.remove()
+        f_ms = sum(a.elapsed_time(b) for a, b in ranges["fwd"] if b is not None)
+        b_ms = sum(a.elapsed_time(b) for a, b in ranges["bwd"] if b is not None)
+        share = {"operators": len(ranges["fwd"]), "forward_ms": round(f_ms, 3), "backward_ms": round(b_ms, 3),
+                 "step_ms": round(s0.elapsed_time(s1), 3), "share_of_step": round((f_ms + b_ms) / s0.elapsed_time(s1), 4)}
+        if world > 1:
+            dist.barrier()
     if rank == 0:
         print(json.dumps({
+            "dk_operator_share": share,
             "metric": "MobileNetV2-DK training step images/sec (global batch %d, fp16 autocast)" % args.global_batch,
             "value": args.global_batch / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
@@ -352,7 +418,7 @@ def run_reference(args, rank):
     from oracle import dk_oracle as O
     O.set_threads(os.cpu_count() or 1)  # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every host core
     cores = O.max_threads()
-    n_img = 4
+    n_img = 16  # about 2 s per step on 16 cores
     for _ in range(args.warmup):
         cpu_sweep(n_img)
     t = [cpu_sweep(n_img) for _ in range(args.steps)]
@@ -721,7 +787,7 @@ def main():
         from oracle import dk_oracle as O
         os.sched_setaffinity(0, all_cpus)  # the CPU baseline gets every host core again
         O.set_threads(os.cpu_count() or 1)
-        n_img = 16
+        n_img = 96  # about 11 s on 16 cores
         cpu_sweep(1)
         sec = cpu_sweep(n_img)
         cpu = {"value": n_img / sec, "unit": "images/s", "cores": O.max_threads(), "kind": "port",
@@ -730,8 +796,17 @@ def main():
 
     if rank == 0:
         # launches of this library per step: ring layers (rows of 112 or 56) run forward, grad-input, the fused
-        # offsets + bank pass and the bank reduction; the others forward, grad-input, grad-offsets, grad-bank + reduction
-        launches = sum(4 if t["hw"] in (112, 56) else 5 for t in layers)
+        # offsets + bank pass and the bank reduction (or forward, the one-pass backward and the reduction); the others
+        # forward, grad-input, grad-offsets (+ the reduction of its partial sums when the channels are split into
+        # groups), grad-bank + reduction
+        def layer_launches(t):
+            if t["hw"] in (112, 56):
+                return 3 if (t["hw"] == 56 and t["s"] == 2 and t["c"] <= 144) else 4
+            q = (ctypes.c_longlong * 8)()
+            geom = C.geom((n, t["c"], t["hw"], t["hw"]), (K, K), (t["s"], t["s"]), (PAD, PAD), (1, 1), (SCOPE, SCOPE), 1)
+            split = C.lib.dk_local_plan_query(geom, C.DK_F16, 2, q) == 0 and q[2] > 1
+            return 6 if split else 5
+        launches = sum(layer_launches(t) for t in layers)
         mhz = clocks.get("sm_mhz") if clocks else None
         line = {
             "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
@@ -740,7 +815,8 @@ def main():
             "config": {"workload": "cfg3 layer sweep: DeformKernel2d (C,HW) in (96,112),(144,56),(192,28),(384,14),(960,7)"
                                    " x stride 1,2; scope 4x4, kernel 3, pad 1; offsets ~N(0,1); batch %s" %
                                    (("%d in total, split over the GPUs" % args.batch) if strong else ("%d per GPU" % n)),
-                       "storage": "f16 tensors; forward and grad-input: fp32 resampled kernel, fp32 products and sums; "
+                       "storage": "f16 tensors; forward and grad-input: resampled kernel rounded to f16 (tensor-core output), "
+                                  "exact f16 x f16 products summed in fp32; "
                                   "grad-offsets and grad-bank: products dy * x rounded to f16 (tensor-core operands), "
                                   "fp32 accumulation",
                        "l2": "the sweep touches %.1f GB per step, far above the 126 MB L2, so every layer's tensors "

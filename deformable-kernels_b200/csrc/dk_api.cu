@@ -182,8 +182,10 @@ size_t dk_sample_depthwise_backward_workspace_bytes(const dk_geom* g, int dtype)
   Geom gg;
   if (dtype == DK_F16 && make_geom(g, &gg)) {
     const size_t c = align256(local_gw_ring_workspace(gg)), d = align256(local_bwd_ring_workspace(gg));
+    const size_t e = align256(local_gw_mma_workspace(gg));
     if (c > need) need = c;
     if (d > need) need = d;
+    if (e > need) need = e;
   }
   return need;
 }
@@ -214,6 +216,9 @@ int dk_sample_depthwise_backward(const void* grad_output, const void* input, con
     if (!grad_output || !input || !rotation || !filter || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
     rc = local_gw_ring(P_(__half, grad_output), P_(__half, input), P_(__half, rotation), P_(__half, filter),
                        M_(__half, grad_rotation), M_(__half, grad_filter), gg, workspace, workspace_bytes, (cudaStream_t)stream);
+    if (rc != DK_ERR_UNSUPPORTED) return rc;
+    rc = local_gw_mma(P_(__half, grad_output), P_(__half, input), P_(__half, rotation), P_(__half, filter),
+                      M_(__half, grad_rotation), M_(__half, grad_filter), gg, workspace, workspace_bytes, (cudaStream_t)stream);
     if (rc != DK_ERR_UNSUPPORTED) return rc;
   }
   if (grad_rotation) {

@@ -196,6 +196,10 @@ int local_conv_ring(const __half* src, const __half* rot, const __half* w, __hal
 size_t local_gw_ring_workspace(const Geom& g);
 int local_gw_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
                   void* ws, size_t ws_bytes, cudaStream_t s);  // grad-offsets and grad-bank in one pass
+// the same pass in band form for the planes the row-ring kernels do not take (dk_local_mma.cu; 4 x 4 scope)
+size_t local_gw_mma_workspace(const Geom& g);
+int local_gw_mma(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
+                 void* ws, size_t ws_bytes, cudaStream_t s);
 size_t local_bwd_ring_workspace(const Geom& g);
 bool local_bwd_ring_preferred(const Geom& g);  // the one-pass backward is expected to beat grad-input + the fused offsets / bank pass
 int local_bwd_ring(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* dx, __half* drot, __half* dw,

@@ -881,6 +881,296 @@ FiltPlan filt_plan(const Geom& g) {
   return cached_plan<FiltPlan>(g, 3, [&] { return filt_plan_search(g); });
 }
 
+// ------------------------------------------------------------------ grad-offsets + grad-bank in one pass
+//
+// Both gradients consume the products dK = dy * x.  For the planes the row-ring kernels do not take (28 x 28 and
+// smaller) this kernel forms them once per item instead of once in each of the two kernels above:
+//   G^T[16 cells x 8 px] += W^T * dK   (per item, over the block's channels) -> four-corner derivative -> d(offsets)
+//   dW[16 ch x 16 cells] += dK * beta  (in registers across the block's items) -> per-block partial sums
+// A block owns a group of up to 96 channels and walks over (sample, row band) units; with more than one group the
+// offset gradients leave as fp32 partial sums per group.  One pass per kernel row (three taps) keeps 12 instead of 36
+// accumulators of G live.  4 x 4 scopes only (G of a tap goes through a 6 x 6 grid with a zero border in shared memory).
+struct GwPlan {
+  bool dy_direct;  // dy straight from global memory into registers (even output rows)
+  bool big;        // one block of up to 16 warps per SM instead of two of up to 8
+  int BH, CG, groups, warps, bands, units_per_block, blocks_x;
+  int mode_x, mode_dy, mode_rot;
+  size_t smem, dw_bytes, ws_bytes;
+};
+constexpr int kGwBandScratch = 3 * 36 * 8 * 4 + 24 * 8;  // per warp: G of three taps on the padded grid + their (u, v)
+
+template <int S, int MAXT, int MINB, bool DYD>
+__global__ void __launch_bounds__(MAXT, MINB) mma_gw_kernel(const __half* __restrict__ dy, const __half* __restrict__ x,
+                                                        const __half* __restrict__ rot, const __half* __restrict__ w,
+                                                        __half* __restrict__ drot, float* __restrict__ gpart,
+                                                        float* __restrict__ partial, const Geom g, const GwPlan pl) {
+  constexpr int NS = 6;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int c0 = blockIdx.y * pl.CG;
+  const int cnt = pl.CG;  // the groups divide the channels evenly
+  const int nslab = cnt >> 4;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int gq = lane >> 2, q = lane & 3;
+  const int NB = (g.Wo + 7) >> 3;
+  const int items = pl.BH * NB;
+  const int Wp = g.W + (g.W & 1), Wpo = g.Wo + (g.Wo & 1);
+  const int xpitch = band_pitch((pl.BH - 1) * S + 3, Wp), ypitch = band_pitch(pl.BH, Wpo);
+  const int pitchT = pl.CG + 8;
+
+  __half* xband = reinterpret_cast<__half*>(smem_raw);
+  __half* yband = xband + (size_t)pl.CG * xpitch;
+  __half* rband = yband + (DYD ? (size_t)0 : (size_t)pl.CG * ypitch);  // [18][ypitch]
+  __half* bankT = rband + (size_t)18 * ypitch;                          // [16 cells][CG + 8]
+  float* Gs = reinterpret_cast<float*>(bankT + 16 * pitchT) + (size_t)warp * (kGwBandScratch / 4);  // [3 taps][36 cells][8 px]
+  float2* uv = reinterpret_cast<float2*>(Gs + 3 * 36 * 8);                                          // [3 taps][8 px]
+  // 4 x 4 scope: the lane's cells 2q, 2q+1 (row q / 2) and 2q+8, 2q+9 (two rows further) share the columns 2 (q % 2), + 1
+  const float cell_row = (float)(q >> 1), cell_col = (float)((q & 1) << 1);
+  const float uh0 = 0.5f, uw0 = 0.5f;  // (scope - kernel) / 2 for a 4 x 4 scope and 3 x 3 taps
+
+  for (int i = threadIdx.x; i < 16 * cnt; i += blockDim.x) {
+    const int cell = i / cnt, c = i - cell * cnt;
+    bankT[cell * pitchT + c] = __ldg(w + (size_t)(c0 + c) * 16 + cell);
+  }
+  {
+    float* gz = reinterpret_cast<float*>(bankT + 16 * pitchT);  // the border cells of the G grids stay zero
+    for (int i = threadIdx.x; i < nwarps * (kGwBandScratch / 4); i += blockDim.x) gz[i] = 0.f;
+  }
+
+  float acc[NS][2][4];  // bank gradient of up to NS slabs of 16 channels x (cells 0-7 | cells 8-15)
+#pragma unroll
+  for (int sidx = 0; sidx < NS; ++sidx)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[sidx][0][k] = acc[sidx][1][k] = 0.f;
+  const __half* wtp = bankT + ((lane & 7) + ((lane >> 3) & 1) * 8) * pitchT + (lane >> 4) * 8;  // this lane's ldmatrix row
+  const int pc6 = ((gq >> 2) + 1) * 6 + (gq & 3) + 1;  // cell gq in the padded grid; cell gq + 8 lies two rows further
+
+  const int total_units = g.N * pl.bands;
+  const int u_begin = blockIdx.x * pl.units_per_block;
+  const int u_end = min(u_begin + pl.units_per_block, total_units);
+  for (int unit = u_begin; unit < u_end; ++unit) {
+    const int n = unit / pl.bands;
+    const int oh0 = (unit - n * pl.bands) * pl.BH;
+    const Band bx = make_band(oh0 * S - 1, (pl.BH - 1) * S + 3, g.H, g.W, pl.mode_x);
+    const Band by = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_dy);
+    const Band br = make_band(oh0, pl.BH, g.Ho, g.Wo, pl.mode_rot);
+    __syncthreads();  // previous unit's readers are done
+    load_band(xband, bx, x, n, g.C, c0, cnt, g.H, g.W);
+    if (!DYD) load_band(yband, by, dy, n, g.C, c0, cnt, g.Ho, g.Wo);
+    load_band(rband, br, rot, n, 18, 0, 18, g.Ho, g.Wo);
+    cp_async_wait_all();
+    __syncthreads();
+    __half* drot_n = drot + (size_t)n * 18 * g.P;
+    float* part_n = gpart + ((size_t)blockIdx.y * g.N + n) * 18 * g.P;
+    for (int item = warp; item < items; item += nwarps) {
+      const int dr = item / NB;
+      const int oh = oh0 + dr;
+      if (oh >= g.Ho) break;
+      const int ow0 = (item - dr * NB) << 3;
+      const int ow = ow0 + 2 * q, pc = ow0 + gq;
+      // DYD: dy of the lane's pixel pair comes from global memory (L1 after the first kernel row), one slab ahead of its
+      // use; a pair beyond the row reads as zero
+      const unsigned* dp = reinterpret_cast<const unsigned*>(dy + ((size_t)n * g.C + c0 + gq) * g.P + (size_t)oh * g.Wo + ow);
+      const size_t dstep8 = (size_t)4 * g.P;  // words between channel rows gq and gq + 8
+      const bool dy_in = ow < g.Wo;
+      const int xoff = window_offset(bx, oh * S - 1, ow, S);
+      const int yoff = kSlack + oh * by.Wp + ow - by.org;
+      const __half* rbase = rband + kSlack - br.org + oh * br.Wp + pc;
+#pragma unroll
+      for (int fh = 0; fh < 3; ++fh) {
+        // hat products of the three taps of this kernel row, transposed into B fragments of dW += dK * beta; a tap
+        // whose source position lies in the padding, or a pixel beyond the row, gets zeros and an invalid (u, v)
+        const int sr = oh * S - 1 + fh;
+        const bool rok = sr >= 0 && sr < g.H;
+        unsigned bw[3][2];
+#pragma unroll
+        for (int fw = 0; fw < 3; ++fw) {
+          const int t = fh * 3 + fw;
+          const int sc = pc * S - 1 + fw;
+          const bool ok = rok && pc < g.Wo && sc >= 0 && sc < g.W;
+          const __half* rp = rbase + (size_t)(2 * t) * br.pitch_c;
+          const float u = ((float)fh + __half2float(rp[0])) + uh0;
+          const float v = ok ? ((float)fw + __half2float(rp[br.pitch_c])) + uw0 : 1e30f;
+          const float du = u - cell_row, dv = v - cell_col;
+          const float hh0 = hat(du), hh1 = hat(du - 2.f);
+          const float hw0 = hat(dv), hw1 = hat(dv - 1.f);
+          bw[fw][0] = movmatrix_trans(pack2(hh0 * hw0, hh0 * hw1));
+          bw[fw][1] = movmatrix_trans(pack2(hh1 * hw0, hh1 * hw1));
+          if (q == 0) uv[fw * 8 + gq] = make_float2(u, v);
+        }
+        float G[3][4];
+#pragma unroll
+        for (int t = 0; t < 3; ++t) G[t][0] = G[t][1] = G[t][2] = G[t][3] = 0.f;
+        unsigned ndy0 = 0u, ndy1 = 0u;
+        if (DYD && dy_in) {
+          ndy0 = __ldg(dp);
+          ndy1 = __ldg(dp + dstep8);
+        }
+#pragma unroll
+        for (int sidx = 0; sidx < NS; ++sidx) {
+          if (sidx < nslab) {
+            const int cb16 = sidx << 4;
+            unsigned dy0, dy1;
+            if (DYD) {
+              dy0 = ndy0;
+              dy1 = ndy1;
+              if (dy_in && sidx + 1 < nslab) {
+                ndy0 = __ldg(dp + (size_t)(2 * sidx + 2) * dstep8);
+                ndy1 = __ldg(dp + (size_t)(2 * sidx + 3) * dstep8);
+              }
+            } else {
+              dy0 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq) * by.pitch_c + yoff);
+              dy1 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq + 8) * by.pitch_c + yoff);
+            }
+            const unsigned* p0 = reinterpret_cast<const unsigned*>(xband + (size_t)(cb16 + gq) * bx.pitch_c + xoff + fh * bx.Wp);
+            const unsigned* p1 = p0 + 4 * bx.pitch_c;  // channel row gq + 8
+            const unsigned w0 = p0[0], w1 = p0[1], w2 = p0[2];
+            const unsigned v0 = p1[0], v1 = p1[1], v2 = p1[2];
+            unsigned d0[3], d1[3];  // dK of channel rows gq and gq + 8 for the three taps
+#pragma unroll
+            for (int fw = 0; fw < 3; ++fw) {
+              d0[fw] = hmul2u(dy0, tap_pair<S>(w0, w1, w2, fw));
+              d1[fw] = hmul2u(dy1, tap_pair<S>(v0, v1, v2, fw));
+            }
+            // A = W^T slab: rows = the 16 cells, k = the slab's 16 channels
+            unsigned a[4];
+            {
+              const unsigned sa = (unsigned)__cvta_generic_to_shared(wtp + cb16);
+              asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                           : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(sa));
+            }
+#pragma unroll
+            for (int fw = 0; fw < 3; ++fw)
+              mma16816_acc(G[fw], a[0], a[1], a[2], a[3], movmatrix_trans(d0[fw]), movmatrix_trans(d1[fw]));
+            // k = 16 = 8 pixels x (tap 0 | tap 1), then 8 pixels x (tap 2 | nothing)
+            mma16816_acc(acc[sidx][0], d0[0], d1[0], d0[1], d1[1], bw[0][0], bw[1][0]);
+            mma16816_acc(acc[sidx][1], d0[0], d1[0], d0[1], d1[1], bw[0][1], bw[1][1]);
+            mma16816_acc(acc[sidx][0], d0[2], d1[2], 0u, 0u, bw[2][0], 0u);
+            mma16816_acc(acc[sidx][1], d0[2], d1[2], 0u, 0u, bw[2][1], 0u);
+          }
+        }
+        // d(offset)[pixel, tap, dir] = sum over the four corner cells of G * d(coefficient)/d(u or v): floor-based, as in
+        // mma_rot_kernel; the zero border of the grid stands for the corners outside the bank
+        __syncwarp();
+#pragma unroll
+        for (int tt = 0; tt < 3; ++tt) {
+          *reinterpret_cast<float2*>(Gs + (tt * 36 + pc6) * 8 + 2 * q) = make_float2(G[tt][0], G[tt][1]);
+          *reinterpret_cast<float2*>(Gs + (tt * 36 + pc6 + 12) * 8 + 2 * q) = make_float2(G[tt][2], G[tt][3]);
+        }
+        __syncwarp();
+        if (lane < 24) {
+          const int px = lane & 7, tt = lane >> 3;
+          const float2 c = uv[tt * 8 + px];
+          const bool valid = c.x > -1.f && c.y > -1.f && c.x < 4.f && c.y < 4.f;
+          const float uc = valid ? c.x : 0.f, vc = valid ? c.y : 0.f;  // floor in -1 .. 3: both corner rows inside the grid
+          const float fu = floorf(uc), fv = floorf(vc);
+          const float lh = uc - fu, lw = vc - fv;
+          const float hh = 1.f - lh, hw = 1.f - lw;
+          const float* Gp = Gs + (tt * 36 + ((int)fu + 1) * 6 + (int)fv + 1) * 8 + px;
+          const float g00 = Gp[0], g01 = Gp[8], g10 = Gp[48], g11 = Gp[56];
+          float gu = hw * (g10 - g00) + lw * (g11 - g01);
+          float gv = hh * (g01 - g00) + lh * (g11 - g10);
+          if (!valid) gu = gv = 0.f;
+          if (ow0 + px < g.Wo) {
+            const size_t o = (size_t)(2 * (fh * 3 + tt)) * g.P + oh * g.Wo + ow0 + px;
+            if (pl.groups == 1) {
+              drot_n[o] = __float2half_rn(gu);
+              drot_n[o + g.P] = __float2half_rn(gv);
+            } else {
+              part_n[o] = gu;
+              part_n[o + g.P] = gv;
+            }
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+  // reduce the warps' bank-gradient accumulators and write this block's partial [cnt][16]
+  __syncthreads();
+  float* red = reinterpret_cast<float*>(smem_raw);  // [nwarps][CG][16]
+#pragma unroll
+  for (int sidx = 0; sidx < NS; ++sidx) {
+    if (sidx < nslab) {
+      float* r0 = red + ((size_t)warp * pl.CG + (sidx << 4) + gq) * 16;
+      float* r1 = r0 + 8 * 16;
+      r0[2 * q] = acc[sidx][0][0]; r0[2 * q + 1] = acc[sidx][0][1];
+      r1[2 * q] = acc[sidx][0][2]; r1[2 * q + 1] = acc[sidx][0][3];
+      r0[8 + 2 * q] = acc[sidx][1][0]; r0[8 + 2 * q + 1] = acc[sidx][1][1];
+      r1[8 + 2 * q] = acc[sidx][1][2]; r1[8 + 2 * q + 1] = acc[sidx][1][3];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < cnt * 16; i += blockDim.x) {
+    float sum = 0.f;
+    for (int wv = 0; wv < nwarps; ++wv) sum += red[(size_t)wv * pl.CG * 16 + i];
+    partial[((size_t)blockIdx.x * g.C + c0) * 16 + i] = sum;
+  }
+}
+
+// Channel groups of up to 96 channels (six slabs of bank-gradient accumulators: 128 registers); bands as tall as shared
+// memory allows, two blocks of up to 8 warps per SM where a band with at least 16 items (or the whole plane) fits, else
+// one block of up to 16 warps; as many blocks as are resident at once, each walking over its share of the units.
+GwPlan gw_plan_search(const Geom& g) {
+  GwPlan pl;
+  pl.BH = 0;
+  if (g.scH != 4 || g.scW != 4) return pl;
+  // Measured on the sweep's layers (batch 128, against grad-offsets + grad-bank as two kernels): 14 x 14 outputs and below
+  // 0.060 / 0.090 / 0.049 / 0.074 / 0.063 ms against 0.069 / 0.100 / 0.063 / 0.100 / 0.080; 28 x 28 outputs 0.186 against
+  // 0.147 (one block of all 192 channels suits that plane better than two groups with partial sums), so those stay apart.
+  if (g.P > 196) return pl;
+  pl.CG = 0;
+  for (int cg = 96; cg >= 48; cg -= 16)
+    if (g.C % cg == 0) { pl.CG = cg; break; }
+  if (!pl.CG) {
+    if (g.C <= 96) pl.CG = g.C;
+    else return pl;
+  }
+  pl.groups = g.C / pl.CG;
+  const int S = g.sH;
+  const int NB = (g.Wo + 7) / 8;
+  const int Wp = g.W + (g.W & 1), Wpo = g.Wo + (g.Wo & 1);
+  pl.dy_direct = (g.Wo & 1) == 0;
+  auto shape = [&](int bh, int warps) {
+    const size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + (pl.dy_direct ? 0 : band_pitch(bh, Wpo))) * 2 +
+                        (size_t)18 * band_pitch(bh, Wpo) * 2 + (size_t)16 * (pl.CG + 8) * 2 + (size_t)warps * kGwBandScratch;
+    const size_t red = (size_t)warps * pl.CG * 16 * 4;
+    return smem < red ? red : smem;
+  };
+  for (int attempt = 0; attempt < 2 && !pl.BH; ++attempt) {
+    const int maxw = attempt == 0 ? 8 : 16;
+    const size_t budget = attempt == 0 ? kTwoPerSm : kOnePerSm;
+    int tallest = 0;
+    for (int bh = 1; bh <= g.Ho; ++bh) {
+      if (shape(bh, pick_warps(bh * NB, maxw)) > budget) break;
+      tallest = bh;
+      if (bh * NB >= 4 * maxw) break;
+    }
+    if (!tallest) continue;
+    if (attempt == 0 && tallest < g.Ho && tallest * NB < 2 * maxw) continue;  // too short a band: one big block instead
+    pl.BH = tallest;
+    pl.big = attempt == 1;
+  }
+  if (!pl.BH) return pl;
+  pl.bands = (g.Ho + pl.BH - 1) / pl.BH;
+  pl.BH = (g.Ho + pl.bands - 1) / pl.bands;  // as many bands, all of (nearly) one height
+  pl.warps = pick_warps(pl.BH * NB, pl.big ? 16 : 8);
+  pl.smem = shape(pl.BH, pl.warps);
+  const long long units = (long long)g.N * pl.bands;
+  long long per_sm = pl.big ? 1 : 2;
+  long long want = per_sm * 148 / pl.groups;
+  if (want > units) want = units;
+  if (want < 1) want = 1;
+  pl.units_per_block = (int)((units + want - 1) / want);
+  pl.blocks_x = (int)((units + pl.units_per_block - 1) / pl.units_per_block);
+  pl.dw_bytes = (((size_t)pl.blocks_x * g.C * 16 * sizeof(float)) + 255) & ~(size_t)255;
+  pl.ws_bytes = pl.dw_bytes + (pl.groups > 1 ? (size_t)pl.groups * g.N * 18 * g.P * sizeof(float) : 0);
+  return pl;
+}
+
+GwPlan gw_plan(const Geom& g) {
+  return cached_plan<GwPlan>(g, 4, [&] { return gw_plan_search(g); });
+}
+
 }  // namespace
 
 // out[c][cell] = sum over blocks of partial[block][c][16]: the second stage of every tensor-core bank gradient
@@ -1019,6 +1309,55 @@ int local_filter_mma(const __half* dy, const __half* x, const __half* rot, __hal
 #undef DK_LAUNCH_FILT3
 #undef DK_LAUNCH_FILT
   if ((rc = check_launch())) return rc;
+  const int n_out = g.C * g.cells;
+  reduce_bank_partials_kernel<<<(n_out + 7) / 8, 256, 0, s>>>(partial, dw, g.C, g.cells, pl.blocks_x);
+  return check_launch();
+}
+
+// Workspace of local_gw_mma (per-block partial bank gradients, then the per-group partial offset gradients); 0 = not covered.
+size_t local_gw_mma_workspace(const Geom& g) {
+  if (!fast_shape(g)) return 0;
+  const GwPlan pl = gw_plan(g);
+  return pl.BH ? pl.ws_bytes : 0;
+}
+
+// grad-offsets and grad-bank of the local deformable kernel in one pass (band form; 4 x 4 scope)
+int local_gw_mma(const __half* dy, const __half* x, const __half* rot, const __half* w, __half* drot, __half* dw, const Geom& g,
+                 void* ws, size_t ws_bytes, cudaStream_t s) {
+  if (!fast_shape(g)) return DK_ERR_UNSUPPORTED;
+  GwPlan pl = gw_plan(g);
+  if (!pl.BH || pl.smem > (size_t)device_smem_optin() || pl.groups > 65535) return DK_ERR_UNSUPPORTED;
+  if (ws == nullptr || ws_bytes < pl.ws_bytes) return DK_ERR_WORKSPACE;
+  pl.mode_x = ptr_mode(x);
+  pl.mode_dy = ptr_mode(dy);
+  pl.mode_rot = ptr_mode(rot);
+  if (pl.dy_direct && pl.mode_dy == 0) return DK_ERR_UNSUPPORTED;  // a dy pointer that is not 4-byte aligned: separate kernels
+  int rc;
+  float* partial = reinterpret_cast<float*>(ws);
+  float* gpart = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(ws) + pl.dw_bytes);
+#define DK_LAUNCH_GW(SS, MAXT, MINB, DD)                                                                       \
+  {                                                                                                          \
+    auto kern = mma_gw_kernel<SS, MAXT, MINB, DD>;                                                           \
+    if ((rc = enable_smem(kern, pl.smem))) return rc;                                                        \
+    kern<<<dim3(pl.blocks_x, pl.groups), pl.warps * 32, pl.smem, s>>>(dy, x, rot, w, drot, gpart, partial, g, pl); \
+  }
+#define DK_LAUNCH_GW2(SS, MAXT, MINB) \
+  if (pl.dy_direct) DK_LAUNCH_GW(SS, MAXT, MINB, true) else DK_LAUNCH_GW(SS, MAXT, MINB, false)
+  if (g.sH == 1) {
+    if (pl.big) DK_LAUNCH_GW2(1, 512, 1) else DK_LAUNCH_GW2(1, 256, 2)
+  } else {
+    if (pl.big) DK_LAUNCH_GW2(2, 512, 1) else DK_LAUNCH_GW2(2, 256, 2)
+  }
+#undef DK_LAUNCH_GW2
+#undef DK_LAUNCH_GW
+  if ((rc = check_launch())) return rc;
+  if (pl.groups > 1) {
+    const size_t n_out = (size_t)g.N * 18 * g.P;
+    const size_t blocks = (n_out + 255) / 256;
+    if (blocks > 0x7fffffffULL) return DK_ERR_UNSUPPORTED;
+    reduce_rot_partials_kernel<<<(unsigned)blocks, 256, 0, s>>>(gpart, drot, n_out, pl.groups);
+    if ((rc = check_launch())) return rc;
+  }
   const int n_out = g.C * g.cells;
   reduce_bank_partials_kernel<<<(n_out + 7) / 8, 256, 0, s>>>(partial, dw, g.C, g.cells, pl.blocks_x);
   return check_launch();

@@ -127,6 +127,40 @@ def test_block_shapes_of_the_fp16_fast_path_are_launchable(cabi):
                 assert ws == blocks // groups * c * 16 * 4, tag
                 assert cabi.lib.dk_sample_depthwise_backward_filter_workspace_bytes(g, cabi.DK_F16) >= ws, tag
     assert seen > 600
+    # the highest shared-memory byte a lane of the forward kernel can read, recomputed from the reported block shape
+    # (band layout of csrc/dk_mma_common.cuh: rows of the group's channels back to back, 8 halves of slack in front, 16
+    # behind; a lane reads six halves from source column ow * S - 2 of the three rows of its item), stays inside the
+    # block's shared memory for every reported shape
+    def band_pitch(rb, wp):
+        need = rb * wp + 8 + 16
+        pitch = ((need + 7) & ~15) + 8
+        return pitch + 16 if pitch < need else pitch
+    checked = 0
+    for n, c, h, w, s, scope in cases:
+        g = cabi.geom((n, c, h, w), (3, 3), (s, s), (1, 1), (1, 1), scope, 1)
+        if cabi.lib.dk_local_plan_query(g, cabi.DK_F16, 0, out):
+            continue
+        bh, cg, groups, warps, bands, smem, blocks, ws = list(out)
+        ho, wo = (h + 2 - 3) // s + 1, (w + 2 - 3) // s + 1
+        wp, rb = w + (w & 1), (bh - 1) * s + 3
+        pitch = band_pitch(rb, wp)
+        nb = (wo + 7) // 8
+        worst = 0
+        for band in (0, bands - 1):
+            row_lo = band * bh * s - 1
+            for mode in (2, 1, 0):                      # 16-byte, 4-byte and 2-byte copies lay the rows out differently
+                if mode == 2 and ((h * w) % 8 or w % 2):
+                    continue
+                if mode == 1 and w % 2:
+                    continue
+                org = ((row_lo * w) & ~7) if mode == 2 else row_lo * wp
+                last_row = min(band * bh + bh, ho) - 1  # last destination row of the band that exists
+                top = 8 + (last_row * s - 1 + 2) * wp + ((nb * 8 - 2) * s - 2) + 6 - org   # one past the last half read
+                worst = max(worst, (cg - 1) * pitch + top)
+        assert worst * 2 <= smem, (n, c, h, w, s, scope, list(out), worst * 2)
+        assert worst <= cg * pitch + 8, (n, c, h, w, s, scope, list(out), worst, cg * pitch)   # within the bands (+ next region's slack)
+        checked += 1
+    assert checked > 150
     # outside the fast path: other dtypes, kernels other than 3x3
     g = cabi.geom((4, 64, 28, 28), (3, 3), (1, 1), (1, 1), (1, 1), (4, 4), 1)
     assert cabi.lib.dk_local_plan_query(g, cabi.DK_F32, 0, out) == 2

@@ -607,6 +607,36 @@ def test_one_pass_backward_matches_oracle(oracle, c, hw, stride, n):
             {k: want[k] for k in ("grad_input", "grad_rotation", "grad_weight")}, torch.float16, "one pass")
 
 
+@pytest.mark.parametrize("n,c,h,w,stride", [(3, 32, 9, 11, 1), (2, 48, 14, 14, 2), (5, 192, 28, 28, 1), (4, 96, 7, 7, 1),
+                                            (6, 96, 7, 7, 2), (3, 160, 13, 20, 2), (130, 384, 14, 14, 1), (2, 16, 1, 1, 1)])
+def test_offsets_and_bank_gradients_in_one_band_pass(oracle, n, c, h, w, stride):
+    """The fused backward on planes the row-ring kernels do not take: grad-offsets and grad-bank come from ONE pass over the
+    products dy * x (band form: channel groups of up to 96, partial sums per group and per block).  Odd and tiny planes,
+    pixels beyond the row inside the last item, several channel groups, more units than blocks."""
+    from deformable_kernels import _cabi as C
+    case = make_case(n, c, h, w, stride=stride, rot_std=1.0, seed=300 + c + h)
+    x, r, wt, dy = (case[k].half().to(DEV) for k in ("input", "rotation", "weight", "grad_output"))
+    g = C.geom(x.shape, (3, 3), (stride, stride), (1, 1), (1, 1), (4, 4), 1)
+    nb = C.lib.dk_sample_depthwise_backward_workspace_bytes(g, C.DK_F16)
+    ws = torch.empty(max(nb, 1), dtype=torch.uint8, device=DEV)
+    gr, gw = torch.full_like(r, float("nan")), torch.full_like(wt, float("nan"))
+    for _ in range(2):  # twice: the partial sums of the first call must not leak into the second
+        C.check(C.lib.dk_sample_depthwise_backward(C.ptr(dy), C.ptr(x), C.ptr(r), C.ptr(wt), None, C.ptr(gr), C.ptr(gw), g,
+                                                   C.DK_F16, C.ptr(ws), nb, C.stream_ptr(x.device)), "fused backward")
+    torch.cuda.synchronize()
+    want = oracle_local(oracle, case, torch.float16)
+    compare(dict(grad_rotation=gr, grad_weight=gw), {k: want[k] for k in ("grad_rotation", "grad_weight")}, torch.float16,
+            "band pass")
+    # and the separate entry points agree
+    gr2, gw2 = torch.empty_like(r), torch.empty_like(wt)
+    C.check(C.lib.dk_sample_depthwise_backward_rotation(C.ptr(dy), C.ptr(x), C.ptr(r), C.ptr(wt), C.ptr(gr2), g, C.DK_F16,
+                                                        C.ptr(ws), nb, C.stream_ptr(x.device)), "grad-offsets")
+    C.check(C.lib.dk_sample_depthwise_backward_filter(C.ptr(dy), C.ptr(x), C.ptr(r), C.ptr(gw2), g, C.DK_F16, C.ptr(ws), nb,
+                                                      C.stream_ptr(x.device)), "grad-bank")
+    torch.cuda.synchronize()
+    assert rel_err(gr, gr2) < 2e-3 and rel_err(gw, gw2) < 2e-3
+
+
 @pytest.mark.parametrize("shift", [10, 11])
 @pytest.mark.parametrize("c,hw,stride", [(96, 56, 1), (32, 112, 2), (64, 28, 1)])
 def test_local_dk_fp16_with_loss_scaled_gradients(ops, oracle, c, hw, stride, shift):
