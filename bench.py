@@ -507,6 +507,7 @@ def main():
     host_cpus = None if os.environ.get("DK_BENCH_NO_BIND") else bind_host_to_gpu(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # stdout carries the one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     if args.workload in ("train", "dcn"):
         (run_training_step if args.workload == "train" else run_dcn_layer)(args, rank, world, local, dev)

@@ -19,8 +19,9 @@
  *   - the return value is a dk_status; nothing is printed and the process is never
  *     terminated (the reference prints launch errors and returns 1 regardless,
  *     csrc/filter_sample_depthwise_cuda_kernel.cu:427-430);
- *   - half inputs are read as fp16, all arithmetic and accumulation is fp32, results
- *     are rounded once on store; DK_F64 computes in fp64.
+ *   - half inputs are read as fp16 and every sum is accumulated in fp32, results are
+ *     rounded once on store (what the tensor-core path of fp16 calls rounds on the way
+ *     is stated under "numeric limits" below); DK_F64 computes in fp64.
  *   - entry points are thread-safe; the only global state is a per-device attribute
  *     cache behind a mutex.
  */
@@ -44,8 +45,11 @@ typedef enum dk_status {
 typedef enum dk_dtype { DK_F32 = 0, DK_F16 = 1, DK_F64 = 2 } dk_dtype;
 
 /* Devices and numeric limits.  Every pointer of a call must belong to the CURRENT device (cudaGetDevice()): the library
- * launches there, on the given stream, and never checks ownership.  fp16 calls: forward and grad-input multiply and sum
- * in fp32; grad-offsets and grad-bank feed the products grad_output * input to the tensor cores as fp16, so
+ * launches there, on the given stream, and never checks ownership.  fp16 calls on the tensor-core path (3x3, pad 1,
+ * stride 1 or 2, at most 16 bank cells, channels a multiple of 16): forward and grad-input take the resampled kernel
+ * value of a (pixel, tap, channel) from the tensor cores rounded to fp16 (relative 2^-11, the precision of the tensors
+ * themselves), multiply it exactly with the fp16 input and sum in fp32;
+ * grad-offsets and grad-bank feed the products grad_output * input to the tensor cores as fp16, so
  * |grad_output * input| must stay below 65504 (an overflow gives Inf / NaN gradients, which a loss scaler's
  * overflow check catches and answers by lowering its scale); all sums are fp32. */
 
