@@ -39,6 +39,28 @@ METRIC = "DK layer fwd+bwd images/sec (MobileNetV2 depthwise sweep, batch 128 fp
 HBM_NOMINAL_GBS = 8000.0
 
 
+_RESULT_FD = None
+
+
+def quiet_stdout():
+    """Everything libraries print on stdout while the benchmark runs (NCCL's version banner, for one) goes to stderr, so
+    that stdout carries the one JSON line and nothing else."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    sys.stdout.flush()
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        os.write(1, data)
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def out_hw(hw, s):
     return (hw + 2 * PAD - K) // s + 1
 
@@ -83,29 +105,46 @@ class ClockSampler:
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.proc, self.lines, self.begin = index, None, [], 0
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
-                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-        except OSError:
-            self.proc = None
+        """Starts nvidia-smi looping every 10 ms and waits for its first line, so that it is already sampling when the
+        timed region begins (the region of the default run lasts 30 ms)."""
+        for period_ms in ("10", "50"):  # a driver that refuses the short period gets the longer one
+            try:
+                self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
+                                              "--format=csv,noheader,nounits", "-lms", period_ms], stdout=subprocess.PIPE,
+                                             stderr=subprocess.DEVNULL, text=True)
+            except OSError:
+                self.proc = None
+                break
+            threading.Thread(target=self._read, args=(self.proc,), daemon=True).start()
+            t0 = time.time()
+            while not self.lines and time.time() - t0 < 3.0 and self.proc.poll() is None:
+                time.sleep(0.005)
+            if self.lines:
+                break
+        self.mark()
 
-    def _read(self):
-        for line in self.proc.stdout:
+    def mark(self):
+        """The timed region begins here: earlier samples are only used if the region turns out shorter than a sample."""
+        self.begin = len(self.lines)
+
+    def _read(self, proc):
+        for line in proc.stdout:
             self.lines.append(line)
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
+        time.sleep(0.03)
         self.proc.terminate()
+        lines, window = self.lines[self.begin:], "timed region"
+        if len(lines) < 2:  # shorter than the sampling period: take the samples of the warm-up steps (same load) as well
+            lines, window = self.lines[max(0, self.begin - 8):], "warm-up + timed region"
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for line in lines:
             f = [v.strip() for v in line.split(",")]
             if len(f) < 6:
                 continue
@@ -117,7 +156,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 def cpu_sweep(n_img, threads=None):
@@ -319,7 +358,7 @@ def run_training_step(args, rank, world, local, dev):
         if world > 1:
             dist.barrier()
     if rank == 0:
-        print(json.dumps({
+        emit(({
             "dk_operator_share": share,
             "metric": "MobileNetV2-DK training step images/sec (global batch %d, fp16 autocast)" % args.global_batch,
             "value": args.global_batch / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world, "steps": args.steps,
@@ -374,7 +413,7 @@ def run_dcn_layer(args, rank, world, local, dev):
     bytes_step = 557.2e6 * n / 64
     peak, peak_kind = measured_peak()
     if rank == 0:
-        print(json.dumps({
+        emit(({
             "metric": "DK+DCN layer fwd+bwd images/sec (C=256, 56x56, fp16)", "value": world * n / (ms_step * 1e-3),
             "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -435,7 +474,7 @@ def run_reference(args, rank):
         "e2e": {"value": val, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 def bind_host_to_gpu(index):
@@ -488,6 +527,7 @@ def main():
     ap.add_argument("--sustained-s", type=float, default=3.0,
                     help="seconds of the back-to-back sustained-clock run reported beside the headline (0 = skip)")
     args = ap.parse_args()
+    quiet_stdout()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -559,12 +599,13 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
     sampler = ClockSampler(local)
-    barrier()
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
@@ -831,7 +872,7 @@ def main():
             "reference_cuda_on_this_gpu": ref_gpu, "other_configs": others,
             "kernel_ms_sum_over_layers": {k: round(v, 4) for k, v in kern_tot.items()},
         }
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 

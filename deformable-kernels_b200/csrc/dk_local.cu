@@ -113,6 +113,21 @@ __global__ void __launch_bounds__(BLOCK) local_conv_kernel(const T* __restrict__
     if (j < cnt) st<T, A>(dst_n + j * dstride, acc[j]);
 }
 
+template <typename T, bool TRANSPOSED, int CC, int BLOCK>
+static int launch_local_conv_simt(const T* src, const T* rot, const T* w, T* dst, const Geom& g, long long total, cudaStream_t s) {
+  using A = typename Compute<T>::type;
+  const long long bx = (total + BLOCK - 1) / BLOCK;
+  const int by = (g.Cg + CC - 1) / CC;
+  if (bx > 0x7fffffffLL || by > 65535 || g.G > 65535) return DK_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)CC * g.cells * sizeof(A);
+  if (smem > (size_t)device_smem_optin()) return DK_ERR_UNSUPPORTED;
+  auto kern = local_conv_kernel<T, CC, BLOCK, TRANSPOSED>;
+  int rc = enable_smem(kern, smem);
+  if (rc) return rc;
+  kern<<<dim3((unsigned)bx, by, g.G), BLOCK, smem, s>>>(src, rot, w, dst, g);
+  return check_launch();
+}
+
 template <typename T, bool TRANSPOSED>
 static int launch_local_conv(const T* src, const T* rot, const T* w, T* dst, const Geom& g, cudaStream_t s) {
   using A = typename Compute<T>::type;
@@ -124,18 +139,13 @@ static int launch_local_conv(const T* src, const T* rot, const T* w, T* dst, con
       if (rc != DK_ERR_UNSUPPORTED) return rc;
     }
   }
-  constexpr int CC = 16, BLOCK = 256;
   const long long total = (long long)g.N * (TRANSPOSED ? g.HW : g.P);
-  const long long bx = (total + BLOCK - 1) / BLOCK;
-  const int by = (g.Cg + CC - 1) / CC;
-  if (bx > 0x7fffffffLL || by > 65535 || g.G > 65535) return DK_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)CC * g.cells * sizeof(A);
-  if (smem > (size_t)device_smem_optin()) return DK_ERR_UNSUPPORTED;
-  auto kern = local_conv_kernel<T, CC, BLOCK, TRANSPOSED>;
-  int rc = enable_smem(kern, smem);
-  if (rc) return rc;
-  kern<<<dim3((unsigned)bx, by, g.G), BLOCK, smem, s>>>(src, rot, w, dst, g);
-  return check_launch();
+  // 16 channels per thread amortise the sampling basis of a (pixel, tap); a call too small to fill the GPU that way
+  // (under two blocks per SM) takes 4 channels per thread and blocks of 64 instead: four times the threads, a quarter
+  // of the serial work in each
+  const bool tiny = ((total + 255) / 256) * ((g.Cg + 15) / 16) * g.G < 2LL * device_sm_count() && g.Cg > 4;
+  return tiny ? launch_local_conv_simt<T, TRANSPOSED, 4, 64>(src, rot, w, dst, g, total, s)
+              : launch_local_conv_simt<T, TRANSPOSED, 16, 256>(src, rot, w, dst, g, total, s);
 }
 
 template <typename T>

@@ -967,11 +967,22 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_gw_kernel(const __half* __rest
       if (oh >= g.Ho) break;
       const int ow0 = (item - dr * NB) << 3;
       const int ow = ow0 + 2 * q, pc = ow0 + gq;
-      // DYD: dy of the lane's pixel pair comes from global memory (L1 after the first kernel row), one slab ahead of its
-      // use; a pair beyond the row reads as zero
-      const unsigned* dp = reinterpret_cast<const unsigned*>(dy + ((size_t)n * g.C + c0 + gq) * g.P + (size_t)oh * g.Wo + ow);
-      const size_t dstep8 = (size_t)4 * g.P;  // words between channel rows gq and gq + 8
-      const bool dy_in = ow < g.Wo;
+      // DYD: dy of the lane's pixel pair in every slab comes from global memory into registers, all loads in flight at once
+      // and kept for the three kernel rows (fetching them again per kernel row, one slab ahead, measured 0.188 against
+      // 0.150 ms on C = 192, 28 x 28); a pair beyond the row reads as zero
+      unsigned dyw[NS][2];
+      if (DYD) {
+        const unsigned* dp = reinterpret_cast<const unsigned*>(dy + ((size_t)n * g.C + c0 + gq) * g.P + (size_t)oh * g.Wo + ow);
+        const size_t dstep8 = (size_t)4 * g.P;  // words between channel rows gq and gq + 8
+#pragma unroll
+        for (int sidx = 0; sidx < NS; ++sidx) {
+          dyw[sidx][0] = dyw[sidx][1] = 0u;
+          if (sidx < nslab && ow < g.Wo) {
+            dyw[sidx][0] = __ldg(dp + (size_t)(2 * sidx) * dstep8);
+            dyw[sidx][1] = __ldg(dp + (size_t)(2 * sidx + 1) * dstep8);
+          }
+        }
+      }
       const int xoff = window_offset(bx, oh * S - 1, ow, S);
       const int yoff = kSlack + oh * by.Wp + ow - by.org;
       const __half* rbase = rband + kSlack - br.org + oh * br.Wp + pc;
@@ -1000,23 +1011,14 @@ __global__ void __launch_bounds__(MAXT, MINB) mma_gw_kernel(const __half* __rest
         float G[3][4];
 #pragma unroll
         for (int t = 0; t < 3; ++t) G[t][0] = G[t][1] = G[t][2] = G[t][3] = 0.f;
-        unsigned ndy0 = 0u, ndy1 = 0u;
-        if (DYD && dy_in) {
-          ndy0 = __ldg(dp);
-          ndy1 = __ldg(dp + dstep8);
-        }
 #pragma unroll
         for (int sidx = 0; sidx < NS; ++sidx) {
           if (sidx < nslab) {
             const int cb16 = sidx << 4;
             unsigned dy0, dy1;
             if (DYD) {
-              dy0 = ndy0;
-              dy1 = ndy1;
-              if (dy_in && sidx + 1 < nslab) {
-                ndy0 = __ldg(dp + (size_t)(2 * sidx + 2) * dstep8);
-                ndy1 = __ldg(dp + (size_t)(2 * sidx + 3) * dstep8);
-              }
+              dy0 = dyw[sidx][0];
+              dy1 = dyw[sidx][1];
             } else {
               dy0 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq) * by.pitch_c + yoff);
               dy1 = *reinterpret_cast<const unsigned*>(yband + (size_t)(cb16 + gq + 8) * by.pitch_c + yoff);
@@ -1115,9 +1117,9 @@ GwPlan gw_plan_search(const Geom& g) {
   pl.BH = 0;
   if (g.scH != 4 || g.scW != 4) return pl;
   // Measured on the sweep's layers (batch 128, against grad-offsets + grad-bank as two kernels): 14 x 14 outputs and below
-  // 0.060 / 0.090 / 0.049 / 0.074 / 0.063 ms against 0.069 / 0.100 / 0.063 / 0.100 / 0.080; 28 x 28 outputs 0.186 against
-  // 0.147 (one block of all 192 channels suits that plane better than two groups with partial sums), so those stay apart.
-  if (g.P > 196) return pl;
+  // 0.053 / 0.084 / 0.049 / 0.074 / 0.059 ms against 0.069 / 0.100 / 0.063 / 0.100 / 0.080; 28 x 28 outputs 0.150 against
+  // 0.147 (there one block over all 192 channels does as well as two groups with partial sums), so those stay apart.
+  if (g.P > 196 && !tuning_env("DK_B200_GW_ANY")) return pl;
   pl.CG = 0;
   for (int cg = 96; cg >= 48; cg -= 16)
     if (g.C % cg == 0) { pl.CG = cg; break; }
@@ -1130,6 +1132,7 @@ GwPlan gw_plan_search(const Geom& g) {
   const int NB = (g.Wo + 7) / 8;
   const int Wp = g.W + (g.W & 1), Wpo = g.Wo + (g.Wo & 1);
   pl.dy_direct = (g.Wo & 1) == 0;
+  if (const char* e = tuning_env("DK_B200_GW_DY_DIRECT")) pl.dy_direct = pl.dy_direct && atoi(e) != 0;  // comparison runs
   auto shape = [&](int bh, int warps) {
     const size_t smem = (size_t)pl.CG * (band_pitch((bh - 1) * S + 3, Wp) + (pl.dy_direct ? 0 : band_pitch(bh, Wpo))) * 2 +
                         (size_t)18 * band_pitch(bh, Wpo) * 2 + (size_t)16 * (pl.CG + 8) * 2 + (size_t)warps * kGwBandScratch;
