@@ -6,8 +6,10 @@ fp32 arithmetic; five layer shapes x stride 1 and 2, scope 4x4, kernel 3, pad 1)
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-One "step" is one forward + backward of all ten layers on one batch.  Rank 0 prints ONE
-JSON line.  `value` is device-timed with inputs resident in HBM; `e2e` is the same step
+One "step" is one forward + backward of all ten layers on one batch, issued through the
+public autograd API; it is captured once as a CUDA graph and replayed (--eager launches it
+call by call).  Rank 0 prints ONE JSON line.  `value` is device-timed with inputs resident
+in HBM; `e2e` is the same step
 through the public autograd API with every input copied from pinned host memory and every
 result copied back inside the timed region.  The batch is sharded by replication of the
 per-GPU batch (weak scaling, no collective: nothing on this path is exchanged between
@@ -516,7 +518,10 @@ def main():
                          "dcn: one DK + DCN layer (BASELINE config 4)")
     ap.add_argument("--global-batch", type=int, default=1024)
     ap.add_argument("--cuda-graph", action="store_true",
-                    help="train workload, one GPU: run the network's forward and backward as captured CUDA graphs")
+                    help="train workload, one GPU: run the network's forward and backward as captured CUDA graphs (the sweep replays "
+                         "its step as a CUDA graph by default, see --eager)")
+    ap.add_argument("--eager", action="store_true",
+                    help="sweep: launch every step through the autograd API instead of replaying it as a CUDA graph")
     ap.add_argument("--dcn-batch", type=int, default=64, help="images per GPU of the dcn workload")
     ap.add_argument("--layers", default="", help="comma-separated indices into the ten-layer sweep (default: all)")
     ap.add_argument("--no-ref-gpu", action="store_true",
@@ -586,12 +591,39 @@ def main():
         gx, gr, gw = torch.autograd.grad(y, [x, rot, t["w"]], dy)
         return y, gx, gr, gw
 
-    def step():
+    def compute():
         gws = []
         for t in layers:
             gws.append(fwd_bwd(t, t["x"], t["rot"], t["dy"])[3])
-        if strong and world > 1:  # the only exchange of the path: 0.46 MB of bank gradients, one NCCL all-reduce
-            flat = torch.cat([g.float().flatten() for g in gws])
+        return torch.cat([g.float().flatten() for g in gws]) if strong and world > 1 else None
+
+    graph = None
+    if not args.eager:
+        # the ten layers' forward + backward captured once (the operators enqueue on the current stream, never synchronise
+        # and take their scratch from the caller) and replayed: one host call per step instead of fifty launches through
+        # the autograd API, which is what a step of a few hundred microseconds per layer shard is otherwise bound by
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                compute()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                flat_static = compute()
+        except Exception as exc:  # no capture on this stack: the step runs eagerly (config.cuda_graph says which)
+            sys.stderr.write("CUDA graph capture failed (%s): eager step\n" % exc)
+            graph = None
+            torch.cuda.synchronize()
+
+    def step():
+        if graph is not None:
+            graph.replay()
+            flat = flat_static
+        else:
+            flat = compute()
+        if flat is not None:  # the only exchange of the path: 0.46 MB of bank gradients, one NCCL all-reduce
             dist.all_reduce(flat)
 
     def barrier():
@@ -857,6 +889,7 @@ def main():
             "config": {"workload": "cfg3 layer sweep: DeformKernel2d (C,HW) in (96,112),(144,56),(192,28),(384,14),(960,7)"
                                    " x stride 1,2; scope 4x4, kernel 3, pad 1; offsets ~N(0,1); batch %s" %
                                    (("%d in total, split over the GPUs" % args.batch) if strong else ("%d per GPU" % n)),
+                       "cuda_graph": graph is not None,
                        "storage": "f16 tensors; forward and grad-input: resampled kernel rounded to f16 (tensor-core output), "
                                   "exact f16 x f16 products summed in fp32; "
                                   "grad-offsets and grad-bank: products dy * x rounded to f16 (tensor-core operands), "

@@ -285,6 +285,8 @@ size_t dk_deform_sample_depthwise_backward_filter_workspace_bytes(const dk_geom*
   if (dtype == DK_F16) {
     const size_t fast = deform_filter_mma_workspace(gg);
     if (fast > need) need = fast;
+    const size_t fused = deform_coords_bank_workspace(gg);  // the bank gradient riding along with the offset gradients
+    if (fused > need) need = fused;
   }
   return align256(need);
 }
@@ -360,12 +362,14 @@ int dk_deform_sample_depthwise_backward(const void* grad_output, const void* inp
                            gg, workspace, data_ws, s);
       if (rc) return rc;
     }
+    bool bank_done = false;
     if (grad_offset) {
       rc = deform_coords_mma(P_(__half, grad_output), P_(__half, input), P_(__half, offset), nullptr, P_(__half, filter),
-                             M_(__half, grad_offset), nullptr, gg, workspace, data_ws, s);
+                             M_(__half, grad_offset), nullptr, gg, workspace, data_ws, s, M_(__half, grad_filter),
+                             (char*)workspace + data_ws, filt_ws, &bank_done);
       if (rc) return rc;
     }
-    if (grad_filter)
+    if (grad_filter && !bank_done)
       rc = deform_filter_mma(P_(__half, grad_output), P_(__half, input), P_(__half, offset), nullptr, M_(__half, grad_filter),
                              gg, (char*)workspace + data_ws, filt_ws, s);
     return rc;
@@ -376,17 +380,21 @@ int dk_deform_sample_depthwise_backward(const void* grad_output, const void* inp
                                                   data_ws, stream);
     if (rc) return rc;
   }
+  bool bank_done = false;
   if (grad_offset || grad_rotation) {
     rc = DK_ERR_UNSUPPORTED;
-    if (dtype == DK_F16 && mma_path_enabled() && workspace && workspace_bytes >= data_ws)
+    if (dtype == DK_F16 && mma_path_enabled() && workspace && workspace_bytes >= data_ws) {
+      const bool room = grad_filter && workspace_bytes >= data_ws + filt_ws;
       rc = deform_coords_mma(P_(__half, grad_output), P_(__half, input), P_(__half, offset), P_(__half, rotation),
                              P_(__half, filter), M_(__half, grad_offset), M_(__half, grad_rotation), gg, workspace, data_ws,
-                             (cudaStream_t)stream);
+                             (cudaStream_t)stream, room ? M_(__half, grad_filter) : nullptr, (char*)workspace + data_ws,
+                             room ? filt_ws : 0, &bank_done);
+    }
     if (rc == DK_ERR_UNSUPPORTED)
       rc = deform_coords_dispatch(grad_output, input, offset, rotation, filter, grad_offset, grad_rotation, gg, dtype, stream);
     if (rc) return rc;
   }
-  if (grad_filter) {
+  if (grad_filter && !bank_done) {
     if (!workspace || workspace_bytes < data_ws + filt_ws) return DK_ERR_WORKSPACE;
     rc = dk_deform_sample_depthwise_backward_filter(grad_output, input, offset, rotation, grad_filter, g, dtype,
                                                     (char*)workspace + data_ws, filt_ws, stream);

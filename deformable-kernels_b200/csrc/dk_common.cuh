@@ -225,8 +225,11 @@ FilterPlan filter_plan(const Geom& g, size_t acc_bytes);
 FilterPlan filter_plan_fit(const Geom& g, size_t acc_bytes, size_t max_bytes);
 size_t deform_filter_mma_workspace(const Geom& g);
 size_t deform_coords_mma_workspace(const Geom& g);
+// with dw / bank_ws / bank_done the bank gradient is computed in the same pass where the plan allows (*bank_done)
+size_t deform_coords_bank_workspace(const Geom& g);
 int deform_coords_mma(const __half* dy, const __half* x, const __half* off, const __half* rot, const __half* w, __half* doff,
-                      __half* drot, const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s);
+                      __half* drot, const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s, __half* dw = nullptr,
+                      void* bank_ws = nullptr, size_t bank_ws_bytes = 0, bool* bank_done = nullptr);
 int deform_data_mma(const __half* dy, const __half* off, const __half* rot, const __half* w, __half* dx, const Geom& g,
                     void* ws, size_t ws_bytes, cudaStream_t s);
 int deform_forward_mma(const __half* x, const __half* off, const __half* rot, const __half* w, __half* y, const Geom& g,

@@ -783,11 +783,14 @@ __device__ __forceinline__ void sample_pair3(unsigned& v, unsigned& dh, unsigned
   dw = hfma2u(x3, cw.w, hfma2u(x2, cw.z, hfma2u(x1, cw.y, hmul2u(x0, cw.x))));
 }
 
-template <int S, int NS, bool DO_OFF, bool DO_ROT, bool ZR>
-__global__ void __launch_bounds__(512, 1)
+// DO_BANK: the bank gradient dW += (dy * xs) * beta rides along (the products dy * xs are formed here anyway for the
+// kernel-offset gradient): accumulators in registers over all units of the block, one partial [CG][16] per block at the end.
+template <int S, int NS, bool DO_OFF, bool DO_ROT, bool ZR, bool DO_BANK>
+__global__ void __launch_bounds__(DO_BANK ? 384 : 512, 1)  // the bank accumulators need the registers of four warps
     mma_deform_coords_kernel(const __half* __restrict__ dy, const __half* __restrict__ x, const __half* __restrict__ off,
                              const __half* __restrict__ rot, const __half* __restrict__ w, __half* __restrict__ doff,
-                             __half* __restrict__ drot, float* __restrict__ partial, const Geom g, const DCoordPlan pl) {
+                             __half* __restrict__ drot, float* __restrict__ partial, float* __restrict__ bank_partial,
+                             const Geom g, const DCoordPlan pl) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int CG = 16 * NS;
   constexpr int pitchT = CG + 8;
@@ -825,6 +828,12 @@ __global__ void __launch_bounds__(512, 1)
     const unsigned z[9] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
     beta_from_regs(bf, z, g, lc, sc44, true);
   }
+
+  float acc[DO_BANK ? NS : 1][2][4];  // bank gradient: slabs of 16 channels x (cells 0-7 | cells 8-15)
+#pragma unroll
+  for (int sidx = 0; sidx < (DO_BANK ? NS : 1); ++sidx)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[sidx][0][k] = acc[sidx][1][k] = 0.f;
 
   const int total_units = g.N * pl.bands;
   const int u_begin = blockIdx.x * pl.units_per_block;
@@ -879,9 +888,18 @@ __global__ void __launch_bounds__(512, 1)
         for (int fw = 0; fw < 3; ++fw)
 #pragma unroll
           for (int k = 0; k < 4; ++k) G[fw][k] = D[fw][k] = 0.f;
+        unsigned bw[3][2];  // DO_BANK: the hat products of this kernel row as B fragments of dW += dK * beta
+        if (DO_BANK) {
+#pragma unroll
+          for (int fw = 0; fw < 3; ++fw) {
+            bw[fw][0] = movmatrix_trans(bf[fh * 3 + fw][0]);
+            bw[fw][1] = movmatrix_trans(bf[fh * 3 + fw][1]);
+          }
+        }
 #pragma unroll
         for (int sidx = 0; sidx < NS; ++sidx) {
           const int cb16 = 16 * sidx;
+          unsigned pa = 0u, pb = 0u;  // DO_BANK: dK of tap 0, waiting for tap 1 to fill the k = 16 of one mma
           // A = W slab (rows = channels gq, gq + 8; k = cells) and A = W^T slab (rows = cells; k = channels)
           const unsigned* b0 = reinterpret_cast<const unsigned*>(bank + (cb16 + gq) * kBankPitch);
           const unsigned* b1 = reinterpret_cast<const unsigned*>(bank + (cb16 + gq + 8) * kBankPitch);
@@ -896,10 +914,23 @@ __global__ void __launch_bounds__(512, 1)
             unsigned vA, hA, wA, vB, hB, wB;  // pixel 2q and pixel 2q + 1: (channel gq | channel gq + 8)
             sample_pair3(vA, hA, wA, base, e0);
             sample_pair3(vB, hB, wB, base, e0 + 4);
-            if (want_rot) {  // kernel offsets: G += W^T * (dy * xs)
-              const unsigned ka = hmul2u(dy0[sidx], __byte_perm(vA, vB, 0x5410));
-              const unsigned kb = hmul2u(dy1[sidx], __byte_perm(vA, vB, 0x7632));
-              mma16816_acc(G[fw], t0, t1, t2, t3, movmatrix_trans(ka), movmatrix_trans(kb));
+            if (want_rot || DO_BANK) {
+              const unsigned ka = hmul2u(dy0[sidx], __byte_perm(vA, vB, 0x5410));  // dK of channel gq: pixels 2q, 2q + 1
+              const unsigned kb = hmul2u(dy1[sidx], __byte_perm(vA, vB, 0x7632));  // channel gq + 8
+              // kernel offsets: G += W^T * (dy * xs)
+              if (want_rot) mma16816_acc(G[fw], t0, t1, t2, t3, movmatrix_trans(ka), movmatrix_trans(kb));
+              if (DO_BANK) {
+                if (fw == 0) {
+                  pa = ka;
+                  pb = kb;
+                } else if (fw == 1) {  // k = 16 = 8 pixels x (tap 0 | tap 1)
+                  mma16816_acc(acc[DO_BANK ? sidx : 0][0], pa, pb, ka, kb, bw[0][0], bw[1][0]);
+                  mma16816_acc(acc[DO_BANK ? sidx : 0][1], pa, pb, ka, kb, bw[0][1], bw[1][1]);
+                } else {  // the third tap, paired with zeros
+                  mma16816_acc(acc[DO_BANK ? sidx : 0][0], ka, kb, 0u, 0u, bw[2][0], 0u);
+                  mma16816_acc(acc[DO_BANK ? sidx : 0][1], ka, kb, 0u, 0u, bw[2][1], 0u);
+                }
+              }
             }
             if (want_off) {  // image offsets: D[pixel, dir] += sum over the slab's channels of dy * K * dxs
               unsigned kk[2];
@@ -975,6 +1006,25 @@ __global__ void __launch_bounds__(512, 1)
         }
       }
       __syncwarp();
+    }
+  }
+  if (DO_BANK) {  // reduce the warps' accumulators and write this block's partial bank gradient [CG channels][16 cells]
+    __syncthreads();
+    float* red = reinterpret_cast<float*>(smem_raw);  // [nwarps][CG][16]
+#pragma unroll
+    for (int sidx = 0; sidx < (DO_BANK ? NS : 1); ++sidx) {
+      float* r0 = red + ((size_t)warp * CG + 16 * sidx + gq) * 16;
+      float* r1 = r0 + 8 * 16;
+      r0[2 * q] = acc[sidx][0][0]; r0[2 * q + 1] = acc[sidx][0][1];
+      r1[2 * q] = acc[sidx][0][2]; r1[2 * q + 1] = acc[sidx][0][3];
+      r0[8 + 2 * q] = acc[sidx][1][0]; r0[8 + 2 * q + 1] = acc[sidx][1][1];
+      r1[8 + 2 * q] = acc[sidx][1][2]; r1[8 + 2 * q + 1] = acc[sidx][1][3];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < CG * 16; i += blockDim.x) {
+      float sum = 0.f;
+      for (int wv = 0; wv < nwarps; ++wv) sum += red[(size_t)wv * CG * 16 + i];
+      bank_partial[((size_t)blockIdx.x * g.C + c0) * 16 + i] = sum;
     }
   }
 }
@@ -1242,13 +1292,31 @@ size_t deform_coords_mma_workspace(const Geom& g) {
   return need;
 }
 
+// Partial bank gradients of the fused call below: [blocks][C][16] floats; 0 = the shape is not covered.
+size_t deform_coords_bank_workspace(const Geom& g) {
+  size_t need = 0;
+  for (int cap = 1; cap <= 2; cap <<= 1) {
+    const DCoordPlan pl = dcoord_plan(g, cap);
+    const size_t b = pl.BH ? (size_t)pl.blocks_x * g.C * 16 * sizeof(float) : 0;
+    if (b > need) need = b;
+  }
+  return need;
+}
+
+// dw != nullptr (with both offset gradients wanted, or the image-space one when rot == nullptr): the bank gradient is
+// computed in the same pass from the products dy * xs; *bank_done tells the caller that dw has been written.
 int deform_coords_mma(const __half* dy, const __half* x, const __half* off, const __half* rot, const __half* w, __half* doff,
-                      __half* drot, const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s) {
+                      __half* drot, const Geom& g, void* ws, size_t ws_bytes, cudaStream_t s, __half* dw, void* bank_ws,
+                      size_t bank_ws_bytes, bool* bank_done) {
+  if (bank_done) *bank_done = false;
   if (!doff && !drot) return DK_OK;
   if (!rot && drot) return DK_ERR_BAD_ARGUMENT;
   DCoordPlan pl = dcoord_plan(g, slab_cap());
   if (!pl.BH || pl.smem > (size_t)device_smem_optin() || g.C / (16 * pl.NS) > 65535) return DK_ERR_UNSUPPORTED;
   if (pl.ws_bytes && (ws == nullptr || ws_bytes < pl.ws_bytes)) return DK_ERR_UNSUPPORTED;  // no scratch: the SIMT kernel
+  const bool with_bank = dw != nullptr && bank_done != nullptr && doff != nullptr && (drot != nullptr || !rot) && bank_ws != nullptr &&
+                         bank_ws_bytes >= (size_t)pl.blocks_x * g.C * 16 * sizeof(float) &&
+                         (size_t)pl.warps * 16 * pl.NS * 16 * sizeof(float) <= pl.smem;
   pl.mode_dy = ptr_mode(dy);
   pl.mode_rot = ptr_mode(rot);
   pl.mode_off = ptr_mode(off);
@@ -1262,23 +1330,34 @@ int deform_coords_mma(const __half* dy, const __half* x, const __half* off, cons
     }
   }
   const dim3 grid(pl.blocks_x, g.C / (16 * pl.NS));
+  float* bank_partial = reinterpret_cast<float*>(bank_ws);
+  if (with_bank && pl.warps > 12) pl.warps = 12;
   auto launch = [&](auto kern) -> int {
     if (int e = enable_smem(kern, pl.smem)) return e;
-    kern<<<grid, pl.warps * 32, pl.smem, s>>>(dy, x, off, rot, w, doff, drot, partial, g, pl);
+    kern<<<grid, pl.warps * 32, pl.smem, s>>>(dy, x, off, rot, w, doff, drot, partial, bank_partial, g, pl);
     return check_launch();
   };
   int rc;
-#define DK_COORDS(SS, NN)                                                                     \
-  (!rot ? launch(mma_deform_coords_kernel<SS, NN, true, false, true>)                         \
-        : doff && drot ? launch(mma_deform_coords_kernel<SS, NN, true, true, false>)         \
-                       : doff ? launch(mma_deform_coords_kernel<SS, NN, true, false, false>) \
-                              : launch(mma_deform_coords_kernel<SS, NN, false, true, false>))
+#define DK_COORDS(SS, NN)                                                                                      \
+  (!rot ? (with_bank ? launch(mma_deform_coords_kernel<SS, NN, true, false, true, true>)                       \
+                     : launch(mma_deform_coords_kernel<SS, NN, true, false, true, false>))                     \
+        : doff && drot ? (with_bank ? launch(mma_deform_coords_kernel<SS, NN, true, true, false, true>)        \
+                                    : launch(mma_deform_coords_kernel<SS, NN, true, true, false, false>))      \
+                       : doff ? launch(mma_deform_coords_kernel<SS, NN, true, false, false, false>)            \
+                              : launch(mma_deform_coords_kernel<SS, NN, false, true, false, false>))
   if (g.sH == 1)
     rc = pl.NS == 2 ? DK_COORDS(1, 2) : DK_COORDS(1, 1);
   else
     rc = pl.NS == 2 ? DK_COORDS(2, 2) : DK_COORDS(2, 1);
 #undef DK_COORDS
-  if (rc || !pl.ws_bytes) return rc;
+  if (rc) return rc;
+  if (with_bank) {
+    const int n_out = g.C * g.cells;
+    reduce_dcn_bank_partials_kernel<<<(n_out + 7) / 8, 256, 0, s>>>(bank_partial, dw, g.C, g.cells, pl.blocks_x);
+    if ((rc = check_launch())) return rc;
+    *bank_done = true;
+  }
+  if (!pl.ws_bytes) return rc;
   const size_t plane18 = (size_t)18 * g.P, count = (size_t)g.N * plane18;
   const unsigned blocks = (unsigned)((count + 255) / 256);
   if (doff) round_coord_partials_kernel<<<blocks, 256, 0, s>>>(partial, doff, g.N, plane18, 0);

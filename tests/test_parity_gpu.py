@@ -244,6 +244,41 @@ def test_deform_dk_fp16_random_shapes_match_oracle(ops, oracle, cfg):
     compare(mine_deform(ops, case, torch.float16), oracle_deform(oracle, case, torch.float16), torch.float16, "random-deform")
 
 
+@pytest.mark.parametrize("n,c,hw,stride,with_rot", [(3, 64, 28, 1, True), (2, 32, 56, 1, True), (4, 48, 14, 2, True),
+                                                     (40, 64, 28, 1, False), (150, 32, 14, 1, True)])   # without kernel-space offsets the C ABI wants a batch the
+                                                     # whole-sample grad-input kernel takes
+def test_deform_bank_gradient_rides_along_with_the_offset_gradients(oracle, n, c, hw, stride, with_rot):
+    """fp16 DK + DCN, fused backward through the C ABI: when both offset gradients (or, without kernel-space offsets, the
+    image-space one) are wanted together with the bank gradient, the bank gradient comes out of the same pass.  It must
+    agree with the stand-alone bank-gradient entry point and with the oracle, twice in a row (partial sums do not leak)."""
+    from deformable_kernels import _cabi as C
+    case = make_case(n, c, hw, hw, stride=stride, rot_std=0.8, off_std=1.5, seed=700 + c + hw)
+    x, o, r, w, dy = (case[k].half().to(DEV) for k in ("input", "offset", "rotation", "weight", "grad_output"))
+    if not with_rot:
+        case["rotation"] = torch.zeros_like(case["rotation"])
+        r = torch.zeros_like(r)
+    g = C.geom(x.shape, (3, 3), (stride, stride), (1, 1), (1, 1), (4, 4), 1)
+    nb = C.lib.dk_deform_sample_depthwise_backward_workspace_bytes(g, C.DK_F16)
+    ws = torch.empty(max(nb, 1), dtype=torch.uint8, device=DEV)
+    gx, go, gr, gw = torch.empty_like(x), torch.empty_like(o), torch.empty_like(r), torch.full_like(w, float("nan"))
+    for _ in range(2):
+        C.check(C.lib.dk_deform_sample_depthwise_backward(
+            C.ptr(dy), C.ptr(x), C.ptr(o), C.ptr(r) if with_rot else None, C.ptr(w), C.ptr(gx), C.ptr(go),
+            C.ptr(gr) if with_rot else None, C.ptr(gw), g, C.DK_F16, C.ptr(ws), nb, C.stream_ptr(x.device)), "fused backward")
+    gw2 = torch.empty_like(w)
+    nbf = C.lib.dk_deform_sample_depthwise_backward_filter_workspace_bytes(g, C.DK_F16)
+    wsf = torch.empty(max(nbf, 1), dtype=torch.uint8, device=DEV)
+    C.check(C.lib.dk_deform_sample_depthwise_backward_filter(C.ptr(dy), C.ptr(x), C.ptr(o), C.ptr(r), C.ptr(gw2), g, C.DK_F16,
+                                                             C.ptr(wsf), nbf, C.stream_ptr(x.device)), "bank gradient")
+    torch.cuda.synchronize()
+    assert rel_err(gw, gw2) < 2e-3
+    want = oracle_deform(oracle, case, torch.float16)
+    got = dict(grad_input=gx, grad_offset=go, grad_weight=gw)
+    if with_rot:
+        got["grad_rotation"] = gr
+    compare(got, {k: want[k] for k in got}, torch.float16, "fused DK+DCN backward")
+
+
 def test_deform_grad_input_fixed_point_accumulation(ops, oracle):
     """The fp16 grad-input kernel sums in fixed point.  Bit-reproducible; an outlier in dy coarsens only its own
     (sample, channel) plane and the result still holds the tolerance on every plane taken by itself; offsets that
