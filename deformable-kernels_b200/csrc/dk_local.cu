@@ -542,16 +542,26 @@ size_t deform_filter_plane_workspace(const Geom& g, int dtype) {
   return pl.ok ? pl.ws_bytes : 0;
 }
 
-// out[i] = sum over partial blocks, fixed order.
+// out[i] = sum over partial blocks, fixed order.  A block of 256 threads takes 32 outputs: thread (x, y) sums the partials
+// y, y + 8, ... of output x (coalesced over x), the eight sums of an output meet in shared memory.
 template <typename T>
 __global__ void reduce_partials_kernel(const typename Compute<T>::type* __restrict__ partial, T* __restrict__ out,
                                        const int n_out, const int n_part) {
   using A = typename Compute<T>::type;
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n_out) return;
+  __shared__ A part[8][33];
+  const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+  const int i = blockIdx.x * 32 + x;
   A s = (A)0;
-  for (int k = 0; k < n_part; ++k) s += partial[(size_t)k * n_out + i];
-  st<T, A>(out + i, s);
+  if (i < n_out)
+    for (int k = y; k < n_part; k += 8) s += partial[(size_t)k * n_out + i];
+  part[y][x] = s;
+  __syncthreads();
+  if (y == 0 && i < n_out) {
+    A t = part[0][x];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) t += part[j][x];
+    st<T, A>(out + i, t);
+  }
 }
 
 FilterPlan filter_plan(const Geom& g, size_t acc_bytes) {
@@ -565,7 +575,7 @@ FilterPlan filter_plan(const Geom& g, size_t acc_bytes) {
   const long long total = (long long)g.N * g.P;
   const long long chan_ctas = (long long)pl.chan_blocks * g.G;
   long long want = (4LL * 148 + chan_ctas - 1) / chan_ctas;  // ~4 blocks per SM over the grid
-  const long long max_by_work = (total + 7) / 8;  // at least eight pixels per block, so that small problems still spread out
+  const long long max_by_work = (total + 3) / 4;  // at least four pixels per block, so that small problems still spread out
   if (want > max_by_work) want = max_by_work;
   if (want > 2048) want = 2048;
   if (want < 1) want = 1;
@@ -610,7 +620,7 @@ static int filter_backward(const T* dy, const T* x, const T* off, const T* rot, 
       rc = check_launch();
       if (rc) return rc;
       const int n_out = g.C * g.cells;
-      reduce_partials_kernel<T><<<(n_out + 255) / 256, 256, 0, s>>>(reinterpret_cast<const A*>(ws), dw, n_out, pp.slots);
+      reduce_partials_kernel<T><<<(n_out + 31) / 32, 256, 0, s>>>(reinterpret_cast<const A*>(ws), dw, n_out, pp.slots);
       return check_launch();
     }
   }
@@ -628,7 +638,7 @@ static int filter_backward(const T* dy, const T* x, const T* off, const T* rot, 
   rc = check_launch();
   if (rc) return rc;
   const int n_out = g.C * g.cells;
-  reduce_partials_kernel<T><<<(n_out + 255) / 256, 256, 0, s>>>(reinterpret_cast<const A*>(ws), dw, n_out, pl.pix_blocks);
+  reduce_partials_kernel<T><<<(n_out + 31) / 32, 256, 0, s>>>(reinterpret_cast<const A*>(ws), dw, n_out, pl.pix_blocks);
   return check_launch();
 }
 
