@@ -348,6 +348,24 @@ def test_empty_and_degenerate_inputs(ops):
     assert torch.count_nonzero(ops.sample_depthwise(x.detach(), r2, w.detach())) == 0
 
 
+@pytest.mark.parametrize("c,hw,stride", [(32, 56, 1), (32, 56, 2), (96, 14, 1), (192, 14, 2), (32, 28, 1), (16, 7, 1)])
+@pytest.mark.parametrize("fill", [50.0, float("nan")])
+def test_fp16_fast_paths_with_offsets_that_sample_nothing(ops, c, hw, stride, fill):
+    """Every kernel-space offset far outside the bank, or NaN (comparisons are false in the reference too): the tensor-core
+    paths (row-ring kernels, the one-pass band kernel, the separate band kernels) return exact zeros in the value and in
+    every gradient, never NaN."""
+    gen = torch.Generator().manual_seed(13)
+    x = torch.randn(3, c, hw, hw, generator=gen).half().to(DEV).requires_grad_(True)
+    w = (torch.randn(c, 1, 4, 4, generator=gen) * 0.3).half().to(DEV).requires_grad_(True)
+    ho = (hw - 1) // stride + 1
+    r = torch.full((3, 18, ho, ho), fill, device=DEV, dtype=torch.float16).requires_grad_(True)
+    y = ops.sample_depthwise(x, r, w, (3, 3), (stride, stride), (1, 1), (1, 1), 1)
+    assert torch.count_nonzero(y) == 0
+    gx, gr, gw = torch.autograd.grad(y, [x, r, w], torch.randn(y.shape, generator=gen).half().to(DEV))
+    for t in (gx, gr, gw):
+        assert torch.isfinite(t).all() and torch.count_nonzero(t) == 0
+
+
 def _golden_files():
     return sorted(glob.glob(os.path.join(GOLDEN, "*.npz")))
 
