@@ -418,7 +418,7 @@ def run_dcn_layer(args, rank, world, local, dev):
         emit(({
             "metric": "DK+DCN layer fwd+bwd images/sec (C=256, 56x56, fp16)", "value": world * n / (ms_step * 1e-3),
             "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 sums", "data": "synthetic",
             "config": {"workload": "cfg4: DeformableSampleDepthwise C=256 56x56 k3 scope 4x4, batch %d per GPU, offsets "
                                    "~N(0,2^2), kernel offsets ~N(0,0.5^2)" % n,
                        "l2": "a 160 MB buffer is written between timed iterations"},
@@ -888,7 +888,7 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "vs_baseline": None, "dtype": "f16 operands, f32 sums", "data": "synthetic",
             "config": {"workload": "cfg3 layer sweep: DeformKernel2d (C,HW) in (96,112),(144,56),(192,28),(384,14),(960,7)"
                                    " x stride 1,2; scope 4x4, kernel 3, pad 1; offsets ~N(0,1); batch %s" %
                                    (("%d in total, split over the GPUs" % args.batch) if strong else ("%d per GPU" % n)),
