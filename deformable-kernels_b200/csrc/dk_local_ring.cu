@@ -26,6 +26,7 @@
 //
 // Covers fp16, 3x3, pad 1, dilation 1, stride 1 or 2, one offset group, scope 4 x 4, channels a multiple
 // of 16, input rows of 112 or 56 elements (TMA needs 16-byte row pitches); other shapes stay on dk_local_mma.cu.
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -52,7 +53,7 @@ struct RingParams {
   int N, C;
   int Hs, Hd;      // rows of the source and of the destination plane
   int CG;          // channels per block (multiple of 16)
-  int lgR, lgRR;   // log2 of the slots in the source ring and in the per-destination-row rings
+  int R, RR;       // slots in the source ring and in the per-destination-row rings
   int L;           // padded source rows per sample in the block's stream
   int rows_total;  // N * Hd
   int rows_per_block;
@@ -122,9 +123,25 @@ __device__ __forceinline__ void fill_rot_row(__half* slot, const __half* __restr
   const size_t plane = (size_t)rows * Wr;
   const __half* sp = rot + (size_t)n * 18 * plane + (size_t)row * Wr;
   if (RL::kPiece) {
-    for (int i = lane; i < 18 * RL::kPieces; i += 32) {
-      const int pl = i / RL::kPieces, pc = i - pl * RL::kPieces;
-      cp_piece<RL::kPiece ? RL::kPiece : 4>(slot + pl * RL::kWop + 8 + pc * (RL::kPiece / 2), sp + pl * plane + pc * (RL::kPiece / 2));
+    if (RL::kPieces <= 16) {
+      // a lane keeps its piece of the row and walks down the 18 planes, 32 / kPieces of them per step
+      constexpr int PLS = 32 / (RL::kPieces <= 16 ? RL::kPieces : 1);
+      const int sub = lane / RL::kPieces, pc = lane - sub * RL::kPieces;
+      if (sub < PLS) {
+        __half* d = slot + sub * RL::kWop + 8 + pc * (RL::kPiece / 2);
+        const __half* g = sp + sub * plane + pc * (RL::kPiece / 2);
+#pragma unroll
+        for (int pl = 0; pl < 18; pl += PLS) {
+          if (pl + sub < 18) cp_piece<RL::kPiece ? RL::kPiece : 4>(d, g);
+          d += PLS * RL::kWop;
+          g += PLS * plane;
+        }
+      }
+    } else {
+      for (int i = lane; i < 18 * RL::kPieces; i += 32) {
+        const int pl = i / RL::kPieces, pc = i - pl * RL::kPieces;
+        cp_piece<RL::kPiece ? RL::kPiece : 4>(slot + pl * RL::kWop + 8 + pc * (RL::kPiece / 2), sp + pl * plane + pc * (RL::kPiece / 2));
+      }
     }
     cp_async_arrive_noinc(full_bar);
   } else {
@@ -156,9 +173,25 @@ __device__ __forceinline__ void fill_plane_row(__half* slot, const __half* __res
   if (L::kPiece) {
     constexpr int PB = L::kPiece ? L::kPiece : 4;
     constexpr int PIECES = Wd * 2 / PB;
-    for (int i = lane; i < cg * PIECES; i += 32) {
-      const int ch = i / PIECES, pc = i - ch * PIECES;
-      cp_piece<PB>(slot + ch * L::kInner + 8 + pc * (PB / 2), sp + ch * plane + pc * (PB / 2));
+    if (PIECES <= 16) {
+      // a lane keeps its piece of the row and walks down the channels, 32 / PIECES of them per step: two additions per copy
+      constexpr int CH = 32 / (PIECES <= 16 ? PIECES : 1);
+      const int sub = lane / PIECES, pc = lane - sub * PIECES;
+      if (sub < CH) {
+        __half* d = slot + sub * L::kInner + 8 + pc * (PB / 2);
+        const __half* g = sp + sub * plane + pc * (PB / 2);
+#pragma unroll 4
+        for (int ch = sub; ch < cg; ch += CH) {
+          cp_piece<PB>(d, g);
+          d += CH * L::kInner;
+          g += CH * plane;
+        }
+      }
+    } else {
+      for (int i = lane; i < cg * PIECES; i += 32) {
+        const int ch = i / PIECES, pc = i - ch * PIECES;
+        cp_piece<PB>(slot + ch * L::kInner + 8 + pc * (PB / 2), sp + ch * plane + pc * (PB / 2));
+      }
     }
     cp_async_arrive_noinc(full_bar);
   } else {
@@ -314,7 +347,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
   constexpr int INNER = Sh::kInner, WOP = RL::kWop, NB = Sh::kNB, Wd = Sh::kWd;
   static_assert(!TR || S == 1, "the transposed form of this kernel is the stride-1 one");
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  const int R = 1 << p.lgR, RR = 1 << p.lgRR;
+  const int R = p.R, RR = p.RR;
   const int CG = p.CG;
   const int c0 = blockIdx.y * CG;
   const int slot_halves = CG * INNER;
@@ -325,8 +358,8 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(
       (reinterpret_cast<uintptr_t>(bank + (size_t)CG * kBankPitch) + 7) & ~(uintptr_t)7);
   Ring rx, rr;
-  rx.full = smem_u32(bars); rx.empty = rx.full + 8 * R; rx.lg = p.lgR;
-  rr.full = rx.empty + 8 * R; rr.empty = rr.full + 8 * RR; rr.lg = p.lgRR;
+  rx.full = smem_u32(bars); rx.empty = rx.full + 8 * R; rx.set_slots(p.R);
+  rr.full = rx.empty + 8 * R; rr.empty = rr.full + 8 * RR; rr.set_slots(p.RR);
   rx.issued = rr.empty + 8 * RR; rr.issued = rx.issued + 4;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -561,7 +594,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_convT2_kernel(const __grid_const
   using RL = RotLayout<Sh::kWo>;
   constexpr int INNER = Sh::kInner, WOP = RL::kWop, NB = Sh::kNB, Wo = Sh::kWo;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  const int R = 1 << p.lgR;  // both rings have R slots and share their fill numbers
+  const int R = p.R;  // both rings have R slots and share their fill numbers
   const int CG = p.CG;
   const int c0 = blockIdx.y * CG;
   const int slot_halves = CG * INNER;
@@ -572,8 +605,8 @@ __global__ void __launch_bounds__(MAXT, 1) ring_convT2_kernel(const __grid_const
   const unsigned bars_off = (unsigned)((((size_t)R * slot_halves + 64 + (size_t)R * RL::kSlot + (size_t)CG * kBankPitch) * 2 + 7) & ~(size_t)7);
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + bars_off);
   Ring rd, rr;
-  rd.full = smem_u32(bars); rd.empty = rd.full + 8 * R; rd.lg = p.lgR;
-  rr.full = rd.empty + 8 * R; rr.empty = rr.full + 8 * R; rr.lg = p.lgR;
+  rd.full = smem_u32(bars); rd.empty = rd.full + 8 * R; rd.set_slots(p.R);
+  rr.full = rd.empty + 8 * R; rr.empty = rr.full + 8 * R; rr.set_slots(p.R);
   rd.issued = rr.empty + 8 * R; rr.issued = rd.issued + 4;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -896,7 +929,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
   using RL = RotLayout<Sh::kWo>;
   constexpr int IX = Sh::kInnerX, ID = Sh::kInnerD, NB = Sh::kNB, Wo = Sh::kWo;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  const int R = 1 << p.lgR, RR = 1 << p.lgRR;
+  const int R = p.R, RR = p.RR;
   const int CG = p.CG;  // = 16 * (slabs <= NS): every channel, or (gpart != null) group blockIdx.y of them
   const int c0 = blockIdx.y * CG;
   const int xslot = CG * IX, dslot = CG * ID;
@@ -915,9 +948,9 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
   unsigned char* scratch = smem_raw + scratch_off;
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + ((scratch_off + (unsigned)ncw * kGwScratch + 7u) & ~7u));
   Ring rx, rd, rr;
-  rx.full = smem_u32(bars); rx.empty = rx.full + 8 * R; rx.lg = p.lgR;
-  rd.full = rx.empty + 8 * R; rd.empty = rd.full + 8 * RR; rd.lg = p.lgRR;
-  rr.full = rd.empty + 8 * RR; rr.empty = rr.full + 8 * RR; rr.lg = p.lgRR;
+  rx.full = smem_u32(bars); rx.empty = rx.full + 8 * R; rx.set_slots(p.R);
+  rd.full = rx.empty + 8 * R; rd.empty = rd.full + 8 * RR; rd.set_slots(p.RR);
+  rr.full = rd.empty + 8 * RR; rr.empty = rr.full + 8 * RR; rr.set_slots(p.RR);
   rx.issued = rr.empty + 8 * RR; rd.issued = rx.issued + 4; rr.issued = rx.issued + 8;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -1079,7 +1112,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant
   using RL = RotLayout<Sh::kWo>;
   constexpr int IX = Sh::kInnerX, ID = Sh::kInnerD, WOP = RL::kWop, NB = Sh::kNB, Wo = Sh::kWo;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  const int Rx = 1 << p.lgR, Rd = 1 << p.lgRR;
+  const int Rx = p.R, Rd = p.RR;
   const int CG = p.CG;  // every channel
   const int xslot = CG * IX, dslot = CG * ID;
   const int ncw = (blockDim.x >> 5) - 1;
@@ -1097,9 +1130,9 @@ __global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant
   unsigned char* scratch = smem_raw + scratch_off;
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + ((scratch_off + (unsigned)ncw * kBwdScratch + 7u) & ~7u));
   Ring rx, rd, rr;
-  rx.full = smem_u32(bars); rx.empty = rx.full + 8 * Rx; rx.lg = p.lgR;
-  rd.full = rx.empty + 8 * Rx; rd.empty = rd.full + 8 * Rd; rd.lg = p.lgRR;
-  rr.full = rd.empty + 8 * Rd; rr.empty = rr.full + 8 * Rd; rr.lg = p.lgRR;
+  rx.full = smem_u32(bars); rx.empty = rx.full + 8 * Rx; rx.set_slots(p.R);
+  rd.full = rx.empty + 8 * Rx; rd.empty = rd.full + 8 * Rd; rd.set_slots(p.RR);
+  rr.full = rd.empty + 8 * Rd; rr.empty = rr.full + 8 * Rd; rr.set_slots(p.RR);
   rx.issued = rr.empty + 8 * Rd; rd.issued = rx.issued + 4; rr.issued = rx.issued + 8;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -1370,6 +1403,19 @@ bool make_row_map(CUtensorMap* tm, const __half* base, int width, int rows, long
   switch (WIDTH) {                            \
     case 112: { constexpr int W = 112; CALL; } \
     case 56: { constexpr int W = 56; CALL; }   \
+    case 28: { constexpr int W = 28; CALL; }   \
+    default: return DK_ERR_UNSUPPORTED;       \
+  }
+
+// The widths whose stride-2 forward and offsets + bank passes run here.  28-wide planes at stride 2 have 14 x 14 outputs,
+// two items per row of which one is three quarters empty: measured on B200 (C = 192, batch 128) the band kernels win the
+// forward pass 0.027 to 0.034 ms and the offsets + bank pass 0.054 to 0.074; the ring kernel wins grad-input 0.025 to 0.041.
+// At stride 1 the ring kernels win all three (0.052 / 0.054 / 0.123 against 0.059 / 0.057 / 0.145).  14-wide planes were
+// measured too: the band kernels win everything there.
+#define DK_RING_FOR_WIDE(WIDTH, CALL)         \
+  switch (WIDTH) {                            \
+    case 112: { constexpr int W = 112; CALL; } \
+    case 56: { constexpr int W = 56; CALL; }   \
     default: return DK_ERR_UNSUPPORTED;       \
   }
 
@@ -1378,7 +1424,7 @@ bool ring_shape(const Geom& g) {
   if (g.sH != g.sW || (g.sH != 1 && g.sH != 2)) return false;
   if (g.G != 1 || g.scH != 4 || g.scW != 4 || (g.C & 15)) return false;
   if ((long long)g.N * (g.H + 2) > 0x3fffffff) return false;  // stream row indices are 32-bit
-  return g.W == 112 || g.W == 56;
+  return g.W == 112 || g.W == 56 || g.W == 28;
 }
 
 void spread_rows(long long rows, int groups, int* blocks_x, int* rows_per_block) {
@@ -1389,11 +1435,21 @@ void spread_rows(long long rows, int groups, int* blocks_x, int* rows_per_block)
   *blocks_x = (int)((rows + *rows_per_block - 1) / *rows_per_block);
 }
 
-// log2 of the smallest ring (4 .. 32 slots) that holds `rows` rows
-int ring_lg(int rows) {
-  int lg = 2;
-  while (lg < 5 && (1 << lg) < rows) ++lg;
-  return lg;
+// ring depth for `rows` rows in flight: 4 .. 32 slots
+int ring_slots(int rows) { return rows < 4 ? 4 : (rows > 32 ? 32 : rows); }
+// the same, rounded up to a power of two: what a ring is given when shared memory is plentiful
+int ring_slots_generous(int rows) {
+  int r = 4;
+  while (r < 32 && r < rows) r *= 2;
+  return r;
+}
+
+// value of a tuning knob (an integer from the environment when the library is built with -DDK_TUNING), else `dflt`
+int tuning_int(const char* name, int dflt, int lo, int hi) {
+  const char* e = tuning_env(name);
+  if (e == nullptr) return dflt;
+  const int v = atoi(e);
+  return v >= lo && v <= hi ? v : dflt;
 }
 
 constexpr int kConvWarps = 24;  // one producer + 23 consumers of 80 registers (the register file is allocated per 128 threads)
@@ -1401,7 +1457,7 @@ constexpr int kConvMaxT = 768;
 
 struct ConvRingPlan {
   bool ok;
-  int CG, groups, lgR, lgRR, warps, blocks_x, rows_per_block;
+  int CG, groups, R, RR, warps, blocks_x, rows_per_block;
   size_t smem;
 };
 
@@ -1417,23 +1473,28 @@ ConvRingPlan conv_ring_plan(const Geom& g) {
   pl.ok = false;
   const size_t budget = (size_t)device_smem_optin();
   const int rows_busy = (kConvWarps - 1 + Sh::kNB - 1) / Sh::kNB + 1;
-  const int want = ring_lg(rows_busy * S + 3), want_rr = TR ? want : ring_lg(rows_busy + 1);
+  // source rows of the destination rows being worked on, plus one destination row of lookahead for the producer
+  const int want = tuning_int("DK_B200_CONV_R", ring_slots_generous(rows_busy * S + 3), 4, 32);
+  const int want_rr = TR ? want : ring_slots_generous(rows_busy + 1);
   // the fewest channel groups (the hat products of an item are shared by the block's channels) that give the wanted depth
   // or at least eight slots
   for (int groups = 1; groups <= g.C / 16 && !pl.ok; ++groups) {
     if (g.C % (16 * groups)) continue;
     const int cg = g.C / groups;
     if (cg > 256) continue;
-    for (int lgR = want; lgR >= (want < 3 ? want : 3) && !pl.ok; --lgR) {
-      const int lgRR = TR ? lgR : (want_rr < lgR ? want_rr : lgR);
-      const size_t smem = conv_ring_smem(cg, Sh::kInner, RL::kSlot, 1 << lgR, 1 << lgRR);
-      if (smem > budget) continue;
-      pl.ok = true;
-      pl.CG = cg;
-      pl.groups = groups;
-      pl.lgR = lgR;
-      pl.lgRR = lgRR;
-      pl.smem = smem;
+    for (int R = want; R >= (want < 8 ? want : 8) && !pl.ok; --R) {
+      // the offset rows are small: their ring gives way, down to the rows in use, before the source ring does
+      const int rr_hi = TR ? R : (want_rr < R ? want_rr : R), rr_lo = TR ? R : (rows_busy + 1 < rr_hi ? rows_busy + 1 : rr_hi);
+      for (int RR = rr_hi; RR >= rr_lo && !pl.ok; --RR) {
+        const size_t smem = conv_ring_smem(cg, Sh::kInner, RL::kSlot, R, RR);
+        if (smem > budget) continue;
+        pl.ok = true;
+        pl.CG = cg;
+        pl.groups = groups;
+        pl.R = R;
+        pl.RR = RR;
+        pl.smem = smem;
+      }
     }
   }
   if (!pl.ok || pl.groups > 65535) {
@@ -1461,7 +1522,8 @@ int launch_conv_ring(const __half* src, const __half* rot, const __half* w, __ha
   }
   RingParams p;
   p.N = g.N; p.C = g.C; p.Hs = Hs; p.Hd = Hd;
-  p.CG = pl.CG; p.lgR = pl.lgR; p.lgRR = pl.lgRR;
+  p.CG = pl.CG; p.R = pl.R; p.RR = pl.RR;
+  if (tuning_env("DK_B200_PLAN_PRINT")) fprintf(stderr, "conv ring S=%d W=%d TR=%d C=%d: CG=%d R=%d RR=%d smem=%zu\n", S, W, (int)TR, g.C, pl.CG, pl.R, pl.RR, pl.smem);
   p.L = (Hd - 1) * S + 3;
   p.rows_total = g.N * Hd;
   p.rows_per_block = pl.rows_per_block;
@@ -1486,15 +1548,15 @@ int launch_convT2_ring(const __half* dy, const __half* rot, const __half* w, __h
   if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(dx) & 7) || (reinterpret_cast<uintptr_t>(dy) & 15))
     return DK_ERR_UNSUPPORTED;
   const size_t budget = (size_t)device_smem_optin();
-  const int want = ring_lg((19 + Sh::kNB - 1) / Sh::kNB + 1 + 2);
-  int cg = 0, groups = 0, lgR = 0;
+  const int want = tuning_int("DK_B200_CONVT2_R", ring_slots_generous((19 + Sh::kNB - 1) / Sh::kNB + 1 + 2), 4, 32);
+  int cg = 0, groups = 0, R = 0;
   size_t smem = 0;
   for (int gr = 1; gr <= g.C / 16 && !cg; ++gr) {
     if (g.C % (16 * gr) || g.C / gr > 256) continue;
-    for (int lg = want; lg >= (want < 3 ? want : 3) && !cg; --lg) {
-      const size_t need = convT2_ring_smem(g.C / gr, Sh::kInner, RL::kSlot, 1 << lg);
+    for (int r = want; r >= (want < 8 ? want : 8) && !cg; --r) {
+      const size_t need = convT2_ring_smem(g.C / gr, Sh::kInner, RL::kSlot, r);
       if (need > budget) continue;
-      cg = g.C / gr; groups = gr; lgR = lg; smem = need;
+      cg = g.C / gr; groups = gr; R = r; smem = need;
     }
   }
   if (!cg || groups > 65535) return DK_ERR_UNSUPPORTED;
@@ -1506,7 +1568,8 @@ int launch_convT2_ring(const __half* dy, const __half* rot, const __half* w, __h
   }
   RingParams p;
   p.N = g.N; p.C = g.C; p.Hs = g.Ho; p.Hd = g.H;
-  p.CG = cg; p.lgR = lgR; p.lgRR = lgR;
+  p.CG = cg; p.R = R; p.RR = R;
+  if (tuning_env("DK_B200_PLAN_PRINT")) fprintf(stderr, "convT2 ring W=%d C=%d: CG=%d R=%d smem=%zu\n", W, g.C, cg, R, smem);
   p.L = g.Ho + 1;
   p.rows_total = g.N * g.Ho;
   int blocks_x;
@@ -1521,7 +1584,7 @@ int launch_convT2_ring(const __half* dy, const __half* rot, const __half* w, __h
 
 struct GwRingPlan {
   bool ok;
-  int CG, groups, lgR, lgRR, warps, blocks_x, rows_per_block, ns;
+  int CG, groups, R, RR, warps, blocks_x, rows_per_block, ns;
   size_t smem, dw_bytes, ws_bytes;
 };
 
@@ -1543,20 +1606,36 @@ GwRingPlan gw_ring_plan(const Geom& g) {
   pl.groups = groups;
   pl.CG = g.C / groups;
   pl.ns = pl.CG <= 96 ? 6 : 9;
-  pl.warps = pl.ns == 6 ? 16 : 12;
+  // 128 or 168 registers per thread; on 28-wide planes 12 warps measured faster than 16 (0.123 against 0.130 ms, C = 192)
+  pl.warps = tuning_int("DK_B200_GW_WARPS", pl.ns == 6 ? (W == 28 ? 12 : 16) : 12, 2, pl.ns == 6 ? 16 : 12);
   const size_t budget = (size_t)device_smem_optin();
   const int rows_busy = (pl.warps - 1 + Sh::kNB - 1) / Sh::kNB + 1;
-  const int want = ring_lg(rows_busy * S + 3), want_rr = ring_lg(rows_busy + 1);
-  for (int lgR = want; lgR >= 2 && !pl.ok; --lgR)
-    for (int lgRR = want_rr; lgRR >= 1 && !pl.ok; --lgRR) {
-      if (lgRR > lgR) continue;
-      const size_t smem = gw_ring_smem(pl.CG, Sh::kInnerX, Sh::kInnerD, RL::kSlot, 1 << lgR, 1 << lgRR, pl.warps - 1);
+  // x rows of the destination rows being worked on plus one destination row of lookahead; dy / offset rows likewise.
+  // Shared memory rarely holds both, so the pair that serves the largest share of both wants is taken.
+  const int want = ring_slots((rows_busy + 1) * S + 2), want_rr = ring_slots(rows_busy + 1);
+  long long best = -1;
+  for (int R = 4; R <= want; ++R)
+    for (int RR = 2; RR <= want_rr && RR <= R; ++RR) {
+      const size_t smem = gw_ring_smem(pl.CG, Sh::kInnerX, Sh::kInnerD, RL::kSlot, R, RR, pl.warps - 1);
       if (smem > budget) continue;
+      const int served = R * want_rr < RR * want ? R * want_rr : RR * want;  // min(R / want, RR / want_rr), cross-multiplied
+      const long long score = (long long)served * 64 + R + RR;
+      if (score <= best) continue;
+      best = score;
       pl.ok = true;
-      pl.lgR = lgR;
-      pl.lgRR = lgRR;
+      pl.R = R;
+      pl.RR = RR;
       pl.smem = smem;
     }
+  if (pl.ok) {
+    const int R = tuning_int("DK_B200_GW_R", pl.R, 4, 32), RR = tuning_int("DK_B200_GW_RR", pl.RR, 2, 32);
+    const size_t smem = gw_ring_smem(pl.CG, Sh::kInnerX, Sh::kInnerD, RL::kSlot, R, RR, pl.warps - 1);
+    if (smem <= budget) {
+      pl.R = R;
+      pl.RR = RR;
+      pl.smem = smem;
+    }
+  }
   if (!pl.ok || pl.groups > 65535) {
     pl.ok = false;
     return pl;
@@ -1583,7 +1662,8 @@ int launch_gw_ring(const __half* dy, const __half* x, const __half* rot, const _
   if (Sh::kDyTma && !make_row_map(&tmd, dy, Sh::kWo, g.Ho, (long long)g.N * g.C, Sh::kInnerD, pl.CG)) return DK_ERR_UNSUPPORTED;
   RingParams p;
   p.N = g.N; p.C = g.C; p.Hs = g.H; p.Hd = g.Ho;
-  p.CG = pl.CG; p.lgR = pl.lgR; p.lgRR = pl.lgRR;
+  p.CG = pl.CG; p.R = pl.R; p.RR = pl.RR;
+  if (tuning_env("DK_B200_PLAN_PRINT")) fprintf(stderr, "gw ring S=%d W=%d C=%d: CG=%d R=%d RR=%d warps=%d smem=%zu\n", S, W, g.C, pl.CG, pl.R, pl.RR, pl.warps, pl.smem);
   p.L = (g.Ho - 1) * S + 3;
   p.rows_total = g.N * g.Ho;
   p.rows_per_block = pl.rows_per_block;
@@ -1608,7 +1688,7 @@ int launch_gw_ring(const __half* dy, const __half* x, const __half* rot, const _
 
 struct BwdRingPlan {
   bool ok;
-  int lgRx, lgRd, warps, blocks_x, rows_per_block, ns;
+  int Rx, Rd, warps, blocks_x, rows_per_block, ns;
   size_t smem, ws_bytes;
 };
 
@@ -1620,21 +1700,42 @@ BwdRingPlan bwd_ring_plan(const Geom& g) {
   pl.ok = false;
   pl.ns = g.C <= 96 ? 6 : 9;
   if (g.C > 144) return pl;  // the bank-gradient accumulators of all channels live in registers
-  const int max_warps = pl.ns == 6 ? 16 : 12;  // 128 or 168 registers per thread
+  // 128 or 168 registers per thread; of the 12 warps the wide form could run, 11 measured faster on the shape that uses it
+  // by default (C = 144, 56 x 56, stride 2: 0.144 against 0.147 ms)
+  const int max_warps = pl.ns == 6 ? 16 : 11;
   const size_t budget = (size_t)device_smem_optin();
-  // Deeper rings first; four slots is the least that lets the producer run one row ahead.  Each consumer warp owns 3.6 KB
-  // of scratch, so where shared memory is short a few warps fewer are launched rather than falling back to two passes.
-  static const int kDepth[][2] = {{3, 3}, {3, 2}, {2, 2}};
-  for (int i = 0; i < 3 && !pl.ok; ++i)
-    for (int warps = max_warps; warps >= max_warps - (i == 2 ? 8 : 0) && !pl.ok; --warps) {
-      const size_t smem = bwd_ring_smem(g.C, Sh::kInnerX, Sh::kInnerD, RL::kSlot, 1 << kDepth[i][0], 1 << kDepth[i][1], warps - 1);
-      if (smem > budget) continue;
-      pl.ok = true;
-      pl.lgRx = kDepth[i][0];
-      pl.lgRd = kDepth[i][1];
-      pl.warps = warps;
+  // Four slots is the least that lets the producer run one row ahead.  Each consumer warp owns 1.7 KB of scratch, so where
+  // shared memory is short a few warps fewer are launched rather than falling back to two passes.  With the warps settled,
+  // the x ring takes what is left: the source rows of the destination rows being worked on, plus the lookahead.
+  const int forced_warps = tuning_int("DK_B200_BWD_WARPS", 0, 2, max_warps);
+  for (int warps = forced_warps ? forced_warps : max_warps; warps >= (forced_warps ? forced_warps : max_warps - 8) && warps >= 2 && !pl.ok; --warps) {
+    const int rows_busy = (warps - 1 + Sh::kNB - 1) / Sh::kNB + 1;
+    const int want_x = ring_slots((rows_busy + 1) * S + 2), want_d = ring_slots(rows_busy + 2);
+    long long best = -1;
+    for (int Rx = 4; Rx <= want_x; ++Rx)
+      for (int Rd = 4; Rd <= want_d && Rd <= Rx; ++Rd) {
+        const size_t smem = bwd_ring_smem(g.C, Sh::kInnerX, Sh::kInnerD, RL::kSlot, Rx, Rd, warps - 1);
+        if (smem > budget) continue;
+        const int served = Rx * want_d < Rd * want_x ? Rx * want_d : Rd * want_x;
+        const long long score = (long long)served * 64 + Rx + Rd;
+        if (score <= best) continue;
+        best = score;
+        pl.ok = true;
+        pl.Rx = Rx;
+        pl.Rd = Rd;
+        pl.warps = warps;
+        pl.smem = smem;
+      }
+  }
+  if (pl.ok) {
+    const int Rx = tuning_int("DK_B200_BWD_RX", pl.Rx, 4, 32), Rd = tuning_int("DK_B200_BWD_RD", pl.Rd, 4, 32);
+    const size_t smem = bwd_ring_smem(g.C, Sh::kInnerX, Sh::kInnerD, RL::kSlot, Rx, Rd, pl.warps - 1);
+    if (smem <= budget) {
+      pl.Rx = Rx;
+      pl.Rd = Rd;
       pl.smem = smem;
     }
+  }
   if (!pl.ok) return pl;
   spread_rows((long long)g.N * g.Ho, 1, &pl.blocks_x, &pl.rows_per_block);
   pl.ws_bytes = (size_t)pl.blocks_x * g.C * 16 * sizeof(float);
@@ -1659,7 +1760,8 @@ int launch_bwd_ring(const __half* dy, const __half* x, const __half* rot, const 
   }
   RingParams p;
   p.N = g.N; p.C = g.C; p.Hs = g.Ho; p.Hd = g.H;
-  p.CG = g.C; p.lgR = pl.lgRx; p.lgRR = pl.lgRd;
+  p.CG = g.C; p.R = pl.Rx; p.RR = pl.Rd;
+  if (tuning_env("DK_B200_PLAN_PRINT")) fprintf(stderr, "bwd ring S=%d W=%d C=%d: Rx=%d Rd=%d warps=%d smem=%zu\n", S, W, g.C, pl.Rx, pl.Rd, pl.warps, pl.smem);
   p.L = (g.Ho - 1) * S + 3;
   p.rows_total = g.N * g.Ho;
   p.rows_per_block = pl.rows_per_block;
@@ -1695,7 +1797,7 @@ int local_conv_ring(const __half* src, const __half* rot, const __half* w, __hal
   if (!ring_shape(g)) return DK_ERR_UNSUPPORTED;
   if (!transposed) {
     if (g.sH == 1) DK_RING_FOR_WIDTH(g.W, return (launch_conv_ring<1, W, false>(src, rot, w, dst, g, s)))
-    DK_RING_FOR_WIDTH(g.W, return (launch_conv_ring<2, W, false>(src, rot, w, dst, g, s)))
+    DK_RING_FOR_WIDE(g.W, return (launch_conv_ring<2, W, false>(src, rot, w, dst, g, s)))
   }
   if (g.sH == 1) DK_RING_FOR_WIDTH(g.W, return (launch_conv_ring<1, W, true>(src, rot, w, dst, g, s)))
   DK_RING_FOR_WIDTH(g.W, return (launch_convT2_ring<W>(src, rot, w, dst, g, s)))
@@ -1709,7 +1811,7 @@ size_t local_gw_ring_workspace(const Geom& g) {
   pl.ok = false;
   auto plan = [&]() -> int {
     if (g.sH == 1) DK_RING_FOR_WIDTH(g.W, return ((pl = gw_ring_plan<1, W>(g)).ok))
-    DK_RING_FOR_WIDTH(g.W, return ((pl = gw_ring_plan<2, W>(g)).ok))
+    DK_RING_FOR_WIDE(g.W, return ((pl = gw_ring_plan<2, W>(g)).ok))
   };
   plan();
   return pl.ok ? pl.ws_bytes : 0;
@@ -1720,7 +1822,10 @@ size_t local_gw_ring_workspace(const Geom& g) {
 // its grad-input half runs at the register count and warp count the offsets / bank half needs (12-15 warps of 128-168
 // registers instead of 20 of 80), and on the 112-wide layers shared memory allows only 12 warps.  So it is the default
 // only on the narrow stride-2 shape where it won; dk_sample_depthwise_backward_one_pass asks for it explicitly.
-bool local_bwd_ring_preferred(const Geom& g) { return ring_shape(g) && g.W == 56 && g.sH == 2 && g.C <= 144; }
+bool local_bwd_ring_preferred(const Geom& g) {
+  if (tuning_env("DK_B200_NO_ONE_PASS")) return false;
+  return ring_shape(g) && g.W == 56 && g.sH == 2 && g.C <= 144;
+}
 
 bool bwd_ring_shape(const Geom& g) { return ring_shape(g) && (g.W == 112 || g.W == 56); }
 
@@ -1749,7 +1854,7 @@ int local_gw_ring(const __half* dy, const __half* x, const __half* rot, const __
                   void* ws, size_t ws_bytes, cudaStream_t s) {
   if (!ring_shape(g) || drot == nullptr || dw == nullptr) return DK_ERR_UNSUPPORTED;
   if (g.sH == 1) DK_RING_FOR_WIDTH(g.W, return (launch_gw_ring<1, W>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s)))
-  DK_RING_FOR_WIDTH(g.W, return (launch_gw_ring<2, W>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s)))
+  DK_RING_FOR_WIDE(g.W, return (launch_gw_ring<2, W>(dy, x, rot, w, drot, dw, g, ws, ws_bytes, s)))
 }
 
 }  // namespace dk

@@ -80,21 +80,28 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* tm) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(tm) : "memory");
 }
 
-// Bookkeeping of one ring of 2^lg slots.  Fill number k goes to slot k & (2^lg - 1) and is phase k >> lg of
-// that slot's two barriers.  A phase can only be told from its parity, so a consumer may wait on the "full"
-// barrier of fill k only once the slot has been reclaimed for that fill (all users of fill k - 2^lg are
-// done); the producer publishes that in `issued`, a counter in shared memory that only grows.
+// Bookkeeping of one ring of n slots (any n from 2 up, not only powers of two: shared memory decides the depth).
+// Fill number k goes to slot k mod n and is phase k / n ("turn") of that slot's two barriers.  A phase can only
+// be told from its parity, so a consumer may wait on the "full" barrier of fill k only once the slot has been
+// reclaimed for that fill (all users of fill k - n are done); the producer publishes that in `issued`, a counter
+// in shared memory that only grows.
 struct Ring {
   unsigned full, empty;  // shared-memory addresses of the two barrier arrays
   unsigned issued;       // shared-memory address of the counter
-  int lg;
+  int n;                 // slots
+  unsigned magic;        // ceil(2^32 / n): k / n = high word of k * magic as long as k * n < 2^32
 
-  __device__ __forceinline__ int slot(int k) const { return k & ((1 << lg) - 1); }
+  __device__ __forceinline__ void set_slots(int slots) {
+    n = slots;
+    magic = (unsigned)((0x100000000ull + (unsigned)slots - 1) / (unsigned)slots);
+  }
+  __device__ __forceinline__ int turn(int k) const { return (int)__umulhi((unsigned)k, magic); }
+  __device__ __forceinline__ int slot(int k) const { return k - turn(k) * n; }
 
   // producer, whole warp: wait until the slot of fill k may be overwritten, then publish that
   __device__ __forceinline__ bool reclaim(int k, int lane) const {
     bool ok = true;
-    if (k >= (1 << lg)) ok = mbar_wait(empty + 8 * slot(k), ((k >> lg) - 1) & 1);
+    if (k >= n) ok = mbar_wait(empty + 8 * slot(k), (turn(k) - 1) & 1);
     if (lane == 0) asm volatile("st.release.cta.shared::cta.b32 [%0], %1;\n" ::"r"(issued), "r"(k + 1) : "memory");
     return ok;
   }
@@ -108,7 +115,7 @@ struct Ring {
       if (++polls > (kMaxPolls << 4)) return false;
       __nanosleep(64);
     }
-    return mbar_wait(full + 8 * slot(k), (k >> lg) & 1);
+    return mbar_wait(full + 8 * slot(k), turn(k) & 1);
   }
   // consumer, one lane: m users of fill k are done with it
   __device__ __forceinline__ void release(int k, int m) const { mbar_arrive_n(empty + 8 * slot(k), m); }

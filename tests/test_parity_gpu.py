@@ -661,18 +661,21 @@ def test_one_pass_backward_matches_oracle(oracle, c, hw, stride, n):
 
 
 @pytest.mark.parametrize("n,c,h,w,stride", [(1, 16, 1, 56, 1), (1, 16, 2, 56, 2), (2, 48, 7, 112, 2), (3, 32, 5, 112, 1),
-                                            (1, 144, 3, 56, 1), (200, 16, 2, 56, 1), (1, 160, 9, 56, 2)])
+                                            (1, 144, 3, 56, 1), (200, 16, 2, 56, 1), (1, 160, 9, 56, 2),
+                                            (5, 192, 28, 28, 1), (3, 48, 5, 28, 1), (2, 64, 9, 28, 2), (150, 16, 1, 28, 1),
+                                            (2, 208, 28, 28, 2)])
 def test_row_ring_kernels_on_short_and_non_square_planes(ops, oracle, n, c, h, w, stride):
-    """Rows of 112 / 56 elements go to the TMA-fed row-ring kernels whatever the plane's height: planes of one to nine
-    rows (fewer rows than ring slots, blocks that own a single row or none), odd heights at stride 2, more samples than
-    blocks, and more channels than one block keeps bank gradients for."""
+    """Rows of 112 / 56 / 28 elements go to the row-ring kernels whatever the plane's height (28-wide rows are not a
+    multiple of 16 bytes: the producer copies them in 8-byte pieces instead of by TMA; at stride 2 only their grad-input
+    runs there): planes of one to nine rows (fewer rows than ring slots, blocks that own a single row or none), odd
+    heights at stride 2, more samples than blocks, and more channels than one block keeps bank gradients for."""
     from deformable_kernels import _cabi as C
     case = make_case(n, c, h, w, stride=stride, rot_std=1.0, seed=500 + h)
     compare(mine_local(ops, case, torch.float16), oracle_local(oracle, case, torch.float16), torch.float16, "short planes")
     assert C.lib.dk_ring_error_status() == 0
 
 
-@pytest.mark.parametrize("n,c,h,w,stride", [(3, 32, 9, 11, 1), (2, 48, 14, 14, 2), (5, 192, 28, 28, 1), (4, 96, 7, 7, 1),
+@pytest.mark.parametrize("n,c,h,w,stride", [(3, 32, 9, 11, 1), (2, 48, 14, 14, 2), (5, 192, 12, 16, 1), (4, 96, 7, 7, 1),
                                             (6, 96, 7, 7, 2), (3, 160, 13, 20, 2), (130, 384, 14, 14, 1), (2, 16, 1, 1, 1)])
 def test_offsets_and_bank_gradients_in_one_band_pass(oracle, n, c, h, w, stride):
     """The fused backward on planes the row-ring kernels do not take: grad-offsets and grad-bank come from ONE pass over the
