@@ -869,14 +869,17 @@ def main():
                          "kernels; the reference has no CPU path" % (n_img, sec)}
 
     if rank == 0:
-        # launches of this library per step: ring layers (rows of 112 or 56) run forward, grad-input, the fused
-        # offsets + bank pass and the bank reduction (or forward, the one-pass backward and the reduction); planes of
+        # launches of this library per step: ring layers (rows of 112 or 56, rows of 28 at stride 1) run forward,
+        # grad-input, the fused offsets + bank pass (+ the reduction of its partial offset gradients when more than 144
+        # channels are split into groups) and the bank reduction (or forward, the one-pass backward and the reduction); planes of
         # 14 x 14 outputs and below forward, grad-input, the fused band pass, the reduction of its partial offset
         # gradients when the channels are split into groups (more than 96 channels) and the bank reduction; the others
         # forward, grad-input, grad-offsets (+ the reduction of its partial sums when split), grad-bank + reduction
         def layer_launches(t):
-            if t["hw"] in (112, 56):
-                return 3 if (t["hw"] == 56 and t["s"] == 2 and t["c"] <= 144) else 4
+            if t["hw"] in (112, 56) or (t["hw"] == 28 and t["s"] == 1):
+                if t["hw"] == 56 and t["s"] == 2 and t["c"] <= 144:
+                    return 3
+                return 5 if t["c"] > 144 else 4
             if t["ho"] * t["ho"] <= 196:
                 return 5 if t["c"] > 96 else 4
             q = (ctypes.c_longlong * 8)()

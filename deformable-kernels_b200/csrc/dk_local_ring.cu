@@ -54,6 +54,7 @@ struct RingParams {
   int Hs, Hd;      // rows of the source and of the destination plane
   int CG;          // channels per block (multiple of 16)
   int R, RR;       // slots in the source ring and in the per-destination-row rings
+  int NP;          // producer warps (more than one only where no ring of the kernel is filled by TMA)
   int L;           // padded source rows per sample in the block's stream
   int rows_total;  // N * Hd
   int rows_per_block;
@@ -113,12 +114,12 @@ __device__ __forceinline__ void cp_piece(void* d, const void* s) {
   else cp_async4(d, s);
 }
 
-// producer warp: row `row` of the 18 offset planes of sample n -> ring slot.  The slot's "full" barrier (count 32) gets one
-// arrival per lane: when that lane's cp.async copies have landed, or, for odd row widths that only allow element-wise
-// copies, after the lane's plain stores.
+// producer warp pw of np: row `row` of the 18 offset planes of sample n -> ring slot.  The slot's "full" barrier (count
+// 32 * np) gets one arrival per lane: when that lane's cp.async copies have landed, or, for odd row widths that only allow
+// element-wise copies, after the lane's plain stores.
 template <int Wr>
 __device__ __forceinline__ void fill_rot_row(__half* slot, const __half* __restrict__ rot, int n, int rows, int row, int lane,
-                                             unsigned full_bar) {
+                                             unsigned full_bar, int pw = 0, int np = 1) {
   using RL = RotLayout<Wr>;
   const size_t plane = (size_t)rows * Wr;
   const __half* sp = rot + (size_t)n * 18 * plane + (size_t)row * Wr;
@@ -128,24 +129,24 @@ __device__ __forceinline__ void fill_rot_row(__half* slot, const __half* __restr
       constexpr int PLS = 32 / (RL::kPieces <= 16 ? RL::kPieces : 1);
       const int sub = lane / RL::kPieces, pc = lane - sub * RL::kPieces;
       if (sub < PLS) {
-        __half* d = slot + sub * RL::kWop + 8 + pc * (RL::kPiece / 2);
-        const __half* g = sp + sub * plane + pc * (RL::kPiece / 2);
-#pragma unroll
-        for (int pl = 0; pl < 18; pl += PLS) {
-          if (pl + sub < 18) cp_piece<RL::kPiece ? RL::kPiece : 4>(d, g);
-          d += PLS * RL::kWop;
-          g += PLS * plane;
+        const int first = PLS * pw + sub, step = PLS * np;
+        __half* d = slot + first * RL::kWop + 8 + pc * (RL::kPiece / 2);
+        const __half* g = sp + first * plane + pc * (RL::kPiece / 2);
+        for (int pl = first; pl < 18; pl += step) {
+          cp_piece<RL::kPiece ? RL::kPiece : 4>(d, g);
+          d += step * RL::kWop;
+          g += step * plane;
         }
       }
     } else {
-      for (int i = lane; i < 18 * RL::kPieces; i += 32) {
+      for (int i = lane + 32 * pw; i < 18 * RL::kPieces; i += 32 * np) {
         const int pl = i / RL::kPieces, pc = i - pl * RL::kPieces;
         cp_piece<RL::kPiece ? RL::kPiece : 4>(slot + pl * RL::kWop + 8 + pc * (RL::kPiece / 2), sp + pl * plane + pc * (RL::kPiece / 2));
       }
     }
     cp_async_arrive_noinc(full_bar);
   } else {
-    for (int base = 0; base < 18 * Wr; base += 256) {  // eight independent loads per lane in flight
+    for (int base = 256 * pw; base < 18 * Wr; base += 256 * np) {  // eight independent loads per lane in flight
       __half v[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
@@ -162,11 +163,11 @@ __device__ __forceinline__ void fill_rot_row(__half* slot, const __half* __restr
   }
 }
 
-// producer warp: row `row` of channels c0 .. c0+cg-1 of sample n of a [N][C][rows][Wd] tensor -> ring slot, for rows TMA
-// cannot fetch (cp.async pieces of 16, 8 or 4 bytes, element-wise for odd widths); full barrier count 32 as above
+// producer warp pw of np: row `row` of channels c0 .. c0+cg-1 of sample n of a [N][C][rows][Wd] tensor -> ring slot, for rows
+// TMA cannot fetch (cp.async pieces of 16, 8 or 4 bytes, element-wise for odd widths); full barrier count 32 * np as above
 template <int Wd>
 __device__ __forceinline__ void fill_plane_row(__half* slot, const __half* __restrict__ src, int n, int C, int c0, int cg, int rows,
-                                               int row, int lane, unsigned full_bar) {
+                                               int row, int lane, unsigned full_bar, int pw = 0, int np = 1) {
   using L = RowLayout<Wd>;
   const size_t plane = (size_t)rows * Wd;
   const __half* sp = src + ((size_t)n * C + c0) * plane + (size_t)row * Wd;
@@ -178,24 +179,25 @@ __device__ __forceinline__ void fill_plane_row(__half* slot, const __half* __res
       constexpr int CH = 32 / (PIECES <= 16 ? PIECES : 1);
       const int sub = lane / PIECES, pc = lane - sub * PIECES;
       if (sub < CH) {
-        __half* d = slot + sub * L::kInner + 8 + pc * (PB / 2);
-        const __half* g = sp + sub * plane + pc * (PB / 2);
+        const int first = CH * pw + sub, step = CH * np;
+        __half* d = slot + first * L::kInner + 8 + pc * (PB / 2);
+        const __half* g = sp + first * plane + pc * (PB / 2);
 #pragma unroll 4
-        for (int ch = sub; ch < cg; ch += CH) {
+        for (int ch = first; ch < cg; ch += step) {
           cp_piece<PB>(d, g);
-          d += CH * L::kInner;
-          g += CH * plane;
+          d += step * L::kInner;
+          g += step * plane;
         }
       }
     } else {
-      for (int i = lane; i < cg * PIECES; i += 32) {
+      for (int i = lane + 32 * pw; i < cg * PIECES; i += 32 * np) {
         const int ch = i / PIECES, pc = i - ch * PIECES;
         cp_piece<PB>(slot + ch * L::kInner + 8 + pc * (PB / 2), sp + ch * plane + pc * (PB / 2));
       }
     }
     cp_async_arrive_noinc(full_bar);
   } else {
-    for (int base = 0; base < cg * Wd; base += 256) {  // eight independent loads per lane in flight
+    for (int base = 256 * pw; base < cg * Wd; base += 256 * np) {  // eight independent loads per lane in flight
       __half v[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
@@ -212,22 +214,23 @@ __device__ __forceinline__ void fill_plane_row(__half* slot, const __half* __res
   }
 }
 
-// producer warp: one source row of the block's channels into its ring slot, whatever the row width allows.  Rows outside
-// the plane (row < 0 or >= rows) become zero rows: the TMA unit fills them by itself, the other paths store zeros.
-// The slot's full barrier counts 1 (TMA: the expect_tx arrival) or 32 (one arrival per lane).
+// producer warp pw of np: one source row of the block's channels into its ring slot, whatever the row width allows.  Rows
+// outside the plane (row < 0 or >= rows) become zero rows: the TMA unit fills them by itself, the other paths store zeros.
+// The slot's full barrier counts 1 (TMA: the expect_tx arrival of the first producer warp; the others have nothing to do) or
+// 32 * np (one arrival per lane).
 template <int Wd>
 __device__ __forceinline__ void fill_src_row(__half* slot, unsigned slot_u32, unsigned slot_bytes, const CUtensorMap* tm,
                                              const __half* __restrict__ src, int n, int C, int c0, int cg, int rows, int row, int lane,
-                                             unsigned full_bar) {
+                                             unsigned full_bar, int pw = 0, int np = 1) {
   if (RowLayout<Wd>::kTma) {
-    if (lane == 0) {
+    if (lane == 0 && pw == 0) {
       mbar_arrive_expect_tx(full_bar, slot_bytes);
       tma_load_3d(slot_u32, tm, -8, row, n * C + c0, full_bar);
     }
   } else if (row >= 0 && row < rows) {
-    fill_plane_row<Wd>(slot, src, n, C, c0, cg, rows, row, lane, full_bar);
+    fill_plane_row<Wd>(slot, src, n, C, c0, cg, rows, row, lane, full_bar, pw, np);
   } else {
-    for (int i = lane; i < (int)(slot_bytes >> 4); i += 32) reinterpret_cast<uint4*>(slot)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = lane + 32 * pw; i < (int)(slot_bytes >> 4); i += 32 * np) reinterpret_cast<uint4*>(slot)[i] = make_uint4(0, 0, 0, 0);
     mbar_arrive(full_bar);
   }
 }
@@ -363,16 +366,16 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
   rx.issued = rr.empty + 8 * RR; rr.issued = rx.issued + 4;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int ncw = (blockDim.x >> 5) - 1;
+  const int np = p.NP, ncw = (blockDim.x >> 5) - np;
 
   // ---- set-up: barriers, zeroed rings (pads and the tail must read as zero from the start), bank copy
   if (threadIdx.x == 0) {
     for (int i = 0; i < R; ++i) {
-      mbar_init(rx.full + 8 * i, Sh::kTma ? 1 : 32);
+      mbar_init(rx.full + 8 * i, Sh::kTma ? 1 : 32 * np);
       mbar_init(rx.empty + 8 * i, (S == 1 ? 3 : 2) * NB);
     }
     for (int i = 0; i < RR; ++i) {
-      mbar_init(rr.full + 8 * i, 32);
+      mbar_init(rr.full + 8 * i, 32 * np);
       mbar_init(rr.empty + 8 * i, (TR ? 3 : 1) * NB);
     }
     int* cnt = reinterpret_cast<int*>(bars + 2 * R + 2 * RR);
@@ -398,8 +401,9 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
   const int n_first = g0 / Hd;
   const int T0 = n_first * L + (g0 - n_first * Hd) * S;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ producer
+  if (warp < np) {
+    // ------------------------------------------------------------ producers
+    const int pw = warp;
     if (lane == 0 && Sh::kTma) prefetch_tensormap(&tm_src);
     const unsigned slot_bytes = (unsigned)slot_halves * 2;
     const unsigned xring_u32 = smem_u32(xring);
@@ -409,23 +413,23 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
       const int n = g / Hd, d = g - n * Hd;
       if (!TR) {
         const int kr = g - g0;
-        ok = rr.reclaim(kr, lane);
-        if (ok) fill_rot_row<Sh::kWr>(rring + (size_t)rr.slot(kr) * RL::kSlot, rot, n, Hd, d, lane, rr.full + 8 * rr.slot(kr));
+        ok = rr.reclaim(kr, lane, pw == 0);
+        if (ok) fill_rot_row<Sh::kWr>(rring + (size_t)rr.slot(kr) * RL::kSlot, rot, n, Hd, d, lane, rr.full + 8 * rr.slot(kr), pw, np);
       }
       const int Tend = n * L + d * S + 2;
       for (; T <= Tend && ok; ++T) {
         const int k = T - T0;
         const int r = T - n * L - 1;  // source row; -1 and >= Hs arrive as zero rows
         if (TR) {
-          ok = rr.reclaim(k, lane);
+          ok = rr.reclaim(k, lane, pw == 0);
           if (ok)
             fill_rot_row<Sh::kWr>(rring + (size_t)rr.slot(k) * RL::kSlot, rot, n, p.Hs, min(max(r, 0), p.Hs - 1), lane,
-                                  rr.full + 8 * rr.slot(k));
+                                  rr.full + 8 * rr.slot(k), pw, np);
         }
-        ok = ok && rx.reclaim(k, lane);
+        ok = ok && rx.reclaim(k, lane, pw == 0);
         if (ok)
           fill_src_row<W>(xring + (size_t)rx.slot(k) * slot_halves, xring_u32 + rx.slot(k) * slot_bytes, slot_bytes, &tm_src, src, n,
-                          p.C, c0, CG, p.Hs, r, lane, rx.full + 8 * rx.slot(k));
+                          p.C, c0, CG, p.Hs, r, lane, rx.full + 8 * rx.slot(k), pw, np);
         __syncwarp();
       }
     }
@@ -435,7 +439,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_conv_kernel(const __grid_constan
   }
 
   // -------------------------------------------------------------- consumers
-  const int cw = warp - 1;
+  const int cw = warp - np;
   const int gq = lane >> 2, q = lane & 3;
   const LaneCells lc = lane_cells_of(p.scW, p.cells, q);
   const float uh0 = (float)(p.scH - 3) * 0.5f, uw0 = (float)(p.scW - 3) * 0.5f;
@@ -610,13 +614,13 @@ __global__ void __launch_bounds__(MAXT, 1) ring_convT2_kernel(const __grid_const
   rd.issued = rr.empty + 8 * R; rr.issued = rd.issued + 4;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int ncw = (blockDim.x >> 5) - 1;
+  const int np = p.NP, ncw = (blockDim.x >> 5) - np;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < R; ++i) {
-      mbar_init(rd.full + 8 * i, Sh::kTma ? 1 : 32);
+      mbar_init(rd.full + 8 * i, Sh::kTma ? 1 : 32 * np);
       mbar_init(rd.empty + 8 * i, 2 * NB);
-      mbar_init(rr.full + 8 * i, 32);
+      mbar_init(rr.full + 8 * i, 32 * np);
       mbar_init(rr.empty + 8 * i, 2 * NB);
     }
     int* cnt = reinterpret_cast<int*>(bars + 4 * R);
@@ -642,8 +646,9 @@ __global__ void __launch_bounds__(MAXT, 1) ring_convT2_kernel(const __grid_const
   const int n_first = g0 / Ho;
   const int T0 = n_first * L + (g0 - n_first * Ho);
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ producer
+  if (warp < np) {
+    // ------------------------------------------------------------ producers
+    const int pw = warp;
     if (lane == 0 && Sh::kTma) prefetch_tensormap(&tm_dy);
     const unsigned slot_bytes = (unsigned)slot_halves * 2;
     const unsigned dring_u32 = smem_u32(dring);
@@ -655,12 +660,12 @@ __global__ void __launch_bounds__(MAXT, 1) ring_convT2_kernel(const __grid_const
       for (; T <= Tend && ok; ++T) {
         const int k = T - T0;
         const int r = T - n * L;  // row of dy and of the offsets; r = Ho is the zero row below the plane
-        ok = rr.reclaim(k, lane);
-        if (ok) fill_rot_row<Wo>(rring + (size_t)rr.slot(k) * RL::kSlot, rot, n, Ho, min(r, Ho - 1), lane, rr.full + 8 * rr.slot(k));
-        ok = ok && rd.reclaim(k, lane);
+        ok = rr.reclaim(k, lane, pw == 0);
+        if (ok) fill_rot_row<Wo>(rring + (size_t)rr.slot(k) * RL::kSlot, rot, n, Ho, min(r, Ho - 1), lane, rr.full + 8 * rr.slot(k), pw, np);
+        ok = ok && rd.reclaim(k, lane, pw == 0);
         if (ok)
           fill_src_row<Wo>(dring + (size_t)rd.slot(k) * slot_halves, dring_u32 + rd.slot(k) * slot_bytes, slot_bytes, &tm_dy, dy, n, p.C,
-                           c0, CG, Ho, r, lane, rd.full + 8 * rd.slot(k));
+                           c0, CG, Ho, r, lane, rd.full + 8 * rd.slot(k), pw, np);
         __syncwarp();
       }
     }
@@ -670,7 +675,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_convT2_kernel(const __grid_const
   }
 
   // -------------------------------------------------------------- consumers
-  const int cw = warp - 1;
+  const int cw = warp - np;
   const int gq = lane >> 2, q = lane & 3;
   const LaneCells lc = lane_cells_of(p.scW, p.cells, q);
   const float uh0 = (float)(p.scH - 3) * 0.5f, uw0 = (float)(p.scW - 3) * 0.5f;
@@ -933,7 +938,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
   const int CG = p.CG;  // = 16 * (slabs <= NS): every channel, or (gpart != null) group blockIdx.y of them
   const int c0 = blockIdx.y * CG;
   const int xslot = CG * IX, dslot = CG * ID;
-  const int ncw = (blockDim.x >> 5) - 1;
+  const int np = p.NP, ncw = (blockDim.x >> 5) - np;
   const int pitchT = CG + 8;
 
   __half* xring = reinterpret_cast<__half*>(smem_raw);
@@ -957,13 +962,13 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < R; ++i) {
-      mbar_init(rx.full + 8 * i, RowLayout<W>::kTma ? 1 : 32);
+      mbar_init(rx.full + 8 * i, RowLayout<W>::kTma ? 1 : 32 * np);
       mbar_init(rx.empty + 8 * i, (S == 1 ? 3 : 2) * NB);
     }
     for (int i = 0; i < RR; ++i) {
-      mbar_init(rd.full + 8 * i, Sh::kDyTma ? 1 : 32);
+      mbar_init(rd.full + 8 * i, Sh::kDyTma ? 1 : 32 * np);
       mbar_init(rd.empty + 8 * i, NB);
-      mbar_init(rr.full + 8 * i, 32);
+      mbar_init(rr.full + 8 * i, 32 * np);
       mbar_init(rr.empty + 8 * i, NB);
     }
     int* cnt = reinterpret_cast<int*>(bars + 2 * R + 4 * RR);
@@ -990,8 +995,9 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
   const int n_first = g0 < g1 ? g0 / Ho : 0;
   const int T0 = n_first * L + (g0 - n_first * Ho) * S;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ producer
+  if (warp < np) {
+    // ------------------------------------------------------------ producers
+    const int pw = warp;
     if (g0 >= g1) return;
     if (lane == 0) {
       if (RowLayout<W>::kTma) prefetch_tensormap(&tm_x);
@@ -1004,19 +1010,19 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
     for (int g = g0; g < g1 && ok; ++g) {
       const int n = g / Ho, oh = g - n * Ho;
       const int kr = g - g0;
-      ok = rr.reclaim(kr, lane);
-      if (ok) fill_rot_row<Wo>(rring + (size_t)rr.slot(kr) * RL::kSlot, rot, n, Ho, oh, lane, rr.full + 8 * rr.slot(kr));
-      ok = ok && rd.reclaim(kr, lane);
+      ok = rr.reclaim(kr, lane, pw == 0);
+      if (ok) fill_rot_row<Wo>(rring + (size_t)rr.slot(kr) * RL::kSlot, rot, n, Ho, oh, lane, rr.full + 8 * rr.slot(kr), pw, np);
+      ok = ok && rd.reclaim(kr, lane, pw == 0);
       if (ok)
         fill_src_row<Wo>(dring + (size_t)rd.slot(kr) * dslot, dring_u32 + rd.slot(kr) * dbytes, dbytes, &tm_dy, dy, n, p.C, c0, CG, Ho,
-                         oh, lane, rd.full + 8 * rd.slot(kr));
+                         oh, lane, rd.full + 8 * rd.slot(kr), pw, np);
       const int Tend = n * L + oh * S + 2;
       for (; T <= Tend && ok; ++T) {
         const int k = T - T0;
-        ok = rx.reclaim(k, lane);
+        ok = rx.reclaim(k, lane, pw == 0);
         if (ok)
           fill_src_row<W>(xring + (size_t)rx.slot(k) * xslot, xring_u32 + rx.slot(k) * xbytes, xbytes, &tm_x, x, n, p.C, c0, CG, p.Hs,
-                          T - n * L - 1, lane, rx.full + 8 * rx.slot(k));
+                          T - n * L - 1, lane, rx.full + 8 * rx.slot(k), pw, np);
         __syncwarp();
       }
     }
@@ -1026,7 +1032,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_gw_kernel(const __grid_constant_
   }
 
   // -------------------------------------------------------------- consumers
-  const int cw = warp - 1;
+  const int cw = warp - np;
   const int gq = lane >> 2, q = lane & 3;
   const LaneCells lc = lane_cells_of(p.scW, p.cells, q);
   const float uh0 = (float)(p.scH - 3) * 0.5f, uw0 = (float)(p.scW - 3) * 0.5f;
@@ -1115,7 +1121,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant
   const int Rx = p.R, Rd = p.RR;
   const int CG = p.CG;  // every channel
   const int xslot = CG * IX, dslot = CG * ID;
-  const int ncw = (blockDim.x >> 5) - 1;
+  const int np = p.NP, ncw = (blockDim.x >> 5) - np;
   const int pitchT = CG + 8;
 
   __half* xring = reinterpret_cast<__half*>(smem_raw);
@@ -1143,9 +1149,9 @@ __global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant
       mbar_init(rx.empty + 8 * i, (S == 1 ? 3 : 2) * NB);
     }
     for (int i = 0; i < Rd; ++i) {
-      mbar_init(rd.full + 8 * i, Sh::kDyTma ? 1 : 32);
+      mbar_init(rd.full + 8 * i, Sh::kDyTma ? 1 : 32 * np);
       mbar_init(rd.empty + 8 * i, Sh::kUsersD * NB);
-      mbar_init(rr.full + 8 * i, 32);
+      mbar_init(rr.full + 8 * i, 32 * np);
       mbar_init(rr.empty + 8 * i, Sh::kUsersD * NB);
     }
     int* cnt = reinterpret_cast<int*>(bars + 2 * Rx + 4 * Rd);
@@ -1176,8 +1182,9 @@ __global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant
   const int Tx0 = n_first * Lx + d_first * S;
   const int Td0 = n_first * Ld + d_first;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ producer
+  if (warp < np) {
+    // ------------------------------------------------------------ producers
+    const int pw = warp;
     if (g0 >= g1) return;
     if (lane == 0) {
       prefetch_tensormap(&tm_x);
@@ -1193,21 +1200,21 @@ __global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant
       for (; Td <= Td_end && ok; ++Td) {
         const int k = Td - Td0;
         const int r = Td - n * Ld - (S == 1 ? 1 : 0);  // row of dy / offsets; -1 and Ho are zero rows
-        ok = rr.reclaim(k, lane);
-        if (ok) fill_rot_row<Wo>(rring + (size_t)rr.slot(k) * RL::kSlot, rot, n, Ho, min(max(r, 0), Ho - 1), lane, rr.full + 8 * rr.slot(k));
-        ok = ok && rd.reclaim(k, lane);
+        ok = rr.reclaim(k, lane, pw == 0);
+        if (ok) fill_rot_row<Wo>(rring + (size_t)rr.slot(k) * RL::kSlot, rot, n, Ho, min(max(r, 0), Ho - 1), lane, rr.full + 8 * rr.slot(k), pw, np);
+        ok = ok && rd.reclaim(k, lane, pw == 0);
         if (ok) {
           if (Sh::kDyTma) {
-            if (lane == 0) {
+            if (lane == 0 && pw == 0) {
               mbar_arrive_expect_tx(rd.full + 8 * rd.slot(k), dbytes);
               tma_load_3d(dring_u32 + rd.slot(k) * dbytes, &tm_dy, -8, r, n * p.C, rd.full + 8 * rd.slot(k));
             }
           } else {
             __half* slot = dring + (size_t)rd.slot(k) * dslot;
             if (r >= 0 && r < Ho) {
-              fill_plane_row<Wo>(slot, dy, n, p.C, 0, CG, Ho, r, lane, rd.full + 8 * rd.slot(k));
-            } else {  // a zero row: plain stores, then the same 32 arrivals
-              for (int i = lane; i < dslot / 8; i += 32) reinterpret_cast<uint4*>(slot)[i] = make_uint4(0, 0, 0, 0);
+              fill_plane_row<Wo>(slot, dy, n, p.C, 0, CG, Ho, r, lane, rd.full + 8 * rd.slot(k), pw, np);
+            } else {  // a zero row: plain stores, then the same arrivals
+              for (int i = lane + 32 * pw; i < dslot / 8; i += 32 * np) reinterpret_cast<uint4*>(slot)[i] = make_uint4(0, 0, 0, 0);
               mbar_arrive(rd.full + 8 * rd.slot(k));
             }
           }
@@ -1217,8 +1224,8 @@ __global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant
       const int Tx_end = n * Lx + j * S + 2;
       for (; Tx <= Tx_end && ok; ++Tx) {
         const int k = Tx - Tx0;
-        ok = rx.reclaim(k, lane);
-        if (lane == 0 && ok) {
+        ok = rx.reclaim(k, lane, pw == 0);
+        if (lane == 0 && ok && pw == 0) {
           mbar_arrive_expect_tx(rx.full + 8 * rx.slot(k), xbytes);
           tma_load_3d(xring_u32 + rx.slot(k) * xbytes, &tm_x, -8, Tx - n * Lx - 1, n * p.C, rx.full + 8 * rx.slot(k));
         }
@@ -1231,7 +1238,7 @@ __global__ void __launch_bounds__(MAXT, 1) ring_bwd_kernel(const __grid_constant
   }
 
   // -------------------------------------------------------------- consumers
-  const int cw = warp - 1;
+  const int cw = warp - np;
   const int gq = lane >> 2, q = lane & 3;
   const LaneCells lc = lane_cells_of(p.scW, p.cells, q);
   const float uh0 = (float)(p.scH - 3) * 0.5f, uw0 = (float)(p.scW - 3) * 0.5f;
@@ -1452,12 +1459,12 @@ int tuning_int(const char* name, int dflt, int lo, int hi) {
   return v >= lo && v <= hi ? v : dflt;
 }
 
-constexpr int kConvWarps = 24;  // one producer + 23 consumers of 80 registers (the register file is allocated per 128 threads)
+constexpr int kConvWarps = 24;  // producer(s) + consumers of 80 registers (the register file is allocated per 128 threads)
 constexpr int kConvMaxT = 768;
 
 struct ConvRingPlan {
   bool ok;
-  int CG, groups, R, RR, warps, blocks_x, rows_per_block;
+  int CG, groups, R, RR, warps, np, blocks_x, rows_per_block;
   size_t smem;
 };
 
@@ -1472,7 +1479,11 @@ ConvRingPlan conv_ring_plan(const Geom& g) {
   ConvRingPlan pl;
   pl.ok = false;
   const size_t budget = (size_t)device_smem_optin();
-  const int rows_busy = (kConvWarps - 1 + Sh::kNB - 1) / Sh::kNB + 1;
+  // Rows TMA cannot fetch arrive in cp.async pieces of 8 or 4 bytes (1344 of them for a row of 192 channels x 28 elements);
+  // four warps share them there.  Measured on B200, C = 192, 28 x 28, batch 128, 1 / 2 / 4 producer warps of 24: forward
+  // 0.056 / 0.052 / 0.050 ms, grad-input 0.056 / 0.050 / 0.049; the stride-2 grad-input kernel 0.027 / 0.024 / 0.023.
+  pl.np = Sh::kTma ? 1 : tuning_int("DK_B200_RING_NP", 4, 1, 8);
+  const int rows_busy = (kConvWarps - pl.np + Sh::kNB - 1) / Sh::kNB + 1;
   // source rows of the destination rows being worked on, plus one destination row of lookahead for the producer
   const int want = tuning_int("DK_B200_CONV_R", ring_slots_generous(rows_busy * S + 3), 4, 32);
   const int want_rr = TR ? want : ring_slots_generous(rows_busy + 1);
@@ -1522,14 +1533,14 @@ int launch_conv_ring(const __half* src, const __half* rot, const __half* w, __ha
   }
   RingParams p;
   p.N = g.N; p.C = g.C; p.Hs = Hs; p.Hd = Hd;
-  p.CG = pl.CG; p.R = pl.R; p.RR = pl.RR;
+  p.CG = pl.CG; p.R = pl.R; p.RR = pl.RR; p.NP = pl.np;
   if (tuning_env("DK_B200_PLAN_PRINT")) fprintf(stderr, "conv ring S=%d W=%d TR=%d C=%d: CG=%d R=%d RR=%d smem=%zu\n", S, W, (int)TR, g.C, pl.CG, pl.R, pl.RR, pl.smem);
   p.L = (Hd - 1) * S + 3;
   p.rows_total = g.N * Hd;
   p.rows_per_block = pl.rows_per_block;
   p.scH = g.scH; p.scW = g.scW; p.cells = g.cells;
   int warps = pl.warps;
-  if (const char* e = tuning_env("DK_B200_RING_WARPS")) warps = atoi(e) > 1 && atoi(e) <= kConvWarps ? atoi(e) : warps;
+  if (const char* e = tuning_env("DK_B200_RING_WARPS")) warps = atoi(e) > pl.np && atoi(e) <= kConvWarps ? atoi(e) : warps;
   auto kern = ring_conv_kernel<S, W, TR, true, kConvMaxT>;
   int rc = enable_smem(kern, pl.smem);
   if (rc) return rc;
@@ -1569,6 +1580,7 @@ int launch_convT2_ring(const __half* dy, const __half* rot, const __half* w, __h
   RingParams p;
   p.N = g.N; p.C = g.C; p.Hs = g.Ho; p.Hd = g.H;
   p.CG = cg; p.R = R; p.RR = R;
+  p.NP = Sh::kTma ? 1 : tuning_int("DK_B200_RING_NP", 4, 1, 8);
   if (tuning_env("DK_B200_PLAN_PRINT")) fprintf(stderr, "convT2 ring W=%d C=%d: CG=%d R=%d smem=%zu\n", W, g.C, cg, R, smem);
   p.L = g.Ho + 1;
   p.rows_total = g.N * g.Ho;
@@ -1584,7 +1596,7 @@ int launch_convT2_ring(const __half* dy, const __half* rot, const __half* w, __h
 
 struct GwRingPlan {
   bool ok;
-  int CG, groups, R, RR, warps, blocks_x, rows_per_block, ns;
+  int CG, groups, R, RR, warps, np, blocks_x, rows_per_block, ns;
   size_t smem, dw_bytes, ws_bytes;
 };
 
@@ -1606,17 +1618,19 @@ GwRingPlan gw_ring_plan(const Geom& g) {
   pl.groups = groups;
   pl.CG = g.C / groups;
   pl.ns = pl.CG <= 96 ? 6 : 9;
-  // 128 or 168 registers per thread; on 28-wide planes 12 warps measured faster than 16 (0.123 against 0.130 ms, C = 192)
-  pl.warps = tuning_int("DK_B200_GW_WARPS", pl.ns == 6 ? (W == 28 ? 12 : 16) : 12, 2, pl.ns == 6 ? 16 : 12);
+  // 128 or 168 registers per thread allow 16 or 12 warps.  On 28-wide planes 12 warps measured faster than 16 (0.123 against
+  // 0.130 ms, C = 192), and more producer warps changed nothing here (this pass is not short of rows), so there is one.
+  pl.np = tuning_int("DK_B200_GW_NP", 1, 1, 8);
+  pl.warps = tuning_int("DK_B200_GW_WARPS", pl.ns == 6 ? (W == 28 ? 12 : 16) : 12, pl.np + 1, pl.ns == 6 ? 16 : 12);
   const size_t budget = (size_t)device_smem_optin();
-  const int rows_busy = (pl.warps - 1 + Sh::kNB - 1) / Sh::kNB + 1;
+  const int rows_busy = (pl.warps - pl.np + Sh::kNB - 1) / Sh::kNB + 1;
   // x rows of the destination rows being worked on plus one destination row of lookahead; dy / offset rows likewise.
   // Shared memory rarely holds both, so the pair that serves the largest share of both wants is taken.
   const int want = ring_slots((rows_busy + 1) * S + 2), want_rr = ring_slots(rows_busy + 1);
   long long best = -1;
   for (int R = 4; R <= want; ++R)
     for (int RR = 2; RR <= want_rr && RR <= R; ++RR) {
-      const size_t smem = gw_ring_smem(pl.CG, Sh::kInnerX, Sh::kInnerD, RL::kSlot, R, RR, pl.warps - 1);
+      const size_t smem = gw_ring_smem(pl.CG, Sh::kInnerX, Sh::kInnerD, RL::kSlot, R, RR, pl.warps - pl.np);
       if (smem > budget) continue;
       const int served = R * want_rr < RR * want ? R * want_rr : RR * want;  // min(R / want, RR / want_rr), cross-multiplied
       const long long score = (long long)served * 64 + R + RR;
@@ -1629,7 +1643,7 @@ GwRingPlan gw_ring_plan(const Geom& g) {
     }
   if (pl.ok) {
     const int R = tuning_int("DK_B200_GW_R", pl.R, 4, 32), RR = tuning_int("DK_B200_GW_RR", pl.RR, 2, 32);
-    const size_t smem = gw_ring_smem(pl.CG, Sh::kInnerX, Sh::kInnerD, RL::kSlot, R, RR, pl.warps - 1);
+    const size_t smem = gw_ring_smem(pl.CG, Sh::kInnerX, Sh::kInnerD, RL::kSlot, R, RR, pl.warps - pl.np);
     if (smem <= budget) {
       pl.R = R;
       pl.RR = RR;
@@ -1662,7 +1676,7 @@ int launch_gw_ring(const __half* dy, const __half* x, const __half* rot, const _
   if (Sh::kDyTma && !make_row_map(&tmd, dy, Sh::kWo, g.Ho, (long long)g.N * g.C, Sh::kInnerD, pl.CG)) return DK_ERR_UNSUPPORTED;
   RingParams p;
   p.N = g.N; p.C = g.C; p.Hs = g.H; p.Hd = g.Ho;
-  p.CG = pl.CG; p.R = pl.R; p.RR = pl.RR;
+  p.CG = pl.CG; p.R = pl.R; p.RR = pl.RR; p.NP = pl.np;
   if (tuning_env("DK_B200_PLAN_PRINT")) fprintf(stderr, "gw ring S=%d W=%d C=%d: CG=%d R=%d RR=%d warps=%d smem=%zu\n", S, W, g.C, pl.CG, pl.R, pl.RR, pl.warps, pl.smem);
   p.L = (g.Ho - 1) * S + 3;
   p.rows_total = g.N * g.Ho;
@@ -1688,7 +1702,7 @@ int launch_gw_ring(const __half* dy, const __half* x, const __half* rot, const _
 
 struct BwdRingPlan {
   bool ok;
-  int Rx, Rd, warps, blocks_x, rows_per_block, ns;
+  int Rx, Rd, warps, np, blocks_x, rows_per_block, ns;
   size_t smem, ws_bytes;
 };
 
@@ -1700,21 +1714,22 @@ BwdRingPlan bwd_ring_plan(const Geom& g) {
   pl.ok = false;
   pl.ns = g.C <= 96 ? 6 : 9;
   if (g.C > 144) return pl;  // the bank-gradient accumulators of all channels live in registers
-  // 128 or 168 registers per thread; of the 12 warps the wide form could run, 11 measured faster on the shape that uses it
-  // by default (C = 144, 56 x 56, stride 2: 0.144 against 0.147 ms)
-  const int max_warps = pl.ns == 6 ? 16 : 11;
+  // 128 or 168 registers per thread allow 16 or 12 warps.  Where the dy rows come in cp.async pieces two producer warps share
+  // them (C = 144, 56 x 56, stride 2: 0.142 ms with 2 + 10 warps, 0.146 with 1 + 10, 0.147 with 1 + 11).
+  pl.np = tuning_int("DK_B200_BWD_NP", Sh::kDyTma ? 1 : 2, 1, 4);
+  const int max_warps = pl.ns == 6 ? 16 : (pl.np > 1 ? 12 : 11);
   const size_t budget = (size_t)device_smem_optin();
   // Four slots is the least that lets the producer run one row ahead.  Each consumer warp owns 1.7 KB of scratch, so where
   // shared memory is short a few warps fewer are launched rather than falling back to two passes.  With the warps settled,
   // the x ring takes what is left: the source rows of the destination rows being worked on, plus the lookahead.
-  const int forced_warps = tuning_int("DK_B200_BWD_WARPS", 0, 2, max_warps);
+  const int forced_warps = tuning_int("DK_B200_BWD_WARPS", 0, 2, 12);
   for (int warps = forced_warps ? forced_warps : max_warps; warps >= (forced_warps ? forced_warps : max_warps - 8) && warps >= 2 && !pl.ok; --warps) {
-    const int rows_busy = (warps - 1 + Sh::kNB - 1) / Sh::kNB + 1;
+    const int rows_busy = (warps - pl.np + Sh::kNB - 1) / Sh::kNB + 1;
     const int want_x = ring_slots((rows_busy + 1) * S + 2), want_d = ring_slots(rows_busy + 2);
     long long best = -1;
     for (int Rx = 4; Rx <= want_x; ++Rx)
       for (int Rd = 4; Rd <= want_d && Rd <= Rx; ++Rd) {
-        const size_t smem = bwd_ring_smem(g.C, Sh::kInnerX, Sh::kInnerD, RL::kSlot, Rx, Rd, warps - 1);
+        const size_t smem = bwd_ring_smem(g.C, Sh::kInnerX, Sh::kInnerD, RL::kSlot, Rx, Rd, warps - pl.np);
         if (smem > budget) continue;
         const int served = Rx * want_d < Rd * want_x ? Rx * want_d : Rd * want_x;
         const long long score = (long long)served * 64 + Rx + Rd;
@@ -1729,7 +1744,7 @@ BwdRingPlan bwd_ring_plan(const Geom& g) {
   }
   if (pl.ok) {
     const int Rx = tuning_int("DK_B200_BWD_RX", pl.Rx, 4, 32), Rd = tuning_int("DK_B200_BWD_RD", pl.Rd, 4, 32);
-    const size_t smem = bwd_ring_smem(g.C, Sh::kInnerX, Sh::kInnerD, RL::kSlot, Rx, Rd, pl.warps - 1);
+    const size_t smem = bwd_ring_smem(g.C, Sh::kInnerX, Sh::kInnerD, RL::kSlot, Rx, Rd, pl.warps - pl.np);
     if (smem <= budget) {
       pl.Rx = Rx;
       pl.Rd = Rd;
@@ -1760,7 +1775,7 @@ int launch_bwd_ring(const __half* dy, const __half* x, const __half* rot, const 
   }
   RingParams p;
   p.N = g.N; p.C = g.C; p.Hs = g.Ho; p.Hd = g.H;
-  p.CG = g.C; p.R = pl.Rx; p.RR = pl.Rd;
+  p.CG = g.C; p.R = pl.Rx; p.RR = pl.Rd; p.NP = pl.np;
   if (tuning_env("DK_B200_PLAN_PRINT")) fprintf(stderr, "bwd ring S=%d W=%d C=%d: Rx=%d Rd=%d warps=%d smem=%zu\n", S, W, g.C, pl.Rx, pl.Rd, pl.warps, pl.smem);
   p.L = (g.Ho - 1) * S + 3;
   p.rows_total = g.N * g.Ho;

@@ -3,8 +3,9 @@
 //
 // A block streams the rows of its part of the tensors through rings of row slots.  One producer
 // warp fills slots (a tiled TMA copy per row of all the block's channels, with the hardware's zero
-// fill supplying the convolution padding; cp.async for the narrow offset rows); the other warps
-// consume them.  Per slot there is a "full" mbarrier (the copy's bytes have landed) and an "empty"
+// fill supplying the convolution padding; cp.async for the narrow offset rows; where a row is not a
+// multiple of 16 bytes and TMA cannot fetch it, up to four producer warps share its cp.async
+// pieces); the other warps consume them.  Per slot there is a "full" mbarrier (the copy's bytes have landed) and an "empty"
 // mbarrier (every consumer item that reads the slot is done).  No block-wide barrier is executed
 // after the set-up, so filling and computing overlap.
 //
@@ -98,11 +99,13 @@ struct Ring {
   __device__ __forceinline__ int turn(int k) const { return (int)__umulhi((unsigned)k, magic); }
   __device__ __forceinline__ int slot(int k) const { return k - turn(k) * n; }
 
-  // producer, whole warp: wait until the slot of fill k may be overwritten, then publish that
-  __device__ __forceinline__ bool reclaim(int k, int lane) const {
+  // producer, whole warp: wait until the slot of fill k may be overwritten, then publish that.  Where several producer
+  // warps share the copies of a fill, all of them wait and the first publishes: a consumer that then waits on the "full"
+  // barrier cannot be released early, because that barrier also counts the arrivals of the producers still on their way.
+  __device__ __forceinline__ bool reclaim(int k, int lane, bool publish = true) const {
     bool ok = true;
     if (k >= n) ok = mbar_wait(empty + 8 * slot(k), (turn(k) - 1) & 1);
-    if (lane == 0) asm volatile("st.release.cta.shared::cta.b32 [%0], %1;\n" ::"r"(issued), "r"(k + 1) : "memory");
+    if (lane == 0 && publish) asm volatile("st.release.cta.shared::cta.b32 [%0], %1;\n" ::"r"(issued), "r"(k + 1) : "memory");
     return ok;
   }
   // consumer: wait until fill k has landed
