@@ -21,7 +21,8 @@ int check_launch() {
 namespace {
 struct DevAttr {
   bool known = false;
-  int smem_optin = 48 * 1024;
+  // without a device (host-only plan queries) the figures of the one target, B200: 227 KB opt-in, 148 SMs
+  int smem_optin = 227 * 1024;
   int sms = 148;
 };
 std::mutex g_attr_mutex;
@@ -110,6 +111,7 @@ int dk_local_plan_query(const dk_geom* g, int dtype, int pass, long long* out8) 
   Geom gg;
   if (!out8 || !make_geom(g, &gg)) return DK_ERR_BAD_ARGUMENT;
   if (dtype != DK_F16 || !mma_path_enabled()) return DK_ERR_UNSUPPORTED;
+  if (pass >= 4 && pass <= 7) return local_ring_plan_query(gg, pass, out8);
   return local_mma_plan_query(gg, pass, out8);
 }
 

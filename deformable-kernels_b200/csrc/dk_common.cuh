@@ -210,6 +210,7 @@ int local_rot_mma(const __half* dy, const __half* x, const __half* rot, const __
                   void* ws, size_t ws_bytes, cudaStream_t s);
 size_t local_filter_mma_workspace(const Geom& g);
 int local_mma_plan_query(const Geom& g, int pass, long long out[8]);
+int local_ring_plan_query(const Geom& g, int pass, long long out[8]);
 int local_filter_mma(const __half* dy, const __half* x, const __half* rot, __half* dw, const Geom& g, void* ws,
                      size_t ws_bytes, cudaStream_t s);
 

@@ -1552,45 +1552,71 @@ __host__ __device__ inline size_t convT2_ring_smem(int cg, int inner, int rot_sl
   return ((size_t)R * cg * inner + 64 + (size_t)R * rot_slot + (size_t)cg * kBankPitch) * 2 + 8 + (size_t)4 * R * 8 + 16 + 128;
 }
 
+constexpr int kConvT2Warps = 20;  // 640 threads of 96 registers
+
+struct ConvT2RingPlan {
+  bool ok;
+  int CG, groups, R, warps, np, blocks_x, rows_per_block;
+  size_t smem;
+};
+
+// Channels per block, ring depth (the dy ring and the offsets ring share their fill numbers) and grid of the stride-2
+// grad-input kernel: as few channel groups as give the wanted depth or at least eight slots.
+template <int W>
+ConvT2RingPlan convT2_ring_plan(const Geom& g) {
+  using Sh = ConvT2Shape<W>;
+  using RL = RotLayout<Sh::kWo>;
+  ConvT2RingPlan pl;
+  pl.ok = false;
+  const size_t budget = (size_t)device_smem_optin();
+  const int want = tuning_int("DK_B200_CONVT2_R", ring_slots_generous((kConvT2Warps - 1 + Sh::kNB - 1) / Sh::kNB + 1 + 2), 4, 32);
+  for (int gr = 1; gr <= g.C / 16 && !pl.ok; ++gr) {
+    if (g.C % (16 * gr) || g.C / gr > 256) continue;
+    for (int r = want; r >= (want < 8 ? want : 8) && !pl.ok; --r) {
+      const size_t need = convT2_ring_smem(g.C / gr, Sh::kInner, RL::kSlot, r);
+      if (need > budget) continue;
+      pl.ok = true;
+      pl.CG = g.C / gr;
+      pl.groups = gr;
+      pl.R = r;
+      pl.smem = need;
+    }
+  }
+  if (!pl.ok || pl.groups > 65535) {
+    pl.ok = false;
+    return pl;
+  }
+  pl.warps = kConvT2Warps;
+  pl.np = Sh::kTma ? 1 : tuning_int("DK_B200_RING_NP", 4, 1, 8);  // see conv_ring_plan
+  spread_rows((long long)g.N * g.Ho, pl.groups, &pl.blocks_x, &pl.rows_per_block);
+  return pl;
+}
+
 template <int W>
 int launch_convT2_ring(const __half* dy, const __half* rot, const __half* w, __half* dx, const Geom& g, cudaStream_t s) {
   using Sh = ConvT2Shape<W>;
-  using RL = RotLayout<Sh::kWo>;
   if ((reinterpret_cast<uintptr_t>(rot) & 15) || (reinterpret_cast<uintptr_t>(dx) & 7) || (reinterpret_cast<uintptr_t>(dy) & 15))
     return DK_ERR_UNSUPPORTED;
-  const size_t budget = (size_t)device_smem_optin();
-  const int want = tuning_int("DK_B200_CONVT2_R", ring_slots_generous((19 + Sh::kNB - 1) / Sh::kNB + 1 + 2), 4, 32);
-  int cg = 0, groups = 0, R = 0;
-  size_t smem = 0;
-  for (int gr = 1; gr <= g.C / 16 && !cg; ++gr) {
-    if (g.C % (16 * gr) || g.C / gr > 256) continue;
-    for (int r = want; r >= (want < 8 ? want : 8) && !cg; --r) {
-      const size_t need = convT2_ring_smem(g.C / gr, Sh::kInner, RL::kSlot, r);
-      if (need > budget) continue;
-      cg = g.C / gr; groups = gr; R = r; smem = need;
-    }
-  }
-  if (!cg || groups > 65535) return DK_ERR_UNSUPPORTED;
+  const ConvT2RingPlan pl = convT2_ring_plan<W>(g);
+  if (!pl.ok) return DK_ERR_UNSUPPORTED;
   CUtensorMap tm;
   if (Sh::kTma) {
-    if (!make_row_map(&tm, dy, Sh::kWo, g.Ho, (long long)g.N * g.C, Sh::kInner, cg)) return DK_ERR_UNSUPPORTED;
+    if (!make_row_map(&tm, dy, Sh::kWo, g.Ho, (long long)g.N * g.C, Sh::kInner, pl.CG)) return DK_ERR_UNSUPPORTED;
   } else {
     memset(&tm, 0, sizeof(tm));
   }
   RingParams p;
   p.N = g.N; p.C = g.C; p.Hs = g.Ho; p.Hd = g.H;
-  p.CG = cg; p.R = R; p.RR = R;
-  p.NP = Sh::kTma ? 1 : tuning_int("DK_B200_RING_NP", 4, 1, 8);
-  if (tuning_env("DK_B200_PLAN_PRINT")) fprintf(stderr, "convT2 ring W=%d C=%d: CG=%d R=%d smem=%zu\n", W, g.C, cg, R, smem);
+  p.CG = pl.CG; p.R = pl.R; p.RR = pl.R; p.NP = pl.np;
+  if (tuning_env("DK_B200_PLAN_PRINT")) fprintf(stderr, "convT2 ring W=%d C=%d: CG=%d R=%d smem=%zu\n", W, g.C, pl.CG, pl.R, pl.smem);
   p.L = g.Ho + 1;
   p.rows_total = g.N * g.Ho;
-  int blocks_x;
-  spread_rows((long long)g.N * g.Ho, groups, &blocks_x, &p.rows_per_block);
+  p.rows_per_block = pl.rows_per_block;
   p.scH = g.scH; p.scW = g.scW; p.cells = g.cells;
   auto kern = ring_convT2_kernel<W, true, 640>;
-  int rc = enable_smem(kern, smem);
+  int rc = enable_smem(kern, pl.smem);
   if (rc) return rc;
-  kern<<<dim3(blocks_x, groups), 20 * 32, smem, s>>>(tm, dy, rot, w, dx, p);
+  kern<<<dim3(pl.blocks_x, pl.groups), pl.warps * 32, pl.smem, s>>>(tm, dy, rot, w, dx, p);
   return check_launch();
 }
 
@@ -1797,6 +1823,62 @@ int launch_bwd_ring(const __half* dy, const __half* x, const __half* rot, const 
 }
 
 }  // namespace
+
+// Plan of the row-ring kernel that a pass of the local deformable kernel would launch (host only).  pass: 4 forward,
+// 5 grad-input, 6 grad-offsets + grad-bank, 7 the one-pass backward.  out = {slots of the source ring (x; dy for the
+// stride-2 grad-input), slots of the per-row rings (offsets; dy where x is the source), warps per block, producer warps
+// among them, channels per block, channel groups, dynamic shared memory in bytes, blocks in the grid}.
+bool bwd_ring_shape(const Geom& g);
+
+int local_ring_plan_query(const Geom& g, int pass, long long out[8]) {
+  if (!ring_shape(g)) return DK_ERR_UNSUPPORTED;
+  auto put = [&](long long r, long long rr, long long warps, long long np, long long cg, long long groups, size_t smem,
+                 long long blocks) {
+    const long long v[8] = {r, rr, warps, np, cg, groups, (long long)smem, blocks};
+    for (int i = 0; i < 8; ++i) out[i] = v[i];
+    return DK_OK;
+  };
+  if (pass == 4 || (pass == 5 && g.sH == 1)) {
+    ConvRingPlan pl;
+    pl.ok = false;
+    auto plan = [&]() -> int {
+      if (pass == 5) DK_RING_FOR_WIDTH(g.W, return ((pl = conv_ring_plan<1, W, true>(g)).ok))
+      if (g.sH == 1) DK_RING_FOR_WIDTH(g.W, return ((pl = conv_ring_plan<1, W, false>(g)).ok))
+      DK_RING_FOR_WIDE(g.W, return ((pl = conv_ring_plan<2, W, false>(g)).ok))
+    };
+    plan();
+    if (!pl.ok) return DK_ERR_UNSUPPORTED;
+    return put(pl.R, pl.RR, pl.warps, pl.np, pl.CG, pl.groups, pl.smem, (long long)pl.blocks_x * pl.groups);
+  }
+  if (pass == 5) {
+    ConvT2RingPlan pl;
+    pl.ok = false;
+    auto plan = [&]() -> int { DK_RING_FOR_WIDTH(g.W, return ((pl = convT2_ring_plan<W>(g)).ok)) };
+    plan();
+    if (!pl.ok) return DK_ERR_UNSUPPORTED;
+    return put(pl.R, pl.R, pl.warps, pl.np, pl.CG, pl.groups, pl.smem, (long long)pl.blocks_x * pl.groups);
+  }
+  if (pass == 6) {
+    GwRingPlan pl;
+    pl.ok = false;
+    auto plan = [&]() -> int {
+      if (g.sH == 1) DK_RING_FOR_WIDTH(g.W, return ((pl = gw_ring_plan<1, W>(g)).ok))
+      DK_RING_FOR_WIDE(g.W, return ((pl = gw_ring_plan<2, W>(g)).ok))
+    };
+    plan();
+    if (!pl.ok) return DK_ERR_UNSUPPORTED;
+    return put(pl.R, pl.RR, pl.warps, pl.np, pl.CG, pl.groups, pl.smem, (long long)pl.blocks_x * pl.groups);
+  }
+  if (pass == 7) {
+    if (!bwd_ring_shape(g)) return DK_ERR_UNSUPPORTED;
+    BwdRingPlan pl;
+    if (g.W == 112) pl = g.sH == 1 ? bwd_ring_plan<1, 112>(g) : bwd_ring_plan<2, 112>(g);
+    else pl = g.sH == 1 ? bwd_ring_plan<1, 56>(g) : bwd_ring_plan<2, 56>(g);
+    if (!pl.ok) return DK_ERR_UNSUPPORTED;
+    return put(pl.Rx, pl.Rd, pl.warps, pl.np, g.C, 1, pl.smem, pl.blocks_x);
+  }
+  return DK_ERR_BAD_ARGUMENT;
+}
 
 // Code of the last bounded wait that ran out in a ring kernel on the current device (0 = none);
 // synchronises with the device.  For tests and diagnosis.

@@ -79,9 +79,13 @@ int dk_last_cuda_error(void);
 const char *dk_version(void);
 
 /* Block shape the fp16 tensor-core kernels of the local deformable kernel would launch for this geometry (no counterpart
- * in the reference; for tuning tools and tests, touches no GPU).  pass: 0 forward, 1 grad-input, 2 grad-offsets,
- * 3 grad-bank.  out8 = {band height, channels per block, channel groups, warps per block, bands, dynamic shared memory in
- * bytes, blocks in the grid, workspace bytes}.  DK_ERR_UNSUPPORTED when the geometry or dtype takes the general kernels. */
+ * in the reference; for tuning tools and tests, touches no GPU: without a device it plans for 227 KB of shared memory and
+ * 148 SMs).  Band kernels, pass: 0 forward, 1 grad-input, 2 grad-offsets, 3 grad-bank; out8 = {band height, channels per
+ * block, channel groups, warps per block, bands, dynamic shared memory in bytes, blocks in the grid, workspace bytes}.
+ * Row-ring kernels, pass: 4 forward, 5 grad-input, 6 grad-offsets + grad-bank, 7 the one-pass backward; out8 = {slots of
+ * the source-row ring, slots of the per-output-row rings, warps per block, producer warps among them, channels per block,
+ * channel groups, dynamic shared memory in bytes, blocks in the grid}.  DK_ERR_UNSUPPORTED when the geometry or dtype
+ * does not take that family of kernels. */
 int dk_local_plan_query(const dk_geom *g, int dtype, int pass, long long *out8);
 /* The producer / consumer kernels of the fp16 path bound every wait on a shared-memory barrier; a wait that
  * runs out records a non-zero code on the device and the kernel returns early instead of hanging.  This reads

@@ -170,6 +170,82 @@ def test_block_shapes_of_the_fp16_fast_path_are_launchable(cabi):
     assert cabi.lib.dk_local_plan_query(g, cabi.DK_F16, 0, None) == 1
 
 
+def test_row_ring_plans_fit_the_kernels_layouts(cabi):
+    """Planner of the producer / consumer row-ring kernels (host only; without a device the library plans for the one
+    target: 227 KB of shared memory, 148 SMs).  For the MobileNetV2 sweep layers and a spread of other shapes: the reported
+    ring depths, warps and channel split are launchable, and the highest shared-memory byte the kernel's own layout reaches
+    (recomputed here region by region: rings, bank copies, per-warp scratch, barriers, fill counters) stays inside the
+    dynamic shared memory the launch asks for."""
+    BUDGET = 227 * 1024
+    def inner(w):                      # halves per channel row of a ring slot (RowLayout)
+        return (w + 8 + 7) // 16 * 16 + 8
+    def rot_slot(w):                   # halves per slot of the offsets ring (RotLayout)
+        return 18 * (8 + (w + 7) // 8 * 8 + 8)
+    BANK, GW_SCRATCH, BWD_SCRATCH = 24, 3 * 36 * 8 * 4 + 24 * 8, 3 * 16 * 8 * 4 + 24 * 8
+    def up(v, a):
+        return (v + a - 1) // a * a
+    def top_conv(w, wr, cg, r, rr):                         # ring_conv_kernel
+        bars = up((r * cg * inner(w) + 16 + rr * rot_slot(wr) + cg * BANK) * 2, 8)
+        return bars + (2 * r + 2 * rr) * 8 + 2 * 4
+    def top_convT2(wo, cg, r):                              # ring_convT2_kernel
+        bars = up((r * cg * inner(wo) + 64 + r * rot_slot(wo) + cg * BANK) * 2, 8)
+        return bars + 4 * r * 8 + 2 * 4
+    def top_gw(w, wo, cg, r, rr, ncw):                      # ring_gw_kernel
+        rings = (r * cg * inner(w) + 64 + rr * cg * inner(wo) + 64 + rr * rot_slot(wo)) * 2
+        after = up(max(rings, ncw * cg * 16 * 4), 16)
+        bars = up(after + 16 * (cg + 8) * 2 + ncw * GW_SCRATCH, 8)
+        return bars + (2 * r + 4 * rr) * 8 + 3 * 4
+    def top_bwd(w, wo, cg, rx, rd, ncw):                    # ring_bwd_kernel
+        rings = (rx * cg * inner(w) + 64 + rd * cg * inner(wo) + 64 + rd * rot_slot(wo)) * 2
+        after = up(max(rings, ncw * cg * 16 * 4), 16)
+        bars = up(after + (cg * BANK + 16 * (cg + 8)) * 2 + ncw * BWD_SCRATCH, 8)
+        return bars + (2 * rx + 4 * rd) * 8 + 3 * 4
+    sweep = [(96, 112), (144, 56), (192, 28), (384, 14), (960, 7)]
+    cases = [(128, c, hw, hw, s) for c, hw in sweep for s in (1, 2)]
+    cases += [(n, c, h, w, s) for w in (112, 56, 28) for s in (1, 2) for n, c, h in
+              ((1, 16, 1), (3, 48, 5), (2, 160, 9), (7, 208, 28), (64, 256, 56), (2, 1024, 3), (300, 32, 2))]
+    out = (ctypes.c_longlong * 8)()
+    plans = {}
+    for n, c, h, w, s in cases:
+        g = cabi.geom((n, c, h, w), (3, 3), (s, s), (1, 1), (1, 1), (4, 4), 1)
+        wo = (w - 1) // s + 1
+        for p in (4, 5, 6, 7):
+            rc = cabi.lib.dk_local_plan_query(g, cabi.DK_F16, p, out)
+            assert rc in (0, 2), (n, c, h, w, s, p, rc)
+            if rc:
+                continue
+            r, rr, warps, np_, cg, groups, smem, blocks = list(out)
+            tag = (n, c, h, w, s, p, list(out))
+            plans[(n, c, h, w, s, p)] = list(out)
+            assert cg % 16 == 0 and cg * groups == c and groups <= 65535, tag
+            assert 1 <= np_ <= 4 and warps - np_ >= 1 and warps <= 24, tag
+            assert (np_ > 1) == ((w if p in (4, 6) or s == 1 else wo) % 8 != 0 and p != 6), tag   # several producers only for rows TMA cannot fetch
+            assert r >= 4 and rr >= 2 and 0 < smem <= BUDGET and 0 < blocks <= 148, tag
+            ncw = warps - np_
+            if p == 4 or (p == 5 and s == 1):
+                top = top_conv(w, w if p == 5 else wo, cg, r, rr)
+            elif p == 5:
+                top = top_convT2(wo, cg, r)
+            elif p == 6:
+                top = top_gw(w, wo, cg, r, rr, ncw)
+                assert cg <= 144, tag
+            else:
+                top = top_bwd(w, wo, cg, r, rr, ncw)
+                assert cg <= 144 and groups == 1, tag
+            assert top <= smem, tag + (top,)
+    # which sweep layers run here: rows of 112 and 56 every pass, rows of 28 at stride 1, and the grad-input of 28 at stride 2
+    for c, hw in sweep:
+        for s in (1, 2):
+            got = sorted(p for p in (4, 5, 6) if (128, c, hw, hw, s, p) in plans)
+            want = [4, 5, 6] if hw in (112, 56) or (hw == 28 and s == 1) else ([5] if hw == 28 else [])
+            assert got == want, (c, hw, s, got)
+    # the stride-2 passes need five source rows for two destination rows: no four-slot source ring on the sweep layers
+    for key in ((128, 96, 112, 112, 2, 6), (128, 144, 56, 56, 2, 6), (128, 144, 56, 56, 2, 7), (128, 96, 112, 112, 2, 4)):
+        assert plans[key][0] >= 5, (key, plans[key])
+    g = cabi.geom((4, 64, 28, 28), (3, 3), (1, 1), (1, 1), (1, 1), (3, 3), 1)
+    assert cabi.lib.dk_local_plan_query(g, cabi.DK_F16, 4, out) == 2          # scope other than 4 x 4: band kernels
+
+
 def test_cpu_tensors_raise_like_the_reference():
     import torch
     from deformable_kernels.ops.deform_kernel.functions import sample_depthwise, nd_linear_sample
