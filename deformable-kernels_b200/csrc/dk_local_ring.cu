@@ -1400,12 +1400,10 @@ bool make_row_map(CUtensorMap* tm, const __half* base, int width, int rows, long
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Input widths the kernels are instantiated for; scope 4 x 4.  The kernels themselves take any width (rows that are not
-// multiples of 16 bytes come by cp.async, odd ones element by element: the 28-wide dy and offset rows of the 56-wide
-// stride-2 layer do), and were measured on 28 x 28, 14 x 14 and 7 x 7 planes too (batch 128, C = 192 / 384 / 960): parity-green
-// but 1.2-4x slower than the band kernels of dk_local_mma.cu there (forward 0.10 / 0.09 / 0.14 ms against 0.06 / 0.04 / 0.04),
-// because one producer warp feeding narrow rows piece by piece and four, two or one items per row do not keep twenty
-// consumer warps busy.  So only the widths TMA can fetch are routed here.
+// Input widths the kernels are instantiated for; scope 4 x 4.  The kernels themselves take any width: rows that are not
+// multiples of 16 bytes come by cp.async pieces (28-wide rows: 8 bytes each, shared by several producer warps), odd ones
+// element by element.  Which widths are routed here was decided by measurement on B200 (batch 128) against the band kernels
+// of dk_local_mma.cu; the figures are at DK_RING_FOR_WIDE below.
 #define DK_RING_FOR_WIDTH(WIDTH, CALL)        \
   switch (WIDTH) {                            \
     case 112: { constexpr int W = 112; CALL; } \
