@@ -5,7 +5,7 @@
 // on mma.sync.m16n8k16, followed by y[c, p] += x[c, p + tap] * K[c, p, tap] on the CUDA cores --
 // but a different way of moving the data.  A block walks down a contiguous range of output rows
 // of ALL its channels.  A producer warp streams the source rows through rings of shared-memory
-// slots, one tiled TMA copy (cp.async.bulk.tensor) per row whose out-of-range elements the
+// slots (as many as shared memory holds: the depth need not be a power of two), one tiled TMA copy (cp.async.bulk.tensor) per row whose out-of-range elements the
 // hardware fills with zeros: that supplies the convolution padding, so no tap needs a mask.  The
 // consumer warps wait on a slot's mbarrier, never on each other: filling and computing overlap,
 // each source row crosses HBM once and shared memory once, and all pitches are compile-time
@@ -25,7 +25,9 @@
 //   ring_bwd_kernel    all three gradients from one stream of rows (least memory traffic; not the fastest, see below)
 //
 // Covers fp16, 3x3, pad 1, dilation 1, stride 1 or 2, one offset group, scope 4 x 4, channels a multiple
-// of 16, input rows of 112 or 56 elements (TMA needs 16-byte row pitches); other shapes stay on dk_local_mma.cu.
+// of 16, input rows of 112 or 56 elements (fetched by TMA, which needs 16-byte row pitches) and of 28 elements
+// (56-byte rows: up to four producer warps copy them in 8-byte cp.async pieces; at stride 2 only the grad-input
+// kernel).  Other shapes stay on dk_local_mma.cu.
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
