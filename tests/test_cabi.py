@@ -246,6 +246,20 @@ def test_row_ring_plans_fit_the_kernels_layouts(cabi):
     assert cabi.lib.dk_local_plan_query(g, cabi.DK_F16, 4, out) == 2          # scope other than 4 x 4: band kernels
 
 
+def test_ring_slot_arithmetic_for_any_depth():
+    """The row rings address fill k as slot k mod n, phase k / n, with k / n taken as the high word of k * ceil(2^32 / n)
+    (csrc/dk_ring.cuh, `Ring::turn`): exact for every depth the planners can choose and every fill number a block can
+    reach (rows per block are far below 2^22), including the largest k with k * n < 2^32."""
+    for n in range(2, 33):
+        magic = (2 ** 32 + n - 1) // n
+        assert magic < 2 ** 32
+        ks = list(range(0, 4096)) + [2 ** 22 - 1, 2 ** 22, 2 ** 22 + 1, 2 ** 32 // n - 1]
+        ks += [m * n + d for m in (1, 7, 1000, 99999) for d in (-1, 0, 1)]
+        for k in ks:
+            turn = (k * magic) >> 32
+            assert turn == k // n and k - turn * n == k % n, (n, k)
+
+
 def test_cpu_tensors_raise_like_the_reference():
     import torch
     from deformable_kernels.ops.deform_kernel.functions import sample_depthwise, nd_linear_sample
